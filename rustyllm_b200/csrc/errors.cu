@@ -1,0 +1,27 @@
+// Error text of the last failed call, per host thread, and library identity.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+static thread_local char g_last_error[1024] = "";
+
+void rl_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+}
+
+extern "C" const char* rl_last_error() { return g_last_error; }
+
+extern "C" int rl_page_size() { return RL_PAGE; }
+
+// Compute capability of the current device as major*10+minor, or a negative code.
+extern "C" int rl_device_arch() {
+  int dev = 0, major = 0, minor = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return RL_ERR_CUDA;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return RL_ERR_CUDA;
+  if (cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev) != cudaSuccess) return RL_ERR_CUDA;
+  return major * 10 + minor;
+}

@@ -1,0 +1,103 @@
+// Rotary position encoding of the step's queries and keys, fused with the write of
+// the rotated keys and the values into the paged cache.
+//
+// Formulas (SimonWaldherr/RustyLLM): angle = float(pos) * inv_freq[i], (sin, cos) of it in
+// 32-bit, (x0, x1) <- (x0*cos - x1*sin, x0*sin + x1*cos) on every query and key
+// head, values untouched (src/model.rs:5562-5647); then K[layer][pos] = k,
+// V[layer][pos] = v (src/model.rs:7233-7236).  Pairing "half" rotates (i, i + r/2),
+// "interleaved" rotates (2i, 2i+1), r being the rotary width (<= head size; the
+// rest of a head passes through unrotated).  The same fusion is the reference's
+// Metal kernel ``rope_store`` (src/metal_backend.m:446-489).
+//
+// Cache layout: pool[page][kv_head][RL_PAGE][head_dim]; the page of position p of
+// the sequence in slot s is page_table[s * max_pages + p / RL_PAGE].
+#include "common.cuh"
+
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int ld, const int* __restrict__ positions,
+                                     const int* __restrict__ slot_of_token,
+                                     const int* __restrict__ page_table, int max_pages,
+                                     const float* __restrict__ inv_freq, int H, int G, int hd,
+                                     int rot, int interleaved, T* __restrict__ k_pool,
+                                     T* __restrict__ v_pool, int write_cache) {
+  const int m = blockIdx.x;
+  const int pos = positions[m];
+  T* row = qkv + (size_t)m * ld;
+  size_t dst = 0;
+  if (write_cache) {
+    const int slot = slot_of_token[m];
+    const int page = page_table[(size_t)slot * max_pages + pos / RL_PAGE];
+    dst = ((size_t)page * G) * RL_PAGE * hd + (size_t)(pos % RL_PAGE) * hd;  // + g * RL_PAGE * hd
+  }
+  const int half = rot / 2;
+  if (half > 0) {
+    const int i = threadIdx.x % half;
+    const int lane_group = threadIdx.x / half;
+    const int groups = blockDim.x / half;
+    if (lane_group < groups) {
+      float s, c;
+      sincosf((float)pos * inv_freq[i], &s, &c);
+      const int i0 = interleaved ? 2 * i : i;
+      const int i1 = interleaved ? 2 * i + 1 : i + half;
+      for (int head = lane_group; head < H + G; head += groups) {
+        T* x = row + (size_t)head * hd;
+        const float x0 = rl_ld(x + i0), x1 = rl_ld(x + i1);
+        const float y0 = x0 * c - x1 * s, y1 = x0 * s + x1 * c;
+        if (head < H) {
+          rl_st(x + i0, y0);
+          rl_st(x + i1, y1);
+        } else if (write_cache) {
+          T* kd = k_pool + dst + (size_t)(head - H) * RL_PAGE * hd;
+          rl_st(kd + i0, y0);
+          rl_st(kd + i1, y1);
+        } else {
+          rl_st(x + i0, y0);
+          rl_st(x + i1, y1);
+        }
+      }
+    }
+  }
+  if (!write_cache) return;
+  // unrotated tail of the key heads
+  const int tail = hd - rot;
+  for (int idx = threadIdx.x; idx < G * tail; idx += blockDim.x) {
+    const int g = idx / tail, e = rot + idx % tail;
+    k_pool[dst + (size_t)g * RL_PAGE * hd + e] = row[(size_t)(H + g) * hd + e];
+  }
+  for (int idx = threadIdx.x; idx < G * hd; idx += blockDim.x) {
+    const int g = idx / hd, e = idx % hd;
+    v_pool[dst + (size_t)g * RL_PAGE * hd + e] = row[(size_t)(H + G + g) * hd + e];
+  }
+}
+
+// qkv: [M, ld] holding per token H query heads, then G key heads, then G value
+// heads, each of head_dim.  Queries are rotated in place; rotated keys and the
+// values go to the cache pools (same dtype as qkv).  With k_pool == nullptr nothing
+// is cached and the keys are rotated in place as well.
+extern "C" int rl_rope_kv_write(void* qkv, int dtype, int ld, const int* positions,
+                                const int* slot_of_token, const int* page_table, int max_pages,
+                                const float* inv_freq, int num_tokens, int num_heads, int num_kv_heads,
+                                int head_dim, int rotary_dim, int interleaved, void* k_pool,
+                                void* v_pool, cudaStream_t stream) {
+  RL_REQUIRE(num_tokens >= 0 && num_heads > 0 && num_kv_heads > 0, "rl_rope_kv_write: bad sizes");
+  RL_REQUIRE(head_dim > 0 && head_dim <= 256, "rl_rope_kv_write: head_dim %d outside (0, 256]", head_dim);
+  RL_REQUIRE(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0,
+             "rl_rope_kv_write: rotary_dim %d must be even and <= head_dim %d", rotary_dim, head_dim);
+  RL_REQUIRE(ld >= (num_heads + 2 * num_kv_heads) * head_dim, "rl_rope_kv_write: row stride %d too small", ld);
+  RL_REQUIRE((k_pool == nullptr) == (v_pool == nullptr), "rl_rope_kv_write: give both cache pools or none");
+  if (num_tokens == 0) return RL_OK;
+  const int write_cache = k_pool != nullptr;
+  const int threads = 128;
+  if (dtype == RL_F32)
+    rope_kv_write_kernel<float><<<num_tokens, threads, 0, stream>>>(
+        (float*)qkv, ld, positions, slot_of_token, page_table, max_pages, inv_freq, num_heads,
+        num_kv_heads, head_dim, rotary_dim, interleaved, (float*)k_pool, (float*)v_pool, write_cache);
+  else if (dtype == RL_BF16)
+    rope_kv_write_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(
+        (__nv_bfloat16*)qkv, ld, positions, slot_of_token, page_table, max_pages, inv_freq, num_heads,
+        num_kv_heads, head_dim, rotary_dim, interleaved, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, write_cache);
+  else
+    RL_REQUIRE(false, "rl_rope_kv_write: unknown dtype %d", dtype);
+  RL_LAUNCH_CHECK("rl_rope_kv_write");
+  return RL_OK;
+}

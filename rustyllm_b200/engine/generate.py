@@ -1,0 +1,176 @@
+"""The generation loop above the step function: batches of unequal prompts, stop
+tokens, sequences that end earlier, and as many batches one after another as there
+are requests.
+
+Per sequence the order of events is the reference's (``generate_chat_stream``,
+SimonWaldherr/RustyLLM src/runtime.rs:3266-3342): the first token is sampled from the prompt's
+last logits; a sampled stop token ends the sequence and is neither emitted nor
+counted (3305-3307); the token is emitted and counted; the sequence ends when
+``max_tokens`` are out or the context is full (3336-3338); otherwise the token is
+fed back for the next logits - so N tokens cost one prompt step and N-1 single-token
+steps.  Stop *strings* of the reference (3312-3325) become stop sequences of token
+ids here (no tokenizer in this library): a match at the tail of the output ends
+the sequence and is cut from it.
+
+The loop only needs ``alloc_slot / free_slot / step`` of an engine and ``sample`` of
+a sampler, so its decisions are tested on the CPU against stand-ins.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence
+
+from ..sampling.config import SamplerConfig
+from ..sampling.sampler import SequenceSamplingState
+
+PAGE = 64
+
+
+@dataclass
+class GenerationOptions:
+    """SimonWaldherr/RustyLLM src/runtime.rs:94-111, minus the text-side fields."""
+    max_tokens: int = 256
+    sampler: SamplerConfig = field(default_factory=SamplerConfig)
+    seed: int = 0                       # 0: from the clock (src/runtime.rs:3205-3213)
+    stop_token_ids: Sequence[int] = ()  # in addition to the model's end-of-sequence ids
+    stop_sequences: Sequence[Sequence[int]] = ()
+    ignore_eos: bool = False            # benchmarks: run to max_tokens
+    max_context: Optional[int] = None   # cap of the context (reference: --max-context)
+
+    def validate(self) -> None:
+        if self.max_tokens <= 0:
+            raise ValueError("max_tokens must be greater than 0.")
+        if self.max_context is not None and self.max_context <= 0:
+            raise ValueError("--max-context must be greater than 0.")
+        self.sampler.validate()
+        for s in self.stop_sequences:
+            if len(s) == 0:
+                raise ValueError("a stop sequence must hold at least one token id")
+
+
+@dataclass
+class GenerationStats:
+    """SimonWaldherr/RustyLLM src/runtime.rs:393-403; times in seconds."""
+    prompt_tokens: int = 0
+    generated_tokens: int = 0
+    prefill_time: float = 0.0
+    decode_time: float = 0.0
+    total_time: float = 0.0
+    cached_tokens: int = 0
+    steps: int = 0
+
+
+@dataclass
+class GenerationResult:
+    token_ids: List[int]
+    stats: GenerationStats
+    finish_reason: str = ""    # "stop" | "length" | "context" | "stop_sequence"
+
+
+def _ends_with(seq: List[int], tail: Sequence[int]) -> bool:
+    n = len(tail)
+    return n <= len(seq) and seq[-n:] == list(tail)
+
+
+def pages_for(prompt_len: int, max_tokens: int) -> int:
+    """Cache pages one request can come to hold: its prompt plus all but the last of
+    its generated tokens (the last one is never fed back)."""
+    return -(-(prompt_len + max_tokens - 1) // PAGE)
+
+
+def plan_batches(prompt_lens: Sequence[int], max_tokens: int, max_batch: int, free_pages: int,
+                 max_seq_len: int) -> List[List[int]]:
+    """Cut the requests, in order, into batches that fit the slots and the pages."""
+    batches: List[List[int]] = []
+    cur: List[int] = []
+    cur_pages = 0
+    for i, p in enumerate(prompt_lens):
+        if p <= 0:
+            raise ValueError(f"request {i}: No prompt provided.")
+        if p > max_seq_len:
+            raise ValueError(f"request {i}: prompt of {p} tokens exceeds the context of {max_seq_len}")
+        need = pages_for(p, min(max_tokens, max_seq_len - p + 1))
+        if need > free_pages:
+            raise ValueError(f"request {i} alone needs {need} cache pages, the cache has {free_pages}")
+        if cur and (len(cur) >= max_batch or cur_pages + need > free_pages):
+            batches.append(cur)
+            cur, cur_pages = [], 0
+        cur.append(i)
+        cur_pages += need
+    if cur:
+        batches.append(cur)
+    return batches
+
+
+def generate_batch(engine, sampler, prompts: Sequence[Sequence[int]], options: GenerationOptions,
+                   seeds: Sequence[int], stop_ids: Sequence[int], max_seq_len: int,
+                   on_token: Optional[Callable[[int, int], None]] = None,
+                   sync: Callable[[], None] = lambda: None) -> List[GenerationResult]:
+    """One batch: its prompts in one step, then one token per live sequence per step."""
+    B = len(prompts)
+    t_start = time.perf_counter()
+    stop = set(() if options.ignore_eos else stop_ids) | set(options.stop_token_ids)
+    cache_len = [min(max_seq_len, len(p) + options.max_tokens + 1) for p in prompts]  # src/runtime.rs:3184-3185
+    states = [SequenceSamplingState(options.sampler, seeds[i], prompts[i]) for i in range(B)]
+    out: List[List[int]] = [[] for _ in range(B)]
+    reason = [""] * B
+    pos = [len(p) for p in prompts]
+    slots: List[Optional[int]] = []
+    try:
+        for _ in range(B):
+            slots.append(engine.alloc_slot())
+        logits = engine.step(slots, [list(p) for p in prompts], "last")
+        sync()
+        t_prefill = time.perf_counter()
+        steps = 1
+        live = list(range(B))
+        while live:
+            toks = sampler.sample(logits, [states[i] for i in live])
+            nxt, feed = [], []
+            for row, i in enumerate(live):
+                tok = int(toks[row])
+                if tok in stop:
+                    reason[i] = "stop"
+                else:
+                    out[i].append(tok)
+                    states[i].push(tok)
+                    hit = next((s for s in options.stop_sequences if _ends_with(out[i], s)), None)
+                    if hit is not None:
+                        del out[i][len(out[i]) - len(hit):]
+                        reason[i] = "stop_sequence"
+                    else:
+                        if on_token is not None:
+                            on_token(i, tok)
+                        if len(out[i]) >= options.max_tokens:
+                            reason[i] = "length"
+                        elif pos[i] >= cache_len[i]:
+                            reason[i] = "context"
+                if reason[i]:
+                    engine.free_slot(slots[i])   # ends earlier: its slot and pages go back at once
+                    slots[i] = None
+                else:
+                    nxt.append(i)
+                    feed.append([tok])
+            live = nxt
+            if not live:
+                break
+            logits = engine.step([slots[i] for i in live], feed, "last")
+            for i in live:
+                pos[i] += 1
+            steps += 1
+        sync()
+        t_end = time.perf_counter()
+    finally:
+        for s in slots:
+            if s is not None:
+                engine.free_slot(s)
+    results = []
+    for i in range(B):
+        results.append(GenerationResult(
+            token_ids=out[i],
+            stats=GenerationStats(prompt_tokens=len(prompts[i]), generated_tokens=len(out[i]),
+                                  prefill_time=t_prefill - t_start, decode_time=t_end - t_prefill,
+                                  total_time=t_end - t_start, cached_tokens=0, steps=steps),
+            finish_reason=reason[i]))
+    return results

@@ -1,0 +1,179 @@
+"""The step function: a batch of sequences, each bringing its next tokens (a whole
+prompt, a chunk, or one token), run as one batch from the cache; logits come back
+for the wanted places only.
+
+The reference runs one token of one sequence per call (``forward_into(token, pos)``,
+src/model.rs:7177-7185; a prompt's last token alone yields logits,
+src/runtime.rs:3405-3427).  Here all tokens of the step are packed one sequence
+after another - no padding exists, so padding cannot change a result - and every
+kernel works from per-token position and slot.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Union
+
+import numpy as np
+import torch
+
+from ..cache.sequence_cache import SequenceCache
+from ..models.decoder import DecoderModel
+
+
+@dataclass
+class StepState:
+    """Device-side description of one step, shared by every part."""
+    num_tokens: int
+    num_seqs: int
+    tokens: torch.Tensor          # int32 [M]
+    positions: torch.Tensor       # int32 [M]  position of each token in its sequence
+    slot_of_token: torch.Tensor   # int32 [M]  cache slot of each token's sequence
+    cu_seqlens: torch.Tensor      # int32 [B+1] token offsets of the sequences
+    seq_slots: torch.Tensor       # int32 [B]
+    kv_lens: torch.Tensor         # int32 [B]  sequence lengths after this step
+    want_rows: torch.Tensor       # int32 [W]  packed rows whose logits are wanted
+    q_lens: List[int]             # host copies
+    kv_lens_host: List[int]
+    max_q_len: int
+    max_kv_len: int
+    is_decode: bool               # every sequence brings exactly one token
+
+
+class _Staging:
+    """Ring of pinned host buffers for the step's integer inputs.  A buffer is
+    reused only after the copy that read it has finished."""
+
+    def __init__(self, device: torch.device, depth: int = 4):
+        self.device = device
+        self.depth = depth
+        self.bufs: List[Optional[torch.Tensor]] = [None] * depth
+        self.events: List[Optional[torch.cuda.Event]] = [None] * depth
+        self.i = 0
+
+    def upload(self, host: np.ndarray) -> torch.Tensor:
+        n = host.shape[0]
+        k = self.i
+        self.i = (self.i + 1) % self.depth
+        if self.events[k] is not None:
+            self.events[k].synchronize()
+        if self.bufs[k] is None or self.bufs[k].numel() < n:
+            self.bufs[k] = torch.empty(max(n, 1024), dtype=torch.int32, pin_memory=True)
+        self.bufs[k][:n].numpy()[:] = host
+        dev = self.bufs[k][:n].to(self.device, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[k] = ev
+        return dev
+
+
+Want = Union[str, None, Sequence[Sequence[int]]]
+
+
+class Engine:
+    """A model with its cache and the step function over them."""
+
+    def __init__(self, model: DecoderModel, cache: SequenceCache):
+        self.model = model
+        self.cache = cache
+        self.device = model.runtime.device
+        self.vocab_size = model.spec.vocab_size
+        self._staging = _Staging(self.device) if self.device.type == "cuda" else None
+        self.h2d_bytes = 0
+
+    # ------------------------------------------------------------------ slots
+    def alloc_slot(self) -> int:
+        return self.cache.alloc_slot()
+
+    def free_slot(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    # ------------------------------------------------------------------ the step
+    def build_step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], want: Want = "last"):
+        """Validate on the host and lay out the step's integer inputs."""
+        B = len(slots)
+        if B == 0:
+            raise ValueError("a step needs at least one sequence")
+        if len(tokens) != B:
+            raise ValueError(f"{B} slots but {len(tokens)} token lists")
+        q_lens = [len(t) for t in tokens]
+        starts = [self.cache.length(s) for s in slots]
+        M = sum(q_lens)
+        flat = np.empty(M, dtype=np.int64)
+        positions = np.empty(M, dtype=np.int32)
+        slot_of_token = np.empty(M, dtype=np.int32)
+        cu = np.zeros(B + 1, dtype=np.int32)
+        o = 0
+        for b in range(B):
+            n = q_lens[b]
+            if n == 0:
+                raise ValueError(f"sequence {b} of the step brings no token")
+            flat[o:o + n] = np.asarray(tokens[b], dtype=np.int64)
+            positions[o:o + n] = np.arange(starts[b], starts[b] + n, dtype=np.int32)
+            slot_of_token[o:o + n] = slots[b]
+            o += n
+            cu[b + 1] = o
+        if flat.min() < 0 or flat.max() >= self.vocab_size:
+            bad = int(flat[(flat < 0) | (flat >= self.vocab_size)][0])
+            raise ValueError(f"token id {bad} lies outside the vocabulary [0, {self.vocab_size})")
+        if want is None:
+            rows: List[int] = []
+        elif isinstance(want, str):
+            if want == "last":
+                rows = [int(cu[b + 1]) - 1 for b in range(B)]
+            elif want == "all":
+                rows = list(range(M))
+            else:
+                raise ValueError(f"want must be 'last', 'all', None or lists of places, got {want!r}")
+        else:
+            if len(want) != B:
+                raise ValueError(f"{B} sequences but {len(want)} lists of wanted places")
+            rows = []
+            for b in range(B):
+                for w in want[b]:
+                    if not (0 <= w < q_lens[b]):
+                        raise ValueError(f"sequence {b}: wanted place {w} is not among its {q_lens[b]} tokens")
+                    rows.append(int(cu[b]) + int(w))
+        kv_lens = [starts[b] + q_lens[b] for b in range(B)]
+        packed = np.concatenate([
+            flat.astype(np.int32), positions, slot_of_token, cu,
+            np.asarray(slots, dtype=np.int32), np.asarray(kv_lens, dtype=np.int32),
+            np.asarray(rows, dtype=np.int32)])
+        return packed, (M, B, len(rows)), q_lens, kv_lens
+
+    def step_state(self, packed_dev: torch.Tensor, sizes, q_lens, kv_lens) -> StepState:
+        M, B, W = sizes
+        o = 0
+        def take(n):
+            nonlocal o
+            t = packed_dev[o:o + n]
+            o += n
+            return t
+        tokens, positions, slot_of_token = take(M), take(M), take(M)
+        cu, seq_slots, kv = take(B + 1), take(B), take(B)
+        rows = take(W)
+        return StepState(M, B, tokens, positions, slot_of_token, cu, seq_slots, kv, rows,
+                         list(q_lens), list(kv_lens), max(q_lens), max(kv_lens),
+                         all(n == 1 for n in q_lens))
+
+    def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], want: Want = "last") -> Optional[torch.Tensor]:
+        """Run the given tokens of the given sequences as one batch from the cache.
+
+        ``slots[b]`` holds sequence b, whose next tokens are ``tokens[b]`` (they take
+        positions ``length(slot) ..``).  ``want``: "last" (each sequence's last
+        token), "all", ``None``, or per sequence the places among its tokens.
+        Returns float32 logits ``[wanted, vocab]`` on the device in the order of the
+        sequences and of their wanted places (``None`` if nothing is wanted).
+        """
+        packed, sizes, q_lens, kv_lens = self.build_step(slots, tokens, want)
+        self.cache.prepare(slots, q_lens)
+        if self._staging is not None:
+            dev = self._staging.upload(packed)
+        else:
+            dev = torch.from_numpy(packed).to(self.device)
+        self.h2d_bytes += packed.nbytes
+        st = self.step_state(dev, sizes, q_lens, kv_lens)
+        x = self.model.forward(st, self.cache)
+        self.cache.commit(slots, q_lens)
+        if sizes[2] == 0:
+            return None
+        return self.model.logits(x, st.want_rows)

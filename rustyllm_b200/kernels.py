@@ -1,0 +1,291 @@
+"""Python face of the CUDA kernel library (csrc/): loads the shared library through
+ctypes and wraps each entry point in a function that takes torch tensors.
+
+There is no fallback: if the library cannot be built or loaded, or a kernel refuses
+its sizes, an exception says so.  Every wrapper launches on torch's current stream,
+so calls are captured by a CUDA graph like any torch operation.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Optional
+
+import torch
+
+from .csrc import build as _build
+
+F32, BF16 = 0, 1
+OUT_SAME, OUT_F32, OUT_ADD_F32 = 0, 1, 2
+
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = None
+_lock = threading.Lock()
+launch_count = 0   # kernels launched through this module (bench.py reports it)
+
+_c_int, _c_float, _c_void_p, _c_ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
+
+_SIGNATURES = {
+    "rl_embedding": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "rl_rmsnorm": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_float, _c_void_p],
+    "rl_swiglu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "rl_convert": [_c_void_p, _c_int, _c_void_p, _c_int, _c_ll, _c_void_p],
+    "rl_gemm_simt": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                     _c_int, _c_int, _c_void_p],
+    "rl_rope_kv_write": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
+                         _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
+    "rl_attention_simt": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
+                          _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
+                          _c_void_p],
+    "rl_repeat_penalty": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_float, _c_void_p],
+    "rl_argmax": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
+    "rl_sample_temperature": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+}
+
+
+def library() -> ctypes.CDLL:
+    """The loaded kernel library; built on first use."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                path = _build.build()
+                try:
+                    lib = ctypes.CDLL(path)
+                except OSError as e:
+                    raise KernelError(f"cannot load the kernel library {path}: {e}") from e
+                lib.rl_last_error.restype = ctypes.c_char_p
+                lib.rl_last_error.argtypes = []
+                for name, args in _SIGNATURES.items():
+                    fn = getattr(lib, name, None)
+                    if fn is None:
+                        raise KernelError(f"kernel library {path} lacks the entry point {name}")
+                    fn.restype = _c_int
+                    fn.argtypes = args
+                if lib.rl_page_size() != PAGE_SIZE:
+                    raise KernelError(f"the kernel library was built for pages of {lib.rl_page_size()} "
+                                      f"tokens, the package expects {PAGE_SIZE}")
+                _lib = lib
+    return _lib
+
+
+def library_file() -> str:
+    library()
+    return _build.library_path()
+
+
+def _check(code: int, name: str) -> None:
+    if code != 0:
+        msg = library().rl_last_error().decode("utf-8", "replace")
+        raise KernelError(f"{name} failed ({code}): {msg}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"dtype {t.dtype} is not handled by the kernels (float32 and bfloat16 are)") from None
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} is on {t.device}; the kernels run on CUDA tensors only (there is no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} has dtype {t.dtype}, expected {dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _count(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
+
+
+# ----------------------------------------------------------------------------- wrappers
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, err_flag: torch.Tensor) -> None:
+    """out[m, :] = table[ids[m], :] as float32.  err_flag (int32[1]) is set to 1 on a bad id."""
+    _need(table, "table"); _need(ids, "ids", torch.int32); _need(out, "out", torch.float32)
+    _need(err_flag, "err_flag", torch.int32)
+    V, d = table.shape
+    M = ids.numel()
+    assert out.shape == (M, d)
+    _check(library().rl_embedding(table.data_ptr(), _dt(table), ids.data_ptr(), out.data_ptr(), M, d, V,
+                                  err_flag.data_ptr(), _stream()), "rl_embedding")
+    _count()
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = rms_norm(x[rows[r]] if rows is given else x[r]) * weight."""
+    _need(x, "x", torch.float32); _need(weight, "weight", torch.float32); _need(out, "out")
+    d = x.shape[-1]
+    n = out.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        assert rows.numel() == n
+    else:
+        assert x.shape[0] == n
+    assert weight.numel() == d and out.shape[-1] == d
+    _check(library().rl_rmsnorm(x.data_ptr(), weight.data_ptr(), out.data_ptr(), _dt(out), _ptr(rows), n, d,
+                                float(eps), _stream()), "rl_rmsnorm")
+    _count()
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    _need(gate_up, "gate_up"); _need(out, "out", gate_up.dtype)
+    M, two_i = gate_up.shape
+    assert two_i % 2 == 0 and out.shape == (M, two_i // 2)
+    _check(library().rl_swiglu(gate_up.data_ptr(), out.data_ptr(), _dt(out), M, two_i // 2, _stream()), "rl_swiglu")
+    _count()
+
+
+def convert(src: torch.Tensor, dst: torch.Tensor) -> None:
+    _need(src, "src"); _need(dst, "dst")
+    assert src.numel() == dst.numel()
+    _check(library().rl_convert(src.data_ptr(), _dt(src), dst.data_ptr(), _dt(dst), src.numel(), _stream()), "rl_convert")
+    _count()
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_mode: int,
+              bias: Optional[torch.Tensor] = None) -> None:
+    """out = a @ w.T (+ bias) on the CUDA cores.  a: [M, K] (rows may be strided),
+    w: [N, K] contiguous, same dtype.  out_mode: OUT_SAME / OUT_F32 / OUT_ADD_F32."""
+    _need(a, "a", contiguous=False); _need(w, "w", a.dtype); _need(out, "out", contiguous=False)
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N)
+    assert a.stride(1) == 1 and out.stride(1) == 1
+    if out_mode == OUT_SAME:
+        assert out.dtype == a.dtype
+    else:
+        assert out.dtype == torch.float32
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        assert bias.numel() == N
+    lda = a.stride(0) if M > 1 else K
+    ldo = out.stride(0) if M > 1 else N
+    _check(library().rl_gemm_simt(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), _dt(a), out_mode,
+                                  M, N, K, lda, ldo, _stream()), "rl_gemm_simt")
+    _count()
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slot_of_token: torch.Tensor,
+                  page_table: torch.Tensor, inv_freq: torch.Tensor, num_heads: int, num_kv_heads: int,
+                  head_dim: int, rotary_dim: int, interleaved: bool,
+                  k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor]) -> None:
+    _need(qkv, "qkv"); _need(positions, "positions", torch.int32)
+    _need(inv_freq, "inv_freq", torch.float32)
+    M = qkv.shape[0]
+    if k_pool is not None:
+        _need(k_pool, "k_pool", qkv.dtype); _need(v_pool, "v_pool", qkv.dtype)
+        _need(slot_of_token, "slot_of_token", torch.int32); _need(page_table, "page_table", torch.int32)
+        assert k_pool.shape[1:] == (num_kv_heads, page_size(), head_dim), k_pool.shape
+        max_pages = page_table.shape[1]
+    else:
+        max_pages = 0
+    assert inv_freq.numel() >= rotary_dim // 2
+    _check(library().rl_rope_kv_write(
+        qkv.data_ptr(), _dt(qkv), qkv.stride(0), positions.data_ptr(), _ptr(slot_of_token), _ptr(page_table),
+        max_pages, inv_freq.data_ptr(), M, num_heads, num_kv_heads, head_dim, rotary_dim, int(interleaved),
+        _ptr(k_pool), _ptr(v_pool), _stream()), "rl_rope_kv_write")
+    _count()
+
+
+def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
+                   slot_of_token: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
+                   num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
+    """q: [M, >= H*hd] (a view into the qkv buffer is fine), out: [M, H*hd]."""
+    _need(q, "q", contiguous=False); _need(k_pool, "k_pool", q.dtype); _need(v_pool, "v_pool", q.dtype)
+    _need(out, "out", q.dtype); _need(page_table, "page_table", torch.int32)
+    _need(slot_of_token, "slot_of_token", torch.int32); _need(positions, "positions", torch.int32)
+    M = q.shape[0]
+    assert q.stride(1) == 1
+    ldq = q.stride(0) if M > 1 else num_heads * head_dim
+    _check(library().rl_attention_simt(
+        q.data_ptr(), ldq, k_pool.data_ptr(), v_pool.data_ptr(), _dt(q), page_table.data_ptr(),
+        page_table.shape[1], slot_of_token.data_ptr(), positions.data_ptr(), out.data_ptr(), out.stride(0),
+        M, num_heads, num_kv_heads, head_dim, float(scale), int(window), _stream()), "rl_attention_simt")
+    _count()
+
+
+def repeat_penalty(logits: torch.Tensor, recent: torch.Tensor, recent_len: torch.Tensor, penalty: float) -> None:
+    _need(logits, "logits", torch.float32); _need(recent, "recent", torch.int32)
+    _need(recent_len, "recent_len", torch.int32)
+    rows, vocab = logits.shape
+    assert recent.shape[0] == rows and recent_len.numel() == rows
+    _check(library().rl_repeat_penalty(logits.data_ptr(), rows, vocab, recent.data_ptr(), recent_len.data_ptr(),
+                                       recent.shape[1], float(penalty), _stream()), "rl_repeat_penalty")
+    _count()
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    _need(logits, "logits", torch.float32); _need(out, "out", torch.int32)
+    rows, vocab = logits.shape
+    assert out.numel() == rows
+    _check(library().rl_argmax(logits.data_ptr(), rows, vocab, out.data_ptr(), _stream()), "rl_argmax")
+    _count()
+
+
+def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
+                       out: torch.Tensor, min_p: Optional[torch.Tensor] = None) -> None:
+    _need(logits, "logits", torch.float32); _need(temperature, "temperature", torch.float32)
+    _need(uniform, "uniform", torch.float32); _need(out, "out", torch.int32)
+    rows, vocab = logits.shape
+    assert temperature.numel() == rows and uniform.numel() == rows and out.numel() == rows
+    if min_p is not None:
+        _need(min_p, "min_p", torch.float32)
+    _check(library().rl_sample_temperature(logits.data_ptr(), rows, vocab, temperature.data_ptr(),
+                                           uniform.data_ptr(), _ptr(min_p), out.data_ptr(), _stream()),
+           "rl_sample_temperature")
+    _count()
+
+
+PAGE_SIZE = 64
+
+
+def page_size() -> int:
+    """Tokens per cache page.  A constant on the Python side so that host-side code
+    (allocators, their tests) runs without a GPU; checked against the value the
+    kernels were compiled with when the library is loaded."""
+    return PAGE_SIZE
+
+
+# ----------------------------------------------------------------------------- tensor-core GEMM
+def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    """Whether the tensor-core kernel takes these operands (else the caller uses
+    the CUDA-core kernel, which takes every shape)."""
+    return False
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_mode: int,
+            bias: Optional[torch.Tensor] = None) -> None:
+    raise KernelError("the tensor-core GEMM is not built")
+
+
+# ----------------------------------------------------------------------------- attention dispatch
+def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
+              step, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+              window: int = 0) -> None:
+    """Attention of the step's tokens over the cache; picks the kernel for the
+    dtype and the shape of the step.  ``step`` carries positions, slots and
+    sequence boundaries (engine.step.StepState)."""
+    attention_simt(q, k_pool, v_pool, page_table, step.slot_of_token, step.positions, out,
+                   num_heads, num_kv_heads, head_dim, scale, window)
+
+
+def sample_candidates(logits, rows, temperature, uniform, min_p, top_k, top_p, out) -> None:
+    raise KernelError("top-k / top-p sampling on the device is not built yet")

@@ -1,0 +1,52 @@
+"""Gated feed-forward (SwiGLU): x += Wdown (silu(Wgate xn) * (Wup xn)).
+
+SimonWaldherr/RustyLLM src/model.rs:7321-7347 with the activation of src/simd.rs:2403-2408
+(``g / (1 + exp(-g)) * u``).  Wgate and Wup are one matrix [2I x d] so that one
+product serves both (the reference reads a fused ``ffn_up`` of 2I rows the same
+way round: gate rows first, src/model.rs:3933-3967).
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from .. import kernels as K
+from ..config.spec import ParamSource, ParamSpec
+from .base import FeedForward, Runtime
+from .linear import OUT_ADD_F32, OUT_SAME, linear
+from .registry import register_feed_forward
+
+
+@register_feed_forward("gated_mlp")
+class GatedMLP(FeedForward):
+    def __init__(self, runtime: Runtime, hidden_size: int, intermediate_size: int, names: Dict[str, str],
+                 activation: str = "silu", bias: bool = False):
+        if activation != "silu":
+            raise ValueError(f"activation {activation!r} is not supported; known: 'silu'")
+        self.runtime = runtime
+        self.d, self.I = hidden_size, intermediate_size
+        self.names = names
+        self.bias = bias
+        self.wgu = self.wdown = self.bgu = self.bdown = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        d, I, n = self.d, self.I, self.names
+        specs = {
+            "wgu": ParamSpec((ParamSource(n["gate"] + ".weight", (I, d)),
+                              ParamSource(n["up"] + ".weight", (I, d)))),
+            "wdown": ParamSpec((ParamSource(n["down"] + ".weight", (d, I)),)),
+        }
+        if self.bias:
+            specs["bgu"] = ParamSpec((ParamSource(n["gate"] + ".bias", (I,)),
+                                      ParamSource(n["up"] + ".bias", (I,))), role="vector")
+            specs["bdown"] = ParamSpec((ParamSource(n["down"] + ".bias", (d,)),), role="vector")
+        return specs
+
+    def forward(self, xn: torch.Tensor, residual: torch.Tensor, step) -> None:
+        M = xn.shape[0]
+        gu = torch.empty((M, 2 * self.I), dtype=xn.dtype, device=xn.device)
+        linear(xn, self.wgu, gu, OUT_SAME, self.bgu)
+        h = torch.empty((M, self.I), dtype=xn.dtype, device=xn.device)
+        K.swiglu(gu, h)
+        linear(h, self.wdown, residual, OUT_ADD_F32, self.bdown)

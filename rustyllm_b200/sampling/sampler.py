@@ -1,0 +1,92 @@
+"""Sampling on the device: rows of float32 logits in, one token id per row out.
+
+Order of operations of ``sample_with_scratch`` (SimonWaldherr/RustyLLM src/sampling.rs:66-212):
+repeat penalty first (also when greedy), then greedy argmax if the temperature is
+below 1e-6, else the candidate path (top-k / top-p) or the full-vocabulary softmax
+draw with the optional min-p cut.  Each row has its own options, its own uniform
+number (from that sequence's host generator) and its own recent-token window, so a
+sequence samples the same tokens alone or in any batch.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import kernels as K
+from .config import RECENT_TOKEN_LIMIT, Rng, SamplerConfig
+
+
+class SequenceSamplingState:
+    """Per-sequence sampler state: options, generator, recent-token window."""
+
+    def __init__(self, config: SamplerConfig, seed: int, prompt: Sequence[int]):
+        config.validate()
+        self.config = config
+        self.rng = Rng(seed)
+        # src/runtime.rs:493-521: the last 64 tokens of prompt + output
+        self.recent: List[int] = list(prompt[-RECENT_TOKEN_LIMIT:])
+
+    def push(self, token: int) -> None:
+        self.recent.append(token)
+        if len(self.recent) > RECENT_TOKEN_LIMIT:
+            del self.recent[0]
+
+
+class Sampler:
+    def __init__(self, device: torch.device):
+        self.device = device
+
+    def sample(self, logits: torch.Tensor, states: Sequence[SequenceSamplingState]) -> List[int]:
+        """logits: float32 [B, V] on the device (modified in place by the repeat
+        penalty).  Draws one uniform from the generator of every row that is not
+        greedy.  Returns host token ids."""
+        B, V = logits.shape
+        assert B == len(states)
+        dev = logits.device
+        out = torch.empty(B, dtype=torch.int32, device=dev)
+
+        penalties = {s.config.repeat_penalty for s in states}
+        if penalties != {1.0}:
+            recent = np.zeros((B, RECENT_TOKEN_LIMIT), dtype=np.int32)
+            lens = np.zeros(B, dtype=np.int32)
+            for b, s in enumerate(states):
+                lens[b] = len(s.recent)
+                recent[b, :lens[b]] = s.recent
+            recent_d = torch.from_numpy(recent).to(dev)
+            lens_d = torch.from_numpy(lens).to(dev)
+            if len(penalties) == 1:
+                K.repeat_penalty(logits, recent_d, lens_d, next(iter(penalties)))
+            else:
+                for b, s in enumerate(states):   # rows with different penalties: one launch each
+                    if s.config.repeat_penalty != 1.0:
+                        K.repeat_penalty(logits[b:b + 1], recent_d[b:b + 1], lens_d[b:b + 1],
+                                         s.config.repeat_penalty)
+
+        if all(s.config.is_greedy for s in states):
+            K.argmax(logits, out)
+            return out.tolist()
+
+        cand_rows = [b for b, s in enumerate(states)
+                     if s.config.needs_candidates and (0 < s.config.top_k < V or s.config.top_p < 1.0)]
+        # one float upload: temperature | uniform | min_p
+        f = np.zeros((3, B), dtype=np.float32)
+        for b, s in enumerate(states):
+            c = s.config
+            greedy = c.is_greedy
+            f[0, b] = 0.0 if greedy else c.temperature
+            f[1, b] = 0.0 if greedy else s.rng.next_f32()
+            f[2, b] = c.min_p
+        fd = torch.from_numpy(f).to(dev)
+        if not cand_rows:
+            K.sample_temperature(logits, fd[0], fd[1], out, fd[2] if f[2].any() else None)
+            return out.tolist()
+        # mixed batch: plain rows through the softmax kernel, candidate rows through theirs
+        K.sample_temperature(logits, fd[0], fd[1], out, fd[2] if f[2].any() else None)
+        top_k = torch.tensor([states[b].config.top_k if 0 < states[b].config.top_k < V else 0 for b in cand_rows],
+                             dtype=torch.int32, device=dev)
+        top_p = torch.tensor([states[b].config.top_p for b in cand_rows], dtype=torch.float32, device=dev)
+        rows = torch.tensor(cand_rows, dtype=torch.int32, device=dev)
+        K.sample_candidates(logits, rows, fd[0], fd[1], fd[2], top_k, top_p, out)
+        return out.tolist()

@@ -1,0 +1,142 @@
+"""Decisions of the generation loop, against stand-ins for the engine and the sampler (no GPU)."""
+import pytest
+import torch
+
+from rustyllm_b200.engine.generate import (GenerationOptions, generate_batch, pages_for, plan_batches)
+from rustyllm_b200.sampling.config import Rng, SamplerConfig
+
+
+class ScriptedEngine:
+    """Each sequence's next token is a function of (its prompt, how many tokens it has been fed)."""
+
+    def __init__(self, script, max_slots=8):
+        self.script = script
+        self.free = list(range(max_slots))[::-1]
+        self.held = {}
+        self.calls = []
+
+    def alloc_slot(self):
+        s = self.free.pop()
+        self.held[s] = []
+        return s
+
+    def free_slot(self, s):
+        assert s in self.held, "slot freed twice"
+        del self.held[s]
+        self.free.append(s)
+
+    def step(self, slots, tokens, want):
+        assert want == "last"
+        self.calls.append((list(slots), [list(t) for t in tokens]))
+        rows = []
+        for s, t in zip(slots, tokens):
+            self.held[s].extend(t)
+            rows.append(self.script(self.held[s]))
+        return torch.tensor(rows)
+
+
+class PickSampler:
+    def sample(self, logits, states):
+        for st in states:
+            if not st.config.is_greedy:
+                st.rng.next_f32()
+        return [int(x) for x in logits.tolist()]
+
+
+def run(script, prompts, **opt):
+    eng = ScriptedEngine(script)
+    stop_ids = opt.pop("eos", (99,))
+    max_seq = opt.pop("max_seq_len", 1000)
+    opts = GenerationOptions(sampler=SamplerConfig.greedy(), **opt)
+    opts.validate()
+    seen = []
+    res = generate_batch(eng, PickSampler(), prompts, opts, [1] * len(prompts), stop_ids, max_seq,
+                         on_token=lambda i, t: seen.append((i, t)))
+    assert eng.held == {}, "every slot goes back"
+    return eng, res, seen
+
+
+def test_first_token_comes_from_the_prompt_step_and_the_last_is_not_fed_back():
+    eng, res, _ = run(lambda held: len(held), [[5, 6, 7]], max_tokens=4)
+    assert res[0].token_ids == [3, 4, 5, 6] and res[0].finish_reason == "length"
+    # 1 prompt step + 3 single-token steps for 4 tokens
+    assert len(eng.calls) == 4 and eng.calls[0][1] == [[5, 6, 7]] and eng.calls[-1][1] == [[5]]
+    assert res[0].stats.prompt_tokens == 3 and res[0].stats.generated_tokens == 4 and res[0].stats.steps == 4
+
+
+def test_stop_token_is_neither_emitted_nor_counted():
+    eng, res, seen = run(lambda held: 99 if len(held) == 5 else 10 + len(held), [[1, 2, 3]], max_tokens=10)
+    assert res[0].token_ids == [13, 14] and res[0].finish_reason == "stop"
+    assert seen == [(0, 13), (0, 14)]
+
+
+def test_ignore_eos_and_extra_stop_ids():
+    _, res, _ = run(lambda held: 99, [[1]], max_tokens=3, ignore_eos=True)
+    assert res[0].token_ids == [99, 99, 99]
+    _, res, _ = run(lambda held: 42, [[1]], max_tokens=3, stop_token_ids=(42,))
+    assert res[0].token_ids == [] and res[0].finish_reason == "stop"
+
+
+def test_shorter_sequences_leave_the_batch_and_the_others_go_on():
+    # sequence with prompt [p] stops after p tokens
+    def script(held):
+        p = held[0]
+        return 99 if len(held) - 1 >= p else 50
+    eng, res, _ = run(script, [[3], [1], [2]], max_tokens=10)
+    assert [r.token_ids for r in res] == [[50, 50, 50], [50], [50, 50]]
+    sizes = [len(c[0]) for c in eng.calls]
+    assert sizes == [3, 3, 2, 1]
+    # freed at once: the slot of the shortest one is free while the others run
+    assert all(r.finish_reason == "stop" for r in res)
+
+
+def test_stop_sequence_of_ids_is_cut_from_the_output():
+    _, res, seen = run(lambda held: len(held), [[0, 0]], max_tokens=10, stop_sequences=[[4, 5]])
+    assert res[0].token_ids == [2, 3] and res[0].finish_reason == "stop_sequence"
+    assert (0, 5) not in seen
+
+
+def test_context_limit_ends_a_sequence():
+    # context of 5 positions, prompt of 3: positions 3 and 4 can still be written
+    eng, res, _ = run(lambda held: 7, [[1, 2, 3]], max_tokens=10, max_seq_len=5)
+    assert res[0].finish_reason == "context"
+    assert res[0].token_ids == [7, 7, 7]
+    assert sum(len(t[0]) for _, t in eng.calls) == 5
+
+
+def test_options_are_validated_like_the_reference():
+    with pytest.raises(ValueError, match="max_tokens"):
+        GenerationOptions(max_tokens=0).validate()
+    with pytest.raises(ValueError, match="top_p"):
+        GenerationOptions(sampler=SamplerConfig(top_p=0.0)).validate()
+    with pytest.raises(ValueError, match="min_p"):
+        GenerationOptions(sampler=SamplerConfig(min_p=1.0)).validate()
+    with pytest.raises(ValueError, match="repeat_penalty"):
+        GenerationOptions(sampler=SamplerConfig(repeat_penalty=0.0)).validate()
+    with pytest.raises(ValueError, match="temperature"):
+        GenerationOptions(sampler=SamplerConfig(temperature=-1.0)).validate()
+
+
+def test_batches_are_cut_by_slots_and_by_pages():
+    assert pages_for(64, 1) == 1 and pages_for(64, 2) == 2 and pages_for(1, 64) == 1
+    assert plan_batches([10] * 5, 8, max_batch=2, free_pages=100, max_seq_len=512) == [[0, 1], [2, 3], [4]]
+    # each request can hold 100 + 29 tokens = 3 pages; 7 pages hold two of them
+    assert plan_batches([100] * 5, 30, max_batch=8, free_pages=7, max_seq_len=512) == [[0, 1], [2, 3], [4]]
+    with pytest.raises(ValueError, match="alone needs"):
+        plan_batches([1000], 30, 8, free_pages=3, max_seq_len=4096)
+    with pytest.raises(ValueError, match="exceeds the context"):
+        plan_batches([600], 30, 8, free_pages=300, max_seq_len=512)
+    with pytest.raises(ValueError, match="No prompt"):
+        plan_batches([0], 30, 8, free_pages=300, max_seq_len=512)
+
+
+def test_rng_matches_the_reference_generator():
+    r = Rng(0)
+    assert r.state == 0xDEADBEEFCAFE1337
+    r = Rng(1)
+    # xorshift64 (13, 7, 17) from state 1, computed by hand
+    s = 1
+    s ^= (s << 13) & (2**64 - 1); s ^= s >> 7; s ^= (s << 17) & (2**64 - 1)
+    assert r.next_f32() == (s >> 40) / 2**24
+    vals = [Rng(12345).next_f32() for _ in range(3)]
+    assert vals[0] == vals[1] == vals[2] and 0.0 <= vals[0] < 1.0

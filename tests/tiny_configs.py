@@ -1,0 +1,39 @@
+"""Tiny configurations of the architecture for tests.  They differ from one another
+in every size and option: heads and groups (GQA / MQA / MHA), head size, sizes that
+are no power of two, number of layers, vocabulary, eps, rope base and scaling,
+tied or untied head, biases."""
+import os
+
+from rustyllm_b200 import write_random_model
+
+TINY = {
+    # 2 layers, GQA 4/2, head 16, untied, plain rope, norm weights 1 + N(0, .02)
+    "A": dict(seed=0, norm_noise=True, dtype="float32", config={
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+        "vocab_size": 256, "hidden_size": 64, "intermediate_size": 172, "num_hidden_layers": 2,
+        "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16,
+        "max_position_embeddings": 128, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+        "rope_scaling": None, "tie_word_embeddings": False, "eos_token_id": 255}),
+    # 3 layers, MQA 3/1, head 32, tied, llama3 rope scaling, bf16 file
+    "B": dict(seed=1, norm_noise=False, dtype="bfloat16", config={
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+        "vocab_size": 384, "hidden_size": 96, "intermediate_size": 256, "num_hidden_layers": 3,
+        "num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 32,
+        "max_position_embeddings": 256, "rms_norm_eps": 1e-6, "rope_theta": 500000.0,
+        "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                         "high_freq_factor": 4.0, "original_max_position_embeddings": 64},
+        "tie_word_embeddings": True, "eos_token_id": [382, 383]}),
+    # 2 layers, MHA 5/5, head 48 (heads * head size != hidden), odd vocabulary, biases, long context
+    "C": dict(seed=2, norm_noise=True, dtype="bfloat16", config={
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+        "vocab_size": 307, "hidden_size": 80, "intermediate_size": 136, "num_hidden_layers": 2,
+        "num_attention_heads": 5, "num_key_value_heads": 5, "head_dim": 48,
+        "max_position_embeddings": 640, "rms_norm_eps": 3e-6, "rope_theta": 25000.0,
+        "tie_word_embeddings": False, "attention_bias": True, "mlp_bias": True}),
+}
+
+
+def write_tiny(name: str, path: str) -> str:
+    t = TINY[name]
+    os.makedirs(path, exist_ok=True)
+    return write_random_model(path, t["config"], seed=t["seed"], dtype=t["dtype"], norm_noise=t["norm_noise"])
