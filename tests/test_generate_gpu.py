@@ -1,0 +1,107 @@
+"""Generation through the entry point against the plain implementation's loop."""
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+from gpu_helpers import load_runner, random_tokens
+from tiny_configs import TINY
+
+pytestmark = pytest.mark.gpu
+
+
+def _plain(d):
+    return P.load_model_dir(d)
+
+
+def test_greedy_batch_of_unequal_prompts_matches_the_plain_loop(model_dirs):
+    """Tiny A: prompts of 5/11/17 tokens, 8 tokens each, greedy, 32-bit."""
+    from rustyllm_b200 import GenerationOptions, SamplerConfig
+    d, cfg = model_dirs["A"]
+    r = load_runner(d, "float32")
+    prompts = [random_tokens(256, n, 40 + n) for n in (5, 11, 17)]
+    res = r.generate(prompts, GenerationOptions(max_tokens=8, sampler=SamplerConfig.greedy(), seed=1))
+    pc, pw = _plain(d)
+    for p, got in zip(prompts, res):
+        want = P.generate(pc, pw, p, 8, temperature=0.0, stop_ids=[255])
+        assert got.token_ids == want
+        assert got.stats.prompt_tokens == len(p) and got.stats.generated_tokens == len(want)
+    alone = r.generate(prompts[1], GenerationOptions(max_tokens=8, sampler=SamplerConfig.greedy(), seed=1))
+    assert alone.token_ids == res[1].token_ids
+    r.cache.check()
+    assert r.cache.free_pages == r.cache.num_pages
+
+
+def test_temperature_batch_matches_the_plain_sampler_with_the_same_seeds(model_dirs):
+    """Tiny B: prompts of 1/7/23/40 tokens, 12 tokens each, temperature 0.8, fixed seeds, 32-bit."""
+    from rustyllm_b200 import GenerationOptions, SamplerConfig
+    d, cfg = model_dirs["B"]
+    r = load_runner(d, "float32")
+    prompts = [random_tokens(384, n, 50 + n) for n in (1, 7, 23, 40)]
+    opts = GenerationOptions(max_tokens=12, sampler=SamplerConfig(temperature=0.8), seed=77)
+    res = r.generate(prompts, opts)
+    pc, pw = _plain(d)
+    for i, (p, got) in enumerate(zip(prompts, res)):
+        want = P.generate(pc, pw, p, 12, temperature=0.8, seed=77 + i, stop_ids=[382, 383])
+        assert got.token_ids == want, f"sequence {i}"
+    # the same sequence alone, with its own seed, samples the same tokens
+    alone = r.generate(prompts[2], opts, seeds=[79])
+    assert alone.token_ids == res[2].token_ids
+
+
+def test_greedy_in_bfloat16_agrees_with_the_plain_loop_where_the_margin_is_clear(model_dirs):
+    """In bf16 a near-tie between two logits may flip; compare up to the first step whose
+    plain margin is smaller than the bf16 tolerance, and require at least a few steps."""
+    from rustyllm_b200 import GenerationOptions, SamplerConfig
+    d, cfg = model_dirs["C"]
+    r = load_runner(d, "bfloat16")
+    pc, pw = _plain(d)
+    checked = 0
+    for seed in range(4):
+        p = random_tokens(307, 20 + seed, 60 + seed)
+        got = r.generate(p, GenerationOptions(max_tokens=10, sampler=SamplerConfig.greedy(), seed=1)).token_ids
+        seq = list(p)
+        for t in got:
+            logits = P.forward(pc, pw, seq)[-1]
+            top2 = torch.topk(logits, 2).values
+            if (top2[0] - top2[1]) < 0.05 * logits.pow(2).mean().sqrt():
+                break
+            assert t == int(torch.argmax(logits))
+            seq.append(t); checked += 1
+    assert checked >= 10
+
+
+def test_stop_tokens_and_batches_one_after_another(model_dirs):
+    from rustyllm_b200 import GenerationOptions, Runner, SamplerConfig
+    d, cfg = model_dirs["A"]
+    r, info = Runner.from_path(d, dtype="float32", max_cache_tokens=64 * 3, max_batch=2)
+    assert info.file_size_bytes > 0 and info.load_time > 0 and r.architecture() == "LlamaForCausalLM"
+    prompts = [random_tokens(256, n, 70 + n) for n in (3, 30, 9, 14, 2)]
+    greedy = GenerationOptions(max_tokens=6, sampler=SamplerConfig.greedy(), seed=1)
+    res = r.generate(prompts, greedy)            # 5 requests through 2 slots: three batches
+    assert [len(x.token_ids) for x in res] == [6] * 5
+    # make the third token of request 1 a stop token: it ends there, the token is not emitted
+    stop = res[1].token_ids[2]
+    res2 = r.generate(prompts, GenerationOptions(max_tokens=6, sampler=SamplerConfig.greedy(), seed=1,
+                                                 stop_token_ids=(stop,)))
+    assert res2[1].token_ids == res[1].token_ids[:2] and res2[1].finish_reason == "stop"
+    for a, b in zip(res, res2):
+        cut = a.token_ids.index(stop) if stop in a.token_ids else len(a.token_ids)
+        assert b.token_ids == a.token_ids[:cut]
+    streamed = []
+    one = r.generate_stream(prompts[0], greedy, streamed.append)
+    assert streamed == one.token_ids == res[0].token_ids
+    r.cache.check()
+    assert r.cache.free_pages == r.cache.num_pages and r.cache.slots.free_count == 2
+
+
+def test_random_weights_without_files_and_layer_override():
+    from rustyllm_b200 import GenerationOptions, Runner, SamplerConfig
+    r = Runner.from_config(TINY["B"]["config"], seed=3, dtype="bfloat16", max_cache_tokens=64 * 4, max_batch=2,
+                           num_layers=2)
+    assert r.config.num_hidden_layers == 2 and len(r.model.blocks) == 2
+    out = r.generate([1, 2, 3], GenerationOptions(max_tokens=4, sampler=SamplerConfig.greedy(), ignore_eos=True))
+    assert len(out.token_ids) == 4 and all(0 <= t < 384 for t in out.token_ids)
+    r2 = Runner.from_config(TINY["B"]["config"], seed=3, dtype="bfloat16", max_cache_tokens=64 * 4, max_batch=2,
+                            num_layers=2)
+    assert r2.generate([1, 2, 3], GenerationOptions(max_tokens=4, sampler=SamplerConfig.greedy(), ignore_eos=True)).token_ids == out.token_ids

@@ -1,0 +1,338 @@
+"""Each kernel alone against a plain PyTorch float32/float64 restatement of the same
+operation, at sizes other than the engine's tiny models use."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+from sampler_cases import CASES
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+PAGE = 64
+
+
+def K():
+    from rustyllm_b200 import kernels
+    return kernels
+
+
+def _rand(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def _tol(dtype):
+    return dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-5)
+
+
+# ----------------------------------------------------------------------------- elementwise
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_gathers_rows_and_flags_bad_ids(dtype):
+    table = _rand(1000, 100, dtype=dtype)
+    ids = torch.tensor([0, 999, 5, 5, 123], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 100, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K().embedding(table, ids, out, flag)
+    assert torch.equal(out, table[ids.long()].float()) and flag.item() == 0
+    K().embedding(table, torch.tensor([1000], dtype=torch.int32, device=DEV), out[:1], flag)
+    assert flag.item() == 1
+
+
+@pytest.mark.parametrize("d", [7, 100, 4096, 5000])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm(d, out_dtype):
+    x = _rand(9, d, seed=1, scale=3.0)
+    w = _rand(d, seed=2) + 1.0
+    out = torch.empty(9, d, dtype=out_dtype, device=DEV)
+    K().rmsnorm(x, w, out, 1e-6)
+    ref = P.rms_norm(x.double().cpu(), w.double().cpu(), 1e-6)
+    torch.testing.assert_close(out.double().cpu(), ref, **(dict(rtol=1e-2, atol=1e-2) if out_dtype == torch.bfloat16 else dict(rtol=2e-6, atol=2e-6)))
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(3, d, dtype=out_dtype, device=DEV)
+    K().rmsnorm(x, w, out2, 1e-6, rows)
+    assert torch.equal(out2, out[rows.long()])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu(dtype):
+    gu = _rand(13, 2 * 172, dtype=dtype, seed=3, scale=2.0)
+    out = torch.empty(13, 172, dtype=dtype, device=DEV)
+    K().swiglu(gu, out)
+    g, u = gu[:, :172].double().cpu(), gu[:, 172:].double().cpu()
+    torch.testing.assert_close(out.double().cpu(), P.swiglu(g, u), **_tol(dtype))
+
+
+def test_convert_rounds_to_nearest_even():
+    # SimonWaldherr/RustyLLM src/simd.rs:88-96 (f32_to_bf16) and its tests at 9203-9225
+    x = torch.tensor([1.0, 1.00390625, 1.005859375, 1.01171875, -2.5, 3.0e38, 1e-40], device=DEV)
+    out = torch.empty(7, dtype=torch.bfloat16, device=DEV)
+    K().convert(x, out)
+    assert torch.equal(out, x.to(torch.bfloat16))
+    assert out[1].item() == 1.0 and out[3].item() == 1.015625   # ties go to the even mantissa
+    back = torch.empty(7, device=DEV)
+    K().convert(out, back)
+    assert torch.equal(back, out.float())
+
+
+# ----------------------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K_", [(1, 7, 5), (3, 96, 96), (17, 130, 172), (64, 64, 64), (65, 300, 33),
+                                    (200, 257, 100), (8, 1000, 256)])
+def test_gemm_simt_all_modes(dtype, M, N, K_):
+    k = K()
+    a = _rand(M, K_, dtype=dtype, seed=4)
+    w = _rand(N, K_, dtype=dtype, seed=5)
+    bias = _rand(N, seed=6)
+    ref = a.double().cpu() @ w.double().cpu().T
+    tol = dict(rtol=1e-2, atol=1e-2 * math.sqrt(K_)) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol=2e-5 * math.sqrt(K_))
+    out = torch.empty(M, N, dtype=dtype, device=DEV)
+    k.gemm_simt(a, w, out, k.OUT_SAME)
+    torch.testing.assert_close(out.double().cpu(), ref, **tol)
+    out32 = torch.empty(M, N, device=DEV)
+    k.gemm_simt(a, w, out32, k.OUT_F32, bias)
+    torch.testing.assert_close(out32.double().cpu(), ref + bias.double().cpu(), rtol=1e-5, atol=2e-5 * math.sqrt(K_))
+    res = _rand(M, N, seed=7)
+    acc = res.clone()
+    k.gemm_simt(a, w, acc, k.OUT_ADD_F32)
+    torch.testing.assert_close(acc.double().cpu(), ref + res.double().cpu(), rtol=1e-5, atol=2e-5 * math.sqrt(K_))
+
+
+def test_gemm_simt_rows_do_not_depend_on_the_batch():
+    k = K()
+    a = _rand(130, 172, seed=8)
+    w = _rand(96, 172, seed=9)
+    full = torch.empty(130, 96, device=DEV)
+    k.gemm_simt(a, w, full, k.OUT_F32)
+    for rows in ([5], [0, 64, 129], list(range(20, 60))):
+        sub = torch.empty(len(rows), 96, device=DEV)
+        k.gemm_simt(a[rows].contiguous(), w, sub, k.OUT_F32)
+        assert torch.equal(sub, full[rows]), "bit-equal whatever else is in the batch"
+    # strided rows of A (a column block of a wider buffer)
+    wide = _rand(10, 300, seed=10)
+    sub = torch.empty(10, 96, device=DEV)
+    k.gemm_simt(wide[:, 100:272], w, sub, k.OUT_F32)
+    ref = torch.empty(10, 96, device=DEV)
+    k.gemm_simt(wide[:, 100:272].contiguous(), w, ref, k.OUT_F32)
+    assert torch.equal(sub, ref)
+
+
+# ----------------------------------------------------------------------------- rope + cache write
+def _paged(G, hd, n_pages, dtype, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    k_pool = torch.randn(n_pages, G, PAGE, hd, generator=g).to(dtype).to(DEV)   # stale contents on purpose
+    v_pool = torch.randn(n_pages, G, PAGE, hd, generator=g).to(dtype).to(DEV)
+    return k_pool, v_pool
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,hd,rot,interleaved", [(4, 2, 16, 16, False), (3, 1, 32, 32, True), (5, 5, 48, 24, False),
+                                                    (8, 2, 128, 128, False), (2, 2, 256, 64, True), (6, 3, 80, 0, False)])
+def test_rope_kv_write(dtype, H, G, hd, rot, interleaved):
+    k = K()
+    M = 11
+    qkv = _rand(M, (H + 2 * G) * hd + 8, dtype=dtype, seed=11)[:, :(H + 2 * G) * hd + 8]   # padded row stride
+    positions = torch.tensor([0, 1, 63, 64, 65, 200, 5, 6, 7, 130, 131], dtype=torch.int32, device=DEV)
+    slot_of_token = torch.tensor([0, 0, 0, 0, 0, 0, 2, 2, 2, 2, 2], dtype=torch.int32, device=DEV)
+    page_table = torch.tensor([[7, 3, 1, 9], [0, 0, 0, 0], [2, 8, 4, 5]], dtype=torch.int32, device=DEV)
+    inv = torch.tensor([1.0 / (10000.0 ** (2 * i / max(rot, 2))) for i in range(max(rot // 2, 1))], device=DEV)
+    k_pool, v_pool = _paged(G, hd, 10, dtype)
+    k_before, v_before = k_pool.clone(), v_pool.clone()
+    src = qkv.clone()
+    k.rope_kv_write(qkv, positions, slot_of_token, page_table, inv, H, G, hd, rot, interleaved, k_pool, v_pool)
+
+    x = src[:, :(H + 2 * G) * hd].double().cpu()
+    q, kk, v = x[:, :H * hd].view(M, H, hd), x[:, H * hd:(H + G) * hd].view(M, G, hd), x[:, (H + G) * hd:].view(M, G, hd)
+    if rot:
+        sin, cos = P.rope_angles(positions.cpu(), inv.cpu())
+        f = P.apply_rope_interleaved if interleaved else P.apply_rope_half
+        q = torch.cat([f(q[..., :rot], sin, cos), q[..., rot:]], -1)
+        kk = torch.cat([f(kk[..., :rot], sin, cos), kk[..., rot:]], -1)
+    tol = _tol(dtype)
+    torch.testing.assert_close(qkv[:, :H * hd].double().cpu().view(M, H, hd), q, **tol)
+    touched = torch.zeros(10, PAGE, dtype=torch.bool)
+    for m in range(M):
+        p = int(positions[m]); page = int(page_table[int(slot_of_token[m]), p // PAGE]); off = p % PAGE
+        touched[page, off] = True
+        torch.testing.assert_close(k_pool[page, :, off].double().cpu(), kk[m], **tol)
+        assert torch.equal(v_pool[page, :, off].double().cpu(), v[m])
+    # nothing else in the pools moved
+    keep = ~touched.to(DEV)
+    assert torch.equal(k_pool.permute(0, 2, 1, 3)[keep], k_before.permute(0, 2, 1, 3)[keep])
+    assert torch.equal(v_pool.permute(0, 2, 1, 3)[keep], v_before.permute(0, 2, 1, 3)[keep])
+
+
+# ----------------------------------------------------------------------------- attention
+def _attention_case(dtype, H, G, hd, lens_q, lens_kv, window=0, seed=0, craft=None):
+    """Builds a paged cache with scrambled pages for sequences of lens_kv tokens; the
+    last lens_q[b] tokens of each are the step's queries.  Returns inputs and the
+    plain float64 result."""
+    B = len(lens_kv)
+    g = torch.Generator().manual_seed(seed)
+    n_pages_each = [-(-n // PAGE) for n in lens_kv]
+    total_pages = sum(n_pages_each) + 3
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    max_pages = max(n_pages_each) + 1
+    page_table = torch.full((B + 1, max_pages), 0, dtype=torch.int32)
+    k_pool = (torch.randn(total_pages, G, PAGE, hd, generator=g) * 3).to(dtype)   # stale values, large
+    v_pool = (torch.randn(total_pages, G, PAGE, hd, generator=g) * 3).to(dtype)
+    slots = list(range(B, 0, -1))      # slots in reverse order
+    ks, vs, qs = [], [], []
+    pi = 0
+    for b in range(B):
+        n = lens_kv[b]
+        kb = torch.randn(n, G, hd, generator=g).to(dtype)
+        vb = torch.randn(n, G, hd, generator=g).to(dtype)
+        qb = torch.randn(lens_q[b], H, hd, generator=g).to(dtype)
+        if craft is not None:
+            craft(b, qb, kb, vb)
+        for p in range(n_pages_each[b]):
+            page = perm[pi]; pi += 1
+            page_table[slots[b], p] = page
+            lo, hi = p * PAGE, min(n, (p + 1) * PAGE)
+            k_pool[page, :, :hi - lo] = kb[lo:hi].transpose(0, 1)
+            v_pool[page, :, :hi - lo] = vb[lo:hi].transpose(0, 1)
+        ks.append(kb); vs.append(vb); qs.append(qb)
+    positions, slot_of_token, refs = [], [], []
+    for b in range(B):
+        n, nq = lens_kv[b], lens_q[b]
+        full_q = torch.zeros(n, H, hd, dtype=torch.float64)
+        full_q[n - nq:] = qs[b].double()
+        out = P.causal_attention(full_q, ks[b].double(), vs[b].double(), window=window or None)
+        refs.append(out[n - nq:].reshape(nq, H * hd))
+        positions += list(range(n - nq, n))
+        slot_of_token += [slots[b]] * nq
+    q = torch.cat([x.reshape(x.shape[0], H * hd) for x in qs]).to(DEV)
+    return (q, k_pool.to(DEV), v_pool.to(DEV), page_table.to(DEV),
+            torch.tensor(slot_of_token, dtype=torch.int32, device=DEV),
+            torch.tensor(positions, dtype=torch.int32, device=DEV), torch.cat(refs))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,hd", [(4, 2, 16), (3, 1, 32), (5, 5, 48), (8, 2, 64), (6, 2, 80), (8, 1, 128), (2, 2, 256), (7, 7, 112)])
+def test_attention_simt_prefill_and_decode_shapes(dtype, H, G, hd):
+    k = K()
+    for lens_q, lens_kv in (([1, 1, 1], [1, 64, 200]), ([5, 70, 1, 33], [5, 70, 129, 97]), ([130], [130])):
+        q, kp, vp, pt, sot, pos, ref = _attention_case(dtype, H, G, hd, lens_q, lens_kv, seed=hd + len(lens_q))
+        out = torch.empty(q.shape[0], H * hd, dtype=dtype, device=DEV)
+        k.attention_simt(q, kp, vp, pt, sot, pos, out, H, G, hd, 1.0 / math.sqrt(hd))
+        torch.testing.assert_close(out.double().cpu(), ref, **(_tol(dtype) if dtype == torch.bfloat16 else dict(rtol=2e-5, atol=2e-5)))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_simt_window(dtype):
+    k = K()
+    H, G, hd, W = 4, 2, 32, 70
+    q, kp, vp, pt, sot, pos, ref = _attention_case(dtype, H, G, hd, [40, 1, 150], [40, 300, 150], window=W, seed=3)
+    out = torch.empty(q.shape[0], H * hd, dtype=dtype, device=DEV)
+    k.attention_simt(q, kp, vp, pt, sot, pos, out, H, G, hd, 1.0 / math.sqrt(hd), W)
+    torch.testing.assert_close(out.double().cpu(), ref, **(_tol(dtype) if dtype == torch.bfloat16 else dict(rtol=2e-5, atol=2e-5)))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("far", [0, 63, 64, 449, 450])
+def test_attention_finds_one_far_key_among_hundreds(dtype, far):
+    """One key is made to stand out (query and key scaled so that its score dominates):
+    the output must be that key's value, wherever in the pages it lies."""
+    H, G, hd, n = 4, 2, 64, 451
+
+    def craft(b, qb, kb, vb):
+        direction = torch.ones(hd) / math.sqrt(hd)
+        qb[:] = (direction * 12.0).to(qb.dtype)          # every head asks for the same direction
+        kb[:] = (kb.float() * 0.05).to(kb.dtype)
+        kb[far] = (direction * 12.0).to(kb.dtype)        # score 144/8 = 18 against ~0 elsewhere
+    q, kp, vp, pt, sot, pos, ref = _attention_case(dtype, H, G, hd, [1], [n], seed=5, craft=craft)
+    out = torch.empty(1, H * hd, dtype=dtype, device=DEV)
+    K().attention_simt(q, kp, vp, pt, sot, pos, out, H, G, hd, 1.0 / math.sqrt(hd))
+    torch.testing.assert_close(out.double().cpu(), ref, **(_tol(dtype) if dtype == torch.bfloat16 else dict(rtol=2e-5, atol=2e-5)))
+    # and the plain result is, to 1e-4, the far key's value: the test would notice a missed key
+    page = int(pt[1, far // PAGE]); v_far = vp[page, :, far % PAGE].double().cpu()   # [G, hd]
+    want = v_far.repeat_interleave(H // G, dim=0).reshape(1, H * hd)
+    assert (ref - want).abs().max() < 1e-3
+
+
+# ----------------------------------------------------------------------------- sampling
+def test_argmax_first_maximum_wins_and_non_finite_is_skipped():
+    k = K()
+    V = 5000
+    logits = _rand(6, V, seed=12)
+    logits[0, 4000] = 50.0; logits[0, 17] = 50.0             # tie: the first wins
+    logits[1, :] = float("-inf"); logits[1, 4999] = -3.0
+    logits[2, 100] = float("nan"); logits[2, 7] = 99.0
+    logits[3, :] = float("nan")                              # nothing finite: token 0
+    logits[4, 0] = float("inf"); logits[4, 9] = 60.0         # +inf is not finite either
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    k.argmax(logits, out)
+    want = [P.argmax_finite(logits[i].cpu().numpy()) for i in range(6)]
+    assert out.tolist() == want and want[:5] == [17, 4999, 7, 0, 9]
+
+
+@pytest.mark.parametrize("V", [7, 384, 5000, 128256])
+def test_temperature_sampling_follows_the_plain_sampler(V):
+    k = K()
+    rows = 24
+    logits = _rand(rows, V, seed=13, scale=2.0)
+    logits[3, 5 % V] = float("-inf"); logits[4, 2 % V] = float("nan")
+    temps = torch.tensor([0.8, 1.0, 0.3, 1.5] * 6)
+    rngs = [P.Rng(100 + i) for i in range(rows)]
+    for trial in range(6):
+        u = torch.tensor([r.next_f32() for r in rngs])
+        out = torch.empty(rows, dtype=torch.int32, device=DEV)
+        k.sample_temperature(logits, temps.to(DEV), u.to(DEV), out)
+        for i in range(rows):
+            class Fixed:                      # hands the plain sampler the same uniform
+                def next_f32(self, v=float(u[i])): return v
+            want = P.sample(logits[i].cpu().numpy(), float(temps[i]), Fixed())
+            assert out[i].item() == want, f"row {i} trial {trial}: {out[i].item()} vs {want}"
+
+
+def test_temperature_zero_rows_are_greedy_and_min_p_cuts():
+    k = K()
+    logits = torch.tensor([[1.0, 5.0, 2.0, 4.9], [10.0, 9.5, 3.0, 1.0]], device=DEV)
+    out = torch.empty(2, dtype=torch.int32, device=DEV)
+    for u in (0.0, 0.5, 0.999):
+        k.sample_temperature(logits, torch.tensor([0.0, 1.0], device=DEV), torch.tensor([u, u], device=DEV), out,
+                             torch.tensor([0.0, 0.3], device=DEV))
+        assert out[0].item() == 1 and out[1].item() in (0, 1)
+    k.sample_temperature(logits, torch.tensor([1.0, 1.0], device=DEV), torch.tensor([0.999999, 0.999999], device=DEV), out,
+                         torch.tensor([0.0, 0.3], device=DEV))
+    assert out[1].item() == 1      # the tail (tokens 2, 3) is cut: the last kept candidate
+
+
+def test_repeat_penalty_kernel():
+    k = K()
+    logits = torch.tensor([[4.0, -4.0, 2.0, float("nan")], [1.0, 2.0, 3.0, 4.0]], device=DEV)
+    recent = torch.zeros(2, 64, dtype=torch.int32, device=DEV)
+    recent[0, :4] = torch.tensor([0, 1, 3, 99]); recent[1, :3] = torch.tensor([2, 2, 0])
+    k.repeat_penalty(logits, recent, torch.tensor([4, 3], dtype=torch.int32, device=DEV), 2.0)
+    assert logits[0, :3].tolist() == [2.0, -8.0, 2.0] and logits[0, 3].item() == float("-inf")
+    assert logits[1].tolist() == [0.5, 2.0, 0.75, 4.0]      # token 2 twice: divided twice
+
+
+def test_sampler_object_runs_the_reference_cases():
+    from rustyllm_b200.sampling.config import SamplerConfig
+    from rustyllm_b200.sampling.sampler import Sampler, SequenceSamplingState
+    s = Sampler(torch.device(DEV))
+    for name, opt, seed, draws, logits, recent, allowed, must in CASES:
+        st = SequenceSamplingState(SamplerConfig(**opt), seed, recent)
+        seen = set()
+        for _ in range(draws):
+            t = s.sample(torch.tensor([logits], device=DEV), [st])[0]
+            assert t in allowed, name
+            seen.add(t)
+        assert must <= seen, name
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    k = K()
+    with pytest.raises(k.KernelError, match="CUDA tensors only"):
+        k.swiglu(torch.zeros(2, 4), torch.zeros(2, 2))
+    q = torch.zeros(1, 2 * 300, device=DEV)
+    with pytest.raises(k.KernelError, match="head_dim"):
+        k.attention_simt(q, torch.zeros(1, 2, PAGE, 300, device=DEV), torch.zeros(1, 2, PAGE, 300, device=DEV),
+                         torch.zeros(1, 1, dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+                         torch.zeros(1, dtype=torch.int32, device=DEV), torch.zeros(1, 600, device=DEV), 2, 2, 300, 1.0)
+    with pytest.raises(k.KernelError, match="not handled"):
+        k.swiglu(torch.zeros(2, 4, dtype=torch.float16, device=DEV), torch.zeros(2, 2, dtype=torch.float16, device=DEV))
