@@ -122,6 +122,12 @@ def build(force: bool = False, verbose: bool = True) -> str:
         raise RuntimeError(f"linking the kernel library failed:\n{p.stdout}")
     os.replace(tmp, lib)  # atomic: a concurrent process sees the old state or the whole file
     shutil.rmtree(objdir, ignore_errors=True)
+    for old in os.listdir(root):   # libraries of earlier source states
+        if old.startswith("librustyllm_b200_") and old.endswith(".so") and os.path.join(root, old) != lib:
+            try:
+                os.remove(os.path.join(root, old))
+            except OSError:
+                pass
     _say(f"built {lib}")
     return lib
 

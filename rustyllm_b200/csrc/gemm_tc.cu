@@ -1,0 +1,324 @@
+// out[M, N] = A[M, K] * W[N, K]^T (+ bias) in bf16 on the 5th-generation tensor cores:
+// tcgen05.mma with the accumulator in tensor memory, operands staged in shared
+// memory by TMA (128-byte swizzle), a ring of stages between one producer thread and
+// one MMA-issuing thread, and four epilogue warps that read the accumulator back
+// with tcgen05.ld.
+//
+// The weight rows are the MMA's M dimension (128 per CTA) and the step's tokens its N
+// dimension (16..256 per CTA): a decode step with a handful of tokens still fills
+// the 128-row instruction with weight rows and streams each weight exactly once,
+// and a prefill uses 128 x 256 tiles.  Both operands are K-major, as every weight
+// of the model is stored ([out x in], SimonWaldherr/RustyLLM src/model.rs:185-186); no
+// transposes anywhere.  Accumulation is float; the epilogue adds the optional bias
+// and stores bf16, stores float, or adds into a float buffer (the residual sum).
+//
+// Every wait on an mbarrier is bounded: when it runs out the kernel records a code
+// in the error word, all roles leave their loops, tensor memory is freed and the
+// kernel returns.
+#include <cuda.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+enum { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_OUT_ADD_F32 = 2 };
+
+static constexpr int BLOCK_N_OUT = 128;   // weight rows per CTA (MMA M)
+static constexpr int BLOCK_K = 64;        // bf16 elements per stage along K = one 128-byte swizzle row
+static constexpr int UMMA_K = 16;
+static constexpr int TC_THREADS = 192;    // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
+static constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false when the limit ran out or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the mbarrier once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16)
+// and swizzled with the 128-byte pattern: start address / 16 in bits 0-13, leading
+// byte offset (unused for this layout, set to 16 bytes) in bits 16-29, stride between
+// groups of 8 rows = 1024 bytes in bits 32-45, descriptor version 1 in bits 46-47,
+// layout type 2 (128-byte swizzle) in bits 61-63.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::f16: float accumulator (bits 4-5 = 1), A and B bf16
+// (bits 7-9 and 10-12 = 1), both K-major (bits 15, 16 = 0), N/8 in bits 17-22, M/16 in
+// bits 24-28.
+__host__ __device__ constexpr uint32_t make_idesc(int mma_m, int mma_n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(mma_n >> 3) << 17) | ((uint32_t)(mma_m >> 4) << 24);
+}
+
+template <int BT>
+struct TcConfig {
+  static constexpr int STAGE_BYTES = (BLOCK_N_OUT + BT) * BLOCK_K * 2;
+  static constexpr int STAGES = (196608 / STAGE_BYTES) < 8 ? (196608 / STAGE_BYTES) : 8;
+  static constexpr int TMEM_COLS = BT < 32 ? 32 : BT;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+// BT: tokens per CTA (MMA N).  Grid: (ceil(N_out / 128), ceil(M_tokens / BT)).
+template <int BT>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+               const float* __restrict__ bias, void* __restrict__ out, int out_mode, int M, int N, int K,
+               int ldo, int* __restrict__ err) {
+  using Cfg = TcConfig<BT>;
+  extern __shared__ uint8_t smem_raw[];
+  // tiles need 1024-byte alignment for the 128-byte swizzle pattern
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* tiles = smem;
+  uint64_t* bars = (uint64_t*)(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full_bar = bars;                       // [STAGES]
+  uint64_t* empty_bar = bars + Cfg::STAGES;        // [STAGES]
+  uint64_t* accum_bar = bars + 2 * Cfg::STAGES;    // [1]
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * Cfg::STAGES + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BLOCK_N_OUT;   // first weight row (output feature) of this CTA
+  const int m0 = blockIdx.y * BT;            // first token of this CTA
+  const int num_kb = (K + BLOCK_K - 1) / BLOCK_K;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    mbar_init(smem_u32(accum_bar), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- producer: TMA loads into the ring ----------------
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % Cfg::STAGES;
+        const uint32_t phase = (kb / Cfg::STAGES) & 1;
+        if (!mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1, abort_flag)) {
+          if (!*abort_flag) { *abort_flag = 1; atomicExch(err, 1); }
+          break;
+        }
+        const uint32_t fb = smem_u32(&full_bar[s]);
+        mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+        uint8_t* st = tiles + (size_t)s * Cfg::STAGE_BYTES;
+        tma_load_2d(smem_u32(st), &map_w, fb, kb * BLOCK_K, n0);
+        tma_load_2d(smem_u32(st + BLOCK_N_OUT * BLOCK_K * 2), &map_a, fb, kb * BLOCK_K, m0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer ----------------
+      constexpr uint32_t idesc = make_idesc(BLOCK_N_OUT, BT);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % Cfg::STAGES;
+        const uint32_t phase = (kb / Cfg::STAGES) & 1;
+        if (!mbar_wait(smem_u32(&full_bar[s]), phase, abort_flag)) {
+          if (!*abort_flag) { *abort_flag = 1; atomicExch(err, 2); }
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        uint8_t* st = tiles + (size_t)s * Cfg::STAGE_BYTES;
+        const uint64_t da = make_smem_desc(smem_u32(st));
+        const uint64_t db = make_smem_desc(smem_u32(st + BLOCK_N_OUT * BLOCK_K * 2));
+#pragma unroll
+        for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+          // advancing 16 elements = 32 bytes inside the swizzled row: +2 in units of 16 bytes
+          umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&empty_bar[s]));   // the stage is free once these MMAs have read it
+      }
+      if (ok) umma_commit(smem_u32(accum_bar));  // the accumulator is complete
+    }
+  } else {
+    // ---------------- epilogue: warps 2..5, each its quarter of the 128 lanes ----------------
+    const bool ok = mbar_wait(smem_u32(accum_bar), 0, abort_flag);
+    if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(err, 3); }
+    tc_fence_after();
+    if (ok) {
+      const int quarter = warp & 3;                    // lanes this warp may read
+      const int n = n0 + quarter * 32 + lane;          // output feature of this thread
+      const float b = (bias != nullptr && n < N) ? bias[n] : 0.f;
+#pragma unroll 1
+      for (int c = 0; c < BT / 16; ++c) {
+        uint32_t r[16];
+        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 16), r);
+        tmem_ld_wait();
+        if (n < N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = m0 + c * 16 + j;
+            if (m < M) {
+              const float v = __uint_as_float(r[j]) + b;
+              const size_t o = (size_t)m * ldo + n;
+              if (out_mode == TC_OUT_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
+              else if (out_mode == TC_OUT_F32) ((float*)out)[o] = v;
+              else ((float*)out)[o] += v;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = (EncodeTiledFn)p;
+  return fn;
+}
+
+// A row-major bf16 matrix [rows, cols] with row stride ld (elements), tiled in boxes
+// of box_rows x 64 columns, 128-byte swizzle, zero fill outside.
+static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  RL_REQUIRE(enc != nullptr, "rl_gemm_tc: the driver does not provide cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  RL_REQUIRE(r == CUDA_SUCCESS, "rl_gemm_tc: cuTensorMapEncodeTiled failed with %d (rows=%d cols=%d ld=%d box_rows=%d)",
+             (int)r, rows, cols, ld, box_rows);
+  return RL_OK;
+}
+
+template <int BT>
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, void* out, int out_mode,
+                     int M, int N, int K, int ldo, int* err, cudaStream_t stream) {
+  using Cfg = TcConfig<BT>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    RL_REQUIRE(e == cudaSuccess, "rl_gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
+    configured = true;
+  }
+  dim3 grid((N + BLOCK_N_OUT - 1) / BLOCK_N_OUT, (M + BT - 1) / BT);
+  gemm_tc_kernel<BT><<<grid, TC_THREADS, Cfg::SMEM_BYTES, stream>>>(mw, ma, bias, out, out_mode, M, N, K, ldo, err);
+  RL_LAUNCH_CHECK("rl_gemm_tc");
+  return RL_OK;
+}
+
+// 1 if the tensor-core kernel takes these operands: TMA needs 16-byte aligned bases
+// and row strides that are multiples of 16 bytes.
+extern "C" int rl_gemm_tc_supported(const void* A, const void* W, int M, int N, int K, int lda) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (K % 8 != 0 || lda % 8 != 0 || lda < K) return 0;
+  if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return 0;
+  return 1;
+}
+
+// A: [M, K] bf16, row stride lda; W: [N, K] bf16 contiguous; out: [M, N] with row stride
+// ldo, bf16 (out_mode 0) or float (1 store, 2 add).  err: device int, set non-zero if a
+// bounded wait inside the kernel ran out.
+extern "C" int rl_gemm_tc(const void* A, const void* W, const float* bias, void* out, int out_mode, int M, int N,
+                          int K, int lda, int ldo, int* err, cudaStream_t stream) {
+  RL_REQUIRE(rl_gemm_tc_supported(A, W, M, N, K, lda), "rl_gemm_tc: operands not supported (M=%d N=%d K=%d lda=%d; K and lda "
+             "must be multiples of 8 and the bases 16-byte aligned)", M, N, K, lda);
+  RL_REQUIRE(out_mode >= 0 && out_mode <= 2, "rl_gemm_tc: unknown output mode %d", out_mode);
+  RL_REQUIRE(ldo >= N && err != nullptr, "rl_gemm_tc: bad output stride or null error word");
+  const int bt = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  CUtensorMap mw, ma;
+  int rc = make_map(&mw, W, N, K, K, BLOCK_N_OUT);
+  if (rc != RL_OK) return rc;
+  rc = make_map(&ma, A, M, K, lda, bt);
+  if (rc != RL_OK) return rc;
+  switch (bt) {
+    case 16: return launch_tc<16>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, stream);
+    case 32: return launch_tc<32>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, stream);
+    case 64: return launch_tc<64>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, stream);
+    case 128: return launch_tc<128>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, stream);
+    default: return launch_tc<256>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, stream);
+  }
+}

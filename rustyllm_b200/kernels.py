@@ -46,6 +46,11 @@ _SIGNATURES = {
     "rl_repeat_penalty": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_float, _c_void_p],
     "rl_argmax": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
     "rl_sample_temperature": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    "rl_sample_candidates": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
+                             _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    "rl_gemm_tc_supported": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int],
+    "rl_gemm_tc": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                   _c_void_p, _c_void_p],
 }
 
 
@@ -265,15 +270,55 @@ def page_size() -> int:
 
 
 # ----------------------------------------------------------------------------- tensor-core GEMM
+_tc_err = {}
+
+
+def _tc_error_word(device: torch.device) -> torch.Tensor:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _tc_err:
+        _tc_err[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tc_err[key]
+
+
+def check_device_errors() -> None:
+    """Raise if a kernel recorded an error on the device (a bounded wait that ran
+    out).  Synchronizes; call it where the host waits for results anyway."""
+    for key, t in _tc_err.items():
+        code = int(t.item())
+        if code != 0:
+            t.zero_()
+            raise KernelError(f"a tensor-core GEMM on cuda:{key} gave up waiting (code {code}: "
+                              "1 = for a free stage, 2 = for a TMA load, 3 = for the accumulator)")
+
+
 def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
     """Whether the tensor-core kernel takes these operands (else the caller uses
-    the CUDA-core kernel, which takes every shape)."""
-    return False
+    the CUDA-core kernel, which takes every shape): bf16, K and the row stride of
+    ``a`` multiples of 8 elements, bases 16-byte aligned."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not w.is_contiguous() or a.stride(1) != 1:
+        return False
+    M, K = a.shape
+    lda = a.stride(0) if M > 1 else K
+    return bool(library().rl_gemm_tc_supported(a.data_ptr(), w.data_ptr(), M, w.shape[0], K, lda))
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_mode: int,
             bias: Optional[torch.Tensor] = None) -> None:
-    raise KernelError("the tensor-core GEMM is not built")
+    """out = a @ w.T (+ bias) on the tensor cores (tcgen05).  a: [M, K] bf16, w: [N, K] bf16;
+    out: bf16 (OUT_SAME) or float32 (OUT_F32 store, OUT_ADD_F32 add)."""
+    _need(a, "a", torch.bfloat16, contiguous=False); _need(w, "w", torch.bfloat16); _need(out, "out", contiguous=False)
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N) and out.stride(1) == 1
+    assert out.dtype == (torch.bfloat16 if out_mode == OUT_SAME else torch.float32)
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        assert bias.numel() == N
+    lda = a.stride(0) if M > 1 else K
+    ldo = out.stride(0) if M > 1 else N
+    _check(library().rl_gemm_tc(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), out_mode, M, N, K, lda, ldo,
+                                _tc_error_word(a.device).data_ptr(), _stream()), "rl_gemm_tc")
+    _count()
 
 
 # ----------------------------------------------------------------------------- attention dispatch
@@ -287,5 +332,26 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
                    num_heads, num_kv_heads, head_dim, scale, window)
 
 
-def sample_candidates(logits, rows, temperature, uniform, min_p, top_k, top_p, out) -> None:
-    raise KernelError("top-k / top-p sampling on the device is not built yet")
+MAX_TOP_K = 1024
+
+
+def sample_candidates(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
+                      min_p: torch.Tensor, out: torch.Tensor, topk_rows, topk_k, topk_p, topp_rows, topp_p) -> None:
+    """Rows that sample from a candidate set.  ``topk_rows`` (host list of row indices)
+    with their ``topk_k`` and ``topk_p`` take the top-k path; ``topp_rows`` with
+    ``topp_p`` the top-p path over the whole vocabulary.  temperature / uniform /
+    min_p / out are indexed by logits row."""
+    _need(logits, "logits", torch.float32); _need(out, "out", torch.int32)
+    _need(temperature, "temperature", torch.float32); _need(uniform, "uniform", torch.float32)
+    _need(min_p, "min_p", torch.float32)
+    if any(k > MAX_TOP_K for k in topk_k):
+        raise KernelError(f"top_k up to {MAX_TOP_K} is supported on the device, got {max(topk_k)}")
+    dev = logits.device
+    i32 = lambda x: torch.tensor(list(x) or [0], dtype=torch.int32, device=dev)
+    f32 = lambda x: torch.tensor(list(x) or [0.0], dtype=torch.float32, device=dev)
+    rk, kk, pk, rp, pp = i32(topk_rows), i32(topk_k), f32(topk_p), i32(topp_rows), f32(topp_p)
+    _check(library().rl_sample_candidates(logits.data_ptr(), logits.shape[1], rk.data_ptr(), kk.data_ptr(), pk.data_ptr(),
+                                          len(topk_rows), rp.data_ptr(), pp.data_ptr(), len(topp_rows),
+                                          temperature.data_ptr(), uniform.data_ptr(), min_p.data_ptr(), out.data_ptr(),
+                                          _stream()), "rl_sample_candidates")
+    _count((1 if topk_rows else 0) + (1 if topp_rows else 0))

@@ -68,8 +68,11 @@ class Sampler:
             K.argmax(logits, out)
             return out.tolist()
 
-        cand_rows = [b for b, s in enumerate(states)
-                     if s.config.needs_candidates and (0 < s.config.top_k < V or s.config.top_p < 1.0)]
+        def takes_top_k(c: SamplerConfig) -> bool:
+            return not c.is_greedy and 1 < c.top_k < V
+        topk = [b for b, s in enumerate(states) if takes_top_k(s.config)]
+        topp = [b for b, s in enumerate(states)
+                if not s.config.is_greedy and not takes_top_k(s.config) and s.config.top_p < 1.0]
         # one float upload: temperature | uniform | min_p
         f = np.zeros((3, B), dtype=np.float32)
         for b, s in enumerate(states):
@@ -79,14 +82,11 @@ class Sampler:
             f[1, b] = 0.0 if greedy else s.rng.next_f32()
             f[2, b] = c.min_p
         fd = torch.from_numpy(f).to(dev)
-        if not cand_rows:
-            K.sample_temperature(logits, fd[0], fd[1], out, fd[2] if f[2].any() else None)
-            return out.tolist()
-        # mixed batch: plain rows through the softmax kernel, candidate rows through theirs
+        # every row goes through the softmax kernel (greedy rows are answered there too);
+        # rows with a candidate set are then answered again by their own kernel
         K.sample_temperature(logits, fd[0], fd[1], out, fd[2] if f[2].any() else None)
-        top_k = torch.tensor([states[b].config.top_k if 0 < states[b].config.top_k < V else 0 for b in cand_rows],
-                             dtype=torch.int32, device=dev)
-        top_p = torch.tensor([states[b].config.top_p for b in cand_rows], dtype=torch.float32, device=dev)
-        rows = torch.tensor(cand_rows, dtype=torch.int32, device=dev)
-        K.sample_candidates(logits, rows, fd[0], fd[1], fd[2], top_k, top_p, out)
+        if topk or topp:
+            K.sample_candidates(logits, fd[0], fd[1], fd[2], out,
+                                topk, [states[b].config.top_k for b in topk], [states[b].config.top_p for b in topk],
+                                topp, [states[b].config.top_p for b in topp])
         return out.tolist()

@@ -29,7 +29,13 @@ def _step(positions, slots_per_token, cu, slots, kv_lens):
                      all(q == 1 for q in q_lens))
 
 
-TOL = {torch.float32: dict(rtol=2e-5, atol=2e-5), torch.bfloat16: dict(rtol=3e-2, atol=3e-2)}
+def close(got, ref, dtype):
+    """Largest error against the rms of the reference: 2e-5 in 32-bit; 2e-2 in bf16,
+    where every stored intermediate carries a relative rounding error of up to 2^-9
+    and a few dozen of them add up in each output."""
+    got, ref = got.double().cpu(), ref.double().cpu()
+    err = (got - ref).abs().max().item() / ref.pow(2).mean().sqrt().item()
+    assert err <= (2e-5 if dtype == torch.float32 else 2e-2), f"max |diff| / rms = {err:.3e}"
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -42,7 +48,7 @@ def test_norm_part(dtype):
     x = _rand(6, 100, seed=2, scale=4)
     got = n.forward(x, dtype)
     assert got.dtype == dtype
-    torch.testing.assert_close(got.double().cpu(), P.rms_norm(x.double().cpu(), n.weight.double().cpu(), 1e-4), **TOL[dtype])
+    close(got, P.rms_norm(x.double().cpu(), n.weight.double().cpu(), 1e-4), dtype)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -69,7 +75,7 @@ def test_feed_forward_part(dtype, bias):
     gu = x64 @ w["wgu"].double().cpu().T + (w["bgu"].double().cpu() if bias else 0)
     h = P.swiglu(gu[:, :I], gu[:, I:])
     ref = res.double().cpu() + h @ w["wdown"].double().cpu().T + (w["bdown"].double().cpu() if bias else 0)
-    torch.testing.assert_close(out.double().cpu(), ref, **TOL[dtype])
+    close(out, ref, dtype)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -88,7 +94,9 @@ def test_attention_part_prompt_then_single_tokens(dtype, H, G, hd, bias, pairing
         "position": rope, "names": {"q": "q", "k": "k", "v": "v", "o": "o"}}), _runtime(dtype))
     need = att.kv_need()
     assert (need.num_kv_heads, need.head_dim, need.window) == (G, hd, None) and att.state_need() is None
-    w = {"wqkv": _rand((H + 2 * G) * hd, d, seed=1, scale=0.3, dtype=dtype), "wo": _rand(d, H * hd, seed=2, scale=0.3, dtype=dtype)}
+    # weights scaled so that scores are of order one (a softmax that is not razor sharp:
+    # with scores of 20 and more, bf16 rounding of q and k alone would move the result)
+    w = {"wqkv": _rand((H + 2 * G) * hd, d, seed=1, scale=0.12, dtype=dtype), "wo": _rand(d, H * hd, seed=2, scale=0.3, dtype=dtype)}
     if bias:
         w.update(bqkv=_rand((H + 2 * G) * hd, seed=3, scale=0.2), bo=_rand(d, seed=4, scale=0.2))
     att.bind(w)
@@ -127,7 +135,7 @@ def test_attention_part_prompt_then_single_tokens(dtype, H, G, hd, bias, pairing
         f = P.apply_rope_half if pairing == "half" else P.apply_rope_interleaved
         a = P.causal_attention(f(q, sin, cos), f(k, sin, cos), v).reshape(T, H * hd)
         ref = a @ w["wo"].double().cpu().T + (w["bo"].double().cpu() if bias else 0)
-        torch.testing.assert_close(torch.cat(got[b]).double().cpu(), ref, **TOL[dtype])
+        close(torch.cat(got[b]), ref, dtype)
 
 
 def test_rope_part_tables():
@@ -161,7 +169,7 @@ def test_embedding_and_head_parts(dtype):
     xn = _rand(4, 40, seed=2, dtype=dtype)
     logits = head.forward(xn)
     assert logits.dtype == torch.float32 and logits.shape == (4, 307)
-    torch.testing.assert_close(logits.double().cpu(), xn.double().cpu() @ table.double().cpu().T, **TOL[dtype])
+    close(logits, xn.double().cpu() @ table.double().cpu().T, dtype)
 
 
 def test_unknown_kind_is_reported_with_the_known_ones():
