@@ -5,6 +5,7 @@ import pytest
 import torch
 
 import plain_llama as P
+from gpu_helpers import BF16_REL_MAX, BF16_REL_MEAN
 
 pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda:0")
@@ -30,12 +31,19 @@ def _step(positions, slots_per_token, cu, slots, kv_lens):
 
 
 def close(got, ref, dtype):
-    """Largest error against the rms of the reference: 2e-5 in 32-bit; 2e-2 in bf16,
-    where every stored intermediate carries a relative rounding error of up to 2^-9
-    and a few dozen of them add up in each output."""
+    """Error against the rms of the reference.  32-bit: at most 2e-5.  bf16: the bound
+    used for logits throughout these tests (gpu_helpers): every stored intermediate
+    carries a relative rounding error of up to 2^-8, a few dozen of them add up in
+    each output, and the maximum is taken over thousands of outputs - at most 3e-2,
+    and 6e-3 on average."""
     got, ref = got.double().cpu(), ref.double().cpu()
-    err = (got - ref).abs().max().item() / ref.pow(2).mean().sqrt().item()
-    assert err <= (2e-5 if dtype == torch.float32 else 2e-2), f"max |diff| / rms = {err:.3e}"
+    rms = ref.pow(2).mean().sqrt().item()
+    err = (got - ref).abs() / rms
+    if dtype == torch.float32:
+        assert err.max().item() <= 2e-5, f"max |diff| / rms = {err.max().item():.3e}"
+    else:
+        assert err.max().item() <= BF16_REL_MAX, f"max |diff| / rms = {err.max().item():.3e}"
+        assert err.mean().item() <= BF16_REL_MEAN, f"mean |diff| / rms = {err.mean().item():.3e}"
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
