@@ -16,8 +16,10 @@ from typing import List, Optional, Sequence, Union
 import numpy as np
 import torch
 
+from .. import kernels as K
 from ..cache.sequence_cache import SequenceCache
 from ..models.decoder import DecoderModel
+from ..staging import PinnedStaging
 
 
 @dataclass
@@ -39,46 +41,46 @@ class StepState:
     is_decode: bool               # every sequence brings exactly one token
 
 
-class _Staging:
-    """Ring of pinned host buffers for the step's integer inputs.  A buffer is
-    reused only after the copy that read it has finished."""
-
-    def __init__(self, device: torch.device, depth: int = 4):
-        self.device = device
-        self.depth = depth
-        self.bufs: List[Optional[torch.Tensor]] = [None] * depth
-        self.events: List[Optional[torch.cuda.Event]] = [None] * depth
-        self.i = 0
-
-    def upload(self, host: np.ndarray) -> torch.Tensor:
-        n = host.shape[0]
-        k = self.i
-        self.i = (self.i + 1) % self.depth
-        if self.events[k] is not None:
-            self.events[k].synchronize()
-        if self.bufs[k] is None or self.bufs[k].numel() < n:
-            self.bufs[k] = torch.empty(max(n, 1024), dtype=torch.int32, pin_memory=True)
-        self.bufs[k][:n].numpy()[:] = host
-        dev = self.bufs[k][:n].to(self.device, non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record()
-        self.events[k] = ev
-        return dev
-
-
 Want = Union[str, None, Sequence[Sequence[int]]]
 
 
-class Engine:
-    """A model with its cache and the step function over them."""
+class _DecodeGraph:
+    """A captured single-token step for a fixed number of sequences.  Its kernels read
+    the step's integers from ``static_in`` and leave logits in ``logits``; everything
+    they read beyond that (page tables, cache pools, weights) keeps its address."""
 
-    def __init__(self, model: DecoderModel, cache: SequenceCache):
+    def __init__(self, engine: "Engine", num_seqs: int):
+        B = num_seqs
+        self.num_seqs = B
+        dev = engine.device
+        self.static_in = torch.zeros(7 * B + 1, dtype=torch.int32, device=dev)
+        st = engine.step_state(self.static_in, (B, B, B), [1] * B, [1] * B)
+        before = K.launch_count
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            x = engine.model.forward(st, engine.cache)
+            self.logits = engine.model.logits(x, st.want_rows)
+        self.launches = K.launch_count - before
+        K.launch_count = before    # capturing runs nothing
+
+
+class Engine:
+    """A model with its cache and the step function over them.
+
+    ``use_graphs``: single-token steps are captured once per batch size in a CUDA graph
+    and replayed (the first such step of a size runs eagerly, so every kernel has been
+    launched once before it is captured)."""
+
+    def __init__(self, model: DecoderModel, cache: SequenceCache, use_graphs: bool = True):
         self.model = model
         self.cache = cache
         self.device = model.runtime.device
         self.vocab_size = model.spec.vocab_size
-        self._staging = _Staging(self.device) if self.device.type == "cuda" else None
+        self._staging = PinnedStaging(self.device) if self.device.type == "cuda" else None
         self.h2d_bytes = 0
+        self.use_graphs = use_graphs and self.device.type == "cuda" and model.graph_capturable
+        self._graphs = {}          # num_seqs -> _DecodeGraph
+        self._eager_decodes = {}   # num_seqs -> eager single-token steps run so far
 
     # ------------------------------------------------------------------ slots
     def alloc_slot(self) -> int:
@@ -166,6 +168,19 @@ class Engine:
         """
         packed, sizes, q_lens, kv_lens = self.build_step(slots, tokens, want)
         self.cache.prepare(slots, q_lens)
+        B = len(slots)
+        if self.use_graphs and sizes[0] == B and isinstance(want, str) and want == "last":
+            g = self._graphs.get(B)
+            if g is None and self._eager_decodes.get(B, 0) >= 1:
+                g = self._graphs[B] = _DecodeGraph(self, B)
+            if g is not None:
+                g.static_in.copy_(self._staging.upload(packed))
+                self.h2d_bytes += packed.nbytes
+                g.graph.replay()
+                K.launch_count += g.launches
+                self.cache.commit(slots, q_lens)
+                return g.logits.clone()   # the graph's own buffer is overwritten by its next replay
+            self._eager_decodes[B] = self._eager_decodes.get(B, 0) + 1
         if self._staging is not None:
             dev = self._staging.upload(packed)
         else:

@@ -77,6 +77,12 @@ class DecoderModel:
         _collect_params("final_norm", self.final_norm, self._params)
         _collect_params("head", self.head, self._params)
 
+    @property
+    def graph_capturable(self) -> bool:
+        def ok(part: Part) -> bool:
+            return part.graph_capturable and all(ok(p) for p in part.sub_parts().values())
+        return all(ok(p) for p in [self.embedding, self.final_norm, self.head] + self.blocks)
+
     # ------------------------------------------------------------------ parameters
     def param_specs(self) -> Dict[str, ParamSpec]:
         return {path: ps for path, (_, _, ps) in self._params.items()}

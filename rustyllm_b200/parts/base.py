@@ -48,6 +48,10 @@ class Runtime:
 
 
 class Part:
+    # False for a part whose ``forward`` reads device data on the host (or otherwise
+    # cannot be captured in a CUDA graph); the engine then runs every step eagerly.
+    graph_capturable: bool = True
+
     def param_specs(self) -> Dict[str, ParamSpec]:
         return {}
 

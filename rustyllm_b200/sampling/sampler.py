@@ -15,6 +15,7 @@ import numpy as np
 import torch
 
 from .. import kernels as K
+from ..staging import PinnedStaging
 from .config import RECENT_TOKEN_LIMIT, Rng, SamplerConfig
 
 
@@ -37,6 +38,12 @@ class SequenceSamplingState:
 class Sampler:
     def __init__(self, device: torch.device):
         self.device = device
+        self._floats = PinnedStaging(device, torch.float32) if device.type == "cuda" else None
+        self._ints = PinnedStaging(device, torch.int32) if device.type == "cuda" else None
+
+    @property
+    def h2d_bytes(self) -> int:
+        return (self._floats.bytes + self._ints.bytes) if self._floats else 0
 
     def sample(self, logits: torch.Tensor, states: Sequence[SequenceSamplingState]) -> List[int]:
         """logits: float32 [B, V] on the device (modified in place by the repeat
@@ -54,8 +61,8 @@ class Sampler:
             for b, s in enumerate(states):
                 lens[b] = len(s.recent)
                 recent[b, :lens[b]] = s.recent
-            recent_d = torch.from_numpy(recent).to(dev)
-            lens_d = torch.from_numpy(lens).to(dev)
+            recent_d = self._ints.upload(recent)
+            lens_d = self._ints.upload(lens)
             if len(penalties) == 1:
                 K.repeat_penalty(logits, recent_d, lens_d, next(iter(penalties)))
             else:
@@ -81,7 +88,7 @@ class Sampler:
             f[0, b] = 0.0 if greedy else c.temperature
             f[1, b] = 0.0 if greedy else s.rng.next_f32()
             f[2, b] = c.min_p
-        fd = torch.from_numpy(f).to(dev)
+        fd = self._floats.upload(f)
         # every row goes through the softmax kernel (greedy rows are answered there too);
         # rows with a candidate set are then answered again by their own kernel
         K.sample_temperature(logits, fd[0], fd[1], out, fd[2] if f[2].any() else None)

@@ -18,6 +18,7 @@ def _register():
     class ToyDecayMixer(Mixer):
         """state <- decay * state + xn (per sequence, token after token); out = W state.
         The state lives in the cache's per-sequence state area as ``d`` floats."""
+        graph_capturable = False      # the loop below reads sequence boundaries on the host
 
         def __init__(self, runtime, hidden_size, decay, name):
             self.d, self.decay, self.name = hidden_size, decay, name
