@@ -1,0 +1,290 @@
+// Decode attention: one new token per sequence attends to its cached keys and values
+// (bf16, paged), split over the context so that a handful of sequences still fills the
+// GPU, with the partial results combined in a fixed order.
+//
+// Math (SimonWaldherr/RustyLLM src/model.rs:5807-5869, grouped as in 6034-6198): for query head h
+// of KV head g = h / (H/G): softmax over t of (q_h . K[t, g]) / sqrt(head_dim), times
+// V[t, g], with running (max, sum, output) in float.  The (H/G) query heads that share
+// a KV head are the rows of one 16-row tensor-core tile (mma.sync m16n8k16, bf16 in,
+// float accumulate), so each key and value row is read once for all of them, as the
+// reference's grouped scan does on the CPU and its Metal kernel
+// ``resident_gqa4_attention`` (src/metal_backend.m:542-592) does for groups of four.
+//
+// The kernel is bound by the read of the cache, so keys and values go straight from
+// global memory into the MMA's register fragments with 16-byte loads and no shared
+// memory on the way.  That works because a dot product does not care in which order
+// its terms are added: the head dimension (for Q.K) and the key index and output
+// column (for P.V) are assigned to fragment positions such that every lane's share is
+// contiguous in memory.
+//
+// Grid: (splits, KV heads, sequences); 4 warps per CTA take the split's 16-key blocks in
+// turn.  With one split the CTA writes the output; otherwise it writes its
+// (max, sum, unnormalised output) to scratch and a second kernel combines the splits.
+#include <math.h>
+
+#include "common.cuh"
+
+#define DEC_WARPS 4
+#define DEC_BLOCK 16   // keys per MMA step
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint4 ldg16(const __nv_bfloat16* p) {
+  return __ldg(reinterpret_cast<const uint4*>(p));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ k_pool,
+                        const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ page_table, int max_pages,
+                        const int* __restrict__ seq_slots, const int* __restrict__ kv_lens,
+                        __nv_bfloat16* __restrict__ out, int ldo, float* __restrict__ part_o,
+                        float* __restrict__ part_ml, int H, int G, float scale_log2e, int window) {
+  constexpr int NT = HD / 8;        // output n-tiles of 8 columns
+  constexpr int KS = HD / 16;       // k-steps of the Q.K product
+  __shared__ float s_acc[DEC_WARPS][16][HD + 4];
+  __shared__ float s_m[DEC_WARPS][16], s_l[DEC_WARPS][16];
+
+  const int split = blockIdx.x, num_splits = gridDim.x;
+  const int gkv = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int m = H / G;                                   // query heads per KV head (<= 16)
+  const int len = kv_lens[b];
+  const int start = (window > 0 && len - window > 0) ? len - window : 0;
+  const int* pages = page_table + (size_t)seq_slots[b] * max_pages;
+
+  // ---- Q fragments: rows = the m heads of this KV head, columns permuted like the keys' ----
+  uint32_t qf[KS][4];
+  {
+    const __nv_bfloat16* q0 = q + (size_t)b * ldq + (size_t)(gkv * m + g) * HD;
+    const __nv_bfloat16* q1 = q0 + (size_t)8 * HD;
+#pragma unroll
+    for (int c = 0; c < HD / 32; ++c) {
+      uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
+      if (g < m) lo = ldg16(q0 + 32 * c + 8 * t);
+      if (g + 8 < m) hi = ldg16(q1 + 32 * c + 8 * t);
+      qf[2 * c][0] = lo.x; qf[2 * c][1] = hi.x; qf[2 * c][2] = lo.y; qf[2 * c][3] = hi.y;
+      qf[2 * c + 1][0] = lo.z; qf[2 * c + 1][1] = hi.z; qf[2 * c + 1][2] = lo.w; qf[2 * c + 1][3] = hi.w;
+    }
+  }
+
+  float acc[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  // ---- this split's blocks of 16 keys, dealt to the warps in turn ----
+  const int first_blk = start / DEC_BLOCK;
+  const int num_blk = (len + DEC_BLOCK - 1) / DEC_BLOCK - first_blk;
+  const int per_split = (num_blk + num_splits - 1) / num_splits;
+  const int blk_lo = first_blk + split * per_split;
+  const int blk_hi = min(blk_lo + per_split, first_blk + num_blk);
+  const size_t page_stride = (size_t)G * RL_PAGE * HD;
+  const size_t head_off = (size_t)gkv * RL_PAGE * HD;
+
+  for (int blk = blk_lo + warp; blk < blk_hi; blk += DEC_WARPS) {
+    const int key0 = blk * DEC_BLOCK;
+    const size_t base = (size_t)pages[key0 / RL_PAGE] * page_stride + head_off + (size_t)(key0 % RL_PAGE) * HD;
+    const __nv_bfloat16* kb = k_pool + base;
+    const __nv_bfloat16* vb = v_pool + base;
+
+    // values first (the loads are independent of the scores; this keeps them in flight)
+    uint4 vr[HD / 64][4];
+    {
+      const int rows[4] = {2 * t, 2 * t + 1, 2 * t + 8, 2 * t + 9};
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const bool valid = key0 + rows[r] < len;     // rows beyond the sequence may hold anything
+#pragma unroll
+        for (int grp = 0; grp < HD / 64; ++grp)
+          vr[grp][r] = valid ? ldg16(vb + (size_t)rows[r] * HD + 64 * grp + 8 * g) : make_uint4(0, 0, 0, 0);
+      }
+    }
+
+    // scores S[16 heads x 16 keys] = Q . K^T
+    float s[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+      const __nv_bfloat16* krow = kb + (size_t)(8 * nt + g) * HD + 8 * t;
+      uint4 kr[HD / 32];
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) kr[c] = ldg16(krow + 32 * c);
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        mma_bf16_16816(s[nt], qf[2 * c][0], qf[2 * c][1], qf[2 * c][2], qf[2 * c][3], kr[c].x, kr[c].y);
+        mma_bf16_16816(s[nt], qf[2 * c + 1][0], qf[2 * c + 1][1], qf[2 * c + 1][2], qf[2 * c + 1][3], kr[c].z, kr[c].w);
+      }
+    }
+    // mask keys outside [start, len), scale into the exp2 domain
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = key0 + 8 * nt + 2 * t + (e & 1);
+        s[nt][e] = (key < len && key >= start) ? s[nt][e] * scale_log2e : -INFINITY;
+      }
+    // streaming softmax for rows g (e = 0, 1) and g + 8 (e = 2, 3)
+    uint32_t pa[4];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      float mx = fmaxf(fmaxf(s[0][2 * half], s[0][2 * half + 1]), fmaxf(s[1][2 * half], s[1][2 * half + 1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[half], mx);           // finite: the block holds a valid key
+      const float corr = exp2f(m_run[half] - m_new);        // exp2(-inf) = 0 on the first block
+      const float p00 = exp2f(s[0][2 * half] - m_new), p01 = exp2f(s[0][2 * half + 1] - m_new);
+      const float p10 = exp2f(s[1][2 * half] - m_new), p11 = exp2f(s[1][2 * half + 1] - m_new);
+      float sum = (p00 + p01) + (p10 + p11);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      l_run[half] = l_run[half] * corr + sum;
+      m_run[half] = m_new;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) { acc[j][2 * half] *= corr; acc[j][2 * half + 1] *= corr; }
+      pa[half] = pack_bf16(p00, p01);          // a0 / a1: keys 2t, 2t+1
+      pa[2 + half] = pack_bf16(p10, p11);      // a2 / a3: keys 2t+8, 2t+9
+    }
+    // output += P . V ; column c of n-tile j in 64-column group grp is dimension 64 grp + 8 c + j
+#pragma unroll
+    for (int grp = 0; grp < HD / 64; ++grp) {
+      const uint32_t* r0 = reinterpret_cast<const uint32_t*>(&vr[grp][0]);
+      const uint32_t* r1 = reinterpret_cast<const uint32_t*>(&vr[grp][1]);
+      const uint32_t* r2 = reinterpret_cast<const uint32_t*>(&vr[grp][2]);
+      const uint32_t* r3 = reinterpret_cast<const uint32_t*>(&vr[grp][3]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
+        const uint32_t b0 = __byte_perm(r0[j >> 1], r1[j >> 1], sel);
+        const uint32_t b1 = __byte_perm(r2[j >> 1], r3[j >> 1], sel);
+        mma_bf16_16816(acc[grp * 8 + j], pa[0], pa[1], pa[2], pa[3], b0, b1);
+      }
+    }
+  }
+
+  // ---- combine the four warps ----
+  if (t == 0) {
+    s_m[warp][g] = m_run[0]; s_l[warp][g] = l_run[0];
+    s_m[warp][g + 8] = m_run[1]; s_l[warp][g + 8] = l_run[1];
+  }
+#pragma unroll
+  for (int grp = 0; grp < HD / 64; ++grp)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int d0 = 64 * grp + 16 * t + j, d1 = d0 + 8;
+      if (g < m) { s_acc[warp][g][d0] = acc[grp * 8 + j][0]; s_acc[warp][g][d1] = acc[grp * 8 + j][1]; }
+      if (g + 8 < m) { s_acc[warp][g + 8][d0] = acc[grp * 8 + j][2]; s_acc[warp][g + 8][d1] = acc[grp * 8 + j][3]; }
+    }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < m * HD; idx += DEC_WARPS * 32) {
+    const int r = idx / HD, d = idx % HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, s_m[w][r]);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float wgt = (s_m[w][r] > -INFINITY) ? exp2f(s_m[w][r] - M) : 0.f;
+      L += s_l[w][r] * wgt;
+      O += s_acc[w][r][d] * wgt;
+    }
+    const int h = gkv * m + r;
+    if (num_splits == 1) {
+      out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    } else {
+      const size_t p = ((size_t)b * H + h) * num_splits + split;
+      part_o[p * HD + d] = O;
+      if (d == 0) { part_ml[2 * p] = M; part_ml[2 * p + 1] = L; }
+    }
+  }
+}
+
+// Combines the splits of one (sequence, head) in split order.
+template <int HD>
+__global__ void attention_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                __nv_bfloat16* __restrict__ out, int ldo, int H, int num_splits) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  const size_t p0 = ((size_t)b * H + h) * num_splits;
+  float M = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[2 * (p0 + s)]);
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float L = 0.f, O = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+      const float ms = part_ml[2 * (p0 + s)];
+      const float wgt = (ms > -INFINITY) ? exp2f(ms - M) : 0.f;
+      L += part_ml[2 * (p0 + s) + 1] * wgt;
+      O += part_o[(p0 + s) * HD + d] * wgt;
+    }
+    out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+  }
+}
+
+template <int HD>
+static int launch_decode(const void* q, int ldq, const void* k_pool, const void* v_pool, const int* page_table,
+                         int max_pages, const int* seq_slots, const int* kv_lens, void* out, int ldo,
+                         float* part_o, float* part_ml, int B, int H, int G, float scale, int window,
+                         int num_splits, cudaStream_t stream) {
+  dim3 grid(num_splits, G, B);
+  attention_decode_kernel<HD><<<grid, DEC_WARPS * 32, 0, stream>>>(
+      (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table, max_pages,
+      seq_slots, kv_lens, (__nv_bfloat16*)out, ldo, part_o, part_ml, H, G, scale * 1.4426950408889634f, window);
+  RL_LAUNCH_CHECK("rl_attention_decode");
+  if (num_splits > 1) {
+    attention_decode_combine_kernel<HD><<<dim3(H, B), HD >= 128 ? 128 : 64, 0, stream>>>(
+        part_o, part_ml, (__nv_bfloat16*)out, ldo, H, num_splits);
+    RL_LAUNCH_CHECK("rl_attention_decode (combine)");
+  }
+  return RL_OK;
+}
+
+// 1 if the decode kernel takes this shape: bf16, head_dim 64 or 128, at most 16 query
+// heads per KV head.  Other shapes go to the any-shape kernel.
+extern "C" int rl_attention_decode_supported(int num_heads, int num_kv_heads, int head_dim) {
+  if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0) return 0;
+  if (num_heads / num_kv_heads > 16) return 0;
+  return head_dim == 64 || head_dim == 128;
+}
+
+// Floats of scratch the call needs for the given sizes (0 with one split).
+extern "C" long long rl_attention_decode_scratch_floats(int num_seqs, int num_heads, int head_dim, int num_splits) {
+  if (num_splits <= 1) return 0;
+  return (long long)num_seqs * num_heads * num_splits * (head_dim + 2);
+}
+
+// q: [B, ldq] bf16, one token per sequence; seq_slots, kv_lens: [B] (kv_lens counts the
+// new token, whose key and value are already in the cache); out: [B, ldo] bf16.
+// scratch: rl_attention_decode_scratch_floats(...) floats (may be null with one split).
+extern "C" int rl_attention_decode(const void* q, int ldq, const void* k_pool, const void* v_pool,
+                                   const int* page_table, int max_pages, const int* seq_slots, const int* kv_lens,
+                                   void* out, int ldo, float* scratch, int num_seqs, int num_heads, int num_kv_heads,
+                                   int head_dim, float scale, int window, int num_splits, cudaStream_t stream) {
+  RL_REQUIRE(rl_attention_decode_supported(num_heads, num_kv_heads, head_dim),
+             "rl_attention_decode: unsupported shape (heads %d, KV heads %d, head_dim %d): needs head_dim 64 or 128 "
+             "and at most 16 heads per KV head", num_heads, num_kv_heads, head_dim);
+  RL_REQUIRE(num_seqs >= 0 && num_splits >= 1 && num_splits <= 65535, "rl_attention_decode: bad sizes");
+  RL_REQUIRE(num_seqs <= 65535 && num_kv_heads <= 65535, "rl_attention_decode: too many sequences or KV heads for one grid");
+  RL_REQUIRE(ldq >= num_heads * head_dim && ldo >= num_heads * head_dim && ldq % 8 == 0,
+             "rl_attention_decode: row strides too small or not a multiple of 8 elements");
+  RL_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)k_pool & 15) == 0 && ((uintptr_t)v_pool & 15) == 0,
+             "rl_attention_decode: q and the cache pools must be 16-byte aligned");
+  RL_REQUIRE(num_splits == 1 || scratch != nullptr, "rl_attention_decode: scratch is null with %d splits", num_splits);
+  RL_REQUIRE(window >= 0, "rl_attention_decode: negative window");
+  if (num_seqs == 0) return RL_OK;
+  float* part_o = scratch;
+  float* part_ml = scratch ? scratch + (size_t)num_seqs * num_heads * num_splits * head_dim : nullptr;
+  if (head_dim == 64)
+    return launch_decode<64>(q, ldq, k_pool, v_pool, page_table, max_pages, seq_slots, kv_lens, out, ldo, part_o,
+                             part_ml, num_seqs, num_heads, num_kv_heads, scale, window, num_splits, stream);
+  return launch_decode<128>(q, ldq, k_pool, v_pool, page_table, max_pages, seq_slots, kv_lens, out, ldo, part_o,
+                            part_ml, num_seqs, num_heads, num_kv_heads, scale, window, num_splits, stream);
+}

@@ -48,6 +48,9 @@ _SIGNATURES = {
     "rl_sample_temperature": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "rl_sample_candidates": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    "rl_attention_decode": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                            _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p],
+    "rl_attention_decode_supported": [_c_int, _c_int, _c_int],
     "rl_gemm_tc_supported": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int],
     "rl_gemm_tc": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                    _c_void_p, _c_void_p],
@@ -321,6 +324,47 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_mode: int,
     _count()
 
 
+# ----------------------------------------------------------------------------- decode attention
+NUM_SMS = 148
+
+
+def attention_decode_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    return dtype == torch.bfloat16 and bool(library().rl_attention_decode_supported(num_heads, num_kv_heads, head_dim))
+
+
+def decode_splits(num_seqs: int, num_kv_heads: int) -> int:
+    """Splits of the context per (sequence, KV head): enough CTAs for about three per
+    SM.  Depends on the batch's size only, so that a captured step keeps its grid."""
+    return max(1, min(32, -(-3 * NUM_SMS // (num_seqs * num_kv_heads))))
+
+
+def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
+                     seq_slots: torch.Tensor, kv_lens: torch.Tensor, out: torch.Tensor, num_heads: int,
+                     num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
+                     num_splits: Optional[int] = None, scratch: Optional[torch.Tensor] = None) -> None:
+    """One token per sequence over the bf16 cache, split over the context (tensor cores).
+    q: [B, >= H*hd] bf16 (a view into the qkv buffer is fine); out: [B, H*hd] bf16."""
+    _need(q, "q", torch.bfloat16, contiguous=False); _need(k_pool, "k_pool", torch.bfloat16)
+    _need(v_pool, "v_pool", torch.bfloat16); _need(out, "out", torch.bfloat16)
+    _need(page_table, "page_table", torch.int32); _need(seq_slots, "seq_slots", torch.int32)
+    _need(kv_lens, "kv_lens", torch.int32)
+    B = q.shape[0]
+    assert seq_slots.numel() == B and kv_lens.numel() == B and q.stride(1) == 1
+    if num_splits is None:
+        num_splits = decode_splits(B, num_kv_heads)
+    if num_splits > 1 and scratch is None:
+        scratch = torch.empty(B * num_heads * num_splits * (head_dim + 2), dtype=torch.float32, device=q.device)
+    if scratch is not None:
+        _need(scratch, "scratch", torch.float32)
+        assert scratch.numel() >= (B * num_heads * num_splits * (head_dim + 2) if num_splits > 1 else 0)
+    ldq = q.stride(0) if B > 1 else max(q.stride(0), num_heads * head_dim)
+    _check(library().rl_attention_decode(
+        q.data_ptr(), ldq, k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr(), page_table.shape[1],
+        seq_slots.data_ptr(), kv_lens.data_ptr(), out.data_ptr(), out.stride(0), _ptr(scratch), B, num_heads,
+        num_kv_heads, head_dim, float(scale), int(window), int(num_splits), _stream()), "rl_attention_decode")
+    _count(2 if num_splits > 1 else 1)
+
+
 # ----------------------------------------------------------------------------- attention dispatch
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
               step, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
@@ -328,6 +372,10 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
     """Attention of the step's tokens over the cache; picks the kernel for the
     dtype and the shape of the step.  ``step`` carries positions, slots and
     sequence boundaries (engine.step.StepState)."""
+    if step.is_decode and attention_decode_supported(q.dtype, num_heads, num_kv_heads, head_dim):
+        attention_decode(q, k_pool, v_pool, page_table, step.seq_slots, step.kv_lens, out,
+                         num_heads, num_kv_heads, head_dim, scale, window)
+        return
     attention_simt(q, k_pool, v_pool, page_table, step.slot_of_token, step.positions, out,
                    num_heads, num_kv_heads, head_dim, scale, window)
 

@@ -8,7 +8,7 @@ from gpu_helpers import assert_close_logits, load_runner, plain_logits, random_t
 
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
-CONFIGS = ["A", "B", "C"]
+CONFIGS = ["A", "B", "C", "D"]
 
 
 def _vocab(cfg):
@@ -89,8 +89,9 @@ def test_unequal_batches_one_after_another_reuse_slots(model_dirs, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_long_decoding_across_pages(model_dirs, dtype):
-    d, cfg = model_dirs["C"]
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_long_decoding_across_pages(model_dirs, name, dtype):
+    d, cfg = model_dirs[name]
     r = load_runner(d, dtype)
     toks = random_tokens(_vocab(cfg), 300, 7)
     ref = plain_logits(d, toks)
@@ -99,7 +100,7 @@ def test_long_decoding_across_pages(model_dirs, dtype):
     for t in toks[3:]:
         rows.append(r.engine.step([s], [[t]], "last"))
     r.engine.free_slot(s)
-    assert_close_logits(torch.cat(rows), ref, dtype, "C long decode")
+    assert_close_logits(torch.cat(rows), ref, dtype, f"{name} long decode")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -300,6 +300,75 @@ def test_attention_finds_one_far_key_among_hundreds(dtype, far):
     assert (ref - want).abs().max() < 1e-3
 
 
+# ----------------------------------------------------------------------------- decode attention (tensor cores)
+def _decode_inputs(case):
+    q, kp, vp, pt, sot, pos, ref = case
+    return q, kp, vp, pt, sot.clone(), (pos + 1).to(torch.int32), ref
+
+
+@pytest.mark.parametrize("H,G,hd", [(32, 8, 128), (8, 8, 128), (6, 2, 64), (16, 1, 64), (5, 5, 128), (24, 8, 64)])
+@pytest.mark.parametrize("splits", [1, 2, 7, 32])
+def test_attention_decode_matches_plain(H, G, hd, splits):
+    k = K()
+    assert k.attention_decode_supported(torch.bfloat16, H, G, hd)
+    lens = [1, 15, 16, 17, 64, 65, 200, 513]
+    case = _attention_case(torch.bfloat16, H, G, hd, [1] * len(lens), lens, seed=hd + H + splits)
+    q, kp, vp, pt, slots, kv_lens, ref = _decode_inputs(case)
+    out = torch.empty(len(lens), H * hd, dtype=torch.bfloat16, device=DEV)
+    k.attention_decode(q, kp, vp, pt, slots, kv_lens, out, H, G, hd, 1.0 / math.sqrt(hd), num_splits=splits)
+    torch.testing.assert_close(out.double().cpu(), ref, **_tol(torch.bfloat16))
+    # and the any-shape kernel gives the same to bf16 rounding
+    simt = torch.empty_like(out)
+    k.attention_simt(q, kp, vp, pt, slots, (kv_lens - 1).to(torch.int32), simt, H, G, hd, 1.0 / math.sqrt(hd))
+    torch.testing.assert_close(out.float(), simt.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_attention_decode_window_and_strided_queries():
+    k = K()
+    H, G, hd, W = 8, 2, 128, 70
+    lens = [10, 70, 71, 300]
+    case = _attention_case(torch.bfloat16, H, G, hd, [1] * 4, lens, window=W, seed=9)
+    q, kp, vp, pt, slots, kv_lens, ref = _decode_inputs(case)
+    wide = torch.zeros(4, (H + 2 * G) * hd, dtype=torch.bfloat16, device=DEV)     # q as a view into a qkv buffer
+    wide[:, :H * hd] = q
+    out = torch.empty(4, H * hd, dtype=torch.bfloat16, device=DEV)
+    k.attention_decode(wide[:, :H * hd], kp, vp, pt, slots, kv_lens, out, H, G, hd, 1.0 / math.sqrt(hd), W, num_splits=3)
+    torch.testing.assert_close(out.double().cpu(), ref, **_tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 449, 450])
+@pytest.mark.parametrize("splits", [1, 5])
+def test_attention_decode_finds_one_far_key_among_hundreds(far, splits):
+    H, G, hd, n = 8, 2, 128, 451
+
+    def craft(b, qb, kb, vb):
+        direction = torch.ones(hd) / math.sqrt(hd)
+        qb[:] = (direction * 14.0).to(qb.dtype)
+        kb[:] = (kb.float() * 0.05).to(kb.dtype)
+        kb[far] = (direction * 14.0).to(kb.dtype)
+    case = _attention_case(torch.bfloat16, H, G, hd, [1], [n], seed=5, craft=craft)
+    q, kp, vp, pt, slots, kv_lens, ref = _decode_inputs(case)
+    out = torch.empty(1, H * hd, dtype=torch.bfloat16, device=DEV)
+    K().attention_decode(q, kp, vp, pt, slots, kv_lens, out, H, G, hd, 1.0 / math.sqrt(hd), num_splits=splits)
+    torch.testing.assert_close(out.double().cpu(), ref, **_tol(torch.bfloat16))
+    page = int(pt[1, far // PAGE]); v_far = vp[page, :, far % PAGE].double().cpu()
+    assert (ref - v_far.repeat_interleave(H // G, dim=0).reshape(1, H * hd)).abs().max() < 1e-3
+
+
+def test_attention_decode_ignores_garbage_beyond_the_sequence():
+    """Rows of a page beyond the sequence's length may hold anything, NaN included."""
+    k = K()
+    H, G, hd = 4, 1, 64
+    case = _attention_case(torch.bfloat16, H, G, hd, [1, 1], [5, 70], seed=2)
+    q, kp, vp, pt, slots, kv_lens, ref = _decode_inputs(case)
+    for b, n in enumerate([5, 70]):
+        page = int(pt[int(slots[b]), (n - 1) // PAGE])
+        kp[page, :, n % PAGE:] = float("nan"); vp[page, :, n % PAGE:] = float("nan")
+    out = torch.empty(2, H * hd, dtype=torch.bfloat16, device=DEV)
+    k.attention_decode(q, kp, vp, pt, slots, kv_lens, out, H, G, hd, 1.0 / math.sqrt(hd), num_splits=2)
+    torch.testing.assert_close(out.double().cpu(), ref, **_tol(torch.bfloat16))
+
+
 # ----------------------------------------------------------------------------- sampling
 def test_argmax_first_maximum_wins_and_non_finite_is_skipped():
     k = K()

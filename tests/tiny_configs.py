@@ -30,6 +30,15 @@ TINY = {
         "num_attention_heads": 5, "num_key_value_heads": 5, "head_dim": 48,
         "max_position_embeddings": 640, "rms_norm_eps": 3e-6, "rope_theta": 25000.0,
         "tie_word_embeddings": False, "attention_bias": True, "mlp_bias": True}),
+    # 2 layers, GQA 4/2, head 64: the shape class the tensor-core attention kernels take
+    "D": dict(seed=3, norm_noise=True, dtype="bfloat16", config={
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+        "vocab_size": 320, "hidden_size": 128, "intermediate_size": 192, "num_hidden_layers": 2,
+        "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
+        "max_position_embeddings": 1024, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+        "rope_scaling": {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0,
+                         "high_freq_factor": 4.0, "original_max_position_embeddings": 256},
+        "tie_word_embeddings": True}),
 }
 
 
