@@ -288,3 +288,57 @@ extern "C" int rl_attention_decode(const void* q, int ldq, const void* k_pool, c
   return launch_decode<128>(q, ldq, k_pool, v_pool, page_table, max_pages, seq_slots, kv_lens, out, ldo, part_o,
                             part_ml, num_seqs, num_heads, num_kv_heads, scale, window, num_splits, stream);
 }
+
+// ------------------------------------------------------------------ entry point that allocates nothing
+// Declared in attention_decode_static.h.  Same kernels as rl_attention_decode; the
+// scratch for the per-split partial results lives in the array below instead of in
+// memory the caller allocates.  The array is part of the loaded library: every GPU
+// that loads it holds these 4 MiB until the process exits.
+#include <mutex>
+
+#include "attention_decode_static.h"
+
+static __device__ __align__(256) float g_decode_static_scratch[RL_DECODE_STATIC_SCRATCH_FLOATS];
+
+// In host code the array's name stands for the symbol, not for device memory: its device
+// address is asked for once per device (with that device current) and kept here.
+static float* g_decode_static_ptr[RL_DECODE_STATIC_MAX_DEVICES] = {nullptr};
+static std::mutex g_decode_static_mutex;
+
+static int decode_static_scratch(float** ptr) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  RL_REQUIRE(e == cudaSuccess, "rl_attention_decode_static: cudaGetDevice failed: %s", cudaGetErrorString(e));
+  RL_REQUIRE(dev >= 0 && dev < RL_DECODE_STATIC_MAX_DEVICES, "rl_attention_decode_static: device %d is beyond the %d "
+             "devices this entry point keeps an address for", dev, RL_DECODE_STATIC_MAX_DEVICES);
+  std::lock_guard<std::mutex> lock(g_decode_static_mutex);
+  if (g_decode_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_decode_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      rl_set_error("rl_attention_decode_static: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+      return RL_ERR_CUDA;
+    }
+    g_decode_static_ptr[dev] = (float*)p;
+  }
+  *ptr = g_decode_static_ptr[dev];
+  return RL_OK;
+}
+
+extern "C" int rl_attention_decode_static(const void* q, int ldq, const void* k_pool, const void* v_pool,
+                                          const int* page_table, int max_pages, const int* seq_slots,
+                                          const int* kv_lens, void* out, int ldo, int num_seqs, int num_heads,
+                                          int num_kv_heads, int head_dim, float scale, int window, int num_splits,
+                                          cudaStream_t stream) {
+  RL_REQUIRE(num_seqs >= 0 && num_heads > 0 && head_dim > 0 && num_splits >= 1, "rl_attention_decode_static: bad sizes");
+  const long long need = rl_attention_decode_scratch_floats(num_seqs, num_heads, head_dim, num_splits);
+  RL_REQUIRE(need <= (long long)RL_DECODE_STATIC_SCRATCH_FLOATS,
+             "rl_attention_decode_static: %d sequences x %d heads x %d splits x (head_dim %d + 2) = %lld floats of "
+             "scratch exceed the built-in %lld; use fewer splits or rl_attention_decode with scratch of your own",
+             num_seqs, num_heads, num_splits, head_dim, need, (long long)RL_DECODE_STATIC_SCRATCH_FLOATS);
+  float* scratch = nullptr;
+  const int rc = decode_static_scratch(&scratch);
+  if (rc != RL_OK) return rc;
+  return rl_attention_decode(q, ldq, k_pool, v_pool, page_table, max_pages, seq_slots, kv_lens, out, ldo, scratch,
+                             num_seqs, num_heads, num_kv_heads, head_dim, scale, window, num_splits, stream);
+}
