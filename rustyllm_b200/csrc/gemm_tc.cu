@@ -12,6 +12,12 @@
 // transposes anywhere.  Accumulation is float; the epilogue adds the optional bias
 // and stores bf16, stores float, or adds into a float buffer (the residual sum).
 //
+// Split-K: with few tokens a product has too few 128-row tiles to keep 148 SMs
+// streaming, so the K range is cut into gridDim.z parts.  Each part leaves its float
+// partial tile in scratch; the part that finishes last (a counter per tile) adds the
+// parts in order 0, 1, 2, ... and runs the epilogue, so the result does not depend on
+// which part finished when.  The counter resets itself for the next launch.
+//
 // Every wait on an mbarrier is bounded: when it runs out the kernel records a code
 // in the error word, all roles leave their loops, tensor memory is freed and the
 // kernel returns.
@@ -116,17 +122,22 @@ __host__ __device__ constexpr uint32_t make_idesc(int mma_m, int mma_n) {
 template <int BT>
 struct TcConfig {
   static constexpr int STAGE_BYTES = (BLOCK_N_OUT + BT) * BLOCK_K * 2;
-  static constexpr int STAGES = (196608 / STAGE_BYTES) < 8 ? (196608 / STAGE_BYTES) : 8;
+  // few tokens: the product streams weights, three stages a CTA and three or four CTAs an
+  // SM keep more loads in flight than one deep ring; many tokens: one CTA, a deep ring
+  static constexpr int SMEM_BUDGET = BT <= 64 ? 73728 : 196608;
+  static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) < 8 ? (SMEM_BUDGET / STAGE_BYTES) : 8;
+  static constexpr int MIN_CTAS = BT <= 64 ? 3 : 1;
   static constexpr int TMEM_COLS = BT < 32 ? 32 : BT;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
 // BT: tokens per CTA (MMA N).  Grid: (ceil(N_out / 128), ceil(M_tokens / BT)).
 template <int BT>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS, TcConfig<BT>::MIN_CTAS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                const float* __restrict__ bias, void* __restrict__ out, int out_mode, int M, int N, int K,
-               int ldo, int* __restrict__ err) {
+               int ldo, int* __restrict__ err, int kb_per_split, float* __restrict__ partial,
+               int* __restrict__ tile_counter) {
   using Cfg = TcConfig<BT>;
   extern __shared__ uint8_t smem_raw[];
   // tiles need 1024-byte alignment for the 128-byte swizzle pattern
@@ -142,7 +153,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BLOCK_N_OUT;   // first weight row (output feature) of this CTA
   const int m0 = blockIdx.y * BT;            // first token of this CTA
-  const int num_kb = (K + BLOCK_K - 1) / BLOCK_K;
+  const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+  const int kb0 = blockIdx.z * kb_per_split;                       // this CTA's part of the K range
+  const int num_kb = min(kb_per_split, total_kb - kb0);            // > 0: the host sizes the grid so
+  const int num_splits = gridDim.z;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::STAGES; ++s) {
@@ -174,8 +188,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const uint32_t fb = smem_u32(&full_bar[s]);
         mbar_expect_tx(fb, Cfg::STAGE_BYTES);
         uint8_t* st = tiles + (size_t)s * Cfg::STAGE_BYTES;
-        tma_load_2d(smem_u32(st), &map_w, fb, kb * BLOCK_K, n0);
-        tma_load_2d(smem_u32(st + BLOCK_N_OUT * BLOCK_K * 2), &map_a, fb, kb * BLOCK_K, m0);
+        tma_load_2d(smem_u32(st), &map_w, fb, (kb0 + kb) * BLOCK_K, n0);
+        tma_load_2d(smem_u32(st + BLOCK_N_OUT * BLOCK_K * 2), &map_a, fb, (kb0 + kb) * BLOCK_K, m0);
       }
     }
   } else if (warp == 1) {
@@ -209,10 +223,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const bool ok = mbar_wait(smem_u32(accum_bar), 0, abort_flag);
     if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(err, 3); }
     tc_fence_after();
-    if (ok) {
-      const int quarter = warp & 3;                    // lanes this warp may read
-      const int n = n0 + quarter * 32 + lane;          // output feature of this thread
-      const float b = (bias != nullptr && n < N) ? bias[n] : 0.f;
+    const int quarter = warp & 3;                    // lanes this warp may read
+    const int row = quarter * 32 + lane;             // accumulator row = weight row of the tile
+    const int n = n0 + row;                          // output feature of this thread
+    const float b = (bias != nullptr && n < N) ? bias[n] : 0.f;
+    if (ok && num_splits == 1) {
 #pragma unroll 1
       for (int c = 0; c < BT / 16; ++c) {
         uint32_t r[16];
@@ -229,6 +244,49 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               else if (out_mode == TC_OUT_F32) ((float*)out)[o] = v;
               else ((float*)out)[o] += v;
             }
+          }
+        }
+      }
+    } else if (num_splits > 1) {
+      // partial tile of this part: [token column][weight row], rows contiguous
+      const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+      const size_t tile_elems = (size_t)BLOCK_N_OUT * BT;
+      float* mine = partial + ((size_t)blockIdx.z * gridDim.x * gridDim.y + tile) * tile_elems;
+      const int cols = min(BT, M - m0);
+      if (ok) {
+#pragma unroll 1
+        for (int c = 0; c < BT / 16; ++c) {
+          if (c * 16 >= cols) break;
+          uint32_t r[16];
+          tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 16), r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (c * 16 + j < cols) mine[(size_t)(c * 16 + j) * BLOCK_N_OUT + row] = __uint_as_float(r[j]);
+        }
+      }
+      // the part that arrives last at the tile's counter reduces all parts in order
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");          // the four epilogue warps
+      int* last_flag = (int*)(tmem_slot + 2);
+      if (threadIdx.x == 64) {
+        const int prev = atomicAdd(&tile_counter[tile], 1);
+        *last_flag = (prev == num_splits - 1);
+        if (prev == num_splits - 1) tile_counter[tile] = 0;     // ready for the next launch
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*last_flag && !*abort_flag) {
+        __threadfence();
+        if (n < N) {
+          for (int j = 0; j < cols; ++j) {
+            float v = 0.f;
+            for (int sp = 0; sp < num_splits; ++sp)
+              v += __ldcg(partial + ((size_t)sp * gridDim.x * gridDim.y + tile) * tile_elems + (size_t)j * BLOCK_N_OUT + row);
+            v += b;
+            const size_t o = (size_t)(m0 + j) * ldo + n;
+            if (out_mode == TC_OUT_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
+            else if (out_mode == TC_OUT_F32) ((float*)out)[o] = v;
+            else ((float*)out)[o] += v;
           }
         }
       }
@@ -276,7 +334,8 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int 
 
 template <int BT>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, void* out, int out_mode,
-                     int M, int N, int K, int ldo, int* err, cudaStream_t stream) {
+                     int M, int N, int K, int ldo, int* err, int splits, int kb_per_split, float* workspace,
+                     int* counters, cudaStream_t stream) {
   using Cfg = TcConfig<BT>;
   static bool configured = false;
   if (!configured) {
@@ -284,8 +343,9 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, const float* 
     RL_REQUIRE(e == cudaSuccess, "rl_gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid((N + BLOCK_N_OUT - 1) / BLOCK_N_OUT, (M + BT - 1) / BT);
-  gemm_tc_kernel<BT><<<grid, TC_THREADS, Cfg::SMEM_BYTES, stream>>>(mw, ma, bias, out, out_mode, M, N, K, ldo, err);
+  dim3 grid((N + BLOCK_N_OUT - 1) / BLOCK_N_OUT, (M + BT - 1) / BT, splits);
+  gemm_tc_kernel<BT><<<grid, TC_THREADS, Cfg::SMEM_BYTES, stream>>>(mw, ma, bias, out, out_mode, M, N, K, ldo, err,
+                                                                    kb_per_split, workspace, counters);
   RL_LAUNCH_CHECK("rl_gemm_tc");
   return RL_OK;
 }
@@ -299,26 +359,53 @@ extern "C" int rl_gemm_tc_supported(const void* A, const void* W, int M, int N, 
   return 1;
 }
 
+static int token_tile(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
+
+// How many parts the K range is cut into for M tokens: enough CTAs for three an SM, at
+// least four 64-wide K blocks a part, partial-tile traffic at most a quarter of the
+// weight traffic, and everything within the workspace.  A function of the shapes only.
+extern "C" int rl_gemm_tc_splits(int M, int N, int K, long long workspace_floats, int num_counters) {
+  const int bt = token_tile(M);
+  if (bt > 64 || workspace_floats <= 0 || num_counters <= 0) return 1;
+  const int tiles = ((N + BLOCK_N_OUT - 1) / BLOCK_N_OUT) * ((M + bt - 1) / bt);
+  const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+  int splits = (3 * 148) / tiles;
+  if (splits > total_kb / 4) splits = total_kb / 4;
+  if (splits > K / (16 * M)) splits = K / (16 * M);
+  if (splits > 32) splits = 32;
+  if (splits < 2 || tiles > num_counters) return 1;
+  while (splits > 1 && (long long)splits * tiles * BLOCK_N_OUT * bt > workspace_floats) --splits;
+  if (splits < 2) return 1;
+  const int kb_per = (total_kb + splits - 1) / splits;
+  return (total_kb + kb_per - 1) / kb_per;      // no part is empty
+}
+
 // A: [M, K] bf16, row stride lda; W: [N, K] bf16 contiguous; out: [M, N] with row stride
 // ldo, bf16 (out_mode 0) or float (1 store, 2 add).  err: device int, set non-zero if a
-// bounded wait inside the kernel ran out.
+// bounded wait inside the kernel ran out.  workspace (floats) and counters (ints, zero
+// before the first use; the kernel leaves them zero) serve split-K and may be null:
+// then the K range is not split.  Launches that share them must not overlap on the GPU.
 extern "C" int rl_gemm_tc(const void* A, const void* W, const float* bias, void* out, int out_mode, int M, int N,
-                          int K, int lda, int ldo, int* err, cudaStream_t stream) {
+                          int K, int lda, int ldo, int* err, float* workspace, long long workspace_floats,
+                          int* counters, int num_counters, cudaStream_t stream) {
   RL_REQUIRE(rl_gemm_tc_supported(A, W, M, N, K, lda), "rl_gemm_tc: operands not supported (M=%d N=%d K=%d lda=%d; K and lda "
              "must be multiples of 8 and the bases 16-byte aligned)", M, N, K, lda);
   RL_REQUIRE(out_mode >= 0 && out_mode <= 2, "rl_gemm_tc: unknown output mode %d", out_mode);
   RL_REQUIRE(ldo >= N && err != nullptr, "rl_gemm_tc: bad output stride or null error word");
-  const int bt = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  const int bt = token_tile(M);
+  const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+  const int splits = (workspace && counters) ? rl_gemm_tc_splits(M, N, K, workspace_floats, num_counters) : 1;
+  const int kb_per = (total_kb + splits - 1) / splits;
   CUtensorMap mw, ma;
   int rc = make_map(&mw, W, N, K, K, BLOCK_N_OUT);
   if (rc != RL_OK) return rc;
   rc = make_map(&ma, A, M, K, lda, bt);
   if (rc != RL_OK) return rc;
   switch (bt) {
-    case 16: return launch_tc<16>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, stream);
-    case 32: return launch_tc<32>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, stream);
-    case 64: return launch_tc<64>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, stream);
-    case 128: return launch_tc<128>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, stream);
-    default: return launch_tc<256>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, stream);
+    case 16: return launch_tc<16>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, workspace, counters, stream);
+    case 32: return launch_tc<32>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, workspace, counters, stream);
+    case 64: return launch_tc<64>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, workspace, counters, stream);
+    case 128: return launch_tc<128>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, workspace, counters, stream);
+    default: return launch_tc<256>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, workspace, counters, stream);
   }
 }

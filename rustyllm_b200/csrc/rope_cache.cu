@@ -13,13 +13,18 @@
 // the sequence in slot s is page_table[s * max_pages + p / RL_PAGE].
 #include "common.cuh"
 
+#define ROPE_HEADS_PER_CTA 8
+#define ROPE_THREADS 128
+
+// Grid: (tokens, ceil((H + 2G) / ROPE_HEADS_PER_CTA)).  A CTA takes one token and a run of
+// "head slots" (query heads, then key heads, then value heads); a thread takes pairs of
+// elements, each pair independent of every other, so all its loads are in flight at once.
 template <typename T>
-__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int ld, const int* __restrict__ positions,
-                                     const int* __restrict__ slot_of_token,
-                                     const int* __restrict__ page_table, int max_pages,
-                                     const float* __restrict__ inv_freq, int H, int G, int hd,
-                                     int rot, int interleaved, T* __restrict__ k_pool,
-                                     T* __restrict__ v_pool, int write_cache) {
+__global__ void __launch_bounds__(ROPE_THREADS)
+rope_kv_write_kernel(T* __restrict__ qkv, int ld, const int* __restrict__ positions,
+                     const int* __restrict__ slot_of_token, const int* __restrict__ page_table, int max_pages,
+                     const float* __restrict__ inv_freq, int H, int G, int hd, int rot, int interleaved,
+                     T* __restrict__ k_pool, T* __restrict__ v_pool, int write_cache) {
   const int m = blockIdx.x;
   const int pos = positions[m];
   T* row = qkv + (size_t)m * ld;
@@ -29,44 +34,36 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int ld, const int* __r
     const int page = page_table[(size_t)slot * max_pages + pos / RL_PAGE];
     dst = ((size_t)page * G) * RL_PAGE * hd + (size_t)(pos % RL_PAGE) * hd;  // + g * RL_PAGE * hd
   }
-  const int half = rot / 2;
-  if (half > 0) {
-    const int i = threadIdx.x % half;
-    const int lane_group = threadIdx.x / half;
-    const int groups = blockDim.x / half;
-    if (lane_group < groups) {
+  const int half = rot / 2, pairs = hd / 2;
+  const int slot0 = blockIdx.y * ROPE_HEADS_PER_CTA;
+  const int nslots = min(ROPE_HEADS_PER_CTA, H + 2 * G - slot0);
+  for (int idx = threadIdx.x; idx < nslots * pairs; idx += ROPE_THREADS) {
+    const int hs = slot0 + idx / pairs;       // head slot: [0, H) q, [H, H+G) k, [H+G, H+2G) v
+    const int i = idx % pairs;
+    const bool is_v = hs >= H + G;
+    const bool rotate = !is_v && i < half;
+    int i0, i1;
+    if (rotate) { i0 = interleaved ? 2 * i : i; i1 = interleaved ? 2 * i + 1 : i + half; }
+    else if (is_v) { i0 = 2 * i; i1 = 2 * i + 1; }
+    else { i0 = rot + 2 * (i - half); i1 = i0 + 1; }          // unrotated tail of a q or k head
+    T* x = row + (size_t)hs * hd;
+    float y0 = rl_ld(x + i0), y1 = rl_ld(x + i1);
+    if (rotate) {
       float s, c;
       sincosf((float)pos * inv_freq[i], &s, &c);
-      const int i0 = interleaved ? 2 * i : i;
-      const int i1 = interleaved ? 2 * i + 1 : i + half;
-      for (int head = lane_group; head < H + G; head += groups) {
-        T* x = row + (size_t)head * hd;
-        const float x0 = rl_ld(x + i0), x1 = rl_ld(x + i1);
-        const float y0 = x0 * c - x1 * s, y1 = x0 * s + x1 * c;
-        if (head < H) {
-          rl_st(x + i0, y0);
-          rl_st(x + i1, y1);
-        } else if (write_cache) {
-          T* kd = k_pool + dst + (size_t)(head - H) * RL_PAGE * hd;
-          rl_st(kd + i0, y0);
-          rl_st(kd + i1, y1);
-        } else {
-          rl_st(x + i0, y0);
-          rl_st(x + i1, y1);
-        }
-      }
+      const float x0 = y0, x1 = y1;
+      y0 = x0 * c - x1 * s;
+      y1 = x0 * s + x1 * c;
     }
-  }
-  if (!write_cache) return;
-  // unrotated tail of the key heads
-  const int tail = hd - rot;
-  for (int idx = threadIdx.x; idx < G * tail; idx += blockDim.x) {
-    const int g = idx / tail, e = rot + idx % tail;
-    k_pool[dst + (size_t)g * RL_PAGE * hd + e] = row[(size_t)(H + g) * hd + e];
-  }
-  for (int idx = threadIdx.x; idx < G * hd; idx += blockDim.x) {
-    const int g = idx / hd, e = idx % hd;
-    v_pool[dst + (size_t)g * RL_PAGE * hd + e] = row[(size_t)(H + G + g) * hd + e];
+    if (hs < H) {
+      if (rotate) { rl_st(x + i0, y0); rl_st(x + i1, y1); }
+    } else if (write_cache) {
+      T* d = (is_v ? v_pool : k_pool) + dst + (size_t)(hs - (is_v ? H + G : H)) * RL_PAGE * hd;
+      if (rotate) { rl_st(d + i0, y0); rl_st(d + i1, y1); }
+      else { d[i0] = x[i0]; d[i1] = x[i1]; }                  // bit copy
+    } else if (rotate) {
+      rl_st(x + i0, y0); rl_st(x + i1, y1);                   // no cache: keys rotate in place
+    }
   }
 }
 
@@ -87,13 +84,15 @@ extern "C" int rl_rope_kv_write(void* qkv, int dtype, int ld, const int* positio
   RL_REQUIRE((k_pool == nullptr) == (v_pool == nullptr), "rl_rope_kv_write: give both cache pools or none");
   if (num_tokens == 0) return RL_OK;
   const int write_cache = k_pool != nullptr;
-  const int threads = 128;
+  RL_REQUIRE(head_dim % 2 == 0, "rl_rope_kv_write: head_dim %d must be even", head_dim);
+  const dim3 grid(num_tokens, (num_heads + 2 * num_kv_heads + ROPE_HEADS_PER_CTA - 1) / ROPE_HEADS_PER_CTA);
+  const int threads = ROPE_THREADS;
   if (dtype == RL_F32)
-    rope_kv_write_kernel<float><<<num_tokens, threads, 0, stream>>>(
+    rope_kv_write_kernel<float><<<grid, threads, 0, stream>>>(
         (float*)qkv, ld, positions, slot_of_token, page_table, max_pages, inv_freq, num_heads,
         num_kv_heads, head_dim, rotary_dim, interleaved, (float*)k_pool, (float*)v_pool, write_cache);
   else if (dtype == RL_BF16)
-    rope_kv_write_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(
+    rope_kv_write_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
         (__nv_bfloat16*)qkv, ld, positions, slot_of_token, page_table, max_pages, inv_freq, num_heads,
         num_kv_heads, head_dim, rotary_dim, interleaved, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, write_cache);
   else

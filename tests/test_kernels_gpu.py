@@ -148,6 +148,33 @@ def test_gemm_tc_all_modes(M, N, K_):
     torch.testing.assert_close(out32, simt, rtol=1e-4, atol=2e-5 * scale * 4)
 
 
+@pytest.mark.parametrize("M,N,K_", [(1, 4096, 4096), (8, 6144, 4096), (8, 4096, 14336), (8, 512, 512), (64, 1024, 4096),
+                                    (33, 300, 1096), (16, 128, 256)])
+def test_gemm_tc_split_k_is_deterministic_and_matches_the_unsplit_product(M, N, K_):
+    k = K()
+    a = _rand(M, K_, dtype=torch.bfloat16, seed=14)
+    w = _rand(N, K_, dtype=torch.bfloat16, seed=15)
+    bias = _rand(N, seed=16)
+    res = _rand(M, N, seed=17)
+    whole = res.clone()
+    k.gemm_tc(a, w, whole, k.OUT_ADD_F32, bias, split_k=False)
+    runs = []
+    for _ in range(3):
+        o = res.clone()
+        k.gemm_tc(a, w, o, k.OUT_ADD_F32, bias)
+        runs.append(o)
+    k.check_device_errors()
+    assert torch.equal(runs[0], runs[1]) and torch.equal(runs[0], runs[2])        # fixed order of the parts
+    torch.testing.assert_close(runs[0], whole, rtol=1e-4, atol=1e-4 * math.sqrt(K_))
+    ref = a.double().cpu() @ w.double().cpu().T + bias.double().cpu() + res.double().cpu()
+    torch.testing.assert_close(runs[0].double().cpu(), ref, rtol=1e-4, atol=1e-4 * math.sqrt(K_))
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    k.gemm_tc(a, w, out, k.OUT_SAME)
+    torch.testing.assert_close(out.double().cpu(), ref - bias.double().cpu() - res.double().cpu(), rtol=1e-2, atol=1e-2 * math.sqrt(K_))
+    if (M, N, K_) in [(1, 4096, 4096), (8, 6144, 4096), (8, 4096, 14336)]:
+        assert k.gemm_tc_splits(M, N, K_) > 1
+
+
 def test_gemm_tc_strided_rows_and_refusals():
     k = K()
     wide = _rand(40, 640, dtype=torch.bfloat16, seed=8)
