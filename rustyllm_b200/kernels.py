@@ -51,6 +51,9 @@ _SIGNATURES = {
     "rl_attention_decode": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
                             _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p],
     "rl_attention_decode_supported": [_c_int, _c_int, _c_int],
+    "rl_attention_prefill": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                             _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p],
+    "rl_attention_prefill_supported": [_c_int, _c_int, _c_int],
     "rl_gemm_tc_supported": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int],
     "rl_gemm_tc": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                    _c_void_p, _c_void_p, _c_ll, _c_void_p, _c_int, _c_void_p],
@@ -388,6 +391,37 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     _count(2 if num_splits > 1 else 1)
 
 
+# ----------------------------------------------------------------------------- prefill attention
+PREFILL_QTILE = 64
+
+
+def attention_prefill_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    return dtype == torch.bfloat16 and bool(library().rl_attention_prefill_supported(num_heads, num_kv_heads, head_dim))
+
+
+def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
+                      cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, kv_lens: torch.Tensor, q_lens,
+                      out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                      window: int = 0) -> None:
+    """Causal attention of packed query tokens over the bf16 cache (tensor cores).
+    q: [M, >= H*hd] bf16; cu_seqlens [B+1], seq_slots [B], kv_lens [B] on the device;
+    q_lens: host list of tokens per sequence; out: [M, H*hd] bf16."""
+    _need(q, "q", torch.bfloat16, contiguous=False); _need(k_pool, "k_pool", torch.bfloat16)
+    _need(v_pool, "v_pool", torch.bfloat16); _need(out, "out", torch.bfloat16)
+    _need(page_table, "page_table", torch.int32); _need(cu_seqlens, "cu_seqlens", torch.int32)
+    _need(seq_slots, "seq_slots", torch.int32); _need(kv_lens, "kv_lens", torch.int32)
+    B = len(q_lens)
+    assert cu_seqlens.numel() == B + 1 and seq_slots.numel() == B and kv_lens.numel() == B
+    assert q.shape[0] == sum(q_lens) and q.stride(1) == 1
+    tiles = sum(-(-n // PREFILL_QTILE) for n in q_lens)
+    ldq = q.stride(0) if q.shape[0] > 1 else max(q.stride(0), num_heads * head_dim)
+    _check(library().rl_attention_prefill(
+        q.data_ptr(), ldq, k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr(), page_table.shape[1],
+        cu_seqlens.data_ptr(), seq_slots.data_ptr(), kv_lens.data_ptr(), B, tiles, out.data_ptr(), out.stride(0),
+        num_heads, num_kv_heads, head_dim, float(scale), int(window), _stream()), "rl_attention_prefill")
+    _count()
+
+
 # ----------------------------------------------------------------------------- attention dispatch
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
               step, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
@@ -398,6 +432,10 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
     if step.is_decode and attention_decode_supported(q.dtype, num_heads, num_kv_heads, head_dim):
         attention_decode(q, k_pool, v_pool, page_table, step.seq_slots, step.kv_lens, out,
                          num_heads, num_kv_heads, head_dim, scale, window)
+        return
+    if not step.is_decode and attention_prefill_supported(q.dtype, num_heads, num_kv_heads, head_dim):
+        attention_prefill(q, k_pool, v_pool, page_table, step.cu_seqlens, step.seq_slots, step.kv_lens,
+                          step.q_lens, out, num_heads, num_kv_heads, head_dim, scale, window)
         return
     attention_simt(q, k_pool, v_pool, page_table, step.slot_of_token, step.positions, out,
                    num_heads, num_kv_heads, head_dim, scale, window)

@@ -396,6 +396,70 @@ def test_attention_decode_ignores_garbage_beyond_the_sequence():
     torch.testing.assert_close(out.double().cpu(), ref, **_tol(torch.bfloat16))
 
 
+# ----------------------------------------------------------------------------- prefill attention (tensor cores)
+def _prefill_inputs(case, lens_q, lens_kv):
+    q, kp, vp, pt, sot, pos, ref = case
+    B = len(lens_q)
+    cu = [0]
+    for n in lens_q:
+        cu.append(cu[-1] + n)
+    slots = list(range(B, 0, -1))        # as _attention_case assigns them
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    return q, kp, vp, pt, i32(cu), i32(slots), i32(lens_kv), ref
+
+
+@pytest.mark.parametrize("H,G,hd", [(32, 8, 128), (4, 4, 128), (6, 2, 64), (3, 1, 64)])
+@pytest.mark.parametrize("lens_q,lens_kv", [([1, 5, 64, 65, 200], [1, 5, 64, 65, 200]),      # whole prompts
+                                            ([130, 1, 33, 64], [130, 300, 97, 128]),            # chunks after a cached prefix
+                                            ([700], [700])])
+def test_attention_prefill_matches_plain(H, G, hd, lens_q, lens_kv):
+    k = K()
+    assert k.attention_prefill_supported(torch.bfloat16, H, G, hd)
+    case = _attention_case(torch.bfloat16, H, G, hd, lens_q, lens_kv, seed=hd + H + len(lens_q))
+    q, kp, vp, pt, cu, slots, kv_lens, ref = _prefill_inputs(case, lens_q, lens_kv)
+    out = torch.full((q.shape[0], H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    k.attention_prefill(q, kp, vp, pt, cu, slots, kv_lens, lens_q, out, H, G, hd, 1.0 / math.sqrt(hd))
+    torch.testing.assert_close(out.double().cpu(), ref, **_tol(torch.bfloat16))
+    simt = torch.empty_like(out)
+    k.attention_simt(q, kp, vp, pt, case[4], case[5], simt, H, G, hd, 1.0 / math.sqrt(hd))
+    torch.testing.assert_close(out.float(), simt.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_attention_prefill_window_and_garbage_beyond_the_sequence():
+    k = K()
+    H, G, hd, W = 4, 2, 64, 70
+    lens_q, lens_kv = [40, 150, 3], [40, 300, 200]
+    case = _attention_case(torch.bfloat16, H, G, hd, lens_q, lens_kv, window=W, seed=4)
+    q, kp, vp, pt, cu, slots, kv_lens, ref = _prefill_inputs(case, lens_q, lens_kv)
+    for b, n in enumerate(lens_kv):       # rows of the last page beyond the sequence: NaN
+        if n % PAGE:
+            page = int(pt[int(slots[b]), (n - 1) // PAGE])
+            kp[page, :, n % PAGE:] = float("nan"); vp[page, :, n % PAGE:] = float("nan")
+    out = torch.empty(q.shape[0], H * hd, dtype=torch.bfloat16, device=DEV)
+    k.attention_prefill(q, kp, vp, pt, cu, slots, kv_lens, lens_q, out, H, G, hd, 1.0 / math.sqrt(hd), W)
+    torch.testing.assert_close(out.double().cpu(), ref, **_tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("far", [0, 63, 64, 300])
+def test_attention_prefill_finds_one_far_key(far):
+    """Every query from position `far` on must return the value of key `far` (its score dominates)."""
+    H, G, hd, n = 4, 2, 128, 451
+
+    def craft(b, qb, kb, vb):
+        direction = torch.ones(hd) / math.sqrt(hd)
+        qb[:] = (direction * 14.0).to(qb.dtype)
+        kb[:] = (kb.float() * 0.05).to(kb.dtype)
+        kb[far] = (direction * 14.0).to(kb.dtype)
+    case = _attention_case(torch.bfloat16, H, G, hd, [n], [n], seed=6, craft=craft)
+    q, kp, vp, pt, cu, slots, kv_lens, ref = _prefill_inputs(case, [n], [n])
+    out = torch.empty(n, H * hd, dtype=torch.bfloat16, device=DEV)
+    K().attention_prefill(q, kp, vp, pt, cu, slots, kv_lens, [n], out, H, G, hd, 1.0 / math.sqrt(hd))
+    torch.testing.assert_close(out.double().cpu(), ref, **_tol(torch.bfloat16))
+    page = int(pt[1, far // PAGE]); v_far = vp[page, :, far % PAGE].double().cpu()
+    want = v_far.repeat_interleave(H // G, dim=0).reshape(1, H * hd)
+    assert (ref[far + 1:] - want).abs().max() < 1e-3
+
+
 # ----------------------------------------------------------------------------- sampling
 def test_argmax_first_maximum_wins_and_non_finite_is_skipped():
     k = K()
