@@ -104,6 +104,28 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
   }
 }
 
+// bf16, I a multiple of 8, 16-byte aligned rows: eight elements a thread
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int M, int I) {
+  const int per_row = I / 8;
+  const size_t total = (size_t)M * per_row;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t m = idx / per_row;
+    const int c = (int)(idx - m * per_row) * 8;
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gu + m * 2 * I + c);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(gu + m * 2 * I + I + c);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 o4;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+      o2[k] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + m * I + c) = o4;
+  }
+}
+
 extern "C" int rl_swiglu(const void* gate_up, void* out, int dtype, int num_tokens,
                          int intermediate, cudaStream_t stream) {
   RL_REQUIRE(num_tokens >= 0 && intermediate > 0, "rl_swiglu: bad sizes M=%d I=%d", num_tokens, intermediate);
@@ -111,7 +133,11 @@ extern "C" int rl_swiglu(const void* gate_up, void* out, int dtype, int num_toke
   const size_t total = (size_t)num_tokens * intermediate;
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
-  if (dtype == RL_F32)
+  if (dtype == RL_BF16 && intermediate % 8 == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    const size_t vec = total / 8;
+    const int vblocks = (int)((vec + threads - 1) / threads < 148 * 16 ? (vec + threads - 1) / threads : 148 * 16);
+    swiglu_bf16x8_kernel<<<vblocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, num_tokens, intermediate);
+  } else if (dtype == RL_F32)
     swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, num_tokens, intermediate);
   else if (dtype == RL_BF16)
     swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, num_tokens, intermediate);

@@ -277,16 +277,53 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (*last_flag && !*abort_flag) {
         __threadfence();
-        if (n < N) {
-          for (int j = 0; j < cols; ++j) {
-            float v = 0.f;
-            for (int sp = 0; sp < num_splits; ++sp)
-              v += __ldcg(partial + ((size_t)sp * gridDim.x * gridDim.y + tile) * tile_elems + (size_t)j * BLOCK_N_OUT + row);
-            v += b;
-            const size_t o = (size_t)(m0 + j) * ldo + n;
-            if (out_mode == TC_OUT_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
-            else if (out_mode == TC_OUT_F32) ((float*)out)[o] = v;
-            else ((float*)out)[o] += v;
+        // 32 lanes x 4 consecutive weight rows cover the tile's 128 rows with 16-byte loads;
+        // the four warps take the token columns in turn.  Parts are added in order 0, 1, 2, ...
+        const int et = threadIdx.x - 64;                 // 0..127 among the epilogue threads
+        const int r4 = (et & 31) * 4, cg = et >> 5;
+        const int nn = n0 + r4;
+        const size_t part_stride = (size_t)gridDim.x * gridDim.y * tile_elems;
+        const float* src = partial + (size_t)tile * tile_elems + r4;
+        const bool vec_ok = (nn + 3 < N) && ((ldo & 3) == 0) && (((uintptr_t)out & 15) == 0);
+        float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (bias != nullptr) {
+          bv.x = nn < N ? bias[nn] : 0.f; bv.y = nn + 1 < N ? bias[nn + 1] : 0.f;
+          bv.z = nn + 2 < N ? bias[nn + 2] : 0.f; bv.w = nn + 3 < N ? bias[nn + 3] : 0.f;
+        }
+        for (int j = cg; j < cols; j += 4) {
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          const float* col = src + (size_t)j * BLOCK_N_OUT;
+          for (int sp0 = 0; sp0 < num_splits; sp0 += 8) {
+            float4 t[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              t[u] = (sp0 + u < num_splits) ? __ldcg(reinterpret_cast<const float4*>(col + (size_t)(sp0 + u) * part_stride))
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) { v.x += t[u].x; v.y += t[u].y; v.z += t[u].z; v.w += t[u].w; }
+          }
+          v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+          const size_t o = (size_t)(m0 + j) * ldo + nn;
+          if (vec_ok) {
+            if (out_mode == TC_OUT_BF16) {
+              __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+              uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+              *reinterpret_cast<uint2*>((__nv_bfloat16*)out + o) = pk;
+            } else if (out_mode == TC_OUT_F32) {
+              *reinterpret_cast<float4*>((float*)out + o) = v;
+            } else {
+              float4 old = *reinterpret_cast<const float4*>((float*)out + o);
+              old.x += v.x; old.y += v.y; old.z += v.z; old.w += v.w;
+              *reinterpret_cast<float4*>((float*)out + o) = old;
+            }
+          } else {
+            const float e[4] = {v.x, v.y, v.z, v.w};
+            for (int u = 0; u < 4; ++u) {
+              if (nn + u >= N) break;
+              if (out_mode == TC_OUT_BF16) ((__nv_bfloat16*)out)[o + u] = __float2bfloat16_rn(e[u]);
+              else if (out_mode == TC_OUT_F32) ((float*)out)[o + u] = e[u];
+              else ((float*)out)[o + u] += e[u];
+            }
           }
         }
       }
@@ -361,17 +398,18 @@ extern "C" int rl_gemm_tc_supported(const void* A, const void* W, int M, int N, 
 
 static int token_tile(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
 
-// How many parts the K range is cut into for M tokens: enough CTAs for three an SM, at
-// least four 64-wide K blocks a part, partial-tile traffic at most a quarter of the
-// weight traffic, and everything within the workspace.  A function of the shapes only.
+// How many parts the K range is cut into for M tokens: enough CTAs for two an SM (one
+// above 16 tokens), at least four 64-wide K blocks a part, partial-tile traffic at most
+// an eighth of the weight traffic, and everything within the workspace.  A function of
+// the shapes only.
 extern "C" int rl_gemm_tc_splits(int M, int N, int K, long long workspace_floats, int num_counters) {
   const int bt = token_tile(M);
   if (bt > 64 || workspace_floats <= 0 || num_counters <= 0) return 1;
   const int tiles = ((N + BLOCK_N_OUT - 1) / BLOCK_N_OUT) * ((M + bt - 1) / bt);
   const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
-  int splits = (3 * 148) / tiles;
+  int splits = ((M <= 16 ? 2 : 1) * 148 + tiles - 1) / tiles;
   if (splits > total_kb / 4) splits = total_kb / 4;
-  if (splits > K / (16 * M)) splits = K / (16 * M);
+  if (splits > K / (32 * M)) splits = K / (32 * M);
   if (splits > 32) splits = 32;
   if (splits < 2 || tiles > num_counters) return 1;
   while (splits > 1 && (long long)splits * tiles * BLOCK_N_OUT * bt > workspace_floats) --splits;

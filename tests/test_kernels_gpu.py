@@ -57,11 +57,12 @@ def test_rmsnorm(d, out_dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_swiglu(dtype):
-    gu = _rand(13, 2 * 172, dtype=dtype, seed=3, scale=2.0)
-    out = torch.empty(13, 172, dtype=dtype, device=DEV)
+@pytest.mark.parametrize("I", [172, 256, 14336])
+def test_swiglu(dtype, I):
+    gu = _rand(13, 2 * I, dtype=dtype, seed=3, scale=2.0)
+    out = torch.empty(13, I, dtype=dtype, device=DEV)
     K().swiglu(gu, out)
-    g, u = gu[:, :172].double().cpu(), gu[:, 172:].double().cpu()
+    g, u = gu[:, :I].double().cpu(), gu[:, I:].double().cpu()
     torch.testing.assert_close(out.double().cpu(), P.swiglu(g, u), **_tol(dtype))
 
 
