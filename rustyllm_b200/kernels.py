@@ -359,9 +359,10 @@ def attention_decode_supported(dtype: torch.dtype, num_heads: int, num_kv_heads:
 
 
 def decode_splits(num_seqs: int, num_kv_heads: int) -> int:
-    """Splits of the context per (sequence, KV head): enough CTAs for about three per
-    SM.  Depends on the batch's size only, so that a captured step keeps its grid."""
-    return max(1, min(32, -(-3 * NUM_SMS // (num_seqs * num_kv_heads))))
+    """Splits of the context per (sequence, KV head): enough CTAs for about one and a
+    half per SM, at most 16 (measured best at 1, 8 and 64 sequences of ~800 tokens).
+    Depends on the batch's size only, so that a captured step keeps its grid."""
+    return max(1, min(16, -(-3 * NUM_SMS // (2 * num_seqs * num_kv_heads))))
 
 
 def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,

@@ -105,3 +105,30 @@ def test_random_weights_without_files_and_layer_override():
     r2 = Runner.from_config(TINY["B"]["config"], seed=3, dtype="bfloat16", max_cache_tokens=64 * 4, max_batch=2,
                             num_layers=2)
     assert r2.generate([1, 2, 3], GenerationOptions(max_tokens=4, sampler=SamplerConfig.greedy(), ignore_eos=True)).token_ids == out.token_ids
+
+
+def test_command_line_generates_benchmarks_and_times_kernels(model_dirs, capsys, tmp_path):
+    import json
+    from rustyllm_b200 import cli
+    d, cfg = model_dirs["D"]
+    pc, pw = _plain(d)
+    prompt = random_tokens(320, 9, 81)
+    assert cli.main([d, "--dtype", "float32", "-p", " ".join(map(str, prompt)), "-n", "5", "-t", "0", "-v"]) == 0
+    cap = capsys.readouterr()
+    assert [int(t) for t in cap.out.split()] == P.generate(pc, pw, prompt, 5)
+    assert "Prompt: 9 tokens" in cap.err and "Generated: 5 tokens" in cap.err and "Decode:" in cap.err
+    pf = tmp_path / "prompts.txt"
+    pf.write_text("1 2 3\n4,5,6,7\n")
+    assert cli.main([d, "--prompt-file", str(pf), "-n", "3", "-t", "0", "--ignore-eos"]) == 0
+    lines = capsys.readouterr().out.strip().splitlines()
+    assert len(lines) == 2 and all(len(l.split()) == 3 for l in lines)
+    assert cli.main([d, "--bench-json", "--bench-runs", "2", "--batch", "3", "--prompt-len", "20", "-n", "4", "--seed", "5",
+                     "--ignore-eos", "--bench-output"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["type"] == "rusty-llm.benchmark" and rep["architecture"] == "LlamaForCausalLM" and rep["runs"] == 2
+    assert rep["results"][0]["prompt_tokens"] == 60 and rep["results"][0]["generated_tokens"] == 12
+    assert rep["summary"]["aggregate_decode_tok_s"] > 0 and len(rep["results"][1]["token_ids"]) == 3
+    assert cli.main([d, "--random", "--kernel-bench-json", "--kernel-bench-runs", "3"]) == 0
+    rows = {r["name"]: r for r in json.loads(capsys.readouterr().out)["rows"]}
+    for name in ("attn_norm.rms", "attn_qkv.fused", "ffn_gate_up.fused", "ffn_activation.silu_mul", "output", "attn_scan.ctx128"):
+        assert rows[name]["avg_us"] > 0
