@@ -54,6 +54,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
   __shared__ float s_acc[DEC_WARPS][16][HD + 4];
   __shared__ float s_m[DEC_WARPS][16], s_l[DEC_WARPS][16];
 
+  rl_pdl_trigger();
+  rl_pdl_wait();
   const int split = blockIdx.x, num_splits = gridDim.x;
   const int gkv = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -213,6 +215,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
 template <int HD>
 __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                 __nv_bfloat16* __restrict__ out, int ldo, int H, int num_splits) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
   const int h = blockIdx.x, b = blockIdx.y;
   const size_t p0 = ((size_t)b * H + h) * num_splits;
   float M = -INFINITY;
@@ -235,13 +239,13 @@ static int launch_decode(const void* q, int ldq, const void* k_pool, const void*
                          float* part_o, float* part_ml, int B, int H, int G, float scale, int window,
                          int num_splits, cudaStream_t stream) {
   dim3 grid(num_splits, G, B);
-  attention_decode_kernel<HD><<<grid, DEC_WARPS * 32, 0, stream>>>(
+  rl_launch_pdl(attention_decode_kernel<HD>, grid, dim3(DEC_WARPS * 32), 0, stream,
       (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table, max_pages,
       seq_slots, kv_lens, (__nv_bfloat16*)out, ldo, part_o, part_ml, H, G, scale * 1.4426950408889634f, window);
   RL_LAUNCH_CHECK("rl_attention_decode");
   if (num_splits > 1) {
-    attention_decode_combine_kernel<HD><<<dim3(H, B), HD >= 128 ? 128 : 64, 0, stream>>>(
-        part_o, part_ml, (__nv_bfloat16*)out, ldo, H, num_splits);
+    rl_launch_pdl(attention_decode_combine_kernel<HD>, dim3(H, B), dim3(HD >= 128 ? 128 : 64), 0, stream,
+                  (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, ldo, H, num_splits);
     RL_LAUNCH_CHECK("rl_attention_decode (combine)");
   }
   return RL_OK;

@@ -65,6 +65,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __n
   extern __shared__ __align__(128) uint8_t pf_smem[];   // [2 buffers][K tile | V tile]
   __shared__ int s_seq, s_tile;
 
+  rl_pdl_trigger();
+  rl_pdl_wait();
   // ---- which sequence and which of its query tiles (heaviest tiles first) ----
   if (threadIdx.x == 0) {
     int t = (int)(gridDim.x - 1 - blockIdx.x), b = 0;
@@ -241,7 +243,7 @@ static int launch_prefill(const void* q, int ldq, const void* k_pool, const void
     configured = true;
   }
   dim3 grid(num_tiles, H);
-  attention_prefill_kernel<HD><<<grid, PF_WARPS * 32, SMEM, stream>>>(
+  rl_launch_pdl(attention_prefill_kernel<HD>, grid, dim3(PF_WARPS * 32), (size_t)SMEM, stream,
       (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table, max_pages,
       cu_seqlens, seq_slots, kv_lens, num_seqs, (__nv_bfloat16*)out, ldo, H, G, scale * 1.4426950408889634f, window);
   RL_LAUNCH_CHECK("rl_attention_prefill");

@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 enum RlDtype { RL_F32 = 0, RL_BF16 = 1 };
 
 enum RlStatus {
@@ -54,4 +56,35 @@ __device__ __forceinline__ float rl_warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
+}
+
+// ---- programmatic dependent launch ----
+// Kernels of a step are launched so that a kernel may start while its predecessor on
+// the stream still runs: its launch, block scheduling and prologue (and, in the matrix
+// products, the first loads of weights, which no kernel of a step writes) overlap the
+// predecessor's tail.  Every such kernel calls rl_pdl_trigger() first and rl_pdl_wait()
+// before it reads anything a predecessor wrote or writes anything at all; the wait
+// returns once all earlier kernels have completed and their writes are visible.  In a
+// kernel launched the ordinary way both are no-ops.
+__device__ __forceinline__ void rl_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void rl_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// 1 (default): launch with programmatic stream serialization; 0: ordinary launches
+// (rl_set_pdl, for measurements and for bisecting a fault).
+extern int g_rl_pdl_enabled;
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t rl_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                        cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_rl_pdl_enabled ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }

@@ -14,6 +14,8 @@
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                  float* __restrict__ out, int d, int vocab, int* __restrict__ err) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
   const int m = blockIdx.x;
   int id = ids[m];
   if (id < 0 || id >= vocab) {  // refuse instead of reading outside the table
@@ -34,9 +36,9 @@ extern "C" int rl_embedding(const void* table, int table_dtype, const int* ids, 
   if (num_tokens == 0) return RL_OK;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == RL_F32)
-    embedding_kernel<float><<<num_tokens, threads, 0, stream>>>((const float*)table, ids, out, hidden, vocab, err);
+    rl_launch_pdl(embedding_kernel<float>, num_tokens, threads, 0, stream, (const float*)table, ids, out, hidden, vocab, err);
   else if (table_dtype == RL_BF16)
-    embedding_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab, err);
+    rl_launch_pdl(embedding_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab, err);
   else
     RL_REQUIRE(false, "rl_embedding: unknown table dtype %d", table_dtype);
   RL_LAUNCH_CHECK("rl_embedding");
@@ -49,6 +51,8 @@ extern "C" int rl_embedding(const void* table, int table_dtype, const int* ids, 
 template <typename TO, int THREADS>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                TO* __restrict__ out, const int* __restrict__ rows, int d, float eps) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * d;
   float ss = 0.f;
@@ -80,9 +84,9 @@ extern "C" int rl_rmsnorm(const float* x, const float* weight, void* out, int ou
   RL_REQUIRE(eps > 0.f, "rl_rmsnorm: eps must be > 0, got %g", (double)eps);
   if (num_rows == 0) return RL_OK;
   if (out_dtype == RL_F32)
-    rmsnorm_kernel<float, 256><<<num_rows, 256, 0, stream>>>(x, weight, (float*)out, rows, hidden, eps);
+    rl_launch_pdl(rmsnorm_kernel<float, 256>, num_rows, 256, 0, stream, x, weight, (float*)out, rows, hidden, eps);
   else if (out_dtype == RL_BF16)
-    rmsnorm_kernel<__nv_bfloat16, 256><<<num_rows, 256, 0, stream>>>(x, weight, (__nv_bfloat16*)out, rows, hidden, eps);
+    rl_launch_pdl(rmsnorm_kernel<__nv_bfloat16, 256>, num_rows, 256, 0, stream, x, weight, (__nv_bfloat16*)out, rows, hidden, eps);
   else
     RL_REQUIRE(false, "rl_rmsnorm: unknown output dtype %d", out_dtype);
   RL_LAUNCH_CHECK("rl_rmsnorm");
@@ -93,6 +97,8 @@ extern "C" int rl_rmsnorm(const float* x, const float* weight, void* out, int ou
 // gate_up: [M, 2*I] with the gate in columns [0, I) and up in [I, 2I).
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int M, int I) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
   const size_t total = (size_t)M * I;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
@@ -106,6 +112,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 
 // bf16, I a multiple of 8, 16-byte aligned rows: eight elements a thread
 __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int M, int I) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
   const int per_row = I / 8;
   const size_t total = (size_t)M * per_row;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -136,11 +144,11 @@ extern "C" int rl_swiglu(const void* gate_up, void* out, int dtype, int num_toke
   if (dtype == RL_BF16 && intermediate % 8 == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0) {
     const size_t vec = total / 8;
     const int vblocks = (int)((vec + threads - 1) / threads < 148 * 16 ? (vec + threads - 1) / threads : 148 * 16);
-    swiglu_bf16x8_kernel<<<vblocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, num_tokens, intermediate);
+    rl_launch_pdl(swiglu_bf16x8_kernel, vblocks, threads, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, num_tokens, intermediate);
   } else if (dtype == RL_F32)
-    swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, num_tokens, intermediate);
+    rl_launch_pdl(swiglu_kernel<float>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out, num_tokens, intermediate);
   else if (dtype == RL_BF16)
-    swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, num_tokens, intermediate);
+    rl_launch_pdl(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, num_tokens, intermediate);
   else
     RL_REQUIRE(false, "rl_swiglu: unknown dtype %d", dtype);
   RL_LAUNCH_CHECK("rl_swiglu");

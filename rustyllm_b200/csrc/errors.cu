@@ -25,3 +25,8 @@ extern "C" int rl_device_arch() {
   if (cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev) != cudaSuccess) return RL_ERR_CUDA;
   return major * 10 + minor;
 }
+
+int g_rl_pdl_enabled = 1;
+
+// Switch programmatic dependent launch on (1, default) or off (0) for all later launches.
+extern "C" void rl_set_pdl(int enabled) { g_rl_pdl_enabled = enabled ? 1 : 0; }

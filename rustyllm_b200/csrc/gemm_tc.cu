@@ -12,11 +12,13 @@
 // transposes anywhere.  Accumulation is float; the epilogue adds the optional bias
 // and stores bf16, stores float, or adds into a float buffer (the residual sum).
 //
-// Split-K: with few tokens a product has too few 128-row tiles to keep 148 SMs
-// streaming, so the K range is cut into gridDim.z parts.  Each part leaves its float
-// partial tile in scratch; the part that finishes last (a counter per tile) adds the
-// parts in order 0, 1, 2, ... and runs the epilogue, so the result does not depend on
-// which part finished when.  The counter resets itself for the next launch.
+// Split-K over a thread-block cluster: with few tokens a product has too few 128-row
+// tiles to keep 148 SMs streaming, so the K range of a tile is cut into 2, 4 or 8 parts
+// that run as the CTAs of one cluster.  Each CTA leaves its float partial tile in its
+// own shared memory; after a cluster barrier every CTA reads "its" token columns from
+// all parts through distributed shared memory, adds them in the order of the parts
+// (0, 1, 2, ...: the result does not depend on timing) and runs the epilogue for those
+// columns.  No global scratch, no atomics.
 //
 // Every wait on an mbarrier is bounded: when it runs out the kernel records a code
 // in the error word, all roles leave their loops, tensor memory is freed and the
@@ -98,6 +100,24 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---- thread-block cluster ----
+__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t cluster_size() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of the same shared-memory location in the cluster's CTA `rank`
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float4 dsmem_ld4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16)
 // and swizzled with the 128-byte pattern: start address / 16 in bits 0-13, leading
 // byte offset (unused for this layout, set to 16 bytes) in bits 16-29, stride between
@@ -131,13 +151,13 @@ struct TcConfig {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-// BT: tokens per CTA (MMA N).  Grid: (ceil(N_out / 128), ceil(M_tokens / BT)).
+// BT: tokens per CTA (MMA N).  Grid: (parts * ceil(N_out / 128), ceil(M_tokens / BT)) in
+// clusters of `parts` CTAs along x; the CTA's rank in its cluster is its part of K.
 template <int BT>
 __global__ void __launch_bounds__(TC_THREADS, TcConfig<BT>::MIN_CTAS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                const float* __restrict__ bias, void* __restrict__ out, int out_mode, int M, int N, int K,
-               int ldo, int* __restrict__ err, int kb_per_split, float* __restrict__ partial,
-               int* __restrict__ tile_counter) {
+               int ldo, int* __restrict__ err, int kb_per_split) {
   using Cfg = TcConfig<BT>;
   extern __shared__ uint8_t smem_raw[];
   // tiles need 1024-byte alignment for the 128-byte swizzle pattern
@@ -151,12 +171,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BLOCK_N_OUT;   // first weight row (output feature) of this CTA
-  const int m0 = blockIdx.y * BT;            // first token of this CTA
+  const int num_splits = (int)cluster_size(), split = (int)cluster_rank();
+  const int n0 = (blockIdx.x / num_splits) * BLOCK_N_OUT;   // first weight row (output feature) of this CTA
+  const int m0 = blockIdx.y * BT;                           // first token of this CTA
   const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
-  const int kb0 = blockIdx.z * kb_per_split;                       // this CTA's part of the K range
-  const int num_kb = min(kb_per_split, total_kb - kb0);            // > 0: the host sizes the grid so
-  const int num_splits = gridDim.z;
+  const int kb0 = split * kb_per_split;                            // this CTA's part of the K range
+  const int num_kb = min(kb_per_split, total_kb - kb0);            // > 0: the host sizes the parts so
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::STAGES; ++s) {
@@ -175,10 +195,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  rl_pdl_trigger();   // the next kernel on the stream may begin its own prologue
   if (warp == 0) {
     if (lane == 0) {
       // ---------------- producer: TMA loads into the ring ----------------
-      for (int kb = 0; kb < num_kb; ++kb) {
+      // Weights are written by no kernel of a step: the first ring of weight tiles is
+      // requested before the wait for the preceding kernels, the activations after it.
+      const int pre = min(num_kb, Cfg::STAGES);
+      for (int kb = 0; kb < pre; ++kb) {
+        const uint32_t fb = smem_u32(&full_bar[kb]);
+        mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+        tma_load_2d(smem_u32(tiles + (size_t)kb * Cfg::STAGE_BYTES), &map_w, fb, (kb0 + kb) * BLOCK_K, n0);
+      }
+      rl_pdl_wait();
+      for (int kb = 0; kb < pre; ++kb)
+        tma_load_2d(smem_u32(tiles + (size_t)kb * Cfg::STAGE_BYTES + BLOCK_N_OUT * BLOCK_K * 2), &map_a,
+                    smem_u32(&full_bar[kb]), (kb0 + kb) * BLOCK_K, m0);
+      for (int kb = pre; kb < num_kb; ++kb) {
         const int s = kb % Cfg::STAGES;
         const uint32_t phase = (kb / Cfg::STAGES) & 1;
         if (!mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1, abort_flag)) {
@@ -220,6 +253,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
   } else {
     // ---------------- epilogue: warps 2..5, each its quarter of the 128 lanes ----------------
+    rl_pdl_wait();      // before this warp reads or writes global memory
     const bool ok = mbar_wait(smem_u32(accum_bar), 0, abort_flag);
     if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(err, 3); }
     tc_fence_after();
@@ -247,87 +281,76 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           }
         }
       }
-    } else if (num_splits > 1) {
-      // partial tile of this part: [token column][weight row], rows contiguous
-      const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-      const size_t tile_elems = (size_t)BLOCK_N_OUT * BT;
-      float* mine = partial + ((size_t)blockIdx.z * gridDim.x * gridDim.y + tile) * tile_elems;
+    } else if (num_splits > 1 && ok) {
+      // this part's partial tile -> own shared memory (the ring is free: every MMA has
+      // completed), as [token column][weight row] floats
+      float* red = reinterpret_cast<float*>(tiles);
       const int cols = min(BT, M - m0);
-      if (ok) {
 #pragma unroll 1
-        for (int c = 0; c < BT / 16; ++c) {
-          if (c * 16 >= cols) break;
-          uint32_t r[16];
-          tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 16), r);
-          tmem_ld_wait();
+      for (int c = 0; c < BT / 16; ++c) {
+        if (c * 16 >= cols) break;
+        uint32_t r[16];
+        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 16), r);
+        tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (c * 16 + j < cols) mine[(size_t)(c * 16 + j) * BLOCK_N_OUT + row] = __uint_as_float(r[j]);
-        }
+        for (int j = 0; j < 16; ++j)
+          if (c * 16 + j < cols) red[(c * 16 + j) * BLOCK_N_OUT + row] = __uint_as_float(r[j]);
       }
-      // the part that arrives last at the tile's counter reduces all parts in order
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");          // the four epilogue warps
-      int* last_flag = (int*)(tmem_slot + 2);
-      if (threadIdx.x == 64) {
-        const int prev = atomicAdd(&tile_counter[tile], 1);
-        *last_flag = (prev == num_splits - 1);
-        if (prev == num_splits - 1) tile_counter[tile] = 0;     // ready for the next launch
+    }
+  }
+  if (num_splits > 1) {
+    // ---- all parts of the tile have their partial in shared memory ----
+    __syncwarp();
+    cluster_sync_all();
+    if (warp >= 2 && !*abort_flag) {
+      // 32 lanes x 4 consecutive weight rows cover the 128 rows with 16-byte loads.  This CTA
+      // owns the token columns j with j % parts == its rank; its four epilogue warps take
+      // them in turn.  Parts are added in order 0, 1, 2, ...
+      const int et = threadIdx.x - 64;
+      const int r4 = (et & 31) * 4, cg = et >> 5;
+      const int nn = n0 + r4;
+      const int cols = min(BT, M - m0);
+      const uint32_t red_local = smem_u32(tiles);
+      const bool vec_ok = (nn + 3 < N) && ((ldo & 3) == 0) && (((uintptr_t)out & 15) == 0);
+      float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (bias != nullptr) {
+        bv.x = nn < N ? bias[nn] : 0.f; bv.y = nn + 1 < N ? bias[nn + 1] : 0.f;
+        bv.z = nn + 2 < N ? bias[nn + 2] : 0.f; bv.w = nn + 3 < N ? bias[nn + 3] : 0.f;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (*last_flag && !*abort_flag) {
-        __threadfence();
-        // 32 lanes x 4 consecutive weight rows cover the tile's 128 rows with 16-byte loads;
-        // the four warps take the token columns in turn.  Parts are added in order 0, 1, 2, ...
-        const int et = threadIdx.x - 64;                 // 0..127 among the epilogue threads
-        const int r4 = (et & 31) * 4, cg = et >> 5;
-        const int nn = n0 + r4;
-        const size_t part_stride = (size_t)gridDim.x * gridDim.y * tile_elems;
-        const float* src = partial + (size_t)tile * tile_elems + r4;
-        const bool vec_ok = (nn + 3 < N) && ((ldo & 3) == 0) && (((uintptr_t)out & 15) == 0);
-        float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (bias != nullptr) {
-          bv.x = nn < N ? bias[nn] : 0.f; bv.y = nn + 1 < N ? bias[nn + 1] : 0.f;
-          bv.z = nn + 2 < N ? bias[nn + 2] : 0.f; bv.w = nn + 3 < N ? bias[nn + 3] : 0.f;
+      for (int j = split + num_splits * cg; j < cols; j += num_splits * 4) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        const uint32_t off = (uint32_t)((j * BLOCK_N_OUT + r4) * 4);
+        for (int sp = 0; sp < num_splits; ++sp) {
+          const float4 t = dsmem_ld4(dsmem_addr(red_local + off, (uint32_t)sp));
+          v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
         }
-        for (int j = cg; j < cols; j += 4) {
-          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-          const float* col = src + (size_t)j * BLOCK_N_OUT;
-          for (int sp0 = 0; sp0 < num_splits; sp0 += 8) {
-            float4 t[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-              t[u] = (sp0 + u < num_splits) ? __ldcg(reinterpret_cast<const float4*>(col + (size_t)(sp0 + u) * part_stride))
-                                            : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int u = 0; u < 8; ++u) { v.x += t[u].x; v.y += t[u].y; v.z += t[u].z; v.w += t[u].w; }
-          }
-          v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
-          const size_t o = (size_t)(m0 + j) * ldo + nn;
-          if (vec_ok) {
-            if (out_mode == TC_OUT_BF16) {
-              __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
-              uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-              *reinterpret_cast<uint2*>((__nv_bfloat16*)out + o) = pk;
-            } else if (out_mode == TC_OUT_F32) {
-              *reinterpret_cast<float4*>((float*)out + o) = v;
-            } else {
-              float4 old = *reinterpret_cast<const float4*>((float*)out + o);
-              old.x += v.x; old.y += v.y; old.z += v.z; old.w += v.w;
-              *reinterpret_cast<float4*>((float*)out + o) = old;
-            }
+        v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+        const size_t o = (size_t)(m0 + j) * ldo + nn;
+        if (vec_ok) {
+          if (out_mode == TC_OUT_BF16) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+            uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            *reinterpret_cast<uint2*>((__nv_bfloat16*)out + o) = pk;
+          } else if (out_mode == TC_OUT_F32) {
+            *reinterpret_cast<float4*>((float*)out + o) = v;
           } else {
-            const float e[4] = {v.x, v.y, v.z, v.w};
-            for (int u = 0; u < 4; ++u) {
-              if (nn + u >= N) break;
-              if (out_mode == TC_OUT_BF16) ((__nv_bfloat16*)out)[o + u] = __float2bfloat16_rn(e[u]);
-              else if (out_mode == TC_OUT_F32) ((float*)out)[o + u] = e[u];
-              else ((float*)out)[o + u] += e[u];
-            }
+            float4 old = *reinterpret_cast<const float4*>((float*)out + o);
+            old.x += v.x; old.y += v.y; old.z += v.z; old.w += v.w;
+            *reinterpret_cast<float4*>((float*)out + o) = old;
+          }
+        } else {
+          const float e[4] = {v.x, v.y, v.z, v.w};
+          for (int u = 0; u < 4; ++u) {
+            if (nn + u >= N) break;
+            if (out_mode == TC_OUT_BF16) ((__nv_bfloat16*)out)[o + u] = __float2bfloat16_rn(e[u]);
+            else if (out_mode == TC_OUT_F32) ((float*)out)[o + u] = e[u];
+            else ((float*)out)[o + u] += e[u];
           }
         }
       }
     }
+    __syncwarp();
+    cluster_sync_all();      // nobody leaves while another part still reads its shared memory
   }
   tc_fence_before();
   __syncthreads();
@@ -371,8 +394,7 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int 
 
 template <int BT>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, void* out, int out_mode,
-                     int M, int N, int K, int ldo, int* err, int splits, int kb_per_split, float* workspace,
-                     int* counters, cudaStream_t stream) {
+                     int M, int N, int K, int ldo, int* err, int splits, int kb_per_split, cudaStream_t stream) {
   using Cfg = TcConfig<BT>;
   static bool configured = false;
   if (!configured) {
@@ -380,10 +402,32 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, const float* 
     RL_REQUIRE(e == cudaSuccess, "rl_gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid((N + BLOCK_N_OUT - 1) / BLOCK_N_OUT, (M + BT - 1) / BT, splits);
-  gemm_tc_kernel<BT><<<grid, TC_THREADS, Cfg::SMEM_BYTES, stream>>>(mw, ma, bias, out, out_mode, M, N, K, ldo, err,
-                                                                    kb_per_split, workspace, counters);
-  RL_LAUNCH_CHECK("rl_gemm_tc");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(splits * ((N + BLOCK_N_OUT - 1) / BLOCK_N_OUT), (M + BT - 1) / BT, 1);
+  cfg.blockDim = dim3(TC_THREADS);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (g_rl_pdl_enabled) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (splits > 1) {     // the parts of a tile are the CTAs of one cluster
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = splits;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BT>, mw, ma, bias, out, out_mode, M, N, K, ldo, err, kb_per_split);
+  if (e != cudaSuccess) {
+    rl_set_error("rl_gemm_tc: launch failed (%d parts): %s", splits, cudaGetErrorString(e));
+    return RL_ERR_CUDA;
+  }
   return RL_OK;
 }
 
@@ -398,41 +442,38 @@ extern "C" int rl_gemm_tc_supported(const void* A, const void* W, int M, int N, 
 
 static int token_tile(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
 
-// How many parts the K range is cut into for M tokens: enough CTAs for two an SM (one
-// above 16 tokens), at least four 64-wide K blocks a part, partial-tile traffic at most
-// an eighth of the weight traffic, and everything within the workspace.  A function of
-// the shapes only.
-extern "C" int rl_gemm_tc_splits(int M, int N, int K, long long workspace_floats, int num_counters) {
+// How many parts (1, 2, 4 or 8: the cluster size) the K range is cut into for M tokens:
+// the smallest that gives about two CTAs an SM, with at least four 64-wide K blocks a
+// part; products with 148 tiles or more, and token tiles above 64, are not split.
+// A function of the shapes only, so a captured step keeps its grid.
+extern "C" int rl_gemm_tc_splits(int M, int N, int K) {
   const int bt = token_tile(M);
-  if (bt > 64 || workspace_floats <= 0 || num_counters <= 0) return 1;
+  if (bt > 64) return 1;
   const int tiles = ((N + BLOCK_N_OUT - 1) / BLOCK_N_OUT) * ((M + bt - 1) / bt);
   const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
-  int splits = ((M <= 16 ? 2 : 1) * 148 + tiles - 1) / tiles;
-  if (splits > total_kb / 4) splits = total_kb / 4;
-  if (splits > K / (32 * M)) splits = K / (32 * M);
-  if (splits > 32) splits = 32;
-  if (splits < 2 || tiles > num_counters) return 1;
-  while (splits > 1 && (long long)splits * tiles * BLOCK_N_OUT * bt > workspace_floats) --splits;
-  if (splits < 2) return 1;
-  const int kb_per = (total_kb + splits - 1) / splits;
-  return (total_kb + kb_per - 1) / kb_per;      // no part is empty
+  if (tiles >= 148) return 1;
+  int splits = 1;
+  while (splits < 8 && tiles * splits < 256 && total_kb / (splits * 2) >= 4) splits *= 2;
+  return splits;
 }
 
 // A: [M, K] bf16, row stride lda; W: [N, K] bf16 contiguous; out: [M, N] with row stride
 // ldo, bf16 (out_mode 0) or float (1 store, 2 add).  err: device int, set non-zero if a
-// bounded wait inside the kernel ran out.  workspace (floats) and counters (ints, zero
-// before the first use; the kernel leaves them zero) serve split-K and may be null:
-// then the K range is not split.  Launches that share them must not overlap on the GPU.
+// bounded wait inside the kernel ran out.  force_splits: 0 = number of K parts chosen
+// from the shapes; 1, 2, 4 or 8 = as given (for measurements).
 extern "C" int rl_gemm_tc(const void* A, const void* W, const float* bias, void* out, int out_mode, int M, int N,
-                          int K, int lda, int ldo, int* err, float* workspace, long long workspace_floats,
-                          int* counters, int num_counters, cudaStream_t stream) {
+                          int K, int lda, int ldo, int* err, int force_splits, cudaStream_t stream) {
   RL_REQUIRE(rl_gemm_tc_supported(A, W, M, N, K, lda), "rl_gemm_tc: operands not supported (M=%d N=%d K=%d lda=%d; K and lda "
              "must be multiples of 8 and the bases 16-byte aligned)", M, N, K, lda);
   RL_REQUIRE(out_mode >= 0 && out_mode <= 2, "rl_gemm_tc: unknown output mode %d", out_mode);
   RL_REQUIRE(ldo >= N && err != nullptr, "rl_gemm_tc: bad output stride or null error word");
+  RL_REQUIRE(force_splits == 0 || force_splits == 1 || force_splits == 2 || force_splits == 4 || force_splits == 8,
+             "rl_gemm_tc: the number of K parts must be 1, 2, 4 or 8, got %d", force_splits);
   const int bt = token_tile(M);
   const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
-  const int splits = (workspace && counters) ? rl_gemm_tc_splits(M, N, K, workspace_floats, num_counters) : 1;
+  int splits = force_splits > 0 ? force_splits : rl_gemm_tc_splits(M, N, K);
+  RL_REQUIRE(splits == 1 || bt <= 64, "rl_gemm_tc: K is split only for up to 64 tokens (the partial tile must fit the ring)");
+  while (splits > 1 && (splits - 1) * ((total_kb + splits - 1) / splits) >= total_kb) splits /= 2;   // no part is empty
   const int kb_per = (total_kb + splits - 1) / splits;
   CUtensorMap mw, ma;
   int rc = make_map(&mw, W, N, K, K, BLOCK_N_OUT);
@@ -440,10 +481,10 @@ extern "C" int rl_gemm_tc(const void* A, const void* W, const float* bias, void*
   rc = make_map(&ma, A, M, K, lda, bt);
   if (rc != RL_OK) return rc;
   switch (bt) {
-    case 16: return launch_tc<16>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, workspace, counters, stream);
-    case 32: return launch_tc<32>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, workspace, counters, stream);
-    case 64: return launch_tc<64>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, workspace, counters, stream);
-    case 128: return launch_tc<128>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, workspace, counters, stream);
-    default: return launch_tc<256>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, workspace, counters, stream);
+    case 16: return launch_tc<16>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, stream);
+    case 32: return launch_tc<32>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, stream);
+    case 64: return launch_tc<64>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, stream);
+    case 128: return launch_tc<128>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, stream);
+    default: return launch_tc<256>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, stream);
   }
 }

@@ -25,6 +25,8 @@ rope_kv_write_kernel(T* __restrict__ qkv, int ld, const int* __restrict__ positi
                      const int* __restrict__ slot_of_token, const int* __restrict__ page_table, int max_pages,
                      const float* __restrict__ inv_freq, int H, int G, int hd, int rot, int interleaved,
                      T* __restrict__ k_pool, T* __restrict__ v_pool, int write_cache) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
   const int m = blockIdx.x;
   const int pos = positions[m];
   T* row = qkv + (size_t)m * ld;
@@ -88,11 +90,11 @@ extern "C" int rl_rope_kv_write(void* qkv, int dtype, int ld, const int* positio
   const dim3 grid(num_tokens, (num_heads + 2 * num_kv_heads + ROPE_HEADS_PER_CTA - 1) / ROPE_HEADS_PER_CTA);
   const int threads = ROPE_THREADS;
   if (dtype == RL_F32)
-    rope_kv_write_kernel<float><<<grid, threads, 0, stream>>>(
+    rl_launch_pdl(rope_kv_write_kernel<float>, grid, threads, 0, stream,
         (float*)qkv, ld, positions, slot_of_token, page_table, max_pages, inv_freq, num_heads,
         num_kv_heads, head_dim, rotary_dim, interleaved, (float*)k_pool, (float*)v_pool, write_cache);
   else if (dtype == RL_BF16)
-    rope_kv_write_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
+    rl_launch_pdl(rope_kv_write_kernel<__nv_bfloat16>, grid, threads, 0, stream,
         (__nv_bfloat16*)qkv, ld, positions, slot_of_token, page_table, max_pages, inv_freq, num_heads,
         num_kv_heads, head_dim, rotary_dim, interleaved, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, write_cache);
   else

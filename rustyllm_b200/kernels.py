@@ -56,8 +56,8 @@ _SIGNATURES = {
     "rl_attention_prefill_supported": [_c_int, _c_int, _c_int],
     "rl_gemm_tc_supported": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int],
     "rl_gemm_tc": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                   _c_void_p, _c_void_p, _c_ll, _c_void_p, _c_int, _c_void_p],
-    "rl_gemm_tc_splits": [_c_int, _c_int, _c_int, _c_ll, _c_int],
+                   _c_void_p, _c_int, _c_void_p],
+    "rl_gemm_tc_splits": [_c_int, _c_int, _c_int],
 }
 
 
@@ -287,24 +287,9 @@ def _tc_error_word(device: torch.device) -> torch.Tensor:
     return _tc_err[key]
 
 
-TC_WORKSPACE_FLOATS = 4 << 20     # 16 MiB: 444 partial tiles of 128 x 64 floats
-TC_COUNTERS = 1024
-_tc_ws = {}
-
-
-def _tc_workspace(device: torch.device):
-    """Per-device scratch of the split-K products: partial tiles and tile counters.
-    Products on one stream use it one after another; launches on different streams that
-    may overlap must not share it (this library runs a model on one stream)."""
-    key = device.index if device.index is not None else torch.cuda.current_device()
-    if key not in _tc_ws:
-        _tc_ws[key] = (torch.empty(TC_WORKSPACE_FLOATS, dtype=torch.float32, device=device),
-                       torch.zeros(TC_COUNTERS, dtype=torch.int32, device=device))
-    return _tc_ws[key]
-
-
 def gemm_tc_splits(M: int, N: int, K: int) -> int:
-    return int(library().rl_gemm_tc_splits(M, N, K, TC_WORKSPACE_FLOATS, TC_COUNTERS))
+    """Parts (cluster size) the kernel cuts the K range into for these shapes."""
+    return int(library().rl_gemm_tc_splits(M, N, K))
 
 
 def check_device_errors() -> None:
@@ -330,9 +315,10 @@ def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bo
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_mode: int,
-            bias: Optional[torch.Tensor] = None, split_k: bool = True) -> None:
+            bias: Optional[torch.Tensor] = None, force_splits: int = 0) -> None:
     """out = a @ w.T (+ bias) on the tensor cores (tcgen05).  a: [M, K] bf16, w: [N, K] bf16;
-    out: bf16 (OUT_SAME) or float32 (OUT_F32 store, OUT_ADD_F32 add)."""
+    out: bf16 (OUT_SAME) or float32 (OUT_F32 store, OUT_ADD_F32 add).  force_splits: 0 = the
+    kernel's own choice of K parts; 1, 2, 4, 8 = as given."""
     _need(a, "a", torch.bfloat16, contiguous=False); _need(w, "w", torch.bfloat16); _need(out, "out", contiguous=False)
     M, K = a.shape
     N = w.shape[0]
@@ -343,10 +329,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_mode: int,
         assert bias.numel() == N
     lda = a.stride(0) if M > 1 else K
     ldo = out.stride(0) if M > 1 else N
-    ws, counters = _tc_workspace(a.device) if split_k else (None, None)
     _check(library().rl_gemm_tc(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), out_mode, M, N, K, lda, ldo,
-                                _tc_error_word(a.device).data_ptr(), _ptr(ws), TC_WORKSPACE_FLOATS if split_k else 0,
-                                _ptr(counters), TC_COUNTERS if split_k else 0, _stream()), "rl_gemm_tc")
+                                _tc_error_word(a.device).data_ptr(), int(force_splits), _stream()), "rl_gemm_tc")
     _count()
 
 

@@ -158,12 +158,14 @@ def test_gemm_tc_split_k_is_deterministic_and_matches_the_unsplit_product(M, N, 
     bias = _rand(N, seed=16)
     res = _rand(M, N, seed=17)
     whole = res.clone()
-    k.gemm_tc(a, w, whole, k.OUT_ADD_F32, bias, split_k=False)
+    k.gemm_tc(a, w, whole, k.OUT_ADD_F32, bias, force_splits=1)
     runs = []
-    for _ in range(3):
+    for parts in (0, 0, 0, 2, 4, 8):
         o = res.clone()
-        k.gemm_tc(a, w, o, k.OUT_ADD_F32, bias)
+        k.gemm_tc(a, w, o, k.OUT_ADD_F32, bias, force_splits=parts)
         runs.append(o)
+    for o in runs[3:]:
+        torch.testing.assert_close(o, whole, rtol=1e-4, atol=1e-4 * math.sqrt(K_))
     k.check_device_errors()
     assert torch.equal(runs[0], runs[1]) and torch.equal(runs[0], runs[2])        # fixed order of the parts
     torch.testing.assert_close(runs[0], whole, rtol=1e-4, atol=1e-4 * math.sqrt(K_))
