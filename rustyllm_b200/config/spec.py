@@ -43,6 +43,8 @@ class ParamSpec:
       - "int_table": integer data, kept as int32.
     ``alias_of`` names another parameter path ("embedding.weight") whose storage
     this one shares when none of its sources is in the file (tied weights).
+    ``layout``: "concat" (sources one after another along dimension 0) or "interleave"
+    (sources of equal shape, their rows taken in turn: s0[0], s1[0], s0[1], s1[1], ...).
     ``init`` tells the random-weights mode what to draw: "normal" (N(0, std)),
     "ones" (1, or 1 + N(0, std) when norm noise is asked for) or "zeros".
     """
@@ -52,6 +54,7 @@ class ParamSpec:
     alias_of: Optional[str] = None
     optional_in_file: bool = False
     init: str = "normal"
+    layout: str = "concat"
 
     @property
     def shape(self) -> Tuple[int, ...]:

@@ -10,12 +10,14 @@
 // reference's grouped scan does on the CPU and its Metal kernel
 // ``resident_gqa4_attention`` (src/metal_backend.m:542-592) does for groups of four.
 //
-// The kernel is bound by the read of the cache, so keys and values go straight from
-// global memory into the MMA's register fragments with 16-byte loads and no shared
-// memory on the way.  That works because a dot product does not care in which order
-// its terms are added: the head dimension (for Q.K) and the key index and output
-// column (for P.V) are assigned to fragment positions such that every lane's share is
-// contiguous in memory.
+// The kernel is bound by the read of the cache.  Every lane fetches exactly the 16-byte
+// pieces of keys and values that its own MMA fragments need: a dot product does not care
+// in which order its terms are added, so the head dimension (for Q.K) and the key index
+// and output column (for P.V) are assigned to fragment positions such that every lane's
+// share is contiguous in memory.  The pieces travel by cp.async into a ring in shared
+// memory that is private to each lane (no lane reads what another copied, so no barrier
+// is needed, and consecutive lanes hit consecutive banks): two blocks of 16 keys are in
+// flight per warp while a third is being multiplied.
 //
 // Grid: (splits, KV heads, sequences); 4 warps per CTA take the split's 16-key blocks in
 // turn.  With one split the CTA writes the output; otherwise it writes its
@@ -42,6 +44,29 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+#define DEC_STAGES 3
+__device__ __forceinline__ void dec_cp_async16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void dec_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void dec_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint4 dec_lds16(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+// shared memory of one CTA: the ring [warp][stage][piece][lane] of 16-byte pieces, reused
+// after the loop for the warps' (max, sum, output)
+template <int HD>
+struct DecSmem {
+  static constexpr int PIECES = HD / 8;                 // per lane and block: HD/16 of keys + HD/16 of values
+  static constexpr int RING_BYTES = DEC_WARPS * DEC_STAGES * PIECES * 32 * 16;
+  static constexpr int MERGE_BYTES = (DEC_WARPS * 16 * (HD + 4) + 2 * DEC_WARPS * 16) * 4;
+  static constexpr int BYTES = RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES;
+};
+
 template <int HD>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ k_pool,
@@ -51,8 +76,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
                         float* __restrict__ part_ml, int H, int G, float scale_log2e, int window) {
   constexpr int NT = HD / 8;        // output n-tiles of 8 columns
   constexpr int KS = HD / 16;       // k-steps of the Q.K product
-  __shared__ float s_acc[DEC_WARPS][16][HD + 4];
-  __shared__ float s_m[DEC_WARPS][16], s_l[DEC_WARPS][16];
+  extern __shared__ __align__(16) uint8_t dec_smem[];
+  float (*s_acc)[16][HD + 4] = reinterpret_cast<float (*)[16][HD + 4]>(dec_smem);
+  float (*s_m)[16] = reinterpret_cast<float (*)[16]>(dec_smem + DEC_WARPS * 16 * (HD + 4) * 4);
+  float (*s_l)[16] = s_m + DEC_WARPS;
 
   rl_pdl_trigger();
   rl_pdl_wait();
@@ -94,38 +121,67 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
   const size_t page_stride = (size_t)G * RL_PAGE * HD;
   const size_t head_off = (size_t)gkv * RL_PAGE * HD;
 
-  for (int blk = blk_lo + warp; blk < blk_hi; blk += DEC_WARPS) {
+  // ring slot of piece p in stage st: lanes are consecutive, so loads and stores are conflict-free
+  constexpr int PIECES = DecSmem<HD>::PIECES;
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(dec_smem) +
+                        (uint32_t)(warp * DEC_STAGES * PIECES * 32 + lane) * 16;
+  auto slot = [&](int st, int p) { return ring + (uint32_t)((st * PIECES + p) * 32) * 16; };
+  // pieces 0 .. HD/16-1: keys (n-tile nt, 32-dimension chunk c); the rest: values (row r, group grp)
+  auto issue = [&](int blk, int st) {
     const int key0 = blk * DEC_BLOCK;
     const size_t base = (size_t)pages[key0 / RL_PAGE] * page_stride + head_off + (size_t)(key0 % RL_PAGE) * HD;
     const __nv_bfloat16* kb = k_pool + base;
     const __nv_bfloat16* vb = v_pool + base;
-
-    // values first (the loads are independent of the scores; this keeps them in flight)
-    uint4 vr[HD / 64][4];
-    {
-      const int rows[4] = {2 * t, 2 * t + 1, 2 * t + 8, 2 * t + 9};
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const bool valid = key0 + rows[r] < len;     // rows beyond the sequence may hold anything
+    for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-        for (int grp = 0; grp < HD / 64; ++grp)
-          vr[grp][r] = valid ? ldg16(vb + (size_t)rows[r] * HD + 64 * grp + 8 * g) : make_uint4(0, 0, 0, 0);
-      }
+      for (int c = 0; c < HD / 32; ++c)
+        dec_cp_async16(slot(st, nt * (HD / 32) + c), kb + (size_t)(8 * nt + g) * HD + 8 * t + 32 * c, 16);
+    const int rows[4] = {2 * t, 2 * t + 1, 2 * t + 8, 2 * t + 9};
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int bytes = key0 + rows[r] < len ? 16 : 0;    // rows beyond the sequence may hold anything: zeros instead
+#pragma unroll
+      for (int grp = 0; grp < HD / 64; ++grp)
+        dec_cp_async16(slot(st, HD / 16 + r * (HD / 64) + grp), vb + (size_t)rows[r] * HD + 64 * grp + 8 * g, bytes);
     }
+  };
+
+  {
+    int pre = blk_lo + warp;
+#pragma unroll
+    for (int st = 0; st < DEC_STAGES - 1; ++st, pre += DEC_WARPS) {
+      if (pre < blk_hi) issue(pre, st);
+      dec_commit();
+    }
+  }
+  int it = 0;
+  for (int blk = blk_lo + warp; blk < blk_hi; blk += DEC_WARPS, ++it) {
+    const int key0 = blk * DEC_BLOCK;
+    const int st = it % DEC_STAGES;
+    {
+      const int ahead = blk + (DEC_STAGES - 1) * DEC_WARPS;
+      if (ahead < blk_hi) issue(ahead, (it + DEC_STAGES - 1) % DEC_STAGES);
+      dec_commit();
+    }
+    dec_wait<DEC_STAGES - 1>();     // this lane's pieces of block `blk` have landed
+
+    uint4 vr[HD / 64][4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int grp = 0; grp < HD / 64; ++grp) vr[grp][r] = dec_lds16(slot(st, HD / 16 + r * (HD / 64) + grp));
 
     // scores S[16 heads x 16 keys] = Q . K^T
     float s[2][4];
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
       s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-      const __nv_bfloat16* krow = kb + (size_t)(8 * nt + g) * HD + 8 * t;
-      uint4 kr[HD / 32];
-#pragma unroll
-      for (int c = 0; c < HD / 32; ++c) kr[c] = ldg16(krow + 32 * c);
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
-        mma_bf16_16816(s[nt], qf[2 * c][0], qf[2 * c][1], qf[2 * c][2], qf[2 * c][3], kr[c].x, kr[c].y);
-        mma_bf16_16816(s[nt], qf[2 * c + 1][0], qf[2 * c + 1][1], qf[2 * c + 1][2], qf[2 * c + 1][3], kr[c].z, kr[c].w);
+        const uint4 kr = dec_lds16(slot(st, nt * (HD / 32) + c));
+        mma_bf16_16816(s[nt], qf[2 * c][0], qf[2 * c][1], qf[2 * c][2], qf[2 * c][3], kr.x, kr.y);
+        mma_bf16_16816(s[nt], qf[2 * c + 1][0], qf[2 * c + 1][1], qf[2 * c + 1][2], qf[2 * c + 1][3], kr.z, kr.w);
       }
     }
     // mask keys outside [start, len), scale into the exp2 domain
@@ -174,7 +230,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
     }
   }
 
-  // ---- combine the four warps ----
+  // ---- combine the four warps (the ring's memory is reused: every copy must have landed) ----
+  dec_wait<0>();
+  __syncthreads();
   if (t == 0) {
     s_m[warp][g] = m_run[0]; s_l[warp][g] = l_run[0];
     s_m[warp][g + 8] = m_run[1]; s_l[warp][g + 8] = l_run[1];
@@ -238,8 +296,14 @@ static int launch_decode(const void* q, int ldq, const void* k_pool, const void*
                          int max_pages, const int* seq_slots, const int* kv_lens, void* out, int ldo,
                          float* part_o, float* part_ml, int B, int H, int G, float scale, int window,
                          int num_splits, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecSmem<HD>::BYTES);
+    RL_REQUIRE(e == cudaSuccess, "rl_attention_decode: cannot reserve %d bytes of shared memory: %s", DecSmem<HD>::BYTES, cudaGetErrorString(e));
+    configured = true;
+  }
   dim3 grid(num_splits, G, B);
-  rl_launch_pdl(attention_decode_kernel<HD>, grid, dim3(DEC_WARPS * 32), 0, stream,
+  rl_launch_pdl(attention_decode_kernel<HD>, grid, dim3(DEC_WARPS * 32), (size_t)DecSmem<HD>::BYTES, stream,
       (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table, max_pages,
       seq_slots, kv_lens, (__nv_bfloat16*)out, ldo, part_o, part_ml, H, G, scale * 1.4426950408889634f, window);
   RL_LAUNCH_CHECK("rl_attention_decode");

@@ -94,9 +94,10 @@ extern "C" int rl_rmsnorm(const float* x, const float* weight, void* out, int ou
 }
 
 // ------------------------------------------------------------------ SwiGLU
-// gate_up: [M, 2*I] with the gate in columns [0, I) and up in [I, 2I).
+// gate_up: [M, 2*I] with the gate in columns [0, I) and up in [I, 2I); or, interleaved,
+// gate_i in column 2i and up_i in column 2i + 1.
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int M, int I) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int M, int I, int interleaved) {
   rl_pdl_trigger();
   rl_pdl_wait();
   const size_t total = (size_t)M * I;
@@ -104,8 +105,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t m = idx / I;
     const int i = (int)(idx - m * I);
-    const float g = rl_ld(gu + m * 2 * I + i);
-    const float u = rl_ld(gu + m * 2 * I + I + i);
+    const float g = rl_ld(gu + m * 2 * I + (interleaved ? 2 * i : i));
+    const float u = rl_ld(gu + m * 2 * I + (interleaved ? 2 * i + 1 : I + i));
     rl_st(out + idx, g / (1.0f + expf(-g)) * u);
   }
 }
@@ -134,21 +135,43 @@ __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_
   }
 }
 
+// bf16, interleaved (gate_i, up_i) pairs: four pairs in, four results out a thread
+__global__ void swiglu_bf16_interleaved_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, size_t quads) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < quads; idx += (size_t)gridDim.x * blockDim.x) {
+    const uint4 v = *reinterpret_cast<const uint4*>(gu + idx * 8);
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+    float r[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 gu2 = __bfloat1622float2(p[k]);
+      r[k] = gu2.x / (1.0f + expf(-gu2.x)) * gu2.y;
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(r[0], r[1]), hi = __floats2bfloat162_rn(r[2], r[3]);
+    *reinterpret_cast<uint2*>(out + idx * 4) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+  }
+}
+
 extern "C" int rl_swiglu(const void* gate_up, void* out, int dtype, int num_tokens,
-                         int intermediate, cudaStream_t stream) {
+                         int intermediate, int interleaved, cudaStream_t stream) {
   RL_REQUIRE(num_tokens >= 0 && intermediate > 0, "rl_swiglu: bad sizes M=%d I=%d", num_tokens, intermediate);
   if (num_tokens == 0) return RL_OK;
   const size_t total = (size_t)num_tokens * intermediate;
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
-  if (dtype == RL_BF16 && intermediate % 8 == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+  if (dtype == RL_BF16 && interleaved && intermediate % 4 == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 7) == 0) {
+    const size_t quads = total / 4;      // rows are contiguous: [M, 2I] in, [M, I] out
+    const int qblocks = (int)((quads + threads - 1) / threads < 148 * 16 ? (quads + threads - 1) / threads : 148 * 16);
+    rl_launch_pdl(swiglu_bf16_interleaved_kernel, qblocks, threads, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, quads);
+  } else if (dtype == RL_BF16 && !interleaved && intermediate % 8 == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0) {
     const size_t vec = total / 8;
     const int vblocks = (int)((vec + threads - 1) / threads < 148 * 16 ? (vec + threads - 1) / threads : 148 * 16);
     rl_launch_pdl(swiglu_bf16x8_kernel, vblocks, threads, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, num_tokens, intermediate);
   } else if (dtype == RL_F32)
-    rl_launch_pdl(swiglu_kernel<float>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out, num_tokens, intermediate);
+    rl_launch_pdl(swiglu_kernel<float>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out, num_tokens, intermediate, interleaved);
   else if (dtype == RL_BF16)
-    rl_launch_pdl(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, num_tokens, intermediate);
+    rl_launch_pdl(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, num_tokens, intermediate, interleaved);
   else
     RL_REQUIRE(false, "rl_swiglu: unknown dtype %d", dtype);
   RL_LAUNCH_CHECK("rl_swiglu");

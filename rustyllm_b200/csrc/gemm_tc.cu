@@ -28,7 +28,9 @@
 
 #include "common.cuh"
 
-enum { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_OUT_ADD_F32 = 2 };
+enum { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_OUT_ADD_F32 = 2, TC_OUT_SWIGLU = 3 };
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
 static constexpr int BLOCK_N_OUT = 128;   // weight rows per CTA (MMA M)
 static constexpr int BLOCK_K = 64;        // bf16 elements per stage along K = one 128-byte swizzle row
@@ -267,16 +269,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         uint32_t r[16];
         tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 16), r);
         tmem_ld_wait();
-        if (n < N) {
+        if (out_mode == TC_OUT_SWIGLU) {
+          // weight rows are (gate_0, up_0, gate_1, up_1, ...): the even lane holds the gate, its
+          // odd neighbour the up value of the same output column n / 2
+          __nv_bfloat16* ob = (__nv_bfloat16*)out;
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
+            const float v = __uint_as_float(r[j]) + b;
+            const float up = __shfl_xor_sync(0xffffffffu, v, 1);
             const int m = m0 + c * 16 + j;
-            if (m < M) {
-              const float v = __uint_as_float(r[j]) + b;
-              const size_t o = (size_t)m * ldo + n;
-              if (out_mode == TC_OUT_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
-              else if (out_mode == TC_OUT_F32) ((float*)out)[o] = v;
-              else ((float*)out)[o] += v;
+            if ((lane & 1) == 0 && n + 1 < N && m < M) ob[(size_t)m * ldo + (n >> 1)] = __float2bfloat16_rn(silu_mul(v, up));
+          }
+        } else if (n < N) {
+          if (out_mode == TC_OUT_ADD_F32) {
+            // all sixteen loads of the residual first, then the stores: a load placed after
+            // a store to the same array would wait for it, one memory latency a column
+            float* of = (float*)out;
+            float prev[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int m = m0 + c * 16 + j;
+              prev[j] = (m < M) ? __ldcg(of + (size_t)m * ldo + n) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int m = m0 + c * 16 + j;
+              if (m < M) of[(size_t)m * ldo + n] = prev[j] + __uint_as_float(r[j]) + b;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int m = m0 + c * 16 + j;
+              if (m < M) {
+                const float v = __uint_as_float(r[j]) + b;
+                const size_t o = (size_t)m * ldo + n;
+                if (out_mode == TC_OUT_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
+                else ((float*)out)[o] = v;
+              }
             }
           }
         }
@@ -325,6 +354,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
         }
         v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+        if (out_mode == TC_OUT_SWIGLU) {      // v = (gate, up, gate, up) of output columns nn/2 and nn/2 + 1
+          __nv_bfloat16* ob = (__nv_bfloat16*)out + (size_t)(m0 + j) * ldo + (nn >> 1);
+          if (nn + 1 < N) ob[0] = __float2bfloat16_rn(silu_mul(v.x, v.y));
+          if (nn + 3 < N) ob[1] = __float2bfloat16_rn(silu_mul(v.z, v.w));
+          continue;
+        }
         const size_t o = (size_t)(m0 + j) * ldo + nn;
         if (vec_ok) {
           if (out_mode == TC_OUT_BF16) {
@@ -458,15 +493,17 @@ extern "C" int rl_gemm_tc_splits(int M, int N, int K) {
 }
 
 // A: [M, K] bf16, row stride lda; W: [N, K] bf16 contiguous; out: [M, N] with row stride
-// ldo, bf16 (out_mode 0) or float (1 store, 2 add).  err: device int, set non-zero if a
+// ldo, bf16 (out_mode 0) or float (1 store, 2 add); out_mode 3: W's rows are (gate_0, up_0,
+// gate_1, ...) and out is bf16 [M, N/2] = silu(gate) * up.  err: device int, set non-zero if a
 // bounded wait inside the kernel ran out.  force_splits: 0 = number of K parts chosen
 // from the shapes; 1, 2, 4 or 8 = as given (for measurements).
 extern "C" int rl_gemm_tc(const void* A, const void* W, const float* bias, void* out, int out_mode, int M, int N,
                           int K, int lda, int ldo, int* err, int force_splits, cudaStream_t stream) {
   RL_REQUIRE(rl_gemm_tc_supported(A, W, M, N, K, lda), "rl_gemm_tc: operands not supported (M=%d N=%d K=%d lda=%d; K and lda "
              "must be multiples of 8 and the bases 16-byte aligned)", M, N, K, lda);
-  RL_REQUIRE(out_mode >= 0 && out_mode <= 2, "rl_gemm_tc: unknown output mode %d", out_mode);
-  RL_REQUIRE(ldo >= N && err != nullptr, "rl_gemm_tc: bad output stride or null error word");
+  RL_REQUIRE(out_mode >= 0 && out_mode <= 3, "rl_gemm_tc: unknown output mode %d", out_mode);
+  RL_REQUIRE(out_mode != TC_OUT_SWIGLU || N % 2 == 0, "rl_gemm_tc: the SwiGLU epilogue needs an even number of weight rows, got %d", N);
+  RL_REQUIRE(ldo >= (out_mode == TC_OUT_SWIGLU ? N / 2 : N) && err != nullptr, "rl_gemm_tc: bad output stride or null error word");
   RL_REQUIRE(force_splits == 0 || force_splits == 1 || force_splits == 2 || force_splits == 4 || force_splits == 8,
              "rl_gemm_tc: the number of K parts must be 1, 2, 4 or 8, got %d", force_splits);
   const int bt = token_tile(M);

@@ -69,6 +69,57 @@ rope_kv_write_kernel(T* __restrict__ qkv, int ld, const int* __restrict__ positi
   }
 }
 
+// Fast path: bf16, half-split pairing over the whole head, head size a multiple of 16,
+// 16-byte aligned rows.  A thread rotates eight pairs (two 16-byte loads, two 16-byte
+// stores) or copies sixteen value elements.
+__global__ void __launch_bounds__(ROPE_THREADS)
+rope_kv_write_bf16_half_kernel(__nv_bfloat16* __restrict__ qkv, int ld, const int* __restrict__ positions,
+                               const int* __restrict__ slot_of_token, const int* __restrict__ page_table, int max_pages,
+                               const float* __restrict__ inv_freq, int H, int G, int hd,
+                               __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  const int m = blockIdx.x;
+  const int pos = positions[m];
+  __nv_bfloat16* row = qkv + (size_t)m * ld;
+  const int slot = slot_of_token[m];
+  const int page = page_table[(size_t)slot * max_pages + pos / RL_PAGE];
+  const size_t dst = ((size_t)page * G) * RL_PAGE * hd + (size_t)(pos % RL_PAGE) * hd;
+  const int half = hd / 2, per_head = half / 8;          // groups of eight pairs a head
+  const int slot0 = blockIdx.y * ROPE_HEADS_PER_CTA;
+  const int nslots = min(ROPE_HEADS_PER_CTA, H + 2 * G - slot0);
+  for (int idx = threadIdx.x; idx < nslots * per_head; idx += ROPE_THREADS) {
+    const int hs = slot0 + idx / per_head;
+    const int i = (idx % per_head) * 8;
+    __nv_bfloat16* x = row + (size_t)hs * hd;
+    const uint4 lo = *reinterpret_cast<const uint4*>(x + i);
+    const uint4 hi = *reinterpret_cast<const uint4*>(x + i + half);
+    if (hs >= H + G) {                                     // values: bit copy
+      __nv_bfloat16* d = v_pool + dst + (size_t)(hs - H - G) * RL_PAGE * hd;
+      *reinterpret_cast<uint4*>(d + i) = lo;
+      *reinterpret_cast<uint4*>(d + i + half) = hi;
+      continue;
+    }
+    const __nv_bfloat162* l2 = reinterpret_cast<const __nv_bfloat162*>(&lo);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&hi);
+    uint4 olo, ohi;
+    __nv_bfloat162* ol = reinterpret_cast<__nv_bfloat162*>(&olo);
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&ohi);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 a = __bfloat1622float2(l2[k]), b = __bfloat1622float2(h2[k]);
+      float s0, c0, s1, c1;
+      sincosf((float)pos * inv_freq[i + 2 * k], &s0, &c0);
+      sincosf((float)pos * inv_freq[i + 2 * k + 1], &s1, &c1);
+      ol[k] = __floats2bfloat162_rn(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
+      oh[k] = __floats2bfloat162_rn(a.x * s0 + b.x * c0, a.y * s1 + b.y * c1);
+    }
+    __nv_bfloat16* d = hs < H ? x : k_pool + dst + (size_t)(hs - H) * RL_PAGE * hd;
+    *reinterpret_cast<uint4*>(d + i) = olo;
+    *reinterpret_cast<uint4*>(d + i + half) = ohi;
+  }
+}
+
 // qkv: [M, ld] holding per token H query heads, then G key heads, then G value
 // heads, each of head_dim.  Queries are rotated in place; rotated keys and the
 // values go to the cache pools (same dtype as qkv).  With k_pool == nullptr nothing
@@ -89,7 +140,12 @@ extern "C" int rl_rope_kv_write(void* qkv, int dtype, int ld, const int* positio
   RL_REQUIRE(head_dim % 2 == 0, "rl_rope_kv_write: head_dim %d must be even", head_dim);
   const dim3 grid(num_tokens, (num_heads + 2 * num_kv_heads + ROPE_HEADS_PER_CTA - 1) / ROPE_HEADS_PER_CTA);
   const int threads = ROPE_THREADS;
-  if (dtype == RL_F32)
+  if (dtype == RL_BF16 && write_cache && !interleaved && rotary_dim == head_dim && head_dim % 16 == 0 && ld % 8 == 0 &&
+      ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_pool & 15) == 0 && ((uintptr_t)v_pool & 15) == 0)
+    rl_launch_pdl(rope_kv_write_bf16_half_kernel, grid, threads, 0, stream, (__nv_bfloat16*)qkv, ld, positions,
+                  slot_of_token, page_table, max_pages, inv_freq, num_heads, num_kv_heads, head_dim,
+                  (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool);
+  else if (dtype == RL_F32)
     rl_launch_pdl(rope_kv_write_kernel<float>, grid, threads, 0, stream,
         (float*)qkv, ld, positions, slot_of_token, page_table, max_pages, inv_freq, num_heads,
         num_kv_heads, head_dim, rotary_dim, interleaved, (float*)k_pool, (float*)v_pool, write_cache);

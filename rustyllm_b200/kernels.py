@@ -16,7 +16,7 @@ import torch
 from .csrc import build as _build
 
 F32, BF16 = 0, 1
-OUT_SAME, OUT_F32, OUT_ADD_F32 = 0, 1, 2
+OUT_SAME, OUT_F32, OUT_ADD_F32, OUT_SWIGLU = 0, 1, 2, 3
 
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
@@ -34,7 +34,7 @@ _c_int, _c_float, _c_void_p, _c_ll = ctypes.c_int, ctypes.c_float, ctypes.c_void
 _SIGNATURES = {
     "rl_embedding": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "rl_rmsnorm": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_float, _c_void_p],
-    "rl_swiglu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "rl_swiglu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "rl_convert": [_c_void_p, _c_int, _c_void_p, _c_int, _c_ll, _c_void_p],
     "rl_gemm_simt": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                      _c_int, _c_int, _c_void_p],
@@ -157,11 +157,14 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float
     _count()
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
+    """out = silu(gate) * up.  gate_up: [M, 2I] holding the gate in columns [0, I) and up
+    in [I, 2I), or, interleaved, gate_i in column 2i and up_i in column 2i + 1."""
     _need(gate_up, "gate_up"); _need(out, "out", gate_up.dtype)
     M, two_i = gate_up.shape
     assert two_i % 2 == 0 and out.shape == (M, two_i // 2)
-    _check(library().rl_swiglu(gate_up.data_ptr(), out.data_ptr(), _dt(out), M, two_i // 2, _stream()), "rl_swiglu")
+    _check(library().rl_swiglu(gate_up.data_ptr(), out.data_ptr(), _dt(out), M, two_i // 2, int(interleaved), _stream()),
+           "rl_swiglu")
     _count()
 
 
@@ -317,18 +320,23 @@ def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bo
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_mode: int,
             bias: Optional[torch.Tensor] = None, force_splits: int = 0) -> None:
     """out = a @ w.T (+ bias) on the tensor cores (tcgen05).  a: [M, K] bf16, w: [N, K] bf16;
-    out: bf16 (OUT_SAME) or float32 (OUT_F32 store, OUT_ADD_F32 add).  force_splits: 0 = the
+    out: bf16 (OUT_SAME) or float32 (OUT_F32 store, OUT_ADD_F32 add), or, with OUT_SWIGLU,
+    bf16 [M, N/2] = silu(even columns) * odd columns of the product.  force_splits: 0 = the
     kernel's own choice of K parts; 1, 2, 4, 8 = as given."""
     _need(a, "a", torch.bfloat16, contiguous=False); _need(w, "w", torch.bfloat16); _need(out, "out", contiguous=False)
     M, K = a.shape
     N = w.shape[0]
-    assert w.shape[1] == K and out.shape == (M, N) and out.stride(1) == 1
-    assert out.dtype == (torch.bfloat16 if out_mode == OUT_SAME else torch.float32)
+    assert w.shape[1] == K and out.stride(1) == 1
+    if out_mode == OUT_SWIGLU:      # rows of w are (gate_0, up_0, gate_1, ...): out = silu(gate) * up, [M, N/2]
+        assert N % 2 == 0 and out.shape == (M, N // 2) and out.dtype == torch.bfloat16
+    else:
+        assert out.shape == (M, N)
+        assert out.dtype == (torch.bfloat16 if out_mode == OUT_SAME else torch.float32)
     if bias is not None:
         _need(bias, "bias", torch.float32)
         assert bias.numel() == N
     lda = a.stride(0) if M > 1 else K
-    ldo = out.stride(0) if M > 1 else N
+    ldo = out.stride(0) if M > 1 else out.shape[1]
     _check(library().rl_gemm_tc(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), out_mode, M, N, K, lda, ldo,
                                 _tc_error_word(a.device).data_ptr(), int(force_splits), _stream()), "rl_gemm_tc")
     _count()

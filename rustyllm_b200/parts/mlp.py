@@ -2,8 +2,11 @@
 
 SimonWaldherr/RustyLLM src/model.rs:7321-7347 with the activation of src/simd.rs:2403-2408
 (``g / (1 + exp(-g)) * u``).  Wgate and Wup are one matrix [2I x d] so that one
-product serves both (the reference reads a fused ``ffn_up`` of 2I rows the same
-way round: gate rows first, src/model.rs:3933-3967).
+product serves both (the reference reads a fused ``ffn_up`` of 2I rows, gate rows
+first, src/model.rs:3933-3967).  In a bf16 run the rows are interleaved (gate_0, up_0,
+gate_1, up_1, ...): a gate and its up value then sit in neighbouring lanes of the
+tensor-core product's epilogue, which applies the activation and writes the
+[M x I] product directly - the [M x 2I] intermediate is never stored.
 """
 from __future__ import annotations
 
@@ -28,25 +31,33 @@ class GatedMLP(FeedForward):
         self.d, self.I = hidden_size, intermediate_size
         self.names = names
         self.bias = bias
+        self.interleaved = runtime.compute_dtype == torch.bfloat16
         self.wgu = self.wdown = self.bgu = self.bdown = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         d, I, n = self.d, self.I, self.names
+        layout = "interleave" if self.interleaved else "concat"
         specs = {
             "wgu": ParamSpec((ParamSource(n["gate"] + ".weight", (I, d)),
-                              ParamSource(n["up"] + ".weight", (I, d)))),
+                              ParamSource(n["up"] + ".weight", (I, d))), layout=layout),
             "wdown": ParamSpec((ParamSource(n["down"] + ".weight", (d, I)),)),
         }
         if self.bias:
             specs["bgu"] = ParamSpec((ParamSource(n["gate"] + ".bias", (I,)),
-                                      ParamSource(n["up"] + ".bias", (I,))), role="vector")
+                                      ParamSource(n["up"] + ".bias", (I,))), role="vector", layout=layout)
             specs["bdown"] = ParamSpec((ParamSource(n["down"] + ".bias", (d,)),), role="vector")
         return specs
 
     def forward(self, xn: torch.Tensor, residual: torch.Tensor, step) -> None:
         M = xn.shape[0]
-        gu = torch.empty((M, 2 * self.I), dtype=xn.dtype, device=xn.device)
-        linear(xn, self.wgu, gu, OUT_SAME, self.bgu)
         h = torch.empty((M, self.I), dtype=xn.dtype, device=xn.device)
-        K.swiglu(gu, h)
+        # Up to 64 tokens the product streams weights and its epilogue is idle time anyway: the
+        # activation runs there.  With more tokens the epilogue is on the critical path of a
+        # compute-bound kernel, and a separate pass over the intermediate is cheaper.
+        if M <= 64 and self.interleaved and self.wgu.dtype == torch.bfloat16 and K.gemm_tc_supported(xn, self.wgu, None):
+            K.gemm_tc(xn, self.wgu, h, K.OUT_SWIGLU, self.bgu)
+        else:
+            gu = torch.empty((M, 2 * self.I), dtype=xn.dtype, device=xn.device)
+            linear(xn, self.wgu, gu, OUT_SAME, self.bgu)
+            K.swiglu(gu, h, interleaved=self.interleaved)
         linear(h, self.wdown, residual, OUT_ADD_F32, self.bdown)

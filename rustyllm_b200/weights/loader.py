@@ -65,6 +65,18 @@ def runtime_dtype(role: str, file_dtype: torch.dtype, compute_dtype: torch.dtype
     return compute_dtype
 
 
+def place_source(dest: torch.Tensor, ps: ParamSpec, index: int, tensor: torch.Tensor) -> None:
+    """Copy source ``index`` of a parameter into its rows of ``dest`` (concatenated or interleaved)."""
+    if ps.layout == "interleave":
+        n = len(ps.sources)
+        if any(s.shape != ps.sources[0].shape for s in ps.sources):
+            raise ValueError("interleaved sources must have equal shapes")
+        dest[index::n].copy_(tensor)
+    else:
+        row = sum(s.shape[0] for s in ps.sources[:index])
+        dest[row:row + ps.sources[index].shape[0]].copy_(tensor)
+
+
 def check_checkpoint(params: Mapping[str, ParamSpec], entries: Mapping[str, object],
                      ignored: Iterable[str] = (), where: str = "") -> None:
     """Compare names, shapes and dtype classes; raise one WeightsError for all faults."""
@@ -115,14 +127,11 @@ def load_parameters(params: Mapping[str, ParamSpec], checkpoint: Checkpoint,
             else next(iter(file_dtypes))
         dt = runtime_dtype(ps.role, widest, compute_dtype)
         dest = torch.empty(ps.shape, dtype=dt, device=device)
-        row = 0
-        for s in ps.sources:
+        for i, s in enumerate(ps.sources):
             t = checkpoint.tensor(s.name)
-            n = s.shape[0] if s.shape else 1
             # bf16/f16 -> f32 widening is exact; f32 -> bf16 rounds to nearest even
             # (the reference's f32_to_bf16, src/simd.rs:88-96).
-            dest[row:row + n].copy_(t.to(dt) if t.dtype != dt else t, non_blocking=False)
-            row += n
+            place_source(dest, ps, i, t.to(dt) if t.dtype != dt else t)
         out[path] = dest
     for path, target in aliases:
         if target not in out:

@@ -91,7 +91,7 @@ def random_parameters(specs: Mapping[str, ParamSpec], seed: int, compute_dtype: 
     values are rounded to ``storage_dtype`` as a file would hold them, then kept in
     the run-time dtype of their role.  Generated on ``device`` (a CUDA generator
     draws other values than the CPU one for the same seed)."""
-    from .loader import runtime_dtype
+    from .loader import place_source, runtime_dtype
     out: Dict[str, torch.Tensor] = {}
     aliases = []
     for path, ps in specs.items():
@@ -100,11 +100,8 @@ def random_parameters(specs: Mapping[str, ParamSpec], seed: int, compute_dtype: 
             continue
         dt = runtime_dtype(ps.role, storage_dtype, compute_dtype)
         dest = torch.empty(ps.shape, dtype=dt, device=device)
-        row = 0
-        for src in ps.sources:
-            n = src.shape[0]
-            dest[row:row + n] = draw(src.name, src.shape, ps.init, seed, std, norm_noise, storage_dtype, device).to(dt)
-            row += n
+        for i, src in enumerate(ps.sources):
+            place_source(dest, ps, i, draw(src.name, src.shape, ps.init, seed, std, norm_noise, storage_dtype, device).to(dt))
         out[path] = dest
     for path, target in aliases:
         out[path] = out[target]

@@ -66,6 +66,29 @@ def test_swiglu(dtype, I):
     torch.testing.assert_close(out.double().cpu(), P.swiglu(g, u), **_tol(dtype))
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("I", [100, 50, 51])
+def test_swiglu_interleaved(dtype, I):
+    gu = _rand(7, 2 * I, dtype=dtype, seed=3, scale=2.0)
+    out = torch.empty(7, I, dtype=dtype, device=DEV)
+    K().swiglu(gu, out, interleaved=True)
+    torch.testing.assert_close(out.double().cpu(), P.swiglu(gu[:, 0::2].double().cpu(), gu[:, 1::2].double().cpu()), **_tol(dtype))
+
+
+@pytest.mark.parametrize("M,N,K_,parts", [(1, 256, 128, 0), (8, 28672, 512, 0), (8, 1024, 4096, 8), (40, 400, 72, 0), (64, 512, 1024, 4),
+                                          (300, 344, 264, 0), (17, 130, 104, 2)])
+def test_gemm_tc_swiglu_epilogue(M, N, K_, parts):
+    k = K()
+    a = _rand(M, K_, dtype=torch.bfloat16, seed=24)
+    w = _rand(N, K_, dtype=torch.bfloat16, seed=25, scale=0.1)
+    bias = _rand(N, seed=26, scale=0.1)
+    out = torch.full((M, N // 2), float("nan"), dtype=torch.bfloat16, device=DEV)
+    k.gemm_tc(a, w, out, k.OUT_SWIGLU, bias, force_splits=parts)
+    k.check_device_errors()
+    y = a.double().cpu() @ w.double().cpu().T + bias.double().cpu()
+    torch.testing.assert_close(out.double().cpu(), P.swiglu(y[:, 0::2], y[:, 1::2]), rtol=2e-2, atol=2e-2)
+
+
 def test_convert_rounds_to_nearest_even():
     # SimonWaldherr/RustyLLM src/simd.rs:88-96 (f32_to_bf16) and its tests at 9203-9225
     x = torch.tensor([1.0, 1.00390625, 1.005859375, 1.01171875, -2.5, 3.0e38, 1e-40], device=DEV)

@@ -71,10 +71,17 @@ def test_feed_forward_part(dtype, bias):
     specs = ff.param_specs()
     assert [s.name for s in specs["wgu"].sources] == ["g.weight", "u.weight"] and specs["wgu"].shape == (2 * I, d)
     assert ("bgu" in specs) == bias
+    # a bf16 run interleaves gate and up rows (the activation runs in the product's epilogue)
+    assert specs["wgu"].layout == ("interleave" if dtype == torch.bfloat16 else "concat")
     w = {"wgu": _rand(2 * I, d, seed=3, scale=0.2, dtype=dtype), "wdown": _rand(d, I, seed=4, scale=0.2, dtype=dtype)}
     if bias:
         w.update(bgu=_rand(2 * I, seed=5, scale=0.1), bdown=_rand(d, seed=6, scale=0.1))
-    ff.bind(w)
+    bound = dict(w)
+    if dtype == torch.bfloat16:      # what the loader would hand over: rows taken in turn
+        for name in ("wgu", "bgu"):
+            if name in w:
+                t = torch.empty_like(w[name]); t[0::2] = w[name][:I]; t[1::2] = w[name][I:]; bound[name] = t
+    ff.bind(bound)
     xn = _rand(M, d, seed=7, dtype=dtype)
     res = _rand(M, d, seed=8)
     out = res.clone()

@@ -111,8 +111,12 @@ def test_load_concatenates_ties_and_keeps_values(tmp_path):
     assert torch.equal(wqkv[:96], ck.tensor("model.layers.2.self_attn.q_proj.weight"))
     assert torch.equal(wqkv[96:128], ck.tensor("model.layers.2.self_attn.k_proj.weight"))
     assert torch.equal(wqkv[128:], ck.tensor("model.layers.2.self_attn.v_proj.weight"))
-    wgu = p["layers.0.feed_forward.wgu"]
-    assert torch.equal(wgu[256:], ck.tensor("model.layers.0.mlp.up_proj.weight"))
+    wgu = p["layers.0.feed_forward.wgu"]          # bf16 run: gate and up rows interleaved
+    assert torch.equal(wgu[1::2], ck.tensor("model.layers.0.mlp.up_proj.weight"))
+    assert torch.equal(wgu[0::2], ck.tensor("model.layers.0.mlp.gate_proj.weight"))
+    model32, _ = _model(cfg, torch.float32)       # 32-bit run: gate rows, then up rows
+    p32 = load_parameters(model32.param_specs(), ck, torch.float32, CPU, spec.ignored_tensors)
+    assert torch.equal(p32["layers.0.feed_forward.wgu"][256:], ck.tensor("model.layers.0.mlp.up_proj.weight").float())
     assert p["layers.0.mixer_norm.weight"].dtype == torch.float32
     model.bind(p)
     # a tied checkpoint that still carries a head copy is tolerated
