@@ -92,21 +92,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
   const int start = (window > 0 && len - window > 0) ? len - window : 0;
   const int* pages = page_table + (size_t)seq_slots[b] * max_pages;
 
-  // ---- Q fragments: rows = the m heads of this KV head, columns permuted like the keys' ----
-  uint32_t qf[KS][4];
-  {
-    const __nv_bfloat16* q0 = q + (size_t)b * ldq + (size_t)(gkv * m + g) * HD;
-    const __nv_bfloat16* q1 = q0 + (size_t)8 * HD;
-#pragma unroll
-    for (int c = 0; c < HD / 32; ++c) {
-      uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
-      if (g < m) lo = ldg16(q0 + 32 * c + 8 * t);
-      if (g + 8 < m) hi = ldg16(q1 + 32 * c + 8 * t);
-      qf[2 * c][0] = lo.x; qf[2 * c][1] = hi.x; qf[2 * c][2] = lo.y; qf[2 * c][3] = hi.y;
-      qf[2 * c + 1][0] = lo.z; qf[2 * c + 1][1] = hi.z; qf[2 * c + 1][2] = lo.w; qf[2 * c + 1][3] = hi.w;
-    }
-  }
-
   float acc[NT][4];
 #pragma unroll
   for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
@@ -155,6 +140,22 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
       dec_commit();
     }
   }
+  // ---- Q fragments (after the first key/value copies are on their way): rows = the m heads
+  // of this KV head, columns permuted like the keys' ----
+  uint32_t qf[KS][4];
+  {
+    const __nv_bfloat16* q0 = q + (size_t)b * ldq + (size_t)(gkv * m + g) * HD;
+    const __nv_bfloat16* q1 = q0 + (size_t)8 * HD;
+#pragma unroll
+    for (int c = 0; c < HD / 32; ++c) {
+      uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
+      if (g < m) lo = ldg16(q0 + 32 * c + 8 * t);
+      if (g + 8 < m) hi = ldg16(q1 + 32 * c + 8 * t);
+      qf[2 * c][0] = lo.x; qf[2 * c][1] = hi.x; qf[2 * c][2] = lo.y; qf[2 * c][3] = hi.y;
+      qf[2 * c + 1][0] = lo.z; qf[2 * c + 1][1] = hi.z; qf[2 * c + 1][2] = lo.w; qf[2 * c + 1][3] = hi.w;
+    }
+  }
+
   int it = 0;
   for (int blk = blk_lo + warp; blk < blk_hi; blk += DEC_WARPS, ++it) {
     const int key0 = blk * DEC_BLOCK;

@@ -21,6 +21,7 @@ import torch
 from ..cache.sequence_cache import SequenceCache
 from ..config.llama import read_config_json
 from ..config.registry import resolve_architecture
+from .. import kernels
 from ..kernels import PAGE_SIZE
 from ..models.decoder import DecoderModel
 from ..parts import Runtime
@@ -221,6 +222,10 @@ class Runner:
                                     on_token=cb, sync=lambda: torch.cuda.synchronize(dev))
                 for i, r in zip(batch, rs):
                     results[i] = r
+            kernels.check_device_errors()      # a kernel that gave up waiting must not pass silently
+            if int(self.model.embedding.bad_token.item()) != 0:
+                self.model.embedding.bad_token.zero_()
+                raise RuntimeError("a token id outside the vocabulary reached the device")
         return results[0] if single else results
 
     def generate_stream(self, prompt: Sequence[int], options: Optional[GenerationOptions],

@@ -73,6 +73,8 @@ def main(argv=None) -> int:
                 engine.free_slot(slot_of.pop(rid))
         sys.stdout.write(f"done {step}\n")
         sys.stdout.flush()
+    from .. import kernels
+    kernels.check_device_errors()
     if int(runner.model.embedding.bad_token.item()) != 0:
         print("trace_run: a token id outside the vocabulary reached the device", file=sys.stderr)
         return 1
