@@ -223,8 +223,9 @@ class Runner:
                 for i, r in zip(batch, rs):
                     results[i] = r
             kernels.check_device_errors()      # a kernel that gave up waiting must not pass silently
-            if int(self.model.embedding.bad_token.item()) != 0:
-                self.model.embedding.bad_token.zero_()
+            bad = getattr(self.model.embedding, "bad_token", None)
+            if bad is not None and int(bad.item()) != 0:
+                bad.zero_()
                 raise RuntimeError("a token id outside the vocabulary reached the device")
         return results[0] if single else results
 
