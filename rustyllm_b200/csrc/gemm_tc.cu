@@ -153,6 +153,64 @@ struct TcConfig {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
+// The epilogue of one finished tile: the accumulator (128 weight rows x BT tokens, float,
+// in tensor memory at `tmem_acc`) goes to the output in the asked form.  Called by the four
+// epilogue warps; `quarter` = warp index % 4 = the 32 lanes of tensor memory the warp may read.
+template <int BT>
+__device__ __forceinline__ void tile_epilogue(uint32_t tmem_acc, int quarter, int lane, int n0, int m0, int M, int N,
+                                              int ldo, const float* __restrict__ bias, void* __restrict__ out,
+                                              int out_mode) {
+  const int n = n0 + quarter * 32 + lane;          // output feature of this thread
+  const float b = (bias != nullptr && n < N) ? bias[n] : 0.f;
+#pragma unroll 1
+  for (int c = 0; c < BT / 16; ++c) {
+    if (m0 + c * 16 >= M) break;
+    uint32_t r[16];
+    tmem_ld16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 16), r);
+    tmem_ld_wait();
+    if (out_mode == TC_OUT_SWIGLU) {
+      // weight rows are (gate_0, up_0, gate_1, up_1, ...): the even lane holds the gate, its
+      // odd neighbour the up value of the same output column n / 2
+      __nv_bfloat16* ob = (__nv_bfloat16*)out;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float v = __uint_as_float(r[j]) + b;
+        const float up = __shfl_xor_sync(0xffffffffu, v, 1);
+        const int m = m0 + c * 16 + j;
+        if ((lane & 1) == 0 && n + 1 < N && m < M) ob[(size_t)m * ldo + (n >> 1)] = __float2bfloat16_rn(silu_mul(v, up));
+      }
+    } else if (n < N) {
+      if (out_mode == TC_OUT_ADD_F32) {
+        // all sixteen loads of the residual first, then the stores: a load placed after
+        // a store to the same array would wait for it, one memory latency a column
+        float* of = (float*)out;
+        float prev[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = m0 + c * 16 + j;
+          prev[j] = (m < M) ? __ldcg(of + (size_t)m * ldo + n) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = m0 + c * 16 + j;
+          if (m < M) of[(size_t)m * ldo + n] = prev[j] + __uint_as_float(r[j]) + b;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = m0 + c * 16 + j;
+          if (m < M) {
+            const float v = __uint_as_float(r[j]) + b;
+            const size_t o = (size_t)m * ldo + n;
+            if (out_mode == TC_OUT_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
+            else ((float*)out)[o] = v;
+          }
+        }
+      }
+    }
+  }
+}
+
 // BT: tokens per CTA (MMA N).  Grid: (parts * ceil(N_out / 128), ceil(M_tokens / BT)) in
 // clusters of `parts` CTAs along x; the CTA's rank in its cluster is its part of K.
 template <int BT>
@@ -261,55 +319,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     tc_fence_after();
     const int quarter = warp & 3;                    // lanes this warp may read
     const int row = quarter * 32 + lane;             // accumulator row = weight row of the tile
-    const int n = n0 + row;                          // output feature of this thread
-    const float b = (bias != nullptr && n < N) ? bias[n] : 0.f;
     if (ok && num_splits == 1) {
-#pragma unroll 1
-      for (int c = 0; c < BT / 16; ++c) {
-        uint32_t r[16];
-        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 16), r);
-        tmem_ld_wait();
-        if (out_mode == TC_OUT_SWIGLU) {
-          // weight rows are (gate_0, up_0, gate_1, up_1, ...): the even lane holds the gate, its
-          // odd neighbour the up value of the same output column n / 2
-          __nv_bfloat16* ob = (__nv_bfloat16*)out;
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float v = __uint_as_float(r[j]) + b;
-            const float up = __shfl_xor_sync(0xffffffffu, v, 1);
-            const int m = m0 + c * 16 + j;
-            if ((lane & 1) == 0 && n + 1 < N && m < M) ob[(size_t)m * ldo + (n >> 1)] = __float2bfloat16_rn(silu_mul(v, up));
-          }
-        } else if (n < N) {
-          if (out_mode == TC_OUT_ADD_F32) {
-            // all sixteen loads of the residual first, then the stores: a load placed after
-            // a store to the same array would wait for it, one memory latency a column
-            float* of = (float*)out;
-            float prev[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int m = m0 + c * 16 + j;
-              prev[j] = (m < M) ? __ldcg(of + (size_t)m * ldo + n) : 0.f;
-            }
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int m = m0 + c * 16 + j;
-              if (m < M) of[(size_t)m * ldo + n] = prev[j] + __uint_as_float(r[j]) + b;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int m = m0 + c * 16 + j;
-              if (m < M) {
-                const float v = __uint_as_float(r[j]) + b;
-                const size_t o = (size_t)m * ldo + n;
-                if (out_mode == TC_OUT_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
-                else ((float*)out)[o] = v;
-              }
-            }
-          }
-        }
-      }
+      tile_epilogue<BT>(tmem_base, quarter, lane, n0, m0, M, N, ldo, bias, out, out_mode);
     } else if (num_splits > 1 && ok) {
       // this part's partial tile -> own shared memory (the ring is free: every MMA has
       // completed), as [token column][weight row] floats
@@ -390,6 +401,169 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+// ------------------------------------------------------------------ persistent variant (128 or 256 tokens a tile)
+// One CTA an SM walks over the tiles (tile index = blockIdx.x, + gridDim.x, ...; token tiles of
+// the same weight rows are neighbours, so CTAs that run together share weight tiles in L2).
+// Tensor memory holds two accumulators: while the epilogue warps drain one, the MMA thread
+// fills the other, and the TMA producer runs ahead through the ring across tile borders.
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+template <int BT>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+                          const float* __restrict__ bias, void* __restrict__ out, int out_mode, int M, int N, int K,
+                          int ldo, int* __restrict__ err, int tiles_m, int num_tiles) {
+  using Cfg = TcConfig<BT>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* tiles = smem;
+  uint64_t* bars = (uint64_t*)(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full_bar = bars;                         // [STAGES]
+  uint64_t* empty_bar = bars + Cfg::STAGES;          // [STAGES]
+  uint64_t* acc_full = bars + 2 * Cfg::STAGES;       // [2]
+  uint64_t* acc_empty = bars + 2 * Cfg::STAGES + 2;  // [2]
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * Cfg::STAGES + 4);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_kb = (K + BLOCK_K - 1) / BLOCK_K;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&acc_full[i]), 1);
+      mbar_init(smem_u32(&acc_empty[i]), 4);       // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 2 * BT);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  rl_pdl_trigger();
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- producer ----------------
+      int it = 0;                                   // k-blocks issued so far, over all tiles
+      bool waited = false, ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int n0 = (tile / tiles_m) * BLOCK_N_OUT, m0 = (tile % tiles_m) * BT;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % Cfg::STAGES;
+          const uint32_t phase = (it / Cfg::STAGES) & 1;
+          if (it >= Cfg::STAGES && !mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1, abort_flag)) {
+            if (!*abort_flag) { *abort_flag = 1; atomicExch(err, 1); }
+            ok = false;
+            break;
+          }
+          const uint32_t fb = smem_u32(&full_bar[s]);
+          mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+          uint8_t* st = tiles + (size_t)s * Cfg::STAGE_BYTES;
+          tma_load_2d(smem_u32(st), &map_w, fb, kb * BLOCK_K, n0);
+          // weights may be requested before the preceding kernels have finished, activations not
+          if (!waited) { rl_pdl_wait(); waited = true; }
+          tma_load_2d(smem_u32(st + BLOCK_N_OUT * BLOCK_K * 2), &map_a, fb, kb * BLOCK_K, m0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer ----------------
+      constexpr uint32_t idesc = make_idesc(BLOCK_N_OUT, BT);
+      int it = 0, t = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+        const int buf = t & 1;
+        const uint32_t acc_phase = (t >> 1) & 1;
+        if (t >= 2 && !mbar_wait(smem_u32(&acc_empty[buf]), acc_phase ^ 1, abort_flag)) {   // epilogue done with this accumulator
+          if (!*abort_flag) { *abort_flag = 1; atomicExch(err, 4); }
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * BT);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % Cfg::STAGES;
+          const uint32_t phase = (it / Cfg::STAGES) & 1;
+          if (!mbar_wait(smem_u32(&full_bar[s]), phase, abort_flag)) {
+            if (!*abort_flag) { *abort_flag = 1; atomicExch(err, 2); }
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          uint8_t* st = tiles + (size_t)s * Cfg::STAGE_BYTES;
+          const uint64_t da = make_smem_desc(smem_u32(st));
+          const uint64_t db = make_smem_desc(smem_u32(st + BLOCK_N_OUT * BLOCK_K * 2));
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+            umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(smem_u32(&empty_bar[s]));
+        }
+        if (ok) umma_commit(smem_u32(&acc_full[buf]));
+      }
+    }
+  } else {
+    // ---------------- epilogue warps ----------------
+    rl_pdl_wait();
+    const int quarter = warp & 3;
+    int t = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
+      const int buf = t & 1;
+      const uint32_t acc_phase = (t >> 1) & 1;
+      if (!mbar_wait(smem_u32(&acc_full[buf]), acc_phase, abort_flag)) {
+        if (!*abort_flag) { *abort_flag = 1; atomicExch(err, 3); }
+        break;
+      }
+      tc_fence_after();
+      const int n0 = (tile / tiles_m) * BLOCK_N_OUT, m0 = (tile % tiles_m) * BT;
+      tile_epilogue<BT>(tmem_base + (uint32_t)(buf * BT), quarter, lane, n0, m0, M, N, ldo, bias, out, out_mode);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));    // this warp has read the accumulator
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 2 * BT);
+}
+
+template <int BT>
+static int launch_tc_persistent(const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, void* out, int out_mode,
+                                int M, int N, int K, int ldo, int* err, cudaStream_t stream) {
+  using Cfg = TcConfig<BT>;
+  static bool configured = false;
+  static int num_sms = 0;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    RL_REQUIRE(e == cudaSuccess, "rl_gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
+    int dev = 0;
+    cudaGetDevice(&dev);
+    e = cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    RL_REQUIRE(e == cudaSuccess && num_sms > 0, "rl_gemm_tc: cannot read the number of SMs");
+    configured = true;
+  }
+  const int tiles_m = (M + BT - 1) / BT, tiles_n = (N + BLOCK_N_OUT - 1) / BLOCK_N_OUT;
+  const int num_tiles = tiles_m * tiles_n;
+  const int grid = num_tiles < num_sms ? num_tiles : num_sms;
+  cudaError_t e = rl_launch_pdl(gemm_tc_persistent_kernel<BT>, dim3(grid), dim3(TC_THREADS), (size_t)Cfg::SMEM_BYTES, stream,
+                                mw, ma, bias, out, out_mode, M, N, K, ldo, err, tiles_m, num_tiles);
+  if (e != cudaSuccess) {
+    rl_set_error("rl_gemm_tc: launch of the persistent kernel failed: %s", cudaGetErrorString(e));
+    return RL_ERR_CUDA;
+  }
+  return RL_OK;
 }
 
 // ------------------------------------------------------------------ host side
@@ -521,7 +695,7 @@ extern "C" int rl_gemm_tc(const void* A, const void* W, const float* bias, void*
     case 16: return launch_tc<16>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, stream);
     case 32: return launch_tc<32>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, stream);
     case 64: return launch_tc<64>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, stream);
-    case 128: return launch_tc<128>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, stream);
-    default: return launch_tc<256>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, stream);
+    case 128: return launch_tc_persistent<128>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, stream);
+    default: return launch_tc_persistent<256>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, stream);
   }
 }
