@@ -30,7 +30,9 @@
 
 enum { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_OUT_ADD_F32 = 2, TC_OUT_SWIGLU = 3 };
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+// silu(g) * u for a result that is stored in bf16: the fast exponential and division are
+// accurate to a few units in the last place of a float, far below bf16's rounding step
+__device__ __forceinline__ float silu_mul(float g, float u) { return g * __fdividef(1.0f, 1.0f + __expf(-g)) * u; }
 
 static constexpr int BLOCK_N_OUT = 128;   // weight rows per CTA (MMA M)
 static constexpr int BLOCK_K = 64;        // bf16 elements per stage along K = one 128-byte swizzle row
@@ -171,13 +173,17 @@ __device__ __forceinline__ void tile_epilogue(uint32_t tmem_acc, int quarter, in
     if (out_mode == TC_OUT_SWIGLU) {
       // weight rows are (gate_0, up_0, gate_1, up_1, ...): the even lane holds the gate, its
       // odd neighbour the up value of the same output column n / 2
+      // ... the even lane finishes columns 0-7 of the chunk, the odd lane columns 8-15: each
+      // sends the other the half it does not need (one shuffle a column pair).
       __nv_bfloat16* ob = (__nv_bfloat16*)out;
+      const bool even = (lane & 1) == 0;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float v = __uint_as_float(r[j]) + b;
-        const float up = __shfl_xor_sync(0xffffffffu, v, 1);
-        const int m = m0 + c * 16 + j;
-        if ((lane & 1) == 0 && n + 1 < N && m < M) ob[(size_t)m * ldo + (n >> 1)] = __float2bfloat16_rn(silu_mul(v, up));
+      for (int j = 0; j < 8; ++j) {
+        const float lo = __uint_as_float(r[j]) + b, hi = __uint_as_float(r[j + 8]) + b;
+        const float got = __shfl_xor_sync(0xffffffffu, even ? hi : lo, 1);
+        const float gate = even ? lo : got, up = even ? got : hi;
+        const int m = m0 + c * 16 + (even ? j : j + 8);
+        if ((n | 1) < N && m < M) ob[(size_t)m * ldo + (n >> 1)] = __float2bfloat16_rn(silu_mul(gate, up));
       }
     } else if (n < N) {
       if (out_mode == TC_OUT_ADD_F32) {

@@ -51,10 +51,10 @@ class GatedMLP(FeedForward):
     def forward(self, xn: torch.Tensor, residual: torch.Tensor, step) -> None:
         M = xn.shape[0]
         h = torch.empty((M, self.I), dtype=xn.dtype, device=xn.device)
-        # Up to 64 tokens the product streams weights and its epilogue is idle time anyway: the
-        # activation runs there.  With more tokens the epilogue is on the critical path of a
-        # compute-bound kernel, and a separate pass over the intermediate is cheaper.
-        if M <= 64 and self.interleaved and self.wgu.dtype == torch.bfloat16 and K.gemm_tc_supported(xn, self.wgu, None):
+        # The activation runs in the product's epilogue: with few tokens the kernel streams
+        # weights and the epilogue is idle time anyway; with many, the persistent kernel drains
+        # one accumulator while the tensor cores fill the other.
+        if self.interleaved and self.wgu.dtype == torch.bfloat16 and K.gemm_tc_supported(xn, self.wgu, None):
             K.gemm_tc(xn, self.wgu, h, K.OUT_SWIGLU, self.bgu)
         else:
             gu = torch.empty((M, 2 * self.I), dtype=xn.dtype, device=xn.device)
