@@ -80,10 +80,15 @@ def attention_prefill(a) -> None:
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
     q = torch.randn(T, (H + 2 * G) * hd, device=DEV).to(BF)
     out = torch.empty(T, H * hd, device=DEV, dtype=BF)
-    us = _time(lambda i: K.attention_prefill(q, pools[i % 2][0], pools[i % 2][1], pt, i32([0, T]), i32([0]), i32([T]), [T], out,
-                                             H, G, hd, 1 / math.sqrt(hd)), a.warmup, a.reps)
+    tc = not a.mma and K.attention_prefill_tc_supported(BF, H, G, hd)
+    fn = K.attention_prefill_tc if tc else K.attention_prefill
+    cu, sl, kl = i32([0, T]), i32([0]), i32([T])
+    us = _time(lambda i: fn(q, pools[i % 2][0], pools[i % 2][1], pt, cu, sl, kl, [T], out, H, G, hd, 1 / math.sqrt(hd)),
+               a.warmup, a.reps)
+    K.check_device_errors()
     flops = 2 * 2 * H * hd * (T * (T + 1) / 2)
-    print(f"attention_prefill T={T} H={H} G={G} hd={hd}: {us:.2f} us, {flops / us / 1e6:.1f} TFLOP/s (causal half counted)")
+    print(f"attention_prefill ({'tcgen05' if tc else 'mma.sync'}) T={T} H={H} G={G} hd={hd}: {us:.2f} us, "
+          f"{flops / us / 1e6:.1f} TFLOP/s (causal half counted)")
 
 
 def small(a) -> None:
@@ -117,6 +122,7 @@ def main(argv=None) -> int:
     p.add_argument("--heads", type=int, default=32); p.add_argument("--kv-heads", type=int, default=8)
     p.add_argument("--head-dim", type=int, default=128); p.add_argument("--hidden", type=int, default=4096)
     p.add_argument("--intermediate", type=int, default=14336)
+    p.add_argument("--mma", action="store_true", help="attention-prefill: the mma.sync kernel also where tcgen05 applies")
     p.add_argument("--warmup", type=int, default=3); p.add_argument("--reps", type=int, default=20)
     a = p.parse_args(argv)
     {"gemm": gemm, "attention-decode": attention_decode, "attention-prefill": attention_prefill}.get(a.kernel, small)(a)

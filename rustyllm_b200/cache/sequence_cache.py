@@ -52,7 +52,10 @@ class KVGroup:
         self.layers = layers
         self.num_pages = num_pages
         self.pages = FreeList(num_pages, "page")
-        self.pool = torch.empty((layers, 2, num_pages, need.num_kv_heads, PAGE_SIZE, need.head_dim),
+        # zero-filled once: rows of a page beyond a sequence's length are never selected, but a
+        # tensor-core attention kernel multiplies them by a probability of exactly 0, so they
+        # must be finite (what earlier sequences left there is)
+        self.pool = torch.zeros((layers, 2, num_pages, need.num_kv_heads, PAGE_SIZE, need.head_dim),
                                 dtype=dtype, device=device)
         self.page_table_host = torch.zeros((max_slots, max_pages_per_slot), dtype=torch.int32)
         self.page_table = self.page_table_host if device.type == "cpu" else \

@@ -54,6 +54,10 @@ _SIGNATURES = {
     "rl_attention_prefill": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
                              _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p],
     "rl_attention_prefill_supported": [_c_int, _c_int, _c_int],
+    "rl_attention_prefill_tc": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                                _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float,
+                                _c_int, _c_void_p, _c_void_p],
+    "rl_attention_prefill_tc_supported": [_c_int, _c_int, _c_int],
     "rl_gemm_tc_supported": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int],
     "rl_gemm_tc": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                    _c_void_p, _c_int, _c_void_p],
@@ -302,8 +306,9 @@ def check_device_errors() -> None:
         code = int(t.item())
         if code != 0:
             t.zero_()
-            raise KernelError(f"a tensor-core GEMM on cuda:{key} gave up waiting (code {code}: "
-                              "1 = for a free stage, 2 = for a TMA load, 3 = for the accumulator)")
+            raise KernelError(f"a tensor-core kernel on cuda:{key} gave up waiting (code {code}; matrix product: "
+                              "1 = for a free stage, 2 = for a TMA load, 3 = for the accumulator, 4 = for a free "
+                              "accumulator; prefill attention: 11 = producer, 12/13 = MMA issuer, 14 = softmax)")
 
 
 def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
@@ -415,6 +420,36 @@ def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     _count()
 
 
+PREFILL_TC_QTILE = 128
+
+
+def attention_prefill_tc_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    return dtype == torch.bfloat16 and bool(library().rl_attention_prefill_tc_supported(num_heads, num_kv_heads, head_dim))
+
+
+def attention_prefill_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
+                         cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, kv_lens: torch.Tensor, q_lens,
+                         out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                         window: int = 0) -> None:
+    """The same as ``attention_prefill`` on tcgen05 tensor cores (head size 128).  The cache pools
+    must hold finite values everywhere (the cache zero-fills them when it allocates them)."""
+    _need(q, "q", torch.bfloat16, contiguous=False); _need(k_pool, "k_pool", torch.bfloat16)
+    _need(v_pool, "v_pool", torch.bfloat16); _need(out, "out", torch.bfloat16)
+    _need(page_table, "page_table", torch.int32); _need(cu_seqlens, "cu_seqlens", torch.int32)
+    _need(seq_slots, "seq_slots", torch.int32); _need(kv_lens, "kv_lens", torch.int32)
+    B = len(q_lens)
+    assert cu_seqlens.numel() == B + 1 and seq_slots.numel() == B and kv_lens.numel() == B
+    assert q.shape[0] == sum(q_lens) and q.stride(1) == 1
+    tiles = sum(-(-n // PREFILL_TC_QTILE) for n in q_lens)
+    ldq = q.stride(0) if q.shape[0] > 1 else max(q.stride(0), num_heads * head_dim)
+    _check(library().rl_attention_prefill_tc(
+        q.data_ptr(), ldq, k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0], page_table.data_ptr(),
+        page_table.shape[1], cu_seqlens.data_ptr(), seq_slots.data_ptr(), kv_lens.data_ptr(), B, tiles, q.shape[0],
+        out.data_ptr(), out.stride(0), num_heads, num_kv_heads, head_dim, float(scale), int(window),
+        _tc_error_word(q.device).data_ptr(), _stream()), "rl_attention_prefill_tc")
+    _count()
+
+
 # ----------------------------------------------------------------------------- attention dispatch
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
               step, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
@@ -425,6 +460,11 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
     if step.is_decode and attention_decode_supported(q.dtype, num_heads, num_kv_heads, head_dim):
         attention_decode(q, k_pool, v_pool, page_table, step.seq_slots, step.kv_lens, out,
                          num_heads, num_kv_heads, head_dim, scale, window)
+        return
+    if not step.is_decode and attention_prefill_tc_supported(q.dtype, num_heads, num_kv_heads, head_dim) \
+            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0:
+        attention_prefill_tc(q, k_pool, v_pool, page_table, step.cu_seqlens, step.seq_slots, step.kv_lens,
+                             step.q_lens, out, num_heads, num_kv_heads, head_dim, scale, window)
         return
     if not step.is_decode and attention_prefill_supported(q.dtype, num_heads, num_kv_heads, head_dim):
         attention_prefill(q, k_pool, v_pool, page_table, step.cu_seqlens, step.seq_slots, step.kv_lens,

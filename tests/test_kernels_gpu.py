@@ -486,6 +486,60 @@ def test_attention_prefill_finds_one_far_key(far):
     assert (ref[far + 1:] - want).abs().max() < 1e-3
 
 
+# ----------------------------------------------------------------------------- prefill attention (tcgen05)
+@pytest.mark.parametrize("H,G", [(32, 8), (4, 4), (3, 1)])
+@pytest.mark.parametrize("lens_q,lens_kv", [([1, 5, 64, 65, 200], [1, 5, 64, 65, 200]),
+                                            ([130, 1, 33, 64], [130, 300, 97, 128]),
+                                            ([129], [129]), ([128, 256], [128, 256]), ([700], [700]), ([40], [1000])])
+def test_attention_prefill_tc_matches_plain(H, G, lens_q, lens_kv):
+    k = K()
+    hd = 128
+    assert k.attention_prefill_tc_supported(torch.bfloat16, H, G, hd)
+    case = _attention_case(torch.bfloat16, H, G, hd, lens_q, lens_kv, seed=H + len(lens_q) + lens_kv[0])
+    q, kp, vp, pt, cu, slots, kv_lens, ref = _prefill_inputs(case, lens_q, lens_kv)
+    out = torch.full((q.shape[0], H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    k.attention_prefill_tc(q, kp, vp, pt, cu, slots, kv_lens, lens_q, out, H, G, hd, 1.0 / math.sqrt(hd))
+    k.check_device_errors()
+    torch.testing.assert_close(out.double().cpu(), ref, **_tol(torch.bfloat16))
+
+
+def test_attention_prefill_tc_window_and_strided_queries():
+    k = K()
+    H, G, hd, W = 4, 2, 128, 200
+    lens_q, lens_kv = [40, 350, 3], [40, 500, 300]
+    case = _attention_case(torch.bfloat16, H, G, hd, lens_q, lens_kv, window=W, seed=4)
+    q, kp, vp, pt, cu, slots, kv_lens, ref = _prefill_inputs(case, lens_q, lens_kv)
+    wide = torch.zeros(q.shape[0], (H + 2 * G) * hd, dtype=torch.bfloat16, device=DEV)
+    wide[:, :H * hd] = q
+    out = torch.empty(q.shape[0], H * hd, dtype=torch.bfloat16, device=DEV)
+    k.attention_prefill_tc(wide[:, :H * hd], kp, vp, pt, cu, slots, kv_lens, lens_q, out, H, G, hd, 1.0 / math.sqrt(hd), W)
+    k.check_device_errors()
+    torch.testing.assert_close(out.double().cpu(), ref, **_tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("far", [0, 63, 64, 127, 128, 300])
+def test_attention_prefill_tc_finds_one_far_key_and_rescales(far):
+    """Every query from position `far` on must return the value of key `far`: its score is far
+    above the running maximum of the tiles before it, so the lazily kept maximum has to move
+    and the accumulator has to be rescaled."""
+    H, G, hd, n = 4, 2, 128, 451
+
+    def craft(b, qb, kb, vb):
+        direction = torch.ones(hd) / math.sqrt(hd)
+        qb[:] = (direction * 14.0).to(qb.dtype)
+        kb[:] = (kb.float() * 0.05).to(kb.dtype)
+        kb[far] = (direction * 14.0).to(kb.dtype)
+    case = _attention_case(torch.bfloat16, H, G, hd, [n], [n], seed=6, craft=craft)
+    q, kp, vp, pt, cu, slots, kv_lens, ref = _prefill_inputs(case, [n], [n])
+    out = torch.empty(n, H * hd, dtype=torch.bfloat16, device=DEV)
+    K().attention_prefill_tc(q, kp, vp, pt, cu, slots, kv_lens, [n], out, H, G, hd, 1.0 / math.sqrt(hd))
+    K().check_device_errors()
+    torch.testing.assert_close(out.double().cpu(), ref, **_tol(torch.bfloat16))
+    page = int(pt[1, far // PAGE]); v_far = vp[page, :, far % PAGE].double().cpu()
+    want = v_far.repeat_interleave(H // G, dim=0).reshape(1, H * hd)
+    assert (ref[far + 1:] - want).abs().max() < 1e-3
+
+
 # ----------------------------------------------------------------------------- sampling
 def test_argmax_first_maximum_wins_and_non_finite_is_skipped():
     k = K()
