@@ -1,14 +1,15 @@
 """Times one kernel of the library alone, at a chosen shape, on random data.
 
     python -m rustyllm_b200.bench_kernels gemm --m 8 --n 28672 --k 4096 [--mode same|f32|add] [--parts 0]
-    python -m rustyllm_b200.bench_kernels attention-decode --batch 8 --context 800 [--splits 0]
+    python -m rustyllm_b200.bench_kernels attention-decode --batch 8 --context 800 [--splits 0] [--contexts 1761,1350,159]
     python -m rustyllm_b200.bench_kernels attention-prefill --tokens 2048
     python -m rustyllm_b200.bench_kernels rmsnorm | swiglu | rope --m 8
 
 Each run launches the kernel ``--reps`` times after ``--warmup`` launches, rotating over
 several copies of the big operand so that the 126 MB L2 cannot serve it, times the
 launches with CUDA events and prints one line with microseconds a launch and the
-achieved bandwidth or arithmetic rate.  It is the program the ncu captures under
+achieved bandwidth or arithmetic rate (``--graph``: the timed launches run from one
+CUDA graph, for kernels shorter than a launch takes the host).  It is the program the ncu captures under
 ``profiles/`` were taken from (few launches, small operands).
 """
 from __future__ import annotations
@@ -25,11 +26,28 @@ DEV = torch.device("cuda:0")
 BF = torch.bfloat16
 
 
+GRAPH = False      # --graph: the timed launches are captured in one CUDA graph (no host time between them)
+
+
 def _time(fn, warmup: int, reps: int) -> float:
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if GRAPH:
+        stream = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(graph, stream=stream):
+                for i in range(reps):
+                    fn(warmup + i)
+            graph.replay()
+            stream.synchronize()
+            e0.record(stream)
+            graph.replay()
+            e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps
     e0.record()
     for i in range(reps):
         fn(warmup + i)
@@ -60,17 +78,20 @@ def _cache(batch: int, context: int, G: int, hd: int, layers: int):
 
 def attention_decode(a) -> None:
     H, G, hd = a.heads, a.kv_heads, a.head_dim
-    kv_bytes = a.batch * a.context * G * hd * 2 * 2
+    lens = [int(x) for x in a.contexts.split(",")] if a.contexts else [a.context] * a.batch
+    a.batch, a.context = len(lens), max(lens)
+    kv_bytes = sum(lens) * G * hd * 2 * 2
     layers = max(2, min(8, int(300e6 // kv_bytes) + 1))
     pools, pt = _cache(a.batch, a.context, G, hd, layers)
     slots = torch.arange(a.batch, dtype=torch.int32, device=DEV)
-    kv = torch.full((a.batch,), a.context, dtype=torch.int32, device=DEV)
+    kv = torch.tensor(lens, dtype=torch.int32, device=DEV)
     q = torch.randn(a.batch, (H + 2 * G) * hd, device=DEV).to(BF)
     out = torch.empty(a.batch, H * hd, device=DEV, dtype=BF)
-    sp = a.splits or None
+    sp = a.splits or K.decode_splits(a.batch, G)
+    plan = K.decode_plan(slots, kv, 0, sp) if a.batch > 1 else None    # once a step, as the engine makes it
     us = _time(lambda i: K.attention_decode(q, pools[i % layers][0], pools[i % layers][1], pt, slots, kv, out, H, G, hd,
-                                            1 / math.sqrt(hd), num_splits=sp), a.warmup, a.reps)
-    print(f"attention_decode B={a.batch} context={a.context} H={H} G={G} hd={hd} splits={sp or K.decode_splits(a.batch, G)}: "
+                                            1 / math.sqrt(hd), num_splits=sp, plan=plan), a.warmup, a.reps)
+    print(f"attention_decode B={a.batch} context={a.contexts or a.context} H={H} G={G} hd={hd} splits={sp}: "
           f"{us:.2f} us, {kv_bytes / us / 1e6:.2f} TB/s of cache")
 
 
@@ -118,13 +139,18 @@ def main(argv=None) -> int:
     p.add_argument("--m", type=int, default=8); p.add_argument("--n", type=int, default=4096); p.add_argument("--k", type=int, default=4096)
     p.add_argument("--mode", default="same", choices=["same", "f32", "add"]); p.add_argument("--parts", type=int, default=0)
     p.add_argument("--batch", type=int, default=8); p.add_argument("--context", type=int, default=800)
+    p.add_argument("--contexts", default="", help="attention-decode: comma-separated lengths, one per sequence (instead of --batch/--context)")
     p.add_argument("--splits", type=int, default=0); p.add_argument("--tokens", type=int, default=2048)
     p.add_argument("--heads", type=int, default=32); p.add_argument("--kv-heads", type=int, default=8)
     p.add_argument("--head-dim", type=int, default=128); p.add_argument("--hidden", type=int, default=4096)
     p.add_argument("--intermediate", type=int, default=14336)
     p.add_argument("--mma", action="store_true", help="attention-prefill: the mma.sync kernel also where tcgen05 applies")
     p.add_argument("--warmup", type=int, default=3); p.add_argument("--reps", type=int, default=20)
+    p.add_argument("--graph", action="store_true", help="capture the timed launches in one CUDA graph: kernels that take "
+                   "less time than a launch costs the host are then timed back to back")
     a = p.parse_args(argv)
+    global GRAPH
+    GRAPH = a.graph
     {"gemm": gemm, "attention-decode": attention_decode, "attention-prefill": attention_prefill}.get(a.kernel, small)(a)
     return 0
 

@@ -19,9 +19,20 @@
 // is needed, and consecutive lanes hit consecutive banks): two blocks of 16 keys are in
 // flight per warp while a third is being multiplied.
 //
-// Grid: (splits, KV heads, sequences); 4 warps per CTA take the split's 16-key blocks in
-// turn.  With one split the CTA writes the output; otherwise it writes its
-// (max, sum, unnormalised output) to scratch and a second kernel combines the splits.
+// Grid: (chunks, KV heads); 4 warps per CTA take their chunk's 16-key blocks in turn.
+// The batch's sequences x `splits` chunks are dealt to the sequences in proportion to
+// their lengths by a one-warp plan kernel: it finds, from the lengths on the device, the
+// smallest chunk size (in rounds of 64 keys) with which all sequences together need no
+// more chunks than the grid has, so a long sequence beside short ones is cut into more
+// pieces and the CTAs carry equal loads.  The plan depends on the lengths only, so one
+// plan serves every layer of a step; the grid depends on the batch's size only (a
+// captured step keeps it while the lengths change).  With one chunk per sequence there is
+// no plan and the CTA writes the output; otherwise it writes its (max, sum, unnormalised
+// output) to scratch and a second kernel combines a sequence's chunks in chunk order.
+// Without a plan every sequence gets `splits` chunks (one sequence needs no dealing).
+// (Working the plan out in every CTA, and letting the last CTA of a sequence do the
+// combining - found by an atomic ticket - were both measured and are slower: dependent
+// round trips to memory at the start and the end of a kernel that runs for 10 us.)
 #include <math.h>
 
 #include "common.cuh"
@@ -57,6 +68,61 @@ __device__ __forceinline__ uint4 dec_lds16(uint32_t addr) {
   return v;
 }
 
+// ---- dealing chunks to sequences (warp-wide: call with all 32 lanes) ----
+// rounds of 64 keys (16 for each of the 4 warps) that sequence holds inside its window
+__device__ __forceinline__ int dec_rounds(int len, int window) {
+  const int start = (window > 0 && len - window > 0) ? len - window : 0;
+  const int num_blk = (len + DEC_BLOCK - 1) / DEC_BLOCK - start / DEC_BLOCK;
+  const int r = (num_blk + DEC_WARPS - 1) / DEC_WARPS;
+  return r > 0 ? r : 1;
+}
+__device__ __forceinline__ int dec_chunks_needed(const int* __restrict__ kv_lens, int B, int window, int c, int lane) {
+  int n = 0;
+  for (int b = lane; b < B; b += 32) n += (dec_rounds(kv_lens[b], window) + c - 1) / c;
+  return __reduce_add_sync(0xffffffffu, n);
+}
+// smallest chunk size (rounds) with which the B sequences need at most `nchunk` (>= B) chunks
+__device__ __forceinline__ int dec_chunk_rounds(const int* __restrict__ kv_lens, int B, int window, int nchunk, int lane) {
+  int tot = 0, mx = 1;
+  for (int b = lane; b < B; b += 32) { const int u = dec_rounds(kv_lens[b], window); tot += u; mx = max(mx, u); }
+  tot = __reduce_add_sync(0xffffffffu, tot);
+  mx = __reduce_max_sync(0xffffffffu, mx);
+  int lo = max(1, (tot + nchunk - 1) / nchunk), hi = mx;      // at hi every sequence is one chunk
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (dec_chunks_needed(kv_lens, B, window, mid, lane) <= nchunk) hi = mid; else lo = mid + 1;
+  }
+  return lo;
+}
+// The plan: entries[x] for chunk x of the grid = {sequence, chunk of the sequence |
+// chunks of the sequence << 16, length, cache slot} (sequence -1: a spare chunk), then
+// seqs[b] = {first chunk of sequence b, number of its chunks}.  One warp.
+__global__ void attention_decode_plan_kernel(const int* __restrict__ seq_slots, const int* __restrict__ kv_lens, int B,
+                                             int window, int nchunk, int4* __restrict__ entries, int2* __restrict__ seqs) {
+  // No early release of the kernels behind this one: whatever is launched after it begins
+  // only when the plan is complete, so those kernels may read the plan before they wait
+  // for their own predecessor.
+  rl_pdl_wait();
+  const int lane = threadIdx.x;
+  const int c = dec_chunk_rounds(kv_lens, B, window, nchunk, lane);
+  int base = 0;
+  for (int b0 = 0; b0 < B; b0 += 32) {
+    const int b = b0 + lane;
+    const int len = b < B ? kv_lens[b] : 0;
+    const int n = b < B ? (dec_rounds(len, window) + c - 1) / c : 0;
+    int incl = n;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += v; }
+    if (b < B) {
+      const int first = base + incl - n, slot = seq_slots[b];
+      seqs[b] = make_int2(first, n);
+      for (int j = 0; j < n; ++j) entries[first + j] = make_int4(b, j | (n << 16), len, slot);
+    }
+    base += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  for (int x = base + lane; x < nchunk; x += 32) entries[x] = make_int4(-1, 0, 0, 0);
+}
+
 // shared memory of one CTA: the ring [warp][stage][piece][lane] of 16-byte pieces, reused
 // after the loop for the warps' (max, sum, output)
 template <int HD>
@@ -72,8 +138,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ k_pool,
                         const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ page_table, int max_pages,
                         const int* __restrict__ seq_slots, const int* __restrict__ kv_lens,
-                        __nv_bfloat16* __restrict__ out, int ldo, float* __restrict__ part_o,
-                        float* __restrict__ part_ml, int H, int G, float scale_log2e, int window) {
+                        const int4* __restrict__ plan, __nv_bfloat16* __restrict__ out, int ldo,
+                        float* __restrict__ part_o, float* __restrict__ part_ml, int H, int G, float scale_log2e,
+                        int window, int even_splits) {
   constexpr int NT = HD / 8;        // output n-tiles of 8 columns
   constexpr int KS = HD / 16;       // k-steps of the Q.K product
   extern __shared__ __align__(16) uint8_t dec_smem[];
@@ -82,15 +149,26 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
   float (*s_l)[16] = s_m + DEC_WARPS;
 
   rl_pdl_trigger();
-  rl_pdl_wait();
-  const int split = blockIdx.x, num_splits = gridDim.x;
-  const int gkv = blockIdx.y, b = blockIdx.z;
+  // Before waiting for the kernel in front (which writes this step's queries, keys and
+  // values): the plan, the sequence's length and slot and its page numbers were complete
+  // before that kernel began, so these dependent loads overlap with its tail.
+  const int gkv = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int m = H / G;                                   // query heads per KV head (<= 16)
-  const int len = kv_lens[b];
+  // which sequence, and which share of its keys
+  int b = blockIdx.x, split = 0, num_splits = 1, len, cache_slot;
+  const bool direct = plan == nullptr && even_splits == 1;   // one chunk per sequence: no scratch
+  if (plan == nullptr) {                                 // no plan: every sequence in `even_splits` chunks
+    b = blockIdx.x / even_splits; split = blockIdx.x % even_splits; num_splits = even_splits;
+    len = kv_lens[b]; cache_slot = seq_slots[b];
+  } else {
+    const int4 e = __ldg(&plan[blockIdx.x]);
+    if (e.x < 0) return;                                 // spare chunk
+    b = e.x; split = e.y & 0xffff; num_splits = e.y >> 16; len = e.z; cache_slot = e.w;
+  }
   const int start = (window > 0 && len - window > 0) ? len - window : 0;
-  const int* pages = page_table + (size_t)seq_slots[b] * max_pages;
+  const int* pages = page_table + (size_t)cache_slot * max_pages;
 
   float acc[NT][4];
 #pragma unroll
@@ -100,7 +178,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
   // ---- this split's blocks of 16 keys, dealt to the warps in turn ----
   const int first_blk = start / DEC_BLOCK;
   const int num_blk = (len + DEC_BLOCK - 1) / DEC_BLOCK - first_blk;
-  const int per_split = (num_blk + num_splits - 1) / num_splits;
+  const int rounds = (num_blk + DEC_WARPS - 1) / DEC_WARPS;
+  const int per_split = (rounds + num_splits - 1) / num_splits * DEC_WARPS;   // whole rounds: every warp gets a block of each
   const int blk_lo = first_blk + split * per_split;
   const int blk_hi = min(blk_lo + per_split, first_blk + num_blk);
   const size_t page_stride = (size_t)G * RL_PAGE * HD;
@@ -112,9 +191,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
                         (uint32_t)(warp * DEC_STAGES * PIECES * 32 + lane) * 16;
   auto slot = [&](int st, int p) { return ring + (uint32_t)((st * PIECES + p) * 32) * 16; };
   // pieces 0 .. HD/16-1: keys (n-tile nt, 32-dimension chunk c); the rest: values (row r, group grp)
-  auto issue = [&](int blk, int st) {
+  auto issue = [&](int blk, int st, int page) {
     const int key0 = blk * DEC_BLOCK;
-    const size_t base = (size_t)pages[key0 / RL_PAGE] * page_stride + head_off + (size_t)(key0 % RL_PAGE) * HD;
+    const size_t base = (size_t)page * page_stride + head_off + (size_t)(key0 % RL_PAGE) * HD;
     const __nv_bfloat16* kb = k_pool + base;
     const __nv_bfloat16* vb = v_pool + base;
 #pragma unroll
@@ -133,10 +212,17 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
   };
 
   {
-    int pre = blk_lo + warp;
+    int first_pages[DEC_STAGES - 1];
 #pragma unroll
-    for (int st = 0; st < DEC_STAGES - 1; ++st, pre += DEC_WARPS) {
-      if (pre < blk_hi) issue(pre, st);
+    for (int st = 0; st < DEC_STAGES - 1; ++st) {
+      const int pre = blk_lo + warp + st * DEC_WARPS;
+      first_pages[st] = pre < blk_hi ? __ldg(&pages[pre * DEC_BLOCK / RL_PAGE]) : 0;
+    }
+    rl_pdl_wait();
+#pragma unroll
+    for (int st = 0; st < DEC_STAGES - 1; ++st) {
+      const int pre = blk_lo + warp + st * DEC_WARPS;
+      if (pre < blk_hi) issue(pre, st, first_pages[st]);
       dec_commit();
     }
   }
@@ -162,7 +248,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
     const int st = it % DEC_STAGES;
     {
       const int ahead = blk + (DEC_STAGES - 1) * DEC_WARPS;
-      if (ahead < blk_hi) issue(ahead, (it + DEC_STAGES - 1) % DEC_STAGES);
+      if (ahead < blk_hi) issue(ahead, (it + DEC_STAGES - 1) % DEC_STAGES, __ldg(&pages[ahead * DEC_BLOCK / RL_PAGE]));
       dec_commit();
     }
     dec_wait<DEC_STAGES - 1>();     // this lane's pieces of block `blk` have landed
@@ -260,33 +346,40 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
       O += s_acc[w][r][d] * wgt;
     }
     const int h = gkv * m + r;
-    if (num_splits == 1) {
+    if (direct) {
       out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
     } else {
-      const size_t p = ((size_t)b * H + h) * num_splits + split;
+      const size_t p = (size_t)blockIdx.x * H + h;         // partial results lie in grid order
       part_o[p * HD + d] = O;
       if (d == 0) { part_ml[2 * p] = M; part_ml[2 * p + 1] = L; }
     }
   }
 }
 
-// Combines the splits of one (sequence, head) in split order.
+// Combines the chunks of one (sequence, head) in chunk order.
 template <int HD>
 __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                                __nv_bfloat16* __restrict__ out, int ldo, int H, int num_splits) {
+                                                const int2* __restrict__ plan_seqs, int even_splits,
+                                                __nv_bfloat16* __restrict__ out, int ldo, int H) {
   rl_pdl_trigger();
-  rl_pdl_wait();
   const int h = blockIdx.x, b = blockIdx.y;
-  const size_t p0 = ((size_t)b * H + h) * num_splits;
+  int first = b * even_splits, count = even_splits;
+  if (plan_seqs != nullptr) {
+    const int2 fc = __ldg(&plan_seqs[b]);      // complete long before the kernel in front began
+    first = fc.x; count = fc.y;
+  }
+  rl_pdl_wait();
   float M = -INFINITY;
-  for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[2 * (p0 + s)]);
+  for (int s = 0; s < count; ++s) M = fmaxf(M, part_ml[2 * ((size_t)(first + s) * H + h)]);
   for (int d = threadIdx.x; d < HD; d += blockDim.x) {
     float L = 0.f, O = 0.f;
-    for (int s = 0; s < num_splits; ++s) {
-      const float ms = part_ml[2 * (p0 + s)];
+#pragma unroll 4
+    for (int s = 0; s < count; ++s) {
+      const size_t p = (size_t)(first + s) * H + h;
+      const float ms = part_ml[2 * p];
       const float wgt = (ms > -INFINITY) ? exp2f(ms - M) : 0.f;
-      L += part_ml[2 * (p0 + s) + 1] * wgt;
-      O += part_o[(p0 + s) * HD + d] * wgt;
+      L += part_ml[2 * p + 1] * wgt;
+      O += part_o[p * HD + d] * wgt;
     }
     out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
   }
@@ -295,7 +388,7 @@ __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o
 template <int HD>
 static int launch_decode(const void* q, int ldq, const void* k_pool, const void* v_pool, const int* page_table,
                          int max_pages, const int* seq_slots, const int* kv_lens, void* out, int ldo,
-                         float* part_o, float* part_ml, int B, int H, int G, float scale, int window,
+                         float* part_o, float* part_ml, const int* plan, int B, int H, int G, float scale, int window,
                          int num_splits, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
@@ -303,14 +396,18 @@ static int launch_decode(const void* q, int ldq, const void* k_pool, const void*
     RL_REQUIRE(e == cudaSuccess, "rl_attention_decode: cannot reserve %d bytes of shared memory: %s", DecSmem<HD>::BYTES, cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid(num_splits, G, B);
+  const int nchunk = B * num_splits;
+  const int4* entries = (const int4*)plan;                                   // null with one split
+  const int2* seqs = plan ? (const int2*)(plan + 4 * (size_t)nchunk) : nullptr;
+  dim3 grid(nchunk, G);
   rl_launch_pdl(attention_decode_kernel<HD>, grid, dim3(DEC_WARPS * 32), (size_t)DecSmem<HD>::BYTES, stream,
       (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table, max_pages,
-      seq_slots, kv_lens, (__nv_bfloat16*)out, ldo, part_o, part_ml, H, G, scale * 1.4426950408889634f, window);
+      seq_slots, kv_lens, entries, (__nv_bfloat16*)out, ldo, part_o, part_ml, H, G, scale * 1.4426950408889634f, window,
+      num_splits);
   RL_LAUNCH_CHECK("rl_attention_decode");
   if (num_splits > 1) {
     rl_launch_pdl(attention_decode_combine_kernel<HD>, dim3(H, B), dim3(HD >= 128 ? 128 : 64), 0, stream,
-                  (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, ldo, H, num_splits);
+                  (const float*)part_o, (const float*)part_ml, seqs, num_splits, (__nv_bfloat16*)out, ldo, H);
     RL_LAUNCH_CHECK("rl_attention_decode (combine)");
   }
   return RL_OK;
@@ -324,38 +421,70 @@ extern "C" int rl_attention_decode_supported(int num_heads, int num_kv_heads, in
   return head_dim == 64 || head_dim == 128;
 }
 
+// Ints of a plan for the given sizes (0 with one split): 4 a chunk, 2 a sequence.
+extern "C" long long rl_attention_decode_plan_ints(int num_seqs, int num_splits) {
+  if (num_splits <= 1) return 0;
+  return 4LL * num_seqs * num_splits + 2LL * num_seqs;
+}
+
 // Floats of scratch the call needs for the given sizes (0 with one split).
 extern "C" long long rl_attention_decode_scratch_floats(int num_seqs, int num_heads, int head_dim, int num_splits) {
   if (num_splits <= 1) return 0;
   return (long long)num_seqs * num_heads * num_splits * (head_dim + 2);
 }
 
+// Deals num_seqs * num_splits chunks to the sequences by their lengths (inside `window`
+// if it is not 0).  plan: rl_attention_decode_plan_ints(...) ints, 16-byte aligned.  The
+// plan holds for every rl_attention_decode call with the same seq_slots, kv_lens, window
+// and num_splits: all layers of a step whose caches have the same window.
+extern "C" int rl_attention_decode_plan(const int* seq_slots, const int* kv_lens, int num_seqs, int window,
+                                        int num_splits, int* plan, cudaStream_t stream) {
+  RL_REQUIRE(num_seqs >= 0 && num_splits >= 1 && window >= 0, "rl_attention_decode_plan: bad sizes");
+  if (num_seqs == 0 || num_splits == 1) return RL_OK;
+  RL_REQUIRE((long long)num_seqs * num_splits <= 65535, "rl_attention_decode_plan: %d sequences x %d splits exceed 65535 "
+             "chunks; use fewer splits", num_seqs, num_splits);
+  RL_REQUIRE(plan != nullptr && ((uintptr_t)plan & 15) == 0, "rl_attention_decode_plan: plan is null or not 16-byte aligned");
+  const int nchunk = num_seqs * num_splits;
+  rl_launch_pdl(attention_decode_plan_kernel, dim3(1), dim3(32), 0, stream, seq_slots, kv_lens, num_seqs, window, nchunk,
+                (int4*)plan, (int2*)(plan + 4 * (size_t)nchunk));
+  RL_LAUNCH_CHECK("rl_attention_decode_plan");
+  return RL_OK;
+}
+
 // q: [B, ldq] bf16, one token per sequence; seq_slots, kv_lens: [B] (kv_lens counts the
 // new token, whose key and value are already in the cache); out: [B, ldo] bf16.
 // scratch: rl_attention_decode_scratch_floats(...) floats (may be null with one split).
+// plan: what rl_attention_decode_plan made for these sequences, window and splits, or
+// null: then every sequence is cut into num_splits equal chunks whatever its length
+// (right for one sequence, or for sequences of like lengths).
 extern "C" int rl_attention_decode(const void* q, int ldq, const void* k_pool, const void* v_pool,
                                    const int* page_table, int max_pages, const int* seq_slots, const int* kv_lens,
-                                   void* out, int ldo, float* scratch, int num_seqs, int num_heads, int num_kv_heads,
-                                   int head_dim, float scale, int window, int num_splits, cudaStream_t stream) {
+                                   void* out, int ldo, float* scratch, const int* plan, int num_seqs, int num_heads,
+                                   int num_kv_heads, int head_dim, float scale, int window, int num_splits,
+                                   cudaStream_t stream) {
   RL_REQUIRE(rl_attention_decode_supported(num_heads, num_kv_heads, head_dim),
              "rl_attention_decode: unsupported shape (heads %d, KV heads %d, head_dim %d): needs head_dim 64 or 128 "
              "and at most 16 heads per KV head", num_heads, num_kv_heads, head_dim);
-  RL_REQUIRE(num_seqs >= 0 && num_splits >= 1 && num_splits <= 65535, "rl_attention_decode: bad sizes");
-  RL_REQUIRE(num_seqs <= 65535 && num_kv_heads <= 65535, "rl_attention_decode: too many sequences or KV heads for one grid");
+  RL_REQUIRE(num_seqs >= 0 && num_splits >= 1, "rl_attention_decode: bad sizes");
+  RL_REQUIRE(num_seqs <= 65535 && num_kv_heads <= 65535 && (long long)num_seqs * num_splits <= (num_splits > 1 ? 65535 : 0x7fffffffLL),
+             "rl_attention_decode: too many sequences, chunks (%d x %d splits) or KV heads for one grid", num_seqs, num_splits);
   RL_REQUIRE(ldq >= num_heads * head_dim && ldo >= num_heads * head_dim && ldq % 8 == 0,
              "rl_attention_decode: row strides too small or not a multiple of 8 elements");
   RL_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)k_pool & 15) == 0 && ((uintptr_t)v_pool & 15) == 0,
              "rl_attention_decode: q and the cache pools must be 16-byte aligned");
   RL_REQUIRE(num_splits == 1 || scratch != nullptr, "rl_attention_decode: scratch is null with %d splits", num_splits);
+  RL_REQUIRE(plan == nullptr || ((uintptr_t)plan & 15) == 0, "rl_attention_decode: plan is not 16-byte aligned");
   RL_REQUIRE(window >= 0, "rl_attention_decode: negative window");
   if (num_seqs == 0) return RL_OK;
+  const size_t parts = (size_t)num_seqs * num_heads * num_splits;
   float* part_o = scratch;
-  float* part_ml = scratch ? scratch + (size_t)num_seqs * num_heads * num_splits * head_dim : nullptr;
+  float* part_ml = scratch ? scratch + parts * head_dim : nullptr;
+  if (num_splits == 1) plan = nullptr;
   if (head_dim == 64)
     return launch_decode<64>(q, ldq, k_pool, v_pool, page_table, max_pages, seq_slots, kv_lens, out, ldo, part_o,
-                             part_ml, num_seqs, num_heads, num_kv_heads, scale, window, num_splits, stream);
+                             part_ml, plan, num_seqs, num_heads, num_kv_heads, scale, window, num_splits, stream);
   return launch_decode<128>(q, ldq, k_pool, v_pool, page_table, max_pages, seq_slots, kv_lens, out, ldo, part_o,
-                            part_ml, num_seqs, num_heads, num_kv_heads, scale, window, num_splits, stream);
+                            part_ml, plan, num_seqs, num_heads, num_kv_heads, scale, window, num_splits, stream);
 }
 
 // ------------------------------------------------------------------ entry point that allocates nothing
@@ -408,6 +537,6 @@ extern "C" int rl_attention_decode_static(const void* q, int ldq, const void* k_
   float* scratch = nullptr;
   const int rc = decode_static_scratch(&scratch);
   if (rc != RL_OK) return rc;
-  return rl_attention_decode(q, ldq, k_pool, v_pool, page_table, max_pages, seq_slots, kv_lens, out, ldo, scratch,
+  return rl_attention_decode(q, ldq, k_pool, v_pool, page_table, max_pages, seq_slots, kv_lens, out, ldo, scratch, nullptr,
                              num_seqs, num_heads, num_kv_heads, head_dim, scale, window, num_splits, stream);
 }

@@ -10,8 +10,14 @@
 //     candidate (98-123, 186-211); min-p drops w_i < min_p (the top weight is 1)
 //     before the draw (125-148).
 // The uniform u in [0, 1) comes from the host's per-sequence generator.  Sums are
-// taken in a fixed order (per-thread contiguous segments, then segment totals in
-// index order), so a row's answer does not depend on the other rows.
+// taken in a fixed order (each warp a contiguous range of the vocabulary, 32
+// neighbouring entries a load; then the ranges' totals in index order), so a row's
+// answer does not depend on the other rows.
+//
+// A row is the work of a thread-block cluster of 8 CTAs, an eighth of the vocabulary
+// each, so that enough loads are in flight to read a row of 128 K logits in a few
+// microseconds; the CTAs exchange their maxima and sums through distributed shared
+// memory.  Every path through a kernel passes the same cluster barriers in all CTAs.
 #include <math.h>
 
 #include "common.cuh"
@@ -47,19 +53,54 @@ extern "C" int rl_repeat_penalty(float* logits, int rows, int vocab, const int* 
   return RL_OK;
 }
 
+// ------------------------------------------------------------------ cluster helpers
+#define SAMPLE_CLUSTER 8
+
+__device__ __forceinline__ uint32_t sample_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void sample_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the 32-bit word at `p` (an address in this CTA's shared memory) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t sample_peer_u32(const void* p, uint32_t rank) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  uint32_t ra, v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a), "r"(rank));
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(ra) : "memory");
+  return v;
+}
+// this CTA's share [lo, hi) of a row: whole multiples of 1024 entries, so that each warp's
+// part of it starts on a multiple of 32
+__device__ __forceinline__ void sample_slice(int vocab, int* lo, int* hi, int* per_warp) {
+  const int slice = ((vocab + SAMPLE_CLUSTER - 1) / SAMPLE_CLUSTER + SAMPLE_THREADS - 1) / SAMPLE_THREADS * SAMPLE_THREADS;
+  *lo = min((int)sample_cluster_rank() * slice, vocab);
+  *hi = min(*lo + slice, vocab);
+  *per_warp = slice / (SAMPLE_THREADS / 32);
+}
+
 // ------------------------------------------------------------------ greedy
 __device__ __forceinline__ void argmax_combine(float& bv, int& bi, float ov, int oi) {
   if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
 }
 
-__device__ int block_argmax(const float* __restrict__ l, int vocab, float scale) {
+// Highest finite logit of the row, the first one wins; token 0 if none is finite.  Called
+// by all threads of all CTAs of the cluster; CTA 0's thread 0 gets the answer (others -1).
+// Passes two cluster barriers.
+__device__ int cluster_argmax(const float* __restrict__ l, int vocab) {
   __shared__ float sv[SAMPLE_THREADS / 32];
   __shared__ int si[SAMPLE_THREADS / 32];
-  __shared__ int result;
+  __shared__ float cta_v;
+  __shared__ int cta_i;
+  int lo, hi, per_warp;
+  sample_slice(vocab, &lo, &hi, &per_warp);
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = finite_or_neg_inf(l[i]) * scale;
+#pragma unroll 8
+  for (int i = lo + (int)threadIdx.x; i < hi; i += SAMPLE_THREADS) {
+    const float v = finite_or_neg_inf(l[i]);
     if (v > bv) { bv = v; bi = i; }
   }
   for (int o = 16; o > 0; o >>= 1) {
@@ -70,24 +111,47 @@ __device__ int block_argmax(const float* __restrict__ l, int vocab, float scale)
   if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) argmax_combine(bv, bi, sv[w], si[w]);
+    for (int w = 1; w < SAMPLE_THREADS / 32; ++w) argmax_combine(bv, bi, sv[w], si[w]);
+    cta_v = bv; cta_i = bi;
+  }
+  sample_cluster_sync();
+  int result = -1;
+  if (threadIdx.x == 0 && sample_cluster_rank() == 0) {
+    for (uint32_t r = 1; r < SAMPLE_CLUSTER; ++r)
+      argmax_combine(bv, bi, __uint_as_float(sample_peer_u32(&cta_v, r)), (int)sample_peer_u32(&cta_i, r));
     result = (bi == 0x7fffffff) ? 0 : bi;   // nothing finite: token 0
   }
-  __syncthreads();
+  sample_cluster_sync();                    // nobody leaves while its shared memory may still be read
   return result;
 }
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
-  const int row = blockIdx.x;
-  const int r = block_argmax(logits + (size_t)row * vocab, vocab, 1.0f);
-  if (threadIdx.x == 0) out[row] = r;
+  const int row = blockIdx.x / SAMPLE_CLUSTER;
+  const int r = cluster_argmax(logits + (size_t)row * vocab, vocab);
+  if (r >= 0) out[row] = r;
+}
+
+static cudaError_t sample_launch_cluster(void (*kernel)(const float*, int, int*), int rows, cudaStream_t stream,
+                                         const float* logits, int vocab, int* out) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(rows * SAMPLE_CLUSTER);
+  cfg.blockDim = dim3(SAMPLE_THREADS);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = SAMPLE_CLUSTER; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, logits, vocab, out);
 }
 
 extern "C" int rl_argmax(const float* logits, int rows, int vocab, int* out, cudaStream_t stream) {
   RL_REQUIRE(rows >= 0 && vocab > 0, "rl_argmax: bad sizes rows=%d vocab=%d", rows, vocab);
+  RL_REQUIRE((long long)rows * SAMPLE_CLUSTER <= 0x7fffffffLL, "rl_argmax: too many rows");
   if (rows == 0) return RL_OK;
-  argmax_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, vocab, out);
+  cudaError_t e = sample_launch_cluster(argmax_kernel, rows, stream, logits, vocab, out);
+  RL_REQUIRE(e == cudaSuccess, "rl_argmax: launch failed: %s", cudaGetErrorString(e));
   RL_LAUNCH_CHECK("rl_argmax");
   return RL_OK;
 }
@@ -99,76 +163,87 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_temperature_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
                           const float* __restrict__ uniform, const float* __restrict__ min_p,
                           int* __restrict__ out) {
-  __shared__ float seg_sum[SAMPLE_THREADS];
-  __shared__ float red[SAMPLE_THREADS / 32];
-  __shared__ float s_max, s_total;
-  __shared__ int s_seg;
-  const int row = blockIdx.x;
+  constexpr int NW = SAMPLE_THREADS / 32;
+  __shared__ float range_sum[NW];
+  __shared__ float red[NW];
+  __shared__ float cta_max, cta_sum;
+  const int row = blockIdx.x / SAMPLE_CLUSTER;
+  const uint32_t rank = sample_cluster_rank();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float* l = logits + (size_t)row * vocab;
   const float temp = temperature[row];
   if (temp < 1e-6f) {
-    const int r = block_argmax(l, vocab, 1.0f);
-    if (threadIdx.x == 0) out[row] = r;
+    const int r = cluster_argmax(l, vocab);
+    if (r >= 0) out[row] = r;
     return;
   }
   const float inv_temp = 1.0f / temp;
   const float cut = min_p ? min_p[row] : 0.f;
+  int lo, hi, per_warp;
+  sample_slice(vocab, &lo, &hi, &per_warp);
 
-  // 1. maximum of the scaled finite logits
+  // 1. maximum of the scaled finite logits: this CTA's share, then the cluster's
   float mx = -INFINITY;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) mx = fmaxf(mx, finite_or_neg_inf(l[i]) * inv_temp);
+#pragma unroll 8
+  for (int i = lo + (int)threadIdx.x; i < hi; i += SAMPLE_THREADS) mx = fmaxf(mx, finite_or_neg_inf(l[i]) * inv_temp);
   mx = rl_warp_max(mx);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+  if (lane == 0) red[warp] = mx;
   __syncthreads();
   if (threadIdx.x == 0) {
     float t = red[0];
-    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) t = fmaxf(t, red[w]);
-    s_max = t;
+    for (int w = 1; w < NW; ++w) t = fmaxf(t, red[w]);
+    cta_max = t;
   }
-  __syncthreads();
-  mx = s_max;
+  sample_cluster_sync();                                       // barrier 1
+  mx = -INFINITY;
+  for (uint32_t r = 0; r < SAMPLE_CLUSTER; ++r) mx = fmaxf(mx, __uint_as_float(sample_peer_u32(&cta_max, r)));
   if (!(mx > -INFINITY)) {  // nothing finite
-    if (threadIdx.x == 0) out[row] = 0;
+    if (threadIdx.x == 0 && rank == 0) out[row] = 0;
+    sample_cluster_sync();
     return;
   }
 
-  // 2. weights, summed over contiguous per-thread segments
-  const int seg = (vocab + blockDim.x - 1) / blockDim.x;
-  const int lo = threadIdx.x * seg, hi = min(lo + seg, vocab);
+  // 2. weights, summed over one contiguous range of the vocabulary per warp
+  const int wlo = min(lo + warp * per_warp, hi), whi = min(wlo + per_warp, hi);
   float mine = 0.f;
-  for (int i = lo; i < hi; ++i) {
+#pragma unroll 8
+  for (int i = wlo + lane; i < whi; i += 32) {
     const float w = expf(finite_or_neg_inf(l[i]) * inv_temp - mx);
     if (w >= cut) mine += w;
   }
-  seg_sum[threadIdx.x] = mine;
+  for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+  if (lane == 0) range_sum[warp] = mine;
   __syncthreads();
   if (threadIdx.x == 0) {
-    float total = 0.f;
-    for (int t = 0; t < (int)blockDim.x; ++t) total += seg_sum[t];
-    s_total = total;
-    const float r = uniform[row] * total;
-    // first segment whose inclusive running sum exceeds r
-    float c = 0.f;
-    int chosen = -1;
-    for (int t = 0; t < (int)blockDim.x; ++t) {
-      const float incl = c + seg_sum[t];
-      if (incl > r && seg_sum[t] > 0.f) { chosen = t; break; }
-      c = incl;
-    }
-    s_seg = chosen;
-    seg_sum[0] = c;  // exclusive sum in front of the chosen segment (slot 0 is consumed)
+    float t = 0.f;
+    for (int w = 0; w < NW; ++w) t += range_sum[w];
+    cta_sum = t;
   }
-  __syncthreads();
-  const float total = s_total;
+  sample_cluster_sync();                                       // barrier 2
+  // every thread walks the CTAs' totals (the same additions in the same order everywhere)
+  float totals[SAMPLE_CLUSTER];
+  float total = 0.f;
+#pragma unroll
+  for (uint32_t r = 0; r < SAMPLE_CLUSTER; ++r) { totals[r] = __uint_as_float(sample_peer_u32(&cta_sum, r)); total += totals[r]; }
+  sample_cluster_sync();                                       // barrier 3: shared memory of peers is not read below
   if (!isfinite(total) || total <= 0.f) {  // src/sampling.rs:112-119: fall back to the best index
-    const int r = block_argmax(l, vocab, 1.0f);
-    if (threadIdx.x == 0) out[row] = r;
+    const int r = cluster_argmax(l, vocab);
+    if (r >= 0) out[row] = r;
     return;
   }
-  const int chosen = s_seg;
-  if (chosen < 0) {
+  const float r = uniform[row] * total;
+  float before = 0.f;       // sum in front of the chosen part
+  int chosen_cta = -1;
+#pragma unroll
+  for (int c = 0; c < SAMPLE_CLUSTER; ++c) {
+    if (chosen_cta < 0) {
+      const float incl = before + totals[c];
+      if (incl > r && totals[c] > 0.f) chosen_cta = c; else before = incl;
+    }
+  }
+  if (chosen_cta < 0) {
     // rounding left r at or above the total: the last kept candidate (src/sampling.rs:210)
-    if (threadIdx.x == 0) {
+    if (threadIdx.x == 0 && rank == 0) {
       int last = vocab - 1;  // without a cut the reference answers n - 1 (src/sampling.rs:211)
       for (int i = vocab - 1; cut > 0.f && i >= 0; --i) {
         const float w = expf(finite_or_neg_inf(l[i]) * inv_temp - mx);
@@ -178,20 +253,40 @@ sample_temperature_kernel(const float* __restrict__ logits, int vocab, const flo
     }
     return;
   }
-  if ((int)threadIdx.x == chosen) {
-    const float r = uniform[row] * total;
-    float c = seg_sum[0];
-    int answer = -1, last = lo;
-    for (int i = lo; i < hi; ++i) {
-      const float w = expf(finite_or_neg_inf(l[i]) * inv_temp - mx);
-      if (w >= cut && w > 0.f) {
-        last = i;
-        c += w;
-        if (c > r) { answer = i; break; }
-      }
-    }
-    out[row] = answer >= 0 ? answer : last;
+  if ((int)rank != chosen_cta) return;
+  int chosen = -1;
+  for (int w = 0; w < NW; ++w) {
+    const float incl = before + range_sum[w];
+    if (incl > r && range_sum[w] > 0.f) { chosen = w; break; }
+    before = incl;
   }
+  if (chosen < 0) {          // the CTA's total said "in here", the walk over its ranges "not yet": its last range that kept anything
+    for (int w = NW - 1; w >= 0; --w) if (range_sum[w] > 0.f) { chosen = w; break; }
+    before = -INFINITY;      // the walk below then never passes r and ends at the range's last kept entry
+  }
+  if (warp != chosen) return;
+  // 3. the chosen warp walks its range, 32 entries at a time, to the entry where the
+  // running sum passes r
+  float c = before;
+  int last_kept = wlo;
+  for (int i0 = wlo; i0 < whi; i0 += 32) {
+    const int i = i0 + lane;
+    float w = i < whi ? expf(finite_or_neg_inf(l[i]) * inv_temp - mx) : 0.f;
+    const bool kept = w >= cut && w > 0.f;
+    if (!kept) w = 0.f;
+    float incl = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const float v = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += v; }
+    const unsigned passed = __ballot_sync(0xffffffffu, kept && c + incl > r);
+    if (passed) {
+      if (lane == 0) out[row] = i0 + __ffs(passed) - 1;
+      return;
+    }
+    const unsigned kept_mask = __ballot_sync(0xffffffffu, kept);
+    if (kept_mask) last_kept = i0 + 31 - __clz(kept_mask);
+    c += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0) out[row] = last_kept;    // rounding in the walk: the range's last kept entry
 }
 
 // temperature, uniform: [rows]; min_p: [rows] or nullptr.
@@ -200,7 +295,17 @@ extern "C" int rl_sample_temperature(const float* logits, int rows, int vocab, c
                                      cudaStream_t stream) {
   RL_REQUIRE(rows >= 0 && vocab > 0, "rl_sample_temperature: bad sizes rows=%d vocab=%d", rows, vocab);
   if (rows == 0) return RL_OK;
-  sample_temperature_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, vocab, temperature, uniform, min_p, out);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(rows * SAMPLE_CLUSTER);
+  cfg.blockDim = dim3(SAMPLE_THREADS);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = SAMPLE_CLUSTER; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, sample_temperature_kernel, logits, vocab, temperature, uniform, min_p, out);
+  RL_REQUIRE(e == cudaSuccess, "rl_sample_temperature: launch failed: %s", cudaGetErrorString(e));
   RL_LAUNCH_CHECK("rl_sample_temperature");
   return RL_OK;
 }

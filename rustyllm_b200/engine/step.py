@@ -10,8 +10,8 @@ kernel works from per-token position and slot.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
-from typing import List, Optional, Sequence, Union
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Union
 
 import numpy as np
 import torch
@@ -39,6 +39,9 @@ class StepState:
     max_q_len: int
     max_kv_len: int
     is_decode: bool               # every sequence brings exactly one token
+    # device data that parts derive from the step and that holds for all layers (a part
+    # that needs, say, a work plan of the sequences makes it once and leaves it here)
+    derived: Dict[object, object] = field(default_factory=dict)
 
 
 Want = Union[str, None, Sequence[Sequence[int]]]
@@ -62,6 +65,37 @@ class _DecodeGraph:
             self.logits = engine.model.logits(x, st.want_rows)
         self.launches = K.launch_count - before
         K.launch_count = before    # capturing runs nothing
+        # pinned host copies of ``static_in``, taken in turn: a buffer is filled again only
+        # after the copy that read it has finished, so the host may run ahead of the device
+        n = self.static_in.numel()
+        self._host = [torch.empty(n, dtype=torch.int32, pin_memory=True) for _ in range(4)]
+        self._host_np = [h.numpy() for h in self._host]
+        self._copied = [torch.cuda.Event() for _ in range(4)]
+        self._in_use = [False] * 4
+        self._next = 0
+        self._rows = np.arange(B + 1, dtype=np.int32)
+
+    def upload(self, tokens, starts, slots) -> int:
+        """The integers of a single-token step from the host into ``static_in``; returns
+        the bytes copied."""
+        B = self.num_seqs
+        k = self._next
+        self._next = (k + 1) % len(self._host)
+        if self._in_use[k]:
+            self._copied[k].synchronize()
+        a = self._host_np[k]
+        a[0:B] = tokens
+        a[B:2 * B] = starts                       # position of the new token
+        a[2 * B:3 * B] = slots                    # slot of each token
+        a[3 * B:4 * B + 1] = self._rows           # token offsets: one token a sequence
+        a[4 * B + 1:5 * B + 1] = slots
+        a[5 * B + 1:6 * B + 1] = starts
+        a[5 * B + 1:6 * B + 1] += 1               # lengths after the step
+        a[6 * B + 1:7 * B + 1] = self._rows[:B]   # wanted rows: every sequence's only token
+        self.static_in.copy_(self._host[k], non_blocking=True)
+        self._copied[k].record()
+        self._in_use[k] = True
+        return a.nbytes
 
 
 class Engine:
@@ -166,21 +200,30 @@ class Engine:
         Returns float32 logits ``[wanted, vocab]`` on the device in the order of the
         sequences and of their wanted places (``None`` if nothing is wanted).
         """
-        packed, sizes, q_lens, kv_lens = self.build_step(slots, tokens, want)
-        self.cache.prepare(slots, q_lens)
         B = len(slots)
-        if self.use_graphs and sizes[0] == B and isinstance(want, str) and want == "last":
+        decode = (self.use_graphs and B > 0 and len(tokens) == B and isinstance(want, str) and want == "last"
+                  and all(len(t) == 1 for t in tokens))
+        if decode:
             g = self._graphs.get(B)
             if g is None and self._eager_decodes.get(B, 0) >= 1:
                 g = self._graphs[B] = _DecodeGraph(self, B)
             if g is not None:
-                g.static_in.copy_(self._staging.upload(packed))
-                self.h2d_bytes += packed.nbytes
+                # the short way for the step that generation repeats: same checks, same layout
+                # of the integers as build_step, no intermediate arrays
+                toks = [t[0] for t in tokens]
+                if min(toks) < 0 or max(toks) >= self.vocab_size:
+                    bad = next(t for t in toks if t < 0 or t >= self.vocab_size)
+                    raise ValueError(f"token id {bad} lies outside the vocabulary [0, {self.vocab_size})")
+                ones = [1] * B
+                self.cache.prepare(slots, ones)
+                self.h2d_bytes += g.upload(toks, [self.cache.length(s) for s in slots], slots)
                 g.graph.replay()
                 K.launch_count += g.launches
-                self.cache.commit(slots, q_lens)
+                self.cache.commit(slots, ones)
                 return g.logits.clone()   # the graph's own buffer is overwritten by its next replay
             self._eager_decodes[B] = self._eager_decodes.get(B, 0) + 1
+        packed, sizes, q_lens, kv_lens = self.build_step(slots, tokens, want)
+        self.cache.prepare(slots, q_lens)
         if self._staging is not None:
             dev = self._staging.upload(packed)
         else:

@@ -49,7 +49,8 @@ _SIGNATURES = {
     "rl_sample_candidates": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "rl_attention_decode": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
-                            _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p],
+                            _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p],
+    "rl_attention_decode_plan": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "rl_attention_decode_supported": [_c_int, _c_int, _c_int],
     "rl_attention_prefill": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
                              _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p],
@@ -362,12 +363,37 @@ def decode_splits(num_seqs: int, num_kv_heads: int) -> int:
     return max(1, min(16, -(-3 * NUM_SMS // (2 * num_seqs * num_kv_heads))))
 
 
+def decode_scratch_floats(num_seqs: int, num_heads: int, head_dim: int, num_splits: int) -> int:
+    if num_splits <= 1:
+        return 0
+    return num_seqs * num_heads * num_splits * (head_dim + 2)
+
+
+def decode_plan(seq_slots: torch.Tensor, kv_lens: torch.Tensor, window: int, num_splits: int) -> Optional[torch.Tensor]:
+    """Deals ``B * num_splits`` chunks to the sequences by their lengths, on the device.
+    The plan serves every ``attention_decode`` call of the step with the same window and
+    splits (``None`` with one split: every sequence is one chunk)."""
+    _need(seq_slots, "seq_slots", torch.int32); _need(kv_lens, "kv_lens", torch.int32)
+    B = seq_slots.numel()
+    if num_splits <= 1 or B == 0:
+        return None
+    plan = torch.empty(4 * B * num_splits + 2 * B, dtype=torch.int32, device=seq_slots.device)
+    _check(library().rl_attention_decode_plan(seq_slots.data_ptr(), kv_lens.data_ptr(), B, int(window), int(num_splits),
+                                              plan.data_ptr(), _stream()), "rl_attention_decode_plan")
+    _count(1)
+    return plan
+
+
 def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
                      seq_slots: torch.Tensor, kv_lens: torch.Tensor, out: torch.Tensor, num_heads: int,
                      num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
-                     num_splits: Optional[int] = None, scratch: Optional[torch.Tensor] = None) -> None:
+                     num_splits: Optional[int] = None, scratch: Optional[torch.Tensor] = None,
+                     plan: Optional[torch.Tensor] = None) -> None:
     """One token per sequence over the bf16 cache, split over the context (tensor cores).
-    q: [B, >= H*hd] bf16 (a view into the qkv buffer is fine); out: [B, H*hd] bf16."""
+    q: [B, >= H*hd] bf16 (a view into the qkv buffer is fine); out: [B, H*hd] bf16.
+    ``num_splits``: chunks per sequence; with a ``plan`` (from ``decode_plan`` with the
+    same sequences, window and splits) that many on average, dealt to the sequences by
+    length."""
     _need(q, "q", torch.bfloat16, contiguous=False); _need(k_pool, "k_pool", torch.bfloat16)
     _need(v_pool, "v_pool", torch.bfloat16); _need(out, "out", torch.bfloat16)
     _need(page_table, "page_table", torch.int32); _need(seq_slots, "seq_slots", torch.int32)
@@ -376,16 +402,20 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     assert seq_slots.numel() == B and kv_lens.numel() == B and q.stride(1) == 1
     if num_splits is None:
         num_splits = decode_splits(B, num_kv_heads)
+    need = decode_scratch_floats(B, num_heads, head_dim, num_splits)
     if num_splits > 1 and scratch is None:
-        scratch = torch.empty(B * num_heads * num_splits * (head_dim + 2), dtype=torch.float32, device=q.device)
+        scratch = torch.empty(need, dtype=torch.float32, device=q.device)
     if scratch is not None:
         _need(scratch, "scratch", torch.float32)
-        assert scratch.numel() >= (B * num_heads * num_splits * (head_dim + 2) if num_splits > 1 else 0)
+        assert scratch.numel() >= need
+    if plan is not None:
+        _need(plan, "plan", torch.int32)
+        assert num_splits > 1 and plan.numel() >= 4 * B * num_splits + 2 * B
     ldq = q.stride(0) if B > 1 else max(q.stride(0), num_heads * head_dim)
     _check(library().rl_attention_decode(
         q.data_ptr(), ldq, k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr(), page_table.shape[1],
-        seq_slots.data_ptr(), kv_lens.data_ptr(), out.data_ptr(), out.stride(0), _ptr(scratch), B, num_heads,
-        num_kv_heads, head_dim, float(scale), int(window), int(num_splits), _stream()), "rl_attention_decode")
+        seq_slots.data_ptr(), kv_lens.data_ptr(), out.data_ptr(), out.stride(0), _ptr(scratch), _ptr(plan), B,
+        num_heads, num_kv_heads, head_dim, float(scale), int(window), int(num_splits), _stream()), "rl_attention_decode")
     _count(2 if num_splits > 1 else 1)
 
 
@@ -458,8 +488,16 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
     dtype and the shape of the step.  ``step`` carries positions, slots and
     sequence boundaries (engine.step.StepState)."""
     if step.is_decode and attention_decode_supported(q.dtype, num_heads, num_kv_heads, head_dim):
+        splits = decode_splits(q.shape[0], num_kv_heads)
+        plan = None
+        derived = getattr(step, "derived", None)     # what layers of one step share
+        if splits > 1 and q.shape[0] > 1 and derived is not None:     # one sequence: nothing to deal
+            key = ("decode_plan", int(window), splits)
+            plan = derived.get(key)
+            if plan is None:
+                plan = derived[key] = decode_plan(step.seq_slots, step.kv_lens, window, splits)
         attention_decode(q, k_pool, v_pool, page_table, step.seq_slots, step.kv_lens, out,
-                         num_heads, num_kv_heads, head_dim, scale, window)
+                         num_heads, num_kv_heads, head_dim, scale, window, num_splits=splits, plan=plan)
         return
     if not step.is_decode and attention_prefill_tc_supported(q.dtype, num_heads, num_kv_heads, head_dim) \
             and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0:

@@ -21,22 +21,24 @@ class PinnedStaging:
         self.depth = depth
         self.bufs: List[Optional[torch.Tensor]] = [None] * depth
         self.events: List[Optional[torch.cuda.Event]] = [None] * depth
+        self.views: List[Optional[np.ndarray]] = [None] * depth
         self.i = 0
         self.bytes = 0
 
     def upload(self, host: np.ndarray) -> torch.Tensor:
-        flat = np.ascontiguousarray(host, dtype=_NP[self.dtype]).reshape(-1)
+        flat = host.reshape(-1)
         n = flat.shape[0]
         k = self.i
         self.i = (self.i + 1) % self.depth
         if self.events[k] is not None:
             self.events[k].synchronize()
+        else:
+            self.events[k] = torch.cuda.Event()
         if self.bufs[k] is None or self.bufs[k].numel() < n:
             self.bufs[k] = torch.empty(max(n, 1024), dtype=self.dtype, pin_memory=True)
-        self.bufs[k][:n].numpy()[:] = flat
+            self.views[k] = self.bufs[k].numpy()
+        self.views[k][:n] = flat          # converts to the buffer's type if need be
         dev = self.bufs[k][:n].to(self.device, non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record()
-        self.events[k] = ev
-        self.bytes += flat.nbytes
+        self.events[k].record()
+        self.bytes += n * self.views[k].itemsize
         return dev.view(host.shape)

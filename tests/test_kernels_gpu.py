@@ -361,19 +361,55 @@ def _decode_inputs(case):
 
 @pytest.mark.parametrize("H,G,hd", [(32, 8, 128), (8, 8, 128), (6, 2, 64), (16, 1, 64), (5, 5, 128), (24, 8, 64)])
 @pytest.mark.parametrize("splits", [1, 2, 7, 32])
-def test_attention_decode_matches_plain(H, G, hd, splits):
+@pytest.mark.parametrize("planned", [False, True])
+def test_attention_decode_matches_plain(H, G, hd, splits, planned):
+    """``planned``: the chunks are dealt to the sequences by length (as the engine does
+    for a batch); otherwise every sequence is cut into ``splits`` equal chunks."""
     k = K()
     assert k.attention_decode_supported(torch.bfloat16, H, G, hd)
     lens = [1, 15, 16, 17, 64, 65, 200, 513]
     case = _attention_case(torch.bfloat16, H, G, hd, [1] * len(lens), lens, seed=hd + H + splits)
     q, kp, vp, pt, slots, kv_lens, ref = _decode_inputs(case)
     out = torch.empty(len(lens), H * hd, dtype=torch.bfloat16, device=DEV)
-    k.attention_decode(q, kp, vp, pt, slots, kv_lens, out, H, G, hd, 1.0 / math.sqrt(hd), num_splits=splits)
+    plan = k.decode_plan(slots, kv_lens, 0, splits) if planned else None
+    assert (plan is not None) == (planned and splits > 1)
+    k.attention_decode(q, kp, vp, pt, slots, kv_lens, out, H, G, hd, 1.0 / math.sqrt(hd), num_splits=splits, plan=plan)
     torch.testing.assert_close(out.double().cpu(), ref, **_tol(torch.bfloat16))
     # and the any-shape kernel gives the same to bf16 rounding
     simt = torch.empty_like(out)
     k.attention_simt(q, kp, vp, pt, slots, (kv_lens - 1).to(torch.int32), simt, H, G, hd, 1.0 / math.sqrt(hd))
     torch.testing.assert_close(out.float(), simt.float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("splits,window", [(2, 0), (7, 0), (3, 100)])
+def test_attention_decode_deals_chunks_by_length(splits, window):
+    """More sequences than a warp has lanes, one of them far longer than the rest: the
+    long one gets most of the chunks, and every sequence is still answered whole."""
+    k = K()
+    H, G, hd = 4, 2, 64
+    lens = [1] * 14 + [1500] + [64, 65, 129] * 6 + [700, 3]
+    assert len(lens) > 32
+    case = _attention_case(torch.bfloat16, H, G, hd, [1] * len(lens), lens, window=window, seed=splits)
+    q, kp, vp, pt, slots, kv_lens, ref = _decode_inputs(case)
+    out = torch.full((len(lens), H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    plan = k.decode_plan(slots, kv_lens, window, splits)
+    # the plan itself: every sequence has at least one chunk, together no more than the grid,
+    # neighbours in the grid, and the longer a sequence the more it gets
+    B = len(lens)
+    entries = plan[:4 * B * splits].view(-1, 4).cpu()
+    seqs = plan[4 * B * splits:].view(-1, 2).cpu()
+    assert int(seqs[:, 1].min()) >= 1 and int(seqs[:, 1].sum()) <= B * splits
+    assert seqs[:, 0].tolist() == [int(x) for x in (torch.cumsum(seqs[:, 1], 0) - seqs[:, 1])]
+    assert int(seqs[14, 1]) == int(seqs[:, 1].max()) and int(seqs[0, 1]) == 1
+    if window == 0:
+        assert int(seqs[14, 1]) > int(seqs[33, 1]) > int(seqs[34, 1])      # 1500, 700 and 3 keys
+    for b in range(B):
+        for j in range(int(seqs[b, 1])):
+            e = entries[int(seqs[b, 0]) + j].tolist()
+            assert e == [b, j | (int(seqs[b, 1]) << 16), lens[b], int(slots[b])]
+    assert (entries[int(seqs[:, 1].sum()):, 0] == -1).all()
+    k.attention_decode(q, kp, vp, pt, slots, kv_lens, out, H, G, hd, 1.0 / math.sqrt(hd), window, num_splits=splits, plan=plan)
+    torch.testing.assert_close(out.double().cpu(), ref, **_tol(torch.bfloat16))
 
 
 def test_attention_decode_window_and_strided_queries():
