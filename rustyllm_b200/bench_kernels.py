@@ -1,9 +1,10 @@
 """Times one kernel of the library alone, at a chosen shape, on random data.
 
-    python -m rustyllm_b200.bench_kernels gemm --m 8 --n 28672 --k 4096 [--mode same|f32|add] [--parts 0]
+    python -m rustyllm_b200.bench_kernels gemm --m 8 --n 28672 --k 4096 [--mode same|f32|add|swiglu] [--parts 0]
     python -m rustyllm_b200.bench_kernels attention-decode --batch 8 --context 800 [--splits 0] [--contexts 1761,1350,159]
     python -m rustyllm_b200.bench_kernels attention-prefill --tokens 2048
     python -m rustyllm_b200.bench_kernels rmsnorm | swiglu | rope --m 8
+    python -m rustyllm_b200.bench_kernels sample --m 8 --n 128256 [--greedy]
 
 Each run launches the kernel ``--reps`` times after ``--warmup`` launches, rotating over
 several copies of the big operand so that the 126 MB L2 cannot serve it, times the
@@ -57,11 +58,14 @@ def _time(fn, warmup: int, reps: int) -> float:
 
 
 def gemm(a) -> None:
-    mode = {"same": K.OUT_SAME, "f32": K.OUT_F32, "add": K.OUT_ADD_F32}[a.mode]
+    mode = {"same": K.OUT_SAME, "f32": K.OUT_F32, "add": K.OUT_ADD_F32, "swiglu": K.OUT_SWIGLU}[a.mode]
     copies = max(2, min(8, int(300e6 // (a.n * a.k * 2)) + 1))
     ws = [torch.randn(a.n, a.k, device=DEV).to(BF) * 0.02 for _ in range(copies)]
     x = torch.randn(a.m, a.k, device=DEV).to(BF)
-    out = torch.zeros(a.m, a.n, device=DEV, dtype=BF if mode == K.OUT_SAME else torch.float32)
+    if mode == K.OUT_SWIGLU:      # weight rows interleaved (gate, up): the epilogue writes silu(gate) * up, [M, N/2]
+        out = torch.zeros(a.m, a.n // 2, device=DEV, dtype=BF)
+    else:
+        out = torch.zeros(a.m, a.n, device=DEV, dtype=BF if mode == K.OUT_SAME else torch.float32)
     us = _time(lambda i: K.gemm_tc(x, ws[i % copies], out, mode, force_splits=a.parts), a.warmup, a.reps)
     K.check_device_errors()
     flops, wbytes = 2.0 * a.m * a.n * a.k, a.n * a.k * 2.0
@@ -112,6 +116,20 @@ def attention_prefill(a) -> None:
           f"{flops / us / 1e6:.1f} TFLOP/s (causal half counted)")
 
 
+def sample(a) -> None:
+    rows, V = a.m, a.n
+    copies = max(2, int(300e6 // (rows * V * 4)) + 1)
+    logits = [torch.randn(rows, V, device=DEV) * 3 for _ in range(copies)]
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    temps = torch.full((rows,), 0.8, device=DEV); u = torch.rand(rows, device=DEV)
+    if a.greedy:
+        us = _time(lambda i: K.argmax(logits[i % copies], out), a.warmup, a.reps)
+    else:
+        us = _time(lambda i: K.sample_temperature(logits[i % copies], temps, u, out), a.warmup, a.reps)
+    print(f"{'argmax' if a.greedy else 'sample_temperature'} rows={rows} vocab={V}: {us:.2f} us, "
+          f"{rows * V * 4 * (1 if a.greedy else 2) / us / 1e3:.1f} GB/s of logits read")
+
+
 def small(a) -> None:
     d, I, H, G, hd, M = a.hidden, a.intermediate, a.heads, a.kv_heads, a.head_dim, a.m
     if a.kernel == "rmsnorm":
@@ -135,15 +153,16 @@ def small(a) -> None:
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="python -m rustyllm_b200.bench_kernels", description=__doc__,
                                 formatter_class=argparse.RawDescriptionHelpFormatter)
-    p.add_argument("kernel", choices=["gemm", "attention-decode", "attention-prefill", "rmsnorm", "swiglu", "rope"])
+    p.add_argument("kernel", choices=["gemm", "attention-decode", "attention-prefill", "rmsnorm", "swiglu", "rope", "sample"])
     p.add_argument("--m", type=int, default=8); p.add_argument("--n", type=int, default=4096); p.add_argument("--k", type=int, default=4096)
-    p.add_argument("--mode", default="same", choices=["same", "f32", "add"]); p.add_argument("--parts", type=int, default=0)
+    p.add_argument("--mode", default="same", choices=["same", "f32", "add", "swiglu"]); p.add_argument("--parts", type=int, default=0)
     p.add_argument("--batch", type=int, default=8); p.add_argument("--context", type=int, default=800)
     p.add_argument("--contexts", default="", help="attention-decode: comma-separated lengths, one per sequence (instead of --batch/--context)")
     p.add_argument("--splits", type=int, default=0); p.add_argument("--tokens", type=int, default=2048)
     p.add_argument("--heads", type=int, default=32); p.add_argument("--kv-heads", type=int, default=8)
     p.add_argument("--head-dim", type=int, default=128); p.add_argument("--hidden", type=int, default=4096)
     p.add_argument("--intermediate", type=int, default=14336)
+    p.add_argument("--greedy", action="store_true", help="sample: the argmax kernel")
     p.add_argument("--mma", action="store_true", help="attention-prefill: the mma.sync kernel also where tcgen05 applies")
     p.add_argument("--warmup", type=int, default=3); p.add_argument("--reps", type=int, default=20)
     p.add_argument("--graph", action="store_true", help="capture the timed launches in one CUDA graph: kernels that take "
@@ -151,7 +170,7 @@ def main(argv=None) -> int:
     a = p.parse_args(argv)
     global GRAPH
     GRAPH = a.graph
-    {"gemm": gemm, "attention-decode": attention_decode, "attention-prefill": attention_prefill}.get(a.kernel, small)(a)
+    {"gemm": gemm, "attention-decode": attention_decode, "attention-prefill": attention_prefill, "sample": sample}.get(a.kernel, small)(a)
     return 0
 
 
