@@ -147,10 +147,13 @@ def main():
     weight_bytes = 2 * (layer_params + head_params)
     kv_bytes_per_token = layers * 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
 
-    def time_decode(batch, steps, warmup):
-        """Prefill `batch` prompts of U[128, 2048) tokens, then time `steps` single-token steps."""
+    def draw_prompts(batch):
         lens = rng.integers(PROMPT_RANGE[0], PROMPT_RANGE[1], size=batch).tolist()
-        prompts = [rng.integers(0, cfg["vocab_size"], size=n).tolist() for n in lens]
+        return [rng.integers(0, cfg["vocab_size"], size=n).tolist() for n in lens]
+
+    def time_decode(batch, steps, warmup, prompts=None):
+        """Prefill `batch` prompts of U[128, 2048) tokens, then time `steps` single-token steps."""
+        prompts = prompts or draw_prompts(batch)
         slots = [eng.alloc_slot() for _ in range(batch)]
         for b in range(batch):            # one prompt a step keeps the prefill's scratch small
             eng.step([slots[b]], [prompts[b]], None)
@@ -175,7 +178,8 @@ def main():
 
     clocks = ClockSampler()
     clocks.start()
-    ms, launches, ctx_tokens = time_decode(args.batch, args.steps, args.warmup)
+    headline_prompts = draw_prompts(args.batch)      # the device-timed and the end-to-end arm decode the same batch
+    ms, launches, ctx_tokens = time_decode(args.batch, args.steps, args.warmup, headline_prompts)
     clock_info = clocks.stop()
     value = args.batch * 1000.0 / ms
     step_bytes = weight_bytes + ctx_tokens * kv_bytes_per_token
@@ -213,8 +217,7 @@ def main():
             points[f"decode_b{b}"] = b * 1000.0 / pm
 
     # ---- end to end through the entry point ----
-    lens = rng.integers(PROMPT_RANGE[0], PROMPT_RANGE[1], size=args.batch).tolist()
-    prompts = [rng.integers(0, cfg["vocab_size"], size=n).tolist() for n in lens]
+    prompts = headline_prompts
     opts = GenerationOptions(max_tokens=args.steps + 1, sampler=SamplerConfig(temperature=0.8), seed=1, ignore_eos=True)
     runner.generate(prompts, GenerationOptions(max_tokens=args.warmup + 1, sampler=SamplerConfig(temperature=0.8),
                                                seed=1, ignore_eos=True))

@@ -20,6 +20,16 @@
 // (0, 1, 2, ...: the result does not depend on timing) and runs the epilogue for those
 // columns.  No global scratch, no atomics.
 //
+// RMSNorm folded into the products around it (both optional).  A product that adds into
+// the residual can, in the same epilogue, write `residual * norm weight` in bf16 and, for
+// every token and every 32 output columns (one epilogue warp of one tile), the sum of the
+// squares of the new residual values, each in its own place (no atomics, no barrier).  The
+// product that consumes that bf16 matrix multiplies its accumulator rows by
+// rsqrt(sum of those sums / K + eps) before the bias: W (r x g) = r W (x g), r being
+// one number a token.  Sums and r are float; the norm's own kernel, one more launch
+// between two products, is not needed then.  For up to 64 tokens (where a launch costs as
+// much as the norm itself); above, the norm keeps its kernel.
+//
 // Every wait on an mbarrier is bounded: when it runs out the kernel records a code
 // in the error word, all roles leave their loops, tensor memory is freed and the
 // kernel returns.
@@ -33,6 +43,23 @@ enum { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_OUT_ADD_F32 = 2, TC_OUT_SWIGLU = 3 };
 // silu(g) * u for a result that is stored in bf16: the fast exponential and division are
 // accurate to a few units in the last place of a float, far below bf16's rounding step
 __device__ __forceinline__ float silu_mul(float g, float u) { return g * __fdividef(1.0f, 1.0f + __expf(-g)) * u; }
+
+// The optional norm work of an epilogue.
+struct TcFuse {
+  // consumer: sums of squares of the input rows, [M, scale_count]; the accumulator row of
+  // token m is multiplied by rsqrt(sum_i scale_partials[m][i] / K + scale_eps).  null: none
+  const float* scale_partials;
+  int scale_count;
+  float scale_eps;
+  // producer (add-into-residual only): norm_out[m][n] = bf16(new residual * norm_weight[n]),
+  // norm_partials[m][4 * tile + w] = sum of (new residual)^2 over columns 32 w .. 32 w + 31
+  // of the tile, norm_count = 4 * tiles numbers a token.  null: none
+  const float* norm_weight;
+  __nv_bfloat16* norm_out;
+  int ld_norm;
+  float* norm_partials;
+  int norm_count;
+};
 
 static constexpr int BLOCK_N_OUT = 128;   // weight rows per CTA (MMA M)
 static constexpr int BLOCK_K = 64;        // bf16 elements per stage along K = one 128-byte swizzle row
@@ -104,6 +131,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+__device__ __forceinline__ float tc_warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
 // ---- thread-block cluster ----
 __device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
 __device__ __forceinline__ uint32_t cluster_size() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
@@ -152,8 +185,42 @@ struct TcConfig {
   static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) < 8 ? (SMEM_BUDGET / STAGE_BYTES) : 8;
   static constexpr int MIN_CTAS = BT <= 64 ? 3 : 1;
   static constexpr int TMEM_COLS = BT < 32 ? 32 : BT;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int FUSE_FLOATS = BT;           // the tile's row scales
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + FUSE_FLOATS * 4;
 };
+
+// the 128 epilogue threads among themselves (barrier 1; barrier 0 is __syncthreads).  Used
+// only where all four epilogue warps arrive whatever happens (before their first bounded wait).
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Row scales of the tile's tokens from the producer's sums of squares, into rs[BT] in shared
+// memory.  Epilogue warp q takes tokens q, q + 4, ...; a token's pieces are summed over the
+// lanes (32 neighbouring numbers a load, all tokens' loads of a round issued together) and
+// then over the warp: the same order everywhere.  Ends with the epilogue warps' barrier.
+template <int BT>
+__device__ __forceinline__ void epilogue_row_scales(const TcFuse& f, int m0, int M, int K, int q, int lane, float* rs) {
+  static_assert(BT <= 64, "row scales are made in the kernel for up to 64 tokens");
+  constexpr int PER = BT / 4;
+  float acc[PER];
+#pragma unroll
+  for (int u = 0; u < PER; ++u) acc[u] = 0.f;
+  for (int i = lane; i < f.scale_count; i += 32) {
+    float v[PER];
+#pragma unroll
+    for (int u = 0; u < PER; ++u) {
+      const int m = m0 + q + 4 * u;
+      v[u] = m < M ? f.scale_partials[(size_t)m * f.scale_count + i] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < PER; ++u) acc[u] += v[u];
+  }
+#pragma unroll
+  for (int u = 0; u < PER; ++u) {
+    const float sum = tc_warp_sum(acc[u]);
+    if (lane == 0) rs[q + 4 * u] = rsqrtf(sum / (float)K + f.scale_eps);
+  }
+  epilogue_sync();
+}
 
 // The epilogue of one finished tile: the accumulator (128 weight rows x BT tokens, float,
 // in tensor memory at `tmem_acc`) goes to the output in the asked form.  Called by the four
@@ -161,15 +228,22 @@ struct TcConfig {
 template <int BT>
 __device__ __forceinline__ void tile_epilogue(uint32_t tmem_acc, int quarter, int lane, int n0, int m0, int M, int N,
                                               int ldo, const float* __restrict__ bias, void* __restrict__ out,
-                                              int out_mode) {
+                                              int out_mode, const TcFuse& fuse, float* fuse_smem) {
   const int n = n0 + quarter * 32 + lane;          // output feature of this thread
   const float b = (bias != nullptr && n < N) ? bias[n] : 0.f;
+  const float* rs = fuse_smem;                     // row scales (made by epilogue_row_scales)
+  const bool make_norm = fuse.norm_weight != nullptr && out_mode == TC_OUT_ADD_F32;
+  const float g = (make_norm && n < N) ? fuse.norm_weight[n] : 0.f;
 #pragma unroll 1
   for (int c = 0; c < BT / 16; ++c) {
     if (m0 + c * 16 >= M) break;
     uint32_t r[16];
     tmem_ld16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 16), r);
     tmem_ld_wait();
+    if (fuse.scale_partials != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * rs[c * 16 + j]);
+    }
     if (out_mode == TC_OUT_SWIGLU) {
       // weight rows are (gate_0, up_0, gate_1, up_1, ...): the even lane holds the gate, its
       // odd neighbour the up value of the same output column n / 2
@@ -185,32 +259,41 @@ __device__ __forceinline__ void tile_epilogue(uint32_t tmem_acc, int quarter, in
         const int m = m0 + c * 16 + (even ? j : j + 8);
         if ((n | 1) < N && m < M) ob[(size_t)m * ldo + (n >> 1)] = __float2bfloat16_rn(silu_mul(gate, up));
       }
+    } else if (out_mode == TC_OUT_ADD_F32) {
+      // all sixteen loads of the residual first, then the stores: a load placed after
+      // a store to the same array would wait for it, one memory latency a column
+      float* of = (float*)out;
+      const bool live = n < N;
+      float nv[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int m = m0 + c * 16 + j;
+        nv[j] = (live && m < M) ? __ldcg(of + (size_t)m * ldo + n) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int m = m0 + c * 16 + j;
+        nv[j] = (live && m < M) ? nv[j] + __uint_as_float(r[j]) + b : 0.f;
+        if (live && m < M) of[(size_t)m * ldo + n] = nv[j];
+      }
+      if (make_norm) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = m0 + c * 16 + j;
+          if (live && m < M) fuse.norm_out[(size_t)m * fuse.ld_norm + n] = __float2bfloat16_rn(nv[j] * g);
+          const float sq = tc_warp_sum(nv[j] * nv[j]);      // this warp's 32 columns of token m
+          if (lane == 0 && m < M) fuse.norm_partials[(size_t)m * fuse.norm_count + 4 * (n0 / BLOCK_N_OUT) + quarter] = sq;
+        }
+      }
     } else if (n < N) {
-      if (out_mode == TC_OUT_ADD_F32) {
-        // all sixteen loads of the residual first, then the stores: a load placed after
-        // a store to the same array would wait for it, one memory latency a column
-        float* of = (float*)out;
-        float prev[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int m = m0 + c * 16 + j;
-          prev[j] = (m < M) ? __ldcg(of + (size_t)m * ldo + n) : 0.f;
-        }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int m = m0 + c * 16 + j;
-          if (m < M) of[(size_t)m * ldo + n] = prev[j] + __uint_as_float(r[j]) + b;
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int m = m0 + c * 16 + j;
-          if (m < M) {
-            const float v = __uint_as_float(r[j]) + b;
-            const size_t o = (size_t)m * ldo + n;
-            if (out_mode == TC_OUT_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
-            else ((float*)out)[o] = v;
-          }
+      for (int j = 0; j < 16; ++j) {
+        const int m = m0 + c * 16 + j;
+        if (m < M) {
+          const float v = __uint_as_float(r[j]) + b;
+          const size_t o = (size_t)m * ldo + n;
+          if (out_mode == TC_OUT_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
+          else ((float*)out)[o] = v;
         }
       }
     }
@@ -223,13 +306,14 @@ template <int BT>
 __global__ void __launch_bounds__(TC_THREADS, TcConfig<BT>::MIN_CTAS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                const float* __restrict__ bias, void* __restrict__ out, int out_mode, int M, int N, int K,
-               int ldo, int* __restrict__ err, int kb_per_split) {
+               int ldo, int* __restrict__ err, int kb_per_split, const TcFuse fuse) {
   using Cfg = TcConfig<BT>;
   extern __shared__ uint8_t smem_raw[];
   // tiles need 1024-byte alignment for the 128-byte swizzle pattern
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* tiles = smem;
   uint64_t* bars = (uint64_t*)(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+  float* fuse_smem = (float*)(smem + Cfg::STAGES * Cfg::STAGE_BYTES + 256);
   uint64_t* full_bar = bars;                       // [STAGES]
   uint64_t* empty_bar = bars + Cfg::STAGES;        // [STAGES]
   uint64_t* accum_bar = bars + 2 * Cfg::STAGES;    // [1]
@@ -320,13 +404,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   } else {
     // ---------------- epilogue: warps 2..5, each its quarter of the 128 lanes ----------------
     rl_pdl_wait();      // before this warp reads or writes global memory
+    if (fuse.scale_partials != nullptr)      // while the products still run
+      epilogue_row_scales<BT>(fuse, m0, M, K, warp & 3, lane, fuse_smem);
     const bool ok = mbar_wait(smem_u32(accum_bar), 0, abort_flag);
     if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(err, 3); }
     tc_fence_after();
     const int quarter = warp & 3;                    // lanes this warp may read
     const int row = quarter * 32 + lane;             // accumulator row = weight row of the tile
     if (ok && num_splits == 1) {
-      tile_epilogue<BT>(tmem_base, quarter, lane, n0, m0, M, N, ldo, bias, out, out_mode);
+      tile_epilogue<BT>(tmem_base, quarter, lane, n0, m0, M, N, ldo, bias, out, out_mode, fuse, fuse_smem);
     } else if (num_splits > 1 && ok) {
       // this part's partial tile -> own shared memory (the ring is free: every MMA has
       // completed), as [token column][weight row] floats
@@ -370,6 +456,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           const float4 t = dsmem_ld4(dsmem_addr(red_local + off, (uint32_t)sp));
           v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
         }
+        if (fuse.scale_partials != nullptr) { const float rj = fuse_smem[j]; v.x *= rj; v.y *= rj; v.z *= rj; v.w *= rj; }
         v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
         if (out_mode == TC_OUT_SWIGLU) {      // v = (gate, up, gate, up) of output columns nn/2 and nn/2 + 1
           __nv_bfloat16* ob = (__nv_bfloat16*)out + (size_t)(m0 + j) * ldo + (nn >> 1);
@@ -389,15 +476,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             float4 old = *reinterpret_cast<const float4*>((float*)out + o);
             old.x += v.x; old.y += v.y; old.z += v.z; old.w += v.w;
             *reinterpret_cast<float4*>((float*)out + o) = old;
+            v = old;
           }
         } else {
-          const float e[4] = {v.x, v.y, v.z, v.w};
+          float e[4] = {v.x, v.y, v.z, v.w};
           for (int u = 0; u < 4; ++u) {
-            if (nn + u >= N) break;
+            if (nn + u >= N) { e[u] = 0.f; continue; }
             if (out_mode == TC_OUT_BF16) ((__nv_bfloat16*)out)[o + u] = __float2bfloat16_rn(e[u]);
             else if (out_mode == TC_OUT_F32) ((float*)out)[o + u] = e[u];
-            else ((float*)out)[o + u] += e[u];
+            else { e[u] += ((float*)out)[o + u]; ((float*)out)[o + u] = e[u]; }
           }
+          v = make_float4(e[0], e[1], e[2], e[3]);
+        }
+        if (fuse.norm_weight != nullptr && out_mode == TC_OUT_ADD_F32) {
+          // v = the new residual of token m0 + j in columns nn .. nn + 3 (0 beyond N); this warp
+          // holds all 128 columns of the tile for this token
+          const float e[4] = {v.x, v.y, v.z, v.w};
+          for (int u = 0; u < 4; ++u)
+            if (nn + u < N)
+              fuse.norm_out[(size_t)(m0 + j) * fuse.ld_norm + nn + u] = __float2bfloat16_rn(e[u] * fuse.norm_weight[nn + u]);
+          const float sq = tc_warp_sum((v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w));
+          // one number for the whole tile here; the places of the other three warps hold 0
+          if ((et & 31) < 4)
+            fuse.norm_partials[(size_t)(m0 + j) * fuse.norm_count + 4 * (n0 / BLOCK_N_OUT) + (et & 31)] = (et & 31) == 0 ? sq : 0.f;
         }
       }
     }
@@ -528,13 +629,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
       const int buf = t & 1;
       const uint32_t acc_phase = (t >> 1) & 1;
+      const int n0 = (tile / tiles_m) * BLOCK_N_OUT, m0 = (tile % tiles_m) * BT;
       if (!mbar_wait(smem_u32(&acc_full[buf]), acc_phase, abort_flag)) {
         if (!*abort_flag) { *abort_flag = 1; atomicExch(err, 3); }
         break;
       }
       tc_fence_after();
-      const int n0 = (tile / tiles_m) * BLOCK_N_OUT, m0 = (tile % tiles_m) * BT;
-      tile_epilogue<BT>(tmem_base + (uint32_t)(buf * BT), quarter, lane, n0, m0, M, N, ldo, bias, out, out_mode);
+      tile_epilogue<BT>(tmem_base + (uint32_t)(buf * BT), quarter, lane, n0, m0, M, N, ldo, bias, out, out_mode, TcFuse{}, nullptr);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));    // this warp has read the accumulator
@@ -609,7 +710,8 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int 
 
 template <int BT>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, void* out, int out_mode,
-                     int M, int N, int K, int ldo, int* err, int splits, int kb_per_split, cudaStream_t stream) {
+                     int M, int N, int K, int ldo, int* err, int splits, int kb_per_split, const TcFuse& fuse,
+                     cudaStream_t stream) {
   using Cfg = TcConfig<BT>;
   static bool configured = false;
   if (!configured) {
@@ -638,7 +740,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, const float* 
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BT>, mw, ma, bias, out, out_mode, M, N, K, ldo, err, kb_per_split);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BT>, mw, ma, bias, out, out_mode, M, N, K, ldo, err, kb_per_split, fuse);
   if (e != cudaSuccess) {
     rl_set_error("rl_gemm_tc: launch failed (%d parts): %s", splits, cudaGetErrorString(e));
     return RL_ERR_CUDA;
@@ -677,8 +779,17 @@ extern "C" int rl_gemm_tc_splits(int M, int N, int K) {
 // gate_1, ...) and out is bf16 [M, N/2] = silu(gate) * up.  err: device int, set non-zero if a
 // bounded wait inside the kernel ran out.  force_splits: 0 = number of K parts chosen
 // from the shapes; 1, 2, 4 or 8 = as given (for measurements).
+// RMSNorm folded in, both optional (null = not):
+//  scale_partials [M, scale_count] float: A is `x * norm weight`, not yet divided by the rms
+//    of x; the sums of squares of x's rows come in scale_count pieces a row, and row m of
+//    the product is multiplied by rsqrt(sum / K + scale_eps) before the bias.
+//  norm_weight [N] float, norm_out [M, ld_norm] bf16, norm_partials [M, 4 * ceil(N / 128)]
+//    float (out_mode 2 only): besides out += product, norm_out = bf16(out * norm_weight) and
+//    the sums of squares of out's rows in 4 * ceil(N / 128) pieces a row, for the next product.
 extern "C" int rl_gemm_tc(const void* A, const void* W, const float* bias, void* out, int out_mode, int M, int N,
-                          int K, int lda, int ldo, int* err, int force_splits, cudaStream_t stream) {
+                          int K, int lda, int ldo, int* err, int force_splits, const float* scale_partials,
+                          int scale_count, float scale_eps, const float* norm_weight, void* norm_out, int ld_norm,
+                          float* norm_partials, cudaStream_t stream) {
   RL_REQUIRE(rl_gemm_tc_supported(A, W, M, N, K, lda), "rl_gemm_tc: operands not supported (M=%d N=%d K=%d lda=%d; K and lda "
              "must be multiples of 8 and the bases 16-byte aligned)", M, N, K, lda);
   RL_REQUIRE(out_mode >= 0 && out_mode <= 3, "rl_gemm_tc: unknown output mode %d", out_mode);
@@ -686,7 +797,16 @@ extern "C" int rl_gemm_tc(const void* A, const void* W, const float* bias, void*
   RL_REQUIRE(ldo >= (out_mode == TC_OUT_SWIGLU ? N / 2 : N) && err != nullptr, "rl_gemm_tc: bad output stride or null error word");
   RL_REQUIRE(force_splits == 0 || force_splits == 1 || force_splits == 2 || force_splits == 4 || force_splits == 8,
              "rl_gemm_tc: the number of K parts must be 1, 2, 4 or 8, got %d", force_splits);
+  RL_REQUIRE(scale_partials == nullptr || scale_count > 0, "rl_gemm_tc: row scales without their sums");
+  RL_REQUIRE(norm_weight == nullptr || (out_mode == TC_OUT_ADD_F32 && norm_out != nullptr && norm_partials != nullptr && ld_norm >= N),
+             "rl_gemm_tc: the norm for the next product needs the add-into-residual mode, its two outputs and ld_norm >= N");
+  TcFuse fuse;
+  fuse.scale_partials = scale_partials; fuse.scale_count = scale_count; fuse.scale_eps = scale_eps;
+  fuse.norm_weight = norm_weight; fuse.norm_out = (__nv_bfloat16*)norm_out; fuse.ld_norm = ld_norm;
+  fuse.norm_partials = norm_partials; fuse.norm_count = 4 * ((N + BLOCK_N_OUT - 1) / BLOCK_N_OUT);
   const int bt = token_tile(M);
+  RL_REQUIRE((scale_partials == nullptr && norm_weight == nullptr) || bt <= 64,
+             "rl_gemm_tc: a norm rides in the epilogue only for up to 64 tokens, got %d", M);
   const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
   int splits = force_splits > 0 ? force_splits : rl_gemm_tc_splits(M, N, K);
   RL_REQUIRE(splits == 1 || bt <= 64, "rl_gemm_tc: K is split only for up to 64 tokens (the partial tile must fit the ring)");
@@ -698,9 +818,9 @@ extern "C" int rl_gemm_tc(const void* A, const void* W, const float* bias, void*
   rc = make_map(&ma, A, M, K, lda, bt);
   if (rc != RL_OK) return rc;
   switch (bt) {
-    case 16: return launch_tc<16>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, stream);
-    case 32: return launch_tc<32>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, stream);
-    case 64: return launch_tc<64>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, stream);
+    case 16: return launch_tc<16>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, fuse, stream);
+    case 32: return launch_tc<32>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, fuse, stream);
+    case 64: return launch_tc<64>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, fuse, stream);
     case 128: return launch_tc_persistent<128>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, stream);
     default: return launch_tc_persistent<256>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, stream);
   }

@@ -61,7 +61,7 @@ _SIGNATURES = {
     "rl_attention_prefill_tc_supported": [_c_int, _c_int, _c_int],
     "rl_gemm_tc_supported": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int],
     "rl_gemm_tc": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                   _c_void_p, _c_int, _c_void_p],
+                   _c_void_p, _c_int, _c_void_p, _c_int, _c_float, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p],
     "rl_gemm_tc_splits": [_c_int, _c_int, _c_int],
 }
 
@@ -323,12 +323,27 @@ def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bo
     return bool(library().rl_gemm_tc_supported(a.data_ptr(), w.data_ptr(), M, w.shape[0], K, lda))
 
 
+def norm_pieces(num_columns: int) -> int:
+    """How many partial sums of squares a row the matrix product writes for ``num_columns``
+    output columns when it prepares the next norm (4 per tile of 128 columns)."""
+    return 4 * (-(-num_columns // 128))
+
+
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_mode: int,
-            bias: Optional[torch.Tensor] = None, force_splits: int = 0) -> None:
+            bias: Optional[torch.Tensor] = None, force_splits: int = 0,
+            row_sumsq: Optional[torch.Tensor] = None, row_eps: float = 0.0,
+            norm_weight: Optional[torch.Tensor] = None, norm_out: Optional[torch.Tensor] = None,
+            norm_sumsq: Optional[torch.Tensor] = None) -> None:
     """out = a @ w.T (+ bias) on the tensor cores (tcgen05).  a: [M, K] bf16, w: [N, K] bf16;
     out: bf16 (OUT_SAME) or float32 (OUT_F32 store, OUT_ADD_F32 add), or, with OUT_SWIGLU,
     bf16 [M, N/2] = silu(even columns) * odd columns of the product.  force_splits: 0 = the
-    kernel's own choice of K parts; 1, 2, 4, 8 = as given."""
+    kernel's own choice of K parts; 1, 2, 4, 8 = as given.
+
+    An RMSNorm around the product can ride along.  ``row_sumsq`` [M, pieces] float32 with
+    ``row_eps``: ``a`` holds ``x * norm weight`` and row m of the product is multiplied by
+    ``rsqrt(sum(row_sumsq[m]) / K + row_eps)``.  ``norm_weight`` [N], ``norm_out`` [M, N]
+    bf16, ``norm_sumsq`` [M, norm_pieces(N)] float32 (OUT_ADD_F32 only): also
+    ``norm_out = out * norm_weight`` and the sums of squares of ``out``'s rows, in pieces."""
     _need(a, "a", torch.bfloat16, contiguous=False); _need(w, "w", torch.bfloat16); _need(out, "out", contiguous=False)
     M, K = a.shape
     N = w.shape[0]
@@ -341,10 +356,22 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_mode: int,
     if bias is not None:
         _need(bias, "bias", torch.float32)
         assert bias.numel() == N
+    pieces = 0
+    if row_sumsq is not None:
+        _need(row_sumsq, "row_sumsq", torch.float32)
+        assert row_sumsq.dim() == 2 and row_sumsq.shape[0] == M
+        pieces = row_sumsq.shape[1]
+    if norm_weight is not None:
+        _need(norm_weight, "norm_weight", torch.float32); _need(norm_out, "norm_out", torch.bfloat16)
+        _need(norm_sumsq, "norm_sumsq", torch.float32)
+        assert out_mode == OUT_ADD_F32 and norm_weight.numel() == N and norm_out.shape == (M, N)
+        assert norm_sumsq.shape == (M, norm_pieces(N))
     lda = a.stride(0) if M > 1 else K
     ldo = out.stride(0) if M > 1 else out.shape[1]
     _check(library().rl_gemm_tc(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), out_mode, M, N, K, lda, ldo,
-                                _tc_error_word(a.device).data_ptr(), int(force_splits), _stream()), "rl_gemm_tc")
+                                _tc_error_word(a.device).data_ptr(), int(force_splits),
+                                _ptr(row_sumsq), pieces, float(row_eps),
+                                _ptr(norm_weight), _ptr(norm_out), N, _ptr(norm_sumsq), _stream()), "rl_gemm_tc")
     _count()
 
 

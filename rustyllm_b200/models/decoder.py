@@ -122,7 +122,9 @@ class DecoderModel:
     def forward(self, step, cache: SequenceCache) -> torch.Tensor:
         """All tokens of the step through all scheduled layers: float32 [M, d]."""
         x = self.embedding.forward(step.tokens)
-        for pos, li in enumerate(self.spec.schedule):
+        schedule = self.spec.schedule
+        pending = None      # the next block's first norm, started by the block in front of it
+        for pos, li in enumerate(schedule):
             entry, writes = self.run_entry[pos]
             where = cache.entry_group[entry]
             view = CacheView(
@@ -130,7 +132,14 @@ class DecoderModel:
                 kv_layer=where[1] if where else 0,
                 state=cache.state_entry(entry),
                 writes=writes)
-            self.blocks[li].forward(x, step, view)
+            block = self.blocks[li]
+            if block.folds_norms:
+                nxt = self.blocks[schedule[pos + 1]] if pos + 1 < len(schedule) else None
+                want = nxt.first_norm_request(x.shape[0]) if nxt is not None and nxt.folds_norms else None
+                pending = block.forward(x, step, view, pending=pending, next_norm=want)
+            else:
+                block.forward(x, step, view)
+                pending = None
         return x
 
     def logits(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:

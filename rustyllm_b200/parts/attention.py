@@ -19,7 +19,7 @@ from .. import kernels as K
 from ..cache.sequence_cache import KVNeed
 from ..config.spec import ParamSource, ParamSpec, PartSpec
 from .base import Mixer, Runtime
-from .linear import OUT_ADD_F32, OUT_SAME, linear
+from .linear import OUT_ADD_F32, OUT_SAME, can_fold_norms, linear
 from .registry import build_part, register_mixer
 
 
@@ -61,7 +61,12 @@ class GQAttention(Mixer):
     def kv_need(self) -> KVNeed:
         return KVNeed(self.G, self.hd, self.window)
 
-    def forward(self, xn: torch.Tensor, residual: torch.Tensor, step, cache) -> None:
+    folds_norms = True
+
+    def takes_normed_input(self, num_tokens: int) -> bool:
+        return can_fold_norms(self.wqkv, self.runtime.compute_dtype, num_tokens)
+
+    def forward(self, xn, residual: torch.Tensor, step, cache, then_norm=None):
         H, G, hd = self.H, self.G, self.hd
         M = xn.shape[0]
         dt = xn.dtype
@@ -76,4 +81,4 @@ class GQAttention(Mixer):
         attn = torch.empty((M, H * hd), dtype=dt, device=xn.device)
         K.attention(qkv, k_pool, v_pool, group.page_table, step, attn, H, G, hd, self.scale,
                     self.window or 0)
-        linear(attn, self.wo, residual, OUT_ADD_F32, self.bo)
+        return linear(attn, self.wo, residual, OUT_ADD_F32, self.bo, then_norm=then_norm)

@@ -27,7 +27,13 @@ Roles and what each must provide:
     ``forward(xn, residual, step) -> None``: same contract without a cache.
 ``Block``
     Built from (mixer, mixer_norm, feed_forward, feed_forward_norm);
-    ``forward(x, step, cache) -> None`` updates the residual x in place.
+    ``forward(x, step, cache, pending=None, next_norm=None)`` updates the residual x in
+    place.
+
+Norm folding (optional, see ``NormRequest`` / ``NormedInput``): a product that adds into the
+residual can start the norm that follows it, and the product behind that norm finishes it,
+which saves the norm's own kernel.  Parts that can do so say ``folds_norms = True``; every
+other part is called with plain tensors as described above.
 """
 from __future__ import annotations
 
@@ -38,6 +44,37 @@ import torch
 
 from ..cache.sequence_cache import KVNeed, StateNeed
 from ..config.spec import ParamSpec
+
+
+@dataclass(frozen=True)
+class NormRequest:
+    """What a product needs to prepare a row norm of its result for whoever reads it
+    next: y = x / sqrt(mean(x^2) + eps) * weight."""
+    weight: torch.Tensor          # [d] float32
+    eps: float
+
+
+@dataclass
+class NormedInput:
+    """A row norm that is started but not finished.  ``weighted`` = x * norm weight in the
+    compute dtype ([M, d]); ``sumsq`` [M, pieces] float32 = the sum of squares of each row
+    of x, in pieces.  The matrix product that reads it multiplies its result rows by
+    rsqrt(sum(sumsq[m]) / d + eps), which is the same as normalising its input."""
+    weighted: torch.Tensor
+    sumsq: torch.Tensor
+    eps: float
+
+    @property
+    def shape(self):
+        return self.weighted.shape
+
+    @property
+    def dtype(self):
+        return self.weighted.dtype
+
+    @property
+    def device(self):
+        return self.weighted.device
 
 
 @dataclass(frozen=True)
@@ -68,12 +105,28 @@ class Norm(Part):
     def forward(self, x: torch.Tensor, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
 
+    def request(self) -> Optional[NormRequest]:
+        """If this norm is y = x / sqrt(mean(x^2) + eps) * weight, what a neighbouring
+        product needs to do it on the way (else ``None``: the norm runs its own kernel)."""
+        return None
+
 
 class PositionEncoding(Part):
     pass
 
 
 class Mixer(Part):
+    # True for a part whose ``forward`` takes the two optional arguments of norm folding:
+    # ``xn`` may be a ``NormedInput`` whenever ``takes_normed_input(num_tokens)`` holds, and
+    # ``then_norm=NormRequest`` asks its last product to prepare the next norm; it returns
+    # the ``NormedInput`` it made or ``None``.  A part that leaves this False is called as
+    # ``forward(xn, residual, step, cache)`` with a plain tensor, and the norms around it
+    # run their own kernels.
+    folds_norms: bool = False
+
+    def takes_normed_input(self, num_tokens: int) -> bool:
+        return False
+
     def kv_need(self) -> Optional[KVNeed]:
         return None
 
@@ -85,10 +138,28 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    folds_norms: bool = False     # as for Mixer; ``forward(xn, residual, step, then_norm=None)``
+
+    def takes_normed_input(self, num_tokens: int) -> bool:
+        return False
+
     def forward(self, xn: torch.Tensor, residual: torch.Tensor, step) -> None:
         raise NotImplementedError
 
 
 class Block(Part):
-    def forward(self, x: torch.Tensor, step, cache) -> None:
+    # True for a block whose ``forward`` takes ``pending`` and ``next_norm``; a block that
+    # leaves this False is called as ``forward(x, step, cache)``.
+    folds_norms: bool = False
+
+    def forward(self, x: torch.Tensor, step, cache, pending=None, next_norm=None):
+        """Updates the residual x in place.  ``pending``: the block's first norm of x,
+        started by the previous block's last product (only given if ``first_norm_request``
+        returned a request).  ``next_norm``: what the next block's first norm needs;
+        returns the ``NormedInput`` made for it, or ``None``."""
         raise NotImplementedError
+
+    def first_norm_request(self, num_tokens: int) -> Optional[NormRequest]:
+        """What a product in front of this block needs to start the block's first norm,
+        if the block can take it that way in a step of ``num_tokens`` tokens."""
+        return None

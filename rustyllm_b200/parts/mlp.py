@@ -16,8 +16,8 @@ import torch
 
 from .. import kernels as K
 from ..config.spec import ParamSource, ParamSpec
-from .base import FeedForward, Runtime
-from .linear import OUT_ADD_F32, OUT_SAME, linear
+from .base import FeedForward, NormedInput, Runtime
+from .linear import OUT_ADD_F32, OUT_SAME, can_fold_norms, linear
 from .registry import register_feed_forward
 
 
@@ -48,16 +48,23 @@ class GatedMLP(FeedForward):
             specs["bdown"] = ParamSpec((ParamSource(n["down"] + ".bias", (d,)),), role="vector")
         return specs
 
-    def forward(self, xn: torch.Tensor, residual: torch.Tensor, step) -> None:
+    folds_norms = True
+
+    def takes_normed_input(self, num_tokens: int) -> bool:
+        return self.interleaved and can_fold_norms(self.wgu, self.runtime.compute_dtype, num_tokens)
+
+    def forward(self, xn, residual: torch.Tensor, step, then_norm=None):
         M = xn.shape[0]
         h = torch.empty((M, self.I), dtype=xn.dtype, device=xn.device)
         # The activation runs in the product's epilogue: with few tokens the kernel streams
         # weights and the epilogue is idle time anyway; with many, the persistent kernel drains
         # one accumulator while the tensor cores fill the other.
-        if self.interleaved and self.wgu.dtype == torch.bfloat16 and K.gemm_tc_supported(xn, self.wgu, None):
-            K.gemm_tc(xn, self.wgu, h, K.OUT_SWIGLU, self.bgu)
+        x = xn.weighted if isinstance(xn, NormedInput) else xn
+        if self.interleaved and self.wgu.dtype == torch.bfloat16 and K.gemm_tc_supported(x, self.wgu, None):
+            kw = dict(row_sumsq=xn.sumsq, row_eps=xn.eps) if isinstance(xn, NormedInput) else {}
+            K.gemm_tc(x, self.wgu, h, K.OUT_SWIGLU, self.bgu, **kw)
         else:
             gu = torch.empty((M, 2 * self.I), dtype=xn.dtype, device=xn.device)
             linear(xn, self.wgu, gu, OUT_SAME, self.bgu)
             K.swiglu(gu, h, interleaved=self.interleaved)
-        linear(h, self.wdown, residual, OUT_ADD_F32, self.bdown)
+        return linear(h, self.wdown, residual, OUT_ADD_F32, self.bdown, then_norm=then_norm)

@@ -12,7 +12,7 @@ import torch
 
 from .. import kernels as K
 from ..config.spec import ParamSource, ParamSpec
-from .base import Norm, Runtime
+from .base import Norm, NormRequest, Runtime
 from .registry import register_norm
 
 
@@ -33,3 +33,6 @@ class RMSNorm(Norm):
         out = torch.empty((n, self.size), dtype=out_dtype, device=x.device)
         K.rmsnorm(x, self.weight, out, self.eps, rows)
         return out
+
+    def request(self) -> Optional[NormRequest]:
+        return NormRequest(self.weight, self.eps) if self.weight is not None else None

@@ -201,8 +201,78 @@ def test_gemm_tc_split_k_is_deterministic_and_matches_the_unsplit_product(M, N, 
         assert k.gemm_tc_splits(M, N, K_) > 1
 
 
+@pytest.mark.parametrize("M,N,K_,parts", [(8, 384, 512, 0), (8, 384, 512, 1), (5, 200, 256, 4), (40, 136, 192, 2),
+                                          (64, 512, 1024, 8), (33, 264, 320, 0), (64, 520, 128, 1)])
+def test_gemm_tc_starts_the_norm_of_the_updated_residual(M, N, K_, parts):
+    """Add-into-residual epilogue with the next RMSNorm riding along: the residual times
+    the norm weight in bf16, and the rows' sums of squares in pieces."""
+    k = K()
+    a = _rand(M, K_, dtype=torch.bfloat16, seed=31)
+    w = _rand(N, K_, dtype=torch.bfloat16, seed=32, scale=0.2)
+    bias = _rand(N, seed=33)
+    g = (_rand(N, seed=34) * 0.3 + 1.0)
+    res = _rand(M, N, seed=35, scale=3.0)
+    out = res.clone()
+    xg = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    sumsq = torch.full((M, k.norm_pieces(N)), float("nan"), device=DEV)
+    k.gemm_tc(a, w, out, k.OUT_ADD_F32, bias, force_splits=parts, norm_weight=g, norm_out=xg, norm_sumsq=sumsq)
+    k.check_device_errors()
+    plain = res.clone()
+    k.gemm_tc(a, w, plain, k.OUT_ADD_F32, bias, force_splits=parts)
+    assert torch.equal(out, plain)                                   # the residual itself is what it was without the norm
+    assert torch.equal(xg, (out * g).to(torch.bfloat16))             # float product, rounded once
+    want = (out.double() ** 2).sum(1)
+    torch.testing.assert_close(sumsq.double().sum(1), want, rtol=1e-5, atol=0)
+    assert not torch.isnan(sumsq).any()
+
+
+@pytest.mark.parametrize("mode", ["same", "f32", "add", "swiglu"])
+@pytest.mark.parametrize("M,N,K_,parts", [(8, 384, 512, 0), (8, 384, 512, 1), (5, 200, 256, 4), (40, 136, 192, 2),
+                                          (33, 264, 320, 0), (64, 520, 128, 1), (17, 4096, 4096, 0)])
+def test_gemm_tc_finishes_a_norm_of_its_input(M, N, K_, parts, mode):
+    """The input is x * norm weight; the epilogue multiplies row m by rsqrt(mean(x_m^2) + eps),
+    the mean coming as sums of squares in pieces: the result is the product with RMSNorm(x)."""
+    k = K()
+    eps = 1e-3
+    x = _rand(M, K_, seed=41, scale=5.0) * (1 + torch.arange(M, device=DEV).float()[:, None])    # rows of very different size
+    g = _rand(K_, seed=42) * 0.3 + 1.0
+    xg = (x * g).to(torch.bfloat16)
+    w = _rand(N, K_, dtype=torch.bfloat16, seed=43, scale=0.2)
+    bias = _rand(N, seed=44)
+    pieces = 7
+    cut = torch.rand(M, pieces, device=DEV) + 0.1
+    sumsq = ((x.double() ** 2).sum(1, keepdim=True) * (cut / cut.sum(1, keepdim=True)).double()).float().contiguous()
+    r = 1.0 / torch.sqrt((x.double().cpu() ** 2).mean(1, keepdim=True) + eps)
+    y = (xg.double().cpu() @ w.double().cpu().T) * r + bias.double().cpu()
+    res = _rand(M, N, seed=45)
+    tol = dict(rtol=1e-4, atol=2e-5 * math.sqrt(K_) * 4)
+    if mode == "same":
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        k.gemm_tc(xg, w, out, k.OUT_SAME, bias, force_splits=parts, row_sumsq=sumsq, row_eps=eps)
+        torch.testing.assert_close(out.double().cpu(), y, rtol=1e-2, atol=1e-2)
+    elif mode == "f32":
+        out = torch.empty(M, N, device=DEV)
+        k.gemm_tc(xg, w, out, k.OUT_F32, bias, force_splits=parts, row_sumsq=sumsq, row_eps=eps)
+        torch.testing.assert_close(out.double().cpu(), y, **tol)
+    elif mode == "add":
+        out = res.clone()
+        k.gemm_tc(xg, w, out, k.OUT_ADD_F32, bias, force_splits=parts, row_sumsq=sumsq, row_eps=eps)
+        torch.testing.assert_close(out.double().cpu(), y + res.double().cpu(), **tol)
+    else:
+        if N % 2:
+            pytest.skip("the SwiGLU epilogue needs an even number of rows")
+        out = torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV)
+        k.gemm_tc(xg, w, out, k.OUT_SWIGLU, bias, force_splits=parts, row_sumsq=sumsq, row_eps=eps)
+        torch.testing.assert_close(out.double().cpu(), P.swiglu(y[:, 0::2], y[:, 1::2]), rtol=2e-2, atol=2e-2)
+    k.check_device_errors()
+
+
 def test_gemm_tc_strided_rows_and_refusals():
     k = K()
+    # a norm rides along for up to 64 tokens only
+    with pytest.raises(k.KernelError, match="up to 64 tokens"):
+        k.gemm_tc(_rand(65, 64, dtype=torch.bfloat16), _rand(128, 64, dtype=torch.bfloat16), torch.empty(65, 128, device=DEV),
+                  k.OUT_F32, row_sumsq=torch.ones(65, 4, device=DEV), row_eps=1e-5)
     wide = _rand(40, 640, dtype=torch.bfloat16, seed=8)
     w = _rand(200, 256, dtype=torch.bfloat16, seed=9)
     a = wide[:, 128:384]
