@@ -160,3 +160,27 @@ def test_bad_requests_are_refused_before_anything_runs(model_dirs):
         r.engine.step([s], [[0] * 129], "last")       # max_position_embeddings is 128
     assert r.cache.length(s) == 0
     r.engine.free_slot(s)
+
+
+@pytest.mark.parametrize("name", ["B", "C", "D"])
+def test_folded_norms_save_launches_and_give_the_norm_kernels_results(model_dirs, name, monkeypatch):
+    """In a bf16 step of up to 64 tokens every RMSNorm between two matrix products rides in
+    their epilogues; with that switched off the norm kernels run.  Same logits either way
+    (to bf16 rounding), 2 * layers - 1 launches apart."""
+    from rustyllm_b200 import kernels
+    from rustyllm_b200.parts import linear
+    d, cfg = model_dirs[name]
+    toks = random_tokens(_vocab(cfg), 40, 7)
+    ref = plain_logits(d, toks)
+    out, launches = {}, {}
+    for mode, limit in (("folded", linear.FOLD_NORMS_UP_TO), ("kernels", 0)):
+        monkeypatch.setattr(linear, "FOLD_NORMS_UP_TO", limit)
+        r = load_runner(d, "bfloat16")
+        s = r.engine.alloc_slot()
+        before = kernels.launch_count
+        out[mode] = r.engine.step([s], [toks], "all")
+        launches[mode] = kernels.launch_count - before
+        r.engine.free_slot(s)
+        assert_close_logits(out[mode], ref, "bfloat16", f"{name} {mode}")
+    assert launches["kernels"] - launches["folded"] == 2 * cfg["num_hidden_layers"] - 1
+    assert not torch.equal(out["folded"], out["kernels"])      # the other order of roundings shows
