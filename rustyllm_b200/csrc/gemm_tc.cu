@@ -30,6 +30,16 @@
 // between two products, is not needed then.  For up to 64 tokens (where a launch costs as
 // much as the norm itself); above, the norm keeps its kernel.
 //
+// Rotary encoding and the cache write folded into the QKV product (optional, head size 128,
+// up to 64 tokens, K split over a cluster): a tile of 128 output columns is one head, and
+// in the cluster epilogue one warp holds all of it for a token, so the pair (i, i + 64) is
+// an exchange between two lanes.  Query heads are rotated and stored to the output; key
+// heads are rotated and stored to their place in the paged cache, value heads stored
+// there as they are (SimonWaldherr/RustyLLM src/model.rs:5562-5647, 7233-7236): the separate
+// rotation kernel and its launch are not needed.  Angles are float(pos) * inv_freq in
+// 32-bit with the accurate sincosf, applied to the float accumulator (one rounding to
+// bf16 instead of two).
+//
 // Every wait on an mbarrier is bounded: when it runs out the kernel records a code
 // in the error word, all roles leave their loops, tensor memory is freed and the
 // kernel returns.
@@ -38,7 +48,7 @@
 
 #include "common.cuh"
 
-enum { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_OUT_ADD_F32 = 2, TC_OUT_SWIGLU = 3 };
+enum { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_OUT_ADD_F32 = 2, TC_OUT_SWIGLU = 3, TC_OUT_ROPE_KV = 4 };
 
 // silu(g) * u for a result that is stored in bf16: the fast exponential and division are
 // accurate to a few units in the last place of a float, far below bf16's rounding step
@@ -59,6 +69,16 @@ struct TcFuse {
   int ld_norm;
   float* norm_partials;
   int norm_count;
+  // rotary encoding + cache write (out_mode TC_OUT_ROPE_KV only)
+  const int* positions;         // [M]
+  const int* slot_of_token;     // [M]
+  const int* page_table;        // [slots, max_pages]
+  int max_pages;
+  const float* inv_freq;        // [64]
+  int interleaved;              // pairs (2i, 2i+1) instead of (i, i + 64)
+  int num_heads, num_kv_heads;
+  __nv_bfloat16* k_pool;        // [pages, kv_heads, RL_PAGE, 128]; null: keys and values are not stored
+  __nv_bfloat16* v_pool;
 };
 
 static constexpr int BLOCK_N_OUT = 128;   // weight rows per CTA (MMA M)
@@ -185,7 +205,7 @@ struct TcConfig {
   static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) < 8 ? (SMEM_BUDGET / STAGE_BYTES) : 8;
   static constexpr int MIN_CTAS = BT <= 64 ? 3 : 1;
   static constexpr int TMEM_COLS = BT < 32 ? 32 : BT;
-  static constexpr int FUSE_FLOATS = BT;           // the tile's row scales
+  static constexpr int FUSE_FLOATS = 3 * BT;       // the tile's row scales; its tokens' positions and cache rows
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + FUSE_FLOATS * 4;
 };
 
@@ -406,6 +426,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     rl_pdl_wait();      // before this warp reads or writes global memory
     if (fuse.scale_partials != nullptr)      // while the products still run
       epilogue_row_scales<BT>(fuse, m0, M, K, warp & 3, lane, fuse_smem);
+    if (out_mode == TC_OUT_ROPE_KV) {
+      // position of every token of the tile and the row of the cache pools it is stored in
+      int* tok_pos = (int*)(fuse_smem + BT);
+      int* tok_row = tok_pos + BT;
+      for (int t = threadIdx.x - 64; t < BT; t += 128) {
+        const int m = m0 + t;
+        int pos = 0, row = 0;
+        if (m < M) {
+          pos = fuse.positions[m];
+          if (fuse.k_pool != nullptr) {
+            const int page = fuse.page_table[(size_t)fuse.slot_of_token[m] * fuse.max_pages + pos / RL_PAGE];
+            row = page * fuse.num_kv_heads * RL_PAGE + pos % RL_PAGE;        // + kv head * RL_PAGE
+          }
+        }
+        tok_pos[t] = pos; tok_row[t] = row;
+      }
+      epilogue_sync();
+    }
     const bool ok = mbar_wait(smem_u32(accum_bar), 0, abort_flag);
     if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(err, 3); }
     tc_fence_after();
@@ -458,6 +496,48 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         if (fuse.scale_partials != nullptr) { const float rj = fuse_smem[j]; v.x *= rj; v.y *= rj; v.z *= rj; v.w *= rj; }
         v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+        if (out_mode == TC_OUT_ROPE_KV) {
+          // the tile is head n0 / 128 of (query heads, key heads, value heads); this lane holds
+          // its dimensions r4 .. r4 + 3 for token m0 + j
+          const int head = n0 / BLOCK_N_OUT;
+          const int H = fuse.num_heads, G = fuse.num_kv_heads;
+          const int* tok_pos = (const int*)(fuse_smem + BT);
+          const int* tok_row = tok_pos + BT;
+          float e[4] = {v.x, v.y, v.z, v.w};
+          if (head < H + G) {
+            const float pos = (float)tok_pos[j];
+            if (fuse.interleaved) {             // pairs (r4, r4 + 1) and (r4 + 2, r4 + 3), frequencies r4 / 2 and r4 / 2 + 1
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                float sn, cs;
+                sincosf(pos * fuse.inv_freq[r4 / 2 + u], &sn, &cs);
+                const float x0 = e[2 * u], x1 = e[2 * u + 1];
+                e[2 * u] = x0 * cs - x1 * sn;
+                e[2 * u + 1] = x0 * sn + x1 * cs;
+              }
+            } else {                            // pairs (i, i + 64): the partner sits 16 lanes away
+              const bool low = r4 < 64;
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const float other = __shfl_xor_sync(0xffffffffu, e[u], 16);
+                float sn, cs;
+                sincosf(pos * fuse.inv_freq[(r4 & 63) + u], &sn, &cs);
+                e[u] = low ? e[u] * cs - other * sn : other * sn + e[u] * cs;
+              }
+            }
+          }
+          __nv_bfloat162 lo = __floats2bfloat162_rn(e[0], e[1]), hi = __floats2bfloat162_rn(e[2], e[3]);
+          const uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+          if (head < H) {
+            *reinterpret_cast<uint2*>((__nv_bfloat16*)out + (size_t)(m0 + j) * ldo + nn) = pk;
+          } else if (fuse.k_pool != nullptr) {
+            const bool is_v = head >= H + G;
+            const int g = head - (is_v ? H + G : H);
+            __nv_bfloat16* pool = is_v ? fuse.v_pool : fuse.k_pool;
+            *reinterpret_cast<uint2*>(pool + ((size_t)tok_row[j] + (size_t)g * RL_PAGE) * BLOCK_N_OUT + r4) = pk;
+          }
+          continue;
+        }
         if (out_mode == TC_OUT_SWIGLU) {      // v = (gate, up, gate, up) of output columns nn/2 and nn/2 + 1
           __nv_bfloat16* ob = (__nv_bfloat16*)out + (size_t)(m0 + j) * ldo + (nn >> 1);
           if (nn + 1 < N) ob[0] = __float2bfloat16_rn(silu_mul(v.x, v.y));
@@ -786,24 +866,21 @@ extern "C" int rl_gemm_tc_splits(int M, int N, int K) {
 //  norm_weight [N] float, norm_out [M, ld_norm] bf16, norm_partials [M, 4 * ceil(N / 128)]
 //    float (out_mode 2 only): besides out += product, norm_out = bf16(out * norm_weight) and
 //    the sums of squares of out's rows in 4 * ceil(N / 128) pieces a row, for the next product.
-extern "C" int rl_gemm_tc(const void* A, const void* W, const float* bias, void* out, int out_mode, int M, int N,
-                          int K, int lda, int ldo, int* err, int force_splits, const float* scale_partials,
-                          int scale_count, float scale_eps, const float* norm_weight, void* norm_out, int ld_norm,
-                          float* norm_partials, cudaStream_t stream) {
+static int gemm_tc_run(const void* A, const void* W, const float* bias, void* out, int out_mode, int M, int N,
+                       int K, int lda, int ldo, int* err, int force_splits, TcFuse fuse, cudaStream_t stream) {
+  const float* scale_partials = fuse.scale_partials;
+  const float* norm_weight = fuse.norm_weight;
   RL_REQUIRE(rl_gemm_tc_supported(A, W, M, N, K, lda), "rl_gemm_tc: operands not supported (M=%d N=%d K=%d lda=%d; K and lda "
              "must be multiples of 8 and the bases 16-byte aligned)", M, N, K, lda);
-  RL_REQUIRE(out_mode >= 0 && out_mode <= 3, "rl_gemm_tc: unknown output mode %d", out_mode);
+  RL_REQUIRE(out_mode >= 0 && out_mode <= 4, "rl_gemm_tc: unknown output mode %d", out_mode);
   RL_REQUIRE(out_mode != TC_OUT_SWIGLU || N % 2 == 0, "rl_gemm_tc: the SwiGLU epilogue needs an even number of weight rows, got %d", N);
   RL_REQUIRE(ldo >= (out_mode == TC_OUT_SWIGLU ? N / 2 : N) && err != nullptr, "rl_gemm_tc: bad output stride or null error word");
   RL_REQUIRE(force_splits == 0 || force_splits == 1 || force_splits == 2 || force_splits == 4 || force_splits == 8,
              "rl_gemm_tc: the number of K parts must be 1, 2, 4 or 8, got %d", force_splits);
-  RL_REQUIRE(scale_partials == nullptr || scale_count > 0, "rl_gemm_tc: row scales without their sums");
-  RL_REQUIRE(norm_weight == nullptr || (out_mode == TC_OUT_ADD_F32 && norm_out != nullptr && norm_partials != nullptr && ld_norm >= N),
+  RL_REQUIRE(scale_partials == nullptr || fuse.scale_count > 0, "rl_gemm_tc: row scales without their sums");
+  RL_REQUIRE(norm_weight == nullptr || (out_mode == TC_OUT_ADD_F32 && fuse.norm_out != nullptr && fuse.norm_partials != nullptr && fuse.ld_norm >= N),
              "rl_gemm_tc: the norm for the next product needs the add-into-residual mode, its two outputs and ld_norm >= N");
-  TcFuse fuse;
-  fuse.scale_partials = scale_partials; fuse.scale_count = scale_count; fuse.scale_eps = scale_eps;
-  fuse.norm_weight = norm_weight; fuse.norm_out = (__nv_bfloat16*)norm_out; fuse.ld_norm = ld_norm;
-  fuse.norm_partials = norm_partials; fuse.norm_count = 4 * ((N + BLOCK_N_OUT - 1) / BLOCK_N_OUT);
+  fuse.norm_count = 4 * ((N + BLOCK_N_OUT - 1) / BLOCK_N_OUT);
   const int bt = token_tile(M);
   RL_REQUIRE((scale_partials == nullptr && norm_weight == nullptr) || bt <= 64,
              "rl_gemm_tc: a norm rides in the epilogue only for up to 64 tokens, got %d", M);
@@ -811,6 +888,9 @@ extern "C" int rl_gemm_tc(const void* A, const void* W, const float* bias, void*
   int splits = force_splits > 0 ? force_splits : rl_gemm_tc_splits(M, N, K);
   RL_REQUIRE(splits == 1 || bt <= 64, "rl_gemm_tc: K is split only for up to 64 tokens (the partial tile must fit the ring)");
   while (splits > 1 && (splits - 1) * ((total_kb + splits - 1) / splits) >= total_kb) splits /= 2;   // no part is empty
+  RL_REQUIRE(out_mode != TC_OUT_ROPE_KV || (splits > 1 && bt <= 64),
+             "rl_gemm_tc_qkv_rope: the rotation rides only in the cluster epilogue (up to 64 tokens, K in 2 or more parts); "
+             "M=%d N=%d K=%d give %d part(s)", M, N, K, splits);
   const int kb_per = (total_kb + splits - 1) / splits;
   CUtensorMap mw, ma;
   int rc = make_map(&mw, W, N, K, K, BLOCK_N_OUT);
@@ -824,4 +904,54 @@ extern "C" int rl_gemm_tc(const void* A, const void* W, const float* bias, void*
     case 128: return launch_tc_persistent<128>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, stream);
     default: return launch_tc_persistent<256>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, stream);
   }
+}
+
+extern "C" int rl_gemm_tc(const void* A, const void* W, const float* bias, void* out, int out_mode, int M, int N,
+                          int K, int lda, int ldo, int* err, int force_splits, const float* scale_partials,
+                          int scale_count, float scale_eps, const float* norm_weight, void* norm_out, int ld_norm,
+                          float* norm_partials, cudaStream_t stream) {
+  RL_REQUIRE(out_mode != TC_OUT_ROPE_KV, "rl_gemm_tc: the rotation epilogue has its own entry point, rl_gemm_tc_qkv_rope");
+  TcFuse fuse = {};
+  fuse.scale_partials = scale_partials; fuse.scale_count = scale_count; fuse.scale_eps = scale_eps;
+  fuse.norm_weight = norm_weight; fuse.norm_out = (__nv_bfloat16*)norm_out; fuse.ld_norm = ld_norm;
+  fuse.norm_partials = norm_partials;
+  return gemm_tc_run(A, W, bias, out, out_mode, M, N, K, lda, ldo, err, force_splits, fuse, stream);
+}
+
+// 1 if rl_gemm_tc_qkv_rope takes the shape: head size 128, the whole head rotated, a step
+// of up to 64 tokens whose product is split over K (a function of the shapes only).
+extern "C" int rl_gemm_tc_qkv_rope_supported(int M, int num_heads, int num_kv_heads, int head_dim, int rotary_dim, int K) {
+  if (head_dim != BLOCK_N_OUT || rotary_dim != head_dim || M <= 0 || M > 64 || K % 8 != 0) return 0;
+  const int N = (num_heads + 2 * num_kv_heads) * head_dim;
+  const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+  int splits = rl_gemm_tc_splits(M, N, K);
+  while (splits > 1 && (splits - 1) * ((total_kb + splits - 1) / splits) >= total_kb) splits /= 2;
+  return splits > 1;
+}
+
+// The QKV product of an attention layer with rotary encoding and cache write in its
+// epilogue.  W: [(H + 2G) * 128, K] (query heads, key heads, value heads); out: [M, ldo] bf16,
+// of which the H query heads are written (rotated); keys (rotated) and values go to
+// k_pool / v_pool [pages, G, RL_PAGE, 128] at each token's position (null pools: they are
+// not stored at all).  positions, slot_of_token: [M]; inv_freq: [64] float.  scale_*: as in
+// rl_gemm_tc.  Refused unless rl_gemm_tc_qkv_rope_supported(...).
+extern "C" int rl_gemm_tc_qkv_rope(const void* A, const void* W, const float* bias, void* out, int M, int K, int lda, int ldo,
+                                   int* err, const float* scale_partials, int scale_count, float scale_eps,
+                                   const int* positions, const int* slot_of_token, const int* page_table, int max_pages,
+                                   const float* inv_freq, int interleaved, int num_heads, int num_kv_heads,
+                                   void* k_pool, void* v_pool, cudaStream_t stream) {
+  RL_REQUIRE(num_heads > 0 && num_kv_heads > 0 && positions != nullptr && inv_freq != nullptr,
+             "rl_gemm_tc_qkv_rope: bad head counts or null positions / frequencies");
+  RL_REQUIRE((k_pool == nullptr) == (v_pool == nullptr), "rl_gemm_tc_qkv_rope: give both pools or neither");
+  RL_REQUIRE(k_pool == nullptr || (slot_of_token != nullptr && page_table != nullptr && max_pages > 0),
+             "rl_gemm_tc_qkv_rope: the cache write needs slots and the page table");
+  RL_REQUIRE(((uintptr_t)out & 7) == 0 && ldo % 4 == 0 && ((uintptr_t)k_pool & 7) == 0 && ((uintptr_t)v_pool & 7) == 0,
+             "rl_gemm_tc_qkv_rope: output and pools must be 8-byte aligned, ldo a multiple of 4");
+  const int N = (num_heads + 2 * num_kv_heads) * BLOCK_N_OUT;
+  TcFuse fuse = {};
+  fuse.scale_partials = scale_partials; fuse.scale_count = scale_count; fuse.scale_eps = scale_eps;
+  fuse.positions = positions; fuse.slot_of_token = slot_of_token; fuse.page_table = page_table; fuse.max_pages = max_pages;
+  fuse.inv_freq = inv_freq; fuse.interleaved = interleaved; fuse.num_heads = num_heads; fuse.num_kv_heads = num_kv_heads;
+  fuse.k_pool = (__nv_bfloat16*)k_pool; fuse.v_pool = (__nv_bfloat16*)v_pool;
+  return gemm_tc_run(A, W, bias, out, TC_OUT_ROPE_KV, M, N, K, lda, ldo, err, 0, fuse, stream);
 }

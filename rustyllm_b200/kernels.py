@@ -63,6 +63,10 @@ _SIGNATURES = {
     "rl_gemm_tc": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                    _c_void_p, _c_int, _c_void_p, _c_int, _c_float, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p],
     "rl_gemm_tc_splits": [_c_int, _c_int, _c_int],
+    "rl_gemm_tc_qkv_rope_supported": [_c_int, _c_int, _c_int, _c_int, _c_int, _c_int],
+    "rl_gemm_tc_qkv_rope": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                            _c_void_p, _c_int, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int,
+                            _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
 }
 
 
@@ -372,6 +376,52 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_mode: int,
                                 _tc_error_word(a.device).data_ptr(), int(force_splits),
                                 _ptr(row_sumsq), pieces, float(row_eps),
                                 _ptr(norm_weight), _ptr(norm_out), N, _ptr(norm_sumsq), _stream()), "rl_gemm_tc")
+    _count()
+
+
+def gemm_tc_qkv_rope_supported(a: torch.Tensor, w: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                               rotary_dim: int) -> bool:
+    """Whether the QKV product of these operands can carry the rotary encoding and the cache
+    write in its epilogue (head size 128 rotated whole, up to 64 tokens, a product that is
+    split over K)."""
+    if not gemm_tc_supported(a, w, None) or w.shape[0] != (num_heads + 2 * num_kv_heads) * head_dim:
+        return False
+    return bool(library().rl_gemm_tc_qkv_rope_supported(a.shape[0], num_heads, num_kv_heads, head_dim, rotary_dim, a.shape[1]))
+
+
+def gemm_tc_qkv_rope(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor],
+                     positions: torch.Tensor, slot_of_token: torch.Tensor, page_table: torch.Tensor,
+                     inv_freq: torch.Tensor, interleaved: bool, num_heads: int, num_kv_heads: int,
+                     k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
+                     row_sumsq: Optional[torch.Tensor] = None, row_eps: float = 0.0) -> None:
+    """qkv = a @ w.T (+ bias) with rotary encoding of the query and key heads and the write of
+    keys and values into the paged cache, all in the product's epilogue.  Of ``out``
+    [M, (H + 2G) * 128] bf16 only the query heads are written; keys and values go to the
+    pools (``None``: nowhere).  ``row_sumsq`` / ``row_eps``: as in ``gemm_tc``."""
+    _need(a, "a", torch.bfloat16, contiguous=False); _need(w, "w", torch.bfloat16); _need(out, "out", torch.bfloat16, contiguous=False)
+    _need(positions, "positions", torch.int32); _need(slot_of_token, "slot_of_token", torch.int32)
+    _need(page_table, "page_table", torch.int32); _need(inv_freq, "inv_freq", torch.float32)
+    M, K = a.shape
+    assert w.shape == ((num_heads + 2 * num_kv_heads) * 128, K) and out.shape == (M, w.shape[0]) and out.stride(1) == 1
+    assert positions.numel() == M and slot_of_token.numel() == M and inv_freq.numel() == 64
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        assert bias.numel() == w.shape[0]
+    if k_pool is not None:
+        _need(k_pool, "k_pool", torch.bfloat16); _need(v_pool, "v_pool", torch.bfloat16)
+        assert k_pool.shape[1:] == (num_kv_heads, PAGE_SIZE, 128) and v_pool.shape == k_pool.shape
+    pieces = 0
+    if row_sumsq is not None:
+        _need(row_sumsq, "row_sumsq", torch.float32)
+        assert row_sumsq.dim() == 2 and row_sumsq.shape[0] == M
+        pieces = row_sumsq.shape[1]
+    lda = a.stride(0) if M > 1 else K
+    ldo = out.stride(0) if M > 1 else out.shape[1]
+    _check(library().rl_gemm_tc_qkv_rope(
+        a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), M, K, lda, ldo, _tc_error_word(a.device).data_ptr(),
+        _ptr(row_sumsq), pieces, float(row_eps), positions.data_ptr(), slot_of_token.data_ptr(), page_table.data_ptr(),
+        page_table.shape[1], inv_freq.data_ptr(), 1 if interleaved else 0, num_heads, num_kv_heads,
+        _ptr(k_pool), _ptr(v_pool), _stream()), "rl_gemm_tc_qkv_rope")
     _count()
 
 

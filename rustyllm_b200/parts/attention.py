@@ -18,7 +18,7 @@ import torch
 from .. import kernels as K
 from ..cache.sequence_cache import KVNeed
 from ..config.spec import ParamSource, ParamSpec, PartSpec
-from .base import Mixer, Runtime
+from .base import Mixer, NormedInput, Runtime
 from .linear import OUT_ADD_F32, OUT_SAME, can_fold_norms, linear
 from .registry import build_part, register_mixer
 
@@ -71,13 +71,22 @@ class GQAttention(Mixer):
         M = xn.shape[0]
         dt = xn.dtype
         qkv = torch.empty((M, (H + 2 * G) * hd), dtype=dt, device=xn.device)
-        linear(xn, self.wqkv, qkv, OUT_SAME, self.bqkv)
         group, layer = cache.kv_group, cache.kv_layer
         k_pool, v_pool = group.k_pool(layer), group.v_pool(layer)
         pos = self.position
-        K.rope_kv_write(qkv, step.positions, step.slot_of_token, group.page_table, pos.inv_freq, H, G, hd,
-                        pos.rotary_dim, pos.interleaved,
-                        k_pool if cache.writes else None, v_pool if cache.writes else None)
+        x = xn.weighted if isinstance(xn, NormedInput) else xn
+        if (dt == torch.bfloat16 and self.wqkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16
+                and K.gemm_tc_qkv_rope_supported(x, self.wqkv, H, G, hd, pos.rotary_dim)):
+            # few tokens: rotation and cache write ride in the product's epilogue
+            kw = dict(row_sumsq=xn.sumsq, row_eps=xn.eps) if isinstance(xn, NormedInput) else {}
+            K.gemm_tc_qkv_rope(x, self.wqkv, qkv, self.bqkv, step.positions, step.slot_of_token, group.page_table,
+                               pos.inv_freq, pos.interleaved, H, G,
+                               k_pool if cache.writes else None, v_pool if cache.writes else None, **kw)
+        else:
+            linear(xn, self.wqkv, qkv, OUT_SAME, self.bqkv)
+            K.rope_kv_write(qkv, step.positions, step.slot_of_token, group.page_table, pos.inv_freq, H, G, hd,
+                            pos.rotary_dim, pos.interleaved,
+                            k_pool if cache.writes else None, v_pool if cache.writes else None)
         attn = torch.empty((M, H * hd), dtype=dt, device=xn.device)
         K.attention(qkv, k_pool, v_pool, group.page_table, step, attn, H, G, hd, self.scale,
                     self.window or 0)

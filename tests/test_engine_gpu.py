@@ -8,7 +8,7 @@ from gpu_helpers import assert_close_logits, load_runner, plain_logits, random_t
 
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
-CONFIGS = ["A", "B", "C", "D"]
+CONFIGS = ["A", "B", "C", "D", "E"]
 
 
 def _vocab(cfg):
@@ -89,7 +89,7 @@ def test_unequal_batches_one_after_another_reuse_slots(model_dirs, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["C", "D"])
+@pytest.mark.parametrize("name", ["C", "D", "E"])
 def test_long_decoding_across_pages(model_dirs, name, dtype):
     d, cfg = model_dirs[name]
     r = load_runner(d, dtype)
@@ -162,7 +162,7 @@ def test_bad_requests_are_refused_before_anything_runs(model_dirs):
     r.engine.free_slot(s)
 
 
-@pytest.mark.parametrize("name", ["B", "C", "D"])
+@pytest.mark.parametrize("name", ["B", "C", "D", "E"])
 def test_folded_norms_save_launches_and_give_the_norm_kernels_results(model_dirs, name, monkeypatch):
     """In a bf16 step of up to 64 tokens every RMSNorm between two matrix products rides in
     their epilogues; with that switched off the norm kernels run.  Same logits either way

@@ -334,6 +334,62 @@ def test_rope_kv_write(dtype, H, G, hd, rot, interleaved):
     assert torch.equal(v_pool.permute(0, 2, 1, 3)[keep], v_before.permute(0, 2, 1, 3)[keep])
 
 
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("M,H,G,K_,normed,store", [(1, 3, 1, 1024, False, True), (8, 3, 1, 1024, True, True),
+                                                  (11, 2, 2, 2048, False, True), (33, 4, 2, 512, True, True),
+                                                  (11, 3, 1, 1024, False, False)])
+def test_gemm_tc_qkv_rope_is_the_product_then_the_rotation_and_the_cache_write(M, H, G, K_, normed, store, interleaved):
+    """The QKV product with rotation and cache write in its epilogue, against float64:
+    product, (finished norm,) bias, rotation of query and key heads, keys and values at
+    their tokens' places of the paged cache, nothing else in the pools touched."""
+    k = K()
+    hd = 128
+    N = (H + 2 * G) * hd
+    x = _rand(M, K_, seed=51, scale=2.0)
+    g = _rand(K_, seed=52) * 0.3 + 1.0
+    a = (x * g).to(torch.bfloat16) if normed else x.to(torch.bfloat16)
+    w = _rand(N, K_, dtype=torch.bfloat16, seed=53, scale=0.05)
+    bias = _rand(N, seed=54, scale=0.5)
+    assert k.gemm_tc_qkv_rope_supported(a, w, H, G, hd, hd)
+    assert not k.gemm_tc_qkv_rope_supported(a, w, H, G, hd, 64)          # partial rotation: the separate kernel
+    positions = torch.tensor(([0, 1, 63, 64, 65, 200, 5, 6, 7, 130, 131] * 3)[:M], dtype=torch.int32, device=DEV)
+    slot_of_token = torch.tensor(([0, 0, 0, 0, 0, 0, 2, 2, 2, 2, 2] + [1] * 11 + [3] * 11)[:M], dtype=torch.int32, device=DEV)
+    page_table = torch.tensor([[7, 3, 1, 9], [10, 11, 12, 13], [2, 8, 4, 5], [14, 15, 16, 17]], dtype=torch.int32, device=DEV)
+    inv = torch.tensor([1.0 / (10000.0 ** (2 * i / hd)) for i in range(hd // 2)], device=DEV)
+    k_pool, v_pool = _paged(G, hd, 18, torch.bfloat16)
+    k_before, v_before = k_pool.clone(), v_pool.clone()
+    eps = 1e-5
+    kw = {}
+    y = a.double().cpu() @ w.double().cpu().T
+    if normed:
+        sumsq = ((x.double() ** 2).sum(1, keepdim=True) * torch.tensor([[0.25, 0.5, 0.25]], device=DEV).double()).float().contiguous()
+        kw = dict(row_sumsq=sumsq, row_eps=eps)
+        y = y / torch.sqrt((x.double().cpu() ** 2).mean(1, keepdim=True) + eps)
+    y = y + bias.double().cpu()
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    k.gemm_tc_qkv_rope(a, w, out, bias, positions, slot_of_token, page_table, inv, interleaved, H, G,
+                       k_pool if store else None, v_pool if store else None, **kw)
+    k.check_device_errors()
+    q, kk, v = y[:, :H * hd].view(M, H, hd), y[:, H * hd:(H + G) * hd].view(M, G, hd), y[:, (H + G) * hd:].view(M, G, hd)
+    sin, cos = P.rope_angles(positions.cpu(), inv.cpu())
+    f = P.apply_rope_interleaved if interleaved else P.apply_rope_half
+    q, kk = f(q, sin, cos), f(kk, sin, cos)
+    tol = dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(out[:, :H * hd].double().cpu().view(M, H, hd), q, **tol)
+    if not store:
+        assert torch.equal(k_pool, k_before) and torch.equal(v_pool, v_before)
+        return
+    touched = torch.zeros(18, PAGE, dtype=torch.bool)
+    for m in range(M):
+        p = int(positions[m]); page = int(page_table[int(slot_of_token[m]), p // PAGE]); off = p % PAGE
+        touched[page, off] = True
+        torch.testing.assert_close(k_pool[page, :, off].double().cpu(), kk[m], **tol)
+        torch.testing.assert_close(v_pool[page, :, off].double().cpu(), v[m], **tol)
+    keep = ~touched.to(DEV)
+    assert torch.equal(k_pool.permute(0, 2, 1, 3)[keep], k_before.permute(0, 2, 1, 3)[keep])
+    assert torch.equal(v_pool.permute(0, 2, 1, 3)[keep], v_before.permute(0, 2, 1, 3)[keep])
+
+
 # ----------------------------------------------------------------------------- attention
 def _attention_case(dtype, H, G, hd, lens_q, lens_kv, window=0, seed=0, craft=None):
     """Builds a paged cache with scrambled pages for sequences of lens_kv tokens; the

@@ -39,6 +39,14 @@ TINY = {
         "rope_scaling": {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0,
                          "high_freq_factor": 4.0, "original_max_position_embeddings": 256},
         "tie_word_embeddings": True}),
+    # 2 layers, GQA 4/2, head 128, hidden 512: decode-sized steps split the QKV product over K, so
+    # rotation and cache write ride in its epilogue; prefill attention takes the tcgen05 kernel
+    "E": dict(seed=4, norm_noise=True, dtype="bfloat16", config={
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+        "vocab_size": 272, "hidden_size": 512, "intermediate_size": 640, "num_hidden_layers": 2,
+        "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 128,
+        "max_position_embeddings": 512, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+        "tie_word_embeddings": False, "attention_bias": True}),
 }
 
 
