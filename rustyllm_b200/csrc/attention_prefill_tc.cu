@@ -10,16 +10,22 @@
 //               128-byte swizzle, K-major like the matrix products), S in tensor memory
 //               (two buffers: the next tile's scores are computed while this tile's
 //               are being exponentiated)
-//   softmax     four warps, one query row a thread (= one lane of tensor memory): no
-//               shuffles; running maximum kept lazily - the accumulator is only rescaled
+//   softmax     eight warps, two threads a query row (= one lane of tensor memory; two
+//               warps may read the same lanes), 64 keys each: no shuffles, the two exchange
+//               their maxima through shared memory once a tile; running maximum kept lazily - the accumulator is only rescaled
 //               when the maximum has grown by more than 2^8, so most tiles skip the
-//               read-modify-write of O in tensor memory; P is written as bf16 into
-//               shared memory in the swizzled K-major layout the MMA reads
-//   O += P V    tcgen05.mma with P from shared memory as A and the value tile as an
+//               read-modify-write of O in tensor memory; P is written as bf16 over the
+//               first 64 columns of the S buffer it came from (tcgen05.st): it never
+//               touches shared memory
+//   O += P V    tcgen05.mma with P in tensor memory as A and the value tile as an
 //               MN-major B operand (values are stored [position][head_dim]); O stays in
-//               tensor memory over all key tiles
+//               tensor memory over all key tiles.  The products of one thread run in the
+//               order they were issued, so the S of tile i + 2, which overwrites P of
+//               tile i, needs no barrier of its own
 // A key tile is two cache pages (128 positions).  Warp 0 feeds TMA, warp 1 issues MMAs,
-// warps 2-5 do the softmax and the final normalisation.  Every mbarrier wait is bounded.
+// warps 2-9 do the softmax and the final normalisation.  Every mbarrier wait is bounded; a
+// softmax warp whose wait ran out stops working but keeps arriving at the softmax warps'
+// own barrier until the loop ends, so that nobody waits there for ever.
 //
 // Rows of a page beyond the sequence's length are never selected (their probabilities
 // are exactly 0), but they are multiplied: the cache pools must not hold NaN or Inf
@@ -35,14 +41,14 @@ namespace {
 constexpr int TQ = 128;          // query rows per CTA
 constexpr int TK = 128;          // keys per tile = two pages
 constexpr int HD = 128;
-constexpr int FA_THREADS = 192;
+constexpr int FA_THREADS = 320;       // warp 0: TMA, warp 1: MMA, warps 2-9: softmax
 constexpr uint32_t FA_WAIT_LIMIT = 1u << 22;
 constexpr int KV_STAGES = 2;
 constexpr int HALF_BYTES = 128 * 64 * 2;               // [128 rows x 64 bf16], 16 KB
 constexpr int Q_BYTES = 2 * HALF_BYTES;                // 32 KB
 constexpr int KV_STAGE_BYTES = 4 * HALF_BYTES;         // K halves, V halves: 64 KB
-constexpr int P_BYTES = 2 * HALF_BYTES;                // 32 KB
-constexpr int FA_SMEM = Q_BYTES + KV_STAGES * KV_STAGE_BYTES + P_BYTES + 1024 + 256;
+constexpr int FA_XCHG_BYTES = 3 * 2 * TQ * 4;          // row maxima (two tiles in turn) and row sums, one number a thread
+constexpr int FA_SMEM = Q_BYTES + KV_STAGES * KV_STAGE_BYTES + 1024 + 256 + FA_XCHG_BYTES;
 constexpr float LAZY_LOG2 = 8.0f;                      // rescale O only when the maximum grew by more than 2^8
 
 __device__ __forceinline__ uint32_t fa_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -85,6 +91,14 @@ __device__ __forceinline__ void fa_mma(uint32_t tmem_d, uint64_t da, uint64_t db
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
+// the same with the A operand in tensor memory (rows = lanes, two bf16 a column)
+__device__ __forceinline__ void fa_mma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void fa_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -117,6 +131,8 @@ __device__ __forceinline__ float fa_exp2(float x) {       // one MUFU; 2^-inf = 
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// the 256 softmax threads among themselves (barrier 1; barrier 0 is __syncthreads)
+__device__ __forceinline__ void fa_softmax_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 __device__ __forceinline__ void fa_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fa_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -147,29 +163,34 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   uint8_t* smem = (uint8_t*)(((uintptr_t)fa_smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* q_tile = smem;                                   // [2 halves][128 x 64]
   uint8_t* kv_ring = smem + Q_BYTES;                        // [stage][K half0, K half1, V half0, V half1]
-  uint8_t* p_tile = kv_ring + KV_STAGES * KV_STAGE_BYTES;   // [2 halves][128 x 64]
-  uint64_t* bars = (uint64_t*)(p_tile + P_BYTES);
+  uint64_t* bars = (uint64_t*)(kv_ring + KV_STAGES * KV_STAGE_BYTES);
   uint64_t* q_full = bars;                 // 1
-  uint64_t* kv_full = bars + 1;            // [KV_STAGES]
-  uint64_t* kv_empty = kv_full + KV_STAGES;
-  uint64_t* s_full = kv_empty + KV_STAGES; // [2]
-  uint64_t* s_empty = s_full + 2;          // [2]
-  uint64_t* p_full = s_empty + 2;          // 1
+  uint64_t* k_full = bars + 1;             // [KV_STAGES] each: keys and values of a stage are
+  uint64_t* k_empty = k_full + KV_STAGES;  //   loaded and given back separately (the keys of a
+  uint64_t* v_full = k_empty + KV_STAGES;  //   tile are done with one product earlier than its
+  uint64_t* v_empty = v_full + KV_STAGES;  //   values, and wanted one product earlier)
+  uint64_t* s_full = v_empty + KV_STAGES;  // [2]
+  uint64_t* p_full = s_full + 2;           // 1
   uint64_t* p_empty = p_full + 1;          // 1
   uint64_t* o_full = p_empty + 1;          // 1
   uint32_t* tmem_slot = (uint32_t*)(o_full + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   int* s_seq = (int*)(tmem_slot + 2);
   int* s_tile = (int*)(tmem_slot + 3);
+  float* x_max = (float*)((uint8_t*)bars + 256);            // [tile parity][key half][row]
+  float* x_sum = x_max + 2 * 2 * TQ;                         // [key half][row]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   rl_pdl_trigger();
   if (threadIdx.x == 0) {
     fa_mbar_init(fa_smem_u32(q_full), 1);
-    for (int i = 0; i < KV_STAGES; ++i) { fa_mbar_init(fa_smem_u32(&kv_full[i]), 1); fa_mbar_init(fa_smem_u32(&kv_empty[i]), 1); }
-    for (int i = 0; i < 2; ++i) { fa_mbar_init(fa_smem_u32(&s_full[i]), 1); fa_mbar_init(fa_smem_u32(&s_empty[i]), 4); }
-    fa_mbar_init(fa_smem_u32(p_full), 4);
+    for (int i = 0; i < KV_STAGES; ++i) {
+      fa_mbar_init(fa_smem_u32(&k_full[i]), 1); fa_mbar_init(fa_smem_u32(&k_empty[i]), 1);
+      fa_mbar_init(fa_smem_u32(&v_full[i]), 1); fa_mbar_init(fa_smem_u32(&v_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) fa_mbar_init(fa_smem_u32(&s_full[i]), 1);
+    fa_mbar_init(fa_smem_u32(p_full), 8);
     fa_mbar_init(fa_smem_u32(p_empty), 1);
     fa_mbar_init(fa_smem_u32(o_full), 1);
     *abort_flag = 0;
@@ -221,26 +242,34 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       fa_expect_tx(fa_smem_u32(q_full), Q_BYTES);
       fa_tma_2d(fa_smem_u32(q_tile), &map_q, fa_smem_u32(q_full), h * HD, row0 + qt0);
       fa_tma_2d(fa_smem_u32(q_tile + HALF_BYTES), &map_q, fa_smem_u32(q_full), h * HD + 64, row0 + qt0);
-      for (int i = 0; i < num_kt; ++i) {
+      // keys of tile i + 1 are asked for before the values of tile i: the keys' stage is free as
+      // soon as S of two tiles back is done, the values' only when that tile's P V is
+      auto load = [&](int i, bool values) -> bool {
         const int kt = kt_begin + i, st = i % KV_STAGES;
         const uint32_t phase = (i / KV_STAGES) & 1;
-        if (i >= KV_STAGES && !fa_wait(fa_smem_u32(&kv_empty[st]), phase ^ 1, abort_flag)) {
+        uint64_t* empty = values ? v_empty : k_empty;
+        if (i >= KV_STAGES && !fa_wait(fa_smem_u32(&empty[st]), phase ^ 1, abort_flag)) {
           if (!*abort_flag) { *abort_flag = 1; atomicExch(err, 11); }
-          break;
+          return false;
         }
         const int p0 = pages[2 * kt];
         const int p1 = (2 * kt + 1) * RL_PAGE < kv_len ? pages[2 * kt + 1] : p0;   // beyond the sequence: any valid page (all masked)
         const int r0 = (p0 * G + gkv) * RL_PAGE, r1 = (p1 * G + gkv) * RL_PAGE;
-        const uint32_t fb = fa_smem_u32(&kv_full[st]);
-        uint8_t* base = kv_ring + (size_t)st * KV_STAGE_BYTES;
-        fa_expect_tx(fb, KV_STAGE_BYTES);
+        const uint32_t fb = fa_smem_u32(values ? &v_full[st] : &k_full[st]);
+        uint8_t* base = kv_ring + (size_t)st * KV_STAGE_BYTES + (values ? 2 * HALF_BYTES : 0);
+        const CUtensorMap* map = values ? &map_v : &map_k;
+        fa_expect_tx(fb, 2 * HALF_BYTES);
 #pragma unroll
         for (int half = 0; half < 2; ++half) {          // 64 head dimensions a half; 64 positions a page
-          fa_tma_2d(fa_smem_u32(base + half * HALF_BYTES), &map_k, fb, 64 * half, r0);
-          fa_tma_2d(fa_smem_u32(base + half * HALF_BYTES + 64 * 128), &map_k, fb, 64 * half, r1);
-          fa_tma_2d(fa_smem_u32(base + (2 + half) * HALF_BYTES), &map_v, fb, 64 * half, r0);
-          fa_tma_2d(fa_smem_u32(base + (2 + half) * HALF_BYTES + 64 * 128), &map_v, fb, 64 * half, r1);
+          fa_tma_2d(fa_smem_u32(base + half * HALF_BYTES), map, fb, 64 * half, r0);
+          fa_tma_2d(fa_smem_u32(base + half * HALF_BYTES + 64 * 128), map, fb, 64 * half, r1);
         }
+        return true;
+      };
+      bool ok = num_kt == 0 || load(0, false);
+      for (int i = 0; i < num_kt && ok; ++i) {
+        if (i + 1 < num_kt) ok = load(i + 1, false);
+        if (ok) ok = load(i, true);
       }
     }
   } else if (warp == 1) {
@@ -252,8 +281,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(err, 12); }
       auto issue_s = [&](int i) -> bool {                   // scores of tile i into S buffer i % 2
         const int st = i % KV_STAGES, sb = i & 1;
-        if (!fa_wait(fa_smem_u32(&kv_full[st]), (i / KV_STAGES) & 1, abort_flag)) return false;
-        if (i >= 2 && !fa_wait(fa_smem_u32(&s_empty[sb]), ((i >> 1) & 1) ^ 1, abort_flag)) return false;
+        if (!fa_wait(fa_smem_u32(&k_full[st]), (i / KV_STAGES) & 1, abort_flag)) return false;
+        // S buffer sb still holds P of tile i - 2; that tile's P V was issued before this and
+        // products run in the order of their issue
         fa_fence_after();
         uint8_t* base = kv_ring + (size_t)st * KV_STAGE_BYTES;
 #pragma unroll
@@ -263,63 +293,71 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           fa_mma(tmem_s0 + (uint32_t)(sb * TK), da, db, idesc_s, k > 0 ? 1u : 0u);
         }
         fa_commit(fa_smem_u32(&s_full[sb]));
+        fa_commit(fa_smem_u32(&k_empty[st]));               // the keys' half of the stage is free once S is done
         return true;
       };
       if (ok && num_kt > 0) ok = issue_s(0);
       for (int i = 0; i < num_kt && ok; ++i) {
         if (i + 1 < num_kt) ok = issue_s(i + 1);            // next tile's scores while this tile's softmax runs
         if (!ok) break;
+        if (!fa_wait(fa_smem_u32(&v_full[i % KV_STAGES]), (i / KV_STAGES) & 1, abort_flag)) { ok = false; break; }
         if (!fa_wait(fa_smem_u32(p_full), i & 1, abort_flag)) { ok = false; break; }
         fa_fence_after();
         uint8_t* vbase = kv_ring + (size_t)(i % KV_STAGES) * KV_STAGE_BYTES + 2 * HALF_BYTES;
 #pragma unroll
         for (int k = 0; k < TK / 16; ++k) {                 // 16 positions a step
-          const uint64_t da = fa_desc_kmajor(fa_smem_u32(p_tile + (k / 4) * HALF_BYTES)) + 2 * (k % 4);
+          // P of this tile: 16 keys = 8 columns of packed bf16 pairs a step, in its S buffer
           const uint64_t db = fa_desc_mnmajor(fa_smem_u32(vbase + k * 16 * 128), HALF_BYTES);
-          fa_mma(tmem_o, da, db, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+          fa_mma_a_tmem(tmem_o, tmem_s0 + (uint32_t)((i & 1) * TK + 8 * k), db, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
         }
         fa_commit(fa_smem_u32(p_empty));                    // P and O are free again once these have completed
-        fa_commit(fa_smem_u32(&kv_empty[i % KV_STAGES]));
+        fa_commit(fa_smem_u32(&v_empty[i % KV_STAGES]));
       }
       if (ok) fa_commit(fa_smem_u32(o_full));
       else if (!*abort_flag) { *abort_flag = 1; atomicExch(err, 13); }
     }
   } else if (have_work) {
-    // ---------------- softmax warps: one query row a thread ----------------
-    const int quarter = warp & 3;
+    // ---------------- softmax warps: two threads a query row, 64 keys each ----------------
+    constexpr int HK = TK / 2;                              // keys (and output columns) a thread
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;                      // row of the tile = lane of tensor memory
     const int pos = start_pos + qt0 + r;                    // position of this row's query
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    float m_used = -INFINITY, l_run = 0.f;                  // maximum the probabilities are scaled by; running sum
-    bool ok = true;
-    for (int i = 0; i < num_kt && ok; ++i) {
-      const int sb = i & 1, key0 = (kt_begin + i) * TK;
-      if (!fa_wait(fa_smem_u32(&s_full[sb]), (i >> 1) & 1, abort_flag)) { ok = false; break; }
-      fa_fence_after();
-      const uint32_t s_addr = tmem_s0 + lane_addr + (uint32_t)(sb * TK);
-      const bool need_mask = key0 + TK - 1 > start_pos + qt0 || window > 0;
-      // the row's 128 scores into registers with one wait; everything below is straight-line
-      // code over them, so the scheduler has independent work to cover every latency
-      uint32_t sv[TK];
+    float m_used = -INFINITY, l_run = 0.f;                  // maximum the probabilities are scaled by; running sum (own keys)
+    bool ok = true;                                         // warp-uniform
+    for (int i = 0; i < num_kt; ++i) {
+      const int sb = i & 1, key0 = (kt_begin + i) * TK + half * HK;
+      if (ok) ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(&s_full[sb]), (i >> 1) & 1, abort_flag));
+      uint32_t sv[HK];
+      float mx_own = -INFINITY;
+      if (ok) {
+        fa_fence_after();
+        const uint32_t s_addr = tmem_s0 + lane_addr + (uint32_t)(sb * TK + half * HK);
+        // the thread's 64 scores into registers with one wait; everything below is straight-line
+        // code over them, so the scheduler has independent work to cover every latency
 #pragma unroll
-      for (int c = 0; c < TK / 32; ++c) fa_ld32(s_addr + c * 32, sv + c * 32);
-      fa_wait_ld();
-      // the scores are in registers: the tensor cores may overwrite this S buffer
-      fa_fence_before();
-      __syncwarp();
-      if (lane == 0) fa_arrive(fa_smem_u32(&s_empty[sb]));
-      if (need_mask) {
+        for (int c = 0; c < HK / 32; ++c) fa_ld32(s_addr + c * 32, sv + c * 32);
+        fa_wait_ld();
+        const bool need_mask = (kt_begin + i) * TK + TK - 1 > start_pos + qt0 || window > 0;
+        if (need_mask) {
 #pragma unroll
-        for (int j = 0; j < TK; ++j) {
-          const int key = key0 + j;
-          const bool vis = key <= pos && (window <= 0 || key > pos - window);
-          if (!vis) sv[j] = 0xff800000u;        // -inf
+          for (int j = 0; j < HK; ++j) {
+            const int key = key0 + j;
+            const bool vis = key <= pos && (window <= 0 || key > pos - window);
+            if (!vis) sv[j] = 0xff800000u;        // -inf
+          }
         }
-      }
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int j = 0; j < TK; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sv[j]));
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2e;
+        for (int j = 0; j < HK; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sv[j]));
+        mx_own = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      }
+      // the row's maximum: the two threads of a row exchange theirs (buffers take turns, so one
+      // barrier a tile is enough)
+      x_max[(sb * 2 + half) * TQ + r] = mx_own;
+      fa_softmax_sync();
+      if (!ok) continue;
+      const float mx = fmaxf(mx_own, x_max[(sb * 2 + (half ^ 1)) * TQ + r]) * scale_log2e;
       // lazy maximum: move it (and rescale O and the sum) only when it grew by more than 2^8
       float corr = 1.0f;
       if (mx > m_used + LAZY_LOG2 || (m_used == -INFINITY && mx > -INFINITY)) {
@@ -328,11 +366,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       const bool any_rescale = __any_sync(0xffffffffu, corr != 1.0f);
       // probabilities, rounded to bf16 (the sum runs over the rounded values, the ones that are
-      // multiplied with V), packed in place: sv[0..63] then hold the row's 128 bf16 values
+      // multiplied with V), packed in place: sv[0..31] then hold the thread's 64 bf16 values
       const float m_sub = m_used == -INFINITY ? 0.f : m_used;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int j = 0; j < TK; j += 2) {
+      for (int j = 0; j < HK; j += 2) {
         const float p0 = fa_exp2(fmaf(__uint_as_float(sv[j]), scale_log2e, -m_sub));
         const float p1 = fa_exp2(fmaf(__uint_as_float(sv[j + 1]), scale_log2e, -m_sub));
         __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
@@ -341,48 +379,53 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         sv[j >> 1] = *reinterpret_cast<uint32_t*>(&pb);
       }
       const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      // P and O are only touched once the previous tile's P V has completed
-      if (i > 0 && !fa_wait(fa_smem_u32(p_empty), (i - 1) & 1, abort_flag)) { ok = false; break; }
-      fa_fence_after();
+      // O is only touched once the previous tile's P V has completed: waited for only if this
+      // warp has a row to rescale (the barrier cannot have run ahead: the next P V needs our arrival)
       if (any_rescale && i > 0) {
+        ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(p_empty), (i - 1) & 1, abort_flag));
+        if (!ok) continue;
+        fa_fence_after();
         l_run *= corr;
 #pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int c = 0; c < HK / 32; ++c) {               // this thread's half of the row of O
           uint32_t v[32];
-          fa_ld32(tmem_o + lane_addr + c * 32, v);
+          const uint32_t o_addr = tmem_o + lane_addr + (uint32_t)(half * HK + c * 32);
+          fa_ld32(o_addr, v);
           fa_wait_ld();
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * corr);
-          fa_st16(tmem_o + lane_addr + c * 32, *reinterpret_cast<uint32_t(*)[16]>(v));
-          fa_st16(tmem_o + lane_addr + c * 32 + 16, *reinterpret_cast<uint32_t(*)[16]>(v + 16));
+          fa_st16(o_addr, *reinterpret_cast<uint32_t(*)[16]>(v));
+          fa_st16(o_addr + 16, *reinterpret_cast<uint32_t(*)[16]>(v + 16));
         }
-        fa_wait_st();
       }
-      // P -> shared memory: row r of the swizzled K-major tile, 16-byte chunk ch of keys 8 ch .. 8 ch + 7
-#pragma unroll
-      for (int ch = 0; ch < TK / 8; ++ch) {
-        uint8_t* rowp = p_tile + (ch / 8) * HALF_BYTES + r * 128;
-        *reinterpret_cast<uint4*>(rowp + (((ch & 7) ^ (r & 7)) * 16)) =
-            make_uint4(sv[4 * ch], sv[4 * ch + 1], sv[4 * ch + 2], sv[4 * ch + 3]);
+      // P over the S buffer: this thread's 64 keys are columns 32 half .. 32 half + 31 (both threads of
+      // the row had their scores in registers before the barrier above)
+      {
+        const uint32_t p_addr = tmem_s0 + lane_addr + (uint32_t)(sb * TK + half * (HK / 2));
+        fa_st16(p_addr, *reinterpret_cast<uint32_t(*)[16]>(sv));
+        fa_st16(p_addr + 16, *reinterpret_cast<uint32_t(*)[16]>(sv + 16));
+        fa_wait_st();
       }
       l_run += sum;
       // P is ready for the tensor cores
       fa_fence_before();
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) fa_arrive(fa_smem_u32(p_full));
     }
     // ---- O / l -> out ----
-    if (ok && !fa_wait(fa_smem_u32(o_full), 0, abort_flag)) ok = false;
+    if (ok) ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(o_full), 0, abort_flag));
     if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(err, 14); }
+    x_sum[half * TQ + r] = l_run;
+    fa_softmax_sync();
     fa_fence_after();
     if (ok) {
-      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-      __nv_bfloat16* orow = out + (size_t)(row0 + qt0 + r) * ldo + (size_t)h * HD;
+      const float l_row = half == 0 ? l_run + x_sum[TQ + r] : x_sum[r] + l_run;    // keys 0-63 first, either way
+      const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
+      __nv_bfloat16* orow = out + (size_t)(row0 + qt0 + r) * ldo + (size_t)h * HD + half * HK;
 #pragma unroll 1
-      for (int c = 0; c < HD / 16; ++c) {
+      for (int c = 0; c < HK / 16; ++c) {
         uint32_t v[16];
-        fa_ld16(tmem_o + lane_addr + c * 16, v);
+        fa_ld16(tmem_o + lane_addr + (uint32_t)(half * HK + c * 16), v);
         fa_wait_ld();
         if (r < rows_here) {
           uint32_t pk[8];

@@ -201,8 +201,8 @@ struct TcConfig {
   static constexpr int STAGE_BYTES = (BLOCK_N_OUT + BT) * BLOCK_K * 2;
   // few tokens: the product streams weights, three stages a CTA and three or four CTAs an
   // SM keep more loads in flight than one deep ring; many tokens: one CTA, a deep ring
-  static constexpr int SMEM_BUDGET = BT <= 64 ? 73728 : 196608;
-  static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) < 8 ? (SMEM_BUDGET / STAGE_BYTES) : 8;
+  static constexpr int RING_BYTES_MAX = BT <= 64 ? 73728 : 196608;
+  static constexpr int STAGES = (RING_BYTES_MAX / STAGE_BYTES) < 8 ? (RING_BYTES_MAX / STAGE_BYTES) : 8;
   static constexpr int MIN_CTAS = BT <= 64 ? 3 : 1;
   static constexpr int TMEM_COLS = BT < 32 ? 32 : BT;
   static constexpr int FUSE_FLOATS = 3 * BT;       // the tile's row scales; its tokens' positions and cache rows
