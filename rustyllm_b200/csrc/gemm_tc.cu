@@ -246,7 +246,7 @@ __device__ __forceinline__ void epilogue_row_scales(const TcFuse& f, int m0, int
 // in tensor memory at `tmem_acc`) goes to the output in the asked form.  Called by the four
 // epilogue warps; `quarter` = warp index % 4 = the 32 lanes of tensor memory the warp may read.
 template <int BT>
-__device__ __forceinline__ void tile_epilogue(uint32_t tmem_acc, int quarter, int lane, int n0, int m0, int M, int N,
+__device__ __forceinline__ void tile_epilogue(uint32_t tmem_acc, int quarter, int lane, int n0, int m0, int cols, int M, int N,
                                               int ldo, const float* __restrict__ bias, void* __restrict__ out,
                                               int out_mode, const TcFuse& fuse, float* fuse_smem) {
   const int n = n0 + quarter * 32 + lane;          // output feature of this thread
@@ -254,9 +254,42 @@ __device__ __forceinline__ void tile_epilogue(uint32_t tmem_acc, int quarter, in
   const float* rs = fuse_smem;                     // row scales (made by epilogue_row_scales)
   const bool make_norm = fuse.norm_weight != nullptr && out_mode == TC_OUT_ADD_F32;
   const float g = (make_norm && n < N) ? fuse.norm_weight[n] : 0.f;
+  if (BT >= 128 && out_mode == TC_OUT_ADD_F32 && !make_norm && fuse.scale_partials == nullptr) {
+    // Many tokens, adding into the residual: the epilogue moves 8 bytes a result and is bound
+    // by how many of its loads are in flight.  The residual values of the next 32 tokens are
+    // requested before this thread turns to the 32 it holds, stores behind loads.
+    float* of = (float*)out;
+    const bool live = n < N;
+    float cur[32], nxt[32];
+    auto fetch = [&](float (&dst)[32], int c0) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int m = m0 + c0 * 16 + j;
+        dst[j] = (live && c0 * 16 + j < cols && m < M) ? __ldcg(of + (size_t)m * ldo + n) : 0.f;
+      }
+    };
+    fetch(cur, 0);
+#pragma unroll 1
+    for (int c = 0; c < BT / 16; c += 2) {
+      if (c * 16 >= cols) break;
+      if ((c + 2) * 16 < cols) fetch(nxt, c + 2);
+      uint32_t r[32];
+      tmem_ld16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 16), *reinterpret_cast<uint32_t(*)[16]>(r));
+      tmem_ld16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 16 + 16), *reinterpret_cast<uint32_t(*)[16]>(r + 16));
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int m = m0 + c * 16 + j;
+        if (live && c * 16 + j < cols && m < M) of[(size_t)m * ldo + n] = cur[j] + __uint_as_float(r[j]) + b;
+      }
+#pragma unroll
+      for (int j = 0; j < 32; ++j) cur[j] = nxt[j];
+    }
+    return;
+  }
 #pragma unroll 1
   for (int c = 0; c < BT / 16; ++c) {
-    if (m0 + c * 16 >= M) break;
+    if (c * 16 >= cols) break;       // cols: the tile's tokens (a multiple of 16, or what is left of M)
     uint32_t r[16];
     tmem_ld16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 16), r);
     tmem_ld_wait();
@@ -450,7 +483,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int quarter = warp & 3;                    // lanes this warp may read
     const int row = quarter * 32 + lane;             // accumulator row = weight row of the tile
     if (ok && num_splits == 1) {
-      tile_epilogue<BT>(tmem_base, quarter, lane, n0, m0, M, N, ldo, bias, out, out_mode, fuse, fuse_smem);
+      tile_epilogue<BT>(tmem_base, quarter, lane, n0, m0, min(BT, M - m0), M, N, ldo, bias, out, out_mode, fuse, fuse_smem);
     } else if (num_splits > 1 && ok) {
       // this part's partial tile -> own shared memory (the ring is free: every MMA has
       // completed), as [token column][weight row] floats
@@ -595,6 +628,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // the same weight rows are neighbours, so CTAs that run together share weight tiles in L2).
 // Tensor memory holds two accumulators: while the epilogue warps drain one, the MMA thread
 // fills the other, and the TMA producer runs ahead through the ring across tile borders.
+// The tiles behind the last full wave of CTAs are cut narrower along the tokens, so that
+// there are about as many of them as CTAs: the last wave then takes bt / BT of a full
+// wave's time instead of a whole one with most CTAs idle.  No partial sums, no fix-up:
+// a narrow tile is a whole tile of its own.
+struct TcTail {
+  int first;         // index of the first narrow tile = number of tiles of full width
+  int bt;            // tokens a narrow tile (a multiple of 16, <= BT)
+  int n_first;       // weight-row tile the narrow tiles begin in
+  int t0_first;      // first token that is not covered by full-width tiles there
+  int count_first;   // narrow tiles in that weight-row tile
+  int per_n;         // narrow tiles in every weight-row tile after it
+};
+struct TcTileAt { int n0, m0, bt; };
+__device__ __forceinline__ TcTileAt tc_tile_at(int tile, int tiles_m, int BT, const TcTail& t) {
+  if (tile < t.first) return {(tile / tiles_m) * BLOCK_N_OUT, (tile % tiles_m) * BT, BT};
+  int idx = tile - t.first;
+  if (idx < t.count_first) return {t.n_first * BLOCK_N_OUT, t.t0_first + idx * t.bt, t.bt};
+  idx -= t.count_first;
+  return {(t.n_first + 1 + idx / t.per_n) * BLOCK_N_OUT, (idx % t.per_n) * t.bt, t.bt};
+}
+
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -602,8 +656,9 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 template <int BT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
-                          const float* __restrict__ bias, void* __restrict__ out, int out_mode, int M, int N, int K,
-                          int ldo, int* __restrict__ err, int tiles_m, int num_tiles) {
+                          const __grid_constant__ CUtensorMap map_a_tail, const float* __restrict__ bias,
+                          void* __restrict__ out, int out_mode, int M, int N, int K,
+                          int ldo, int* __restrict__ err, int tiles_m, int num_tiles, const TcTail tail) {
   using Cfg = TcConfig<BT>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -632,6 +687,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a_tail) : "memory");
   }
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 2 * BT);
   tc_fence_before();
@@ -646,7 +702,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
       int it = 0;                                   // k-blocks issued so far, over all tiles
       bool waited = false, ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int n0 = (tile / tiles_m) * BLOCK_N_OUT, m0 = (tile % tiles_m) * BT;
+        const TcTileAt at = tc_tile_at(tile, tiles_m, BT, tail);
+        const int n0 = at.n0, m0 = at.m0;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % Cfg::STAGES;
           const uint32_t phase = (it / Cfg::STAGES) & 1;
@@ -656,22 +713,23 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             break;
           }
           const uint32_t fb = smem_u32(&full_bar[s]);
-          mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+          mbar_expect_tx(fb, (BLOCK_N_OUT + at.bt) * BLOCK_K * 2);
           uint8_t* st = tiles + (size_t)s * Cfg::STAGE_BYTES;
           tma_load_2d(smem_u32(st), &map_w, fb, kb * BLOCK_K, n0);
           // weights may be requested before the preceding kernels have finished, activations not
           if (!waited) { rl_pdl_wait(); waited = true; }
-          tma_load_2d(smem_u32(st + BLOCK_N_OUT * BLOCK_K * 2), &map_a, fb, kb * BLOCK_K, m0);
+          uint8_t* sa = st + BLOCK_N_OUT * BLOCK_K * 2;
+          tma_load_2d(smem_u32(sa), at.bt == BT ? &map_a : &map_a_tail, fb, kb * BLOCK_K, m0);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       // ---------------- MMA issuer ----------------
-      constexpr uint32_t idesc = make_idesc(BLOCK_N_OUT, BT);
       int it = 0, t = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+        const uint32_t idesc = make_idesc(BLOCK_N_OUT, tc_tile_at(tile, tiles_m, BT, tail).bt);
         const int buf = t & 1;
         const uint32_t acc_phase = (t >> 1) & 1;
         if (t >= 2 && !mbar_wait(smem_u32(&acc_empty[buf]), acc_phase ^ 1, abort_flag)) {   // epilogue done with this accumulator
@@ -709,13 +767,14 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
       const int buf = t & 1;
       const uint32_t acc_phase = (t >> 1) & 1;
-      const int n0 = (tile / tiles_m) * BLOCK_N_OUT, m0 = (tile % tiles_m) * BT;
+      const TcTileAt at = tc_tile_at(tile, tiles_m, BT, tail);
       if (!mbar_wait(smem_u32(&acc_full[buf]), acc_phase, abort_flag)) {
         if (!*abort_flag) { *abort_flag = 1; atomicExch(err, 3); }
         break;
       }
       tc_fence_after();
-      tile_epilogue<BT>(tmem_base + (uint32_t)(buf * BT), quarter, lane, n0, m0, M, N, ldo, bias, out, out_mode, TcFuse{}, nullptr);
+      tile_epilogue<BT>(tmem_base + (uint32_t)(buf * BT), quarter, lane, at.n0, at.m0, min(at.bt, M - at.m0), M, N, ldo, bias, out,
+                        out_mode, TcFuse{}, nullptr);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));    // this warp has read the accumulator
@@ -726,9 +785,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
   if (warp == 1) tmem_dealloc(tmem_base, 2 * BT);
 }
 
+static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows);
+
 template <int BT>
-static int launch_tc_persistent(const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, void* out, int out_mode,
-                                int M, int N, int K, int ldo, int* err, cudaStream_t stream) {
+static int launch_tc_persistent(const CUtensorMap& mw, const CUtensorMap& ma, const void* A, int lda, const float* bias,
+                                void* out, int out_mode, int M, int N, int K, int ldo, int* err, cudaStream_t stream) {
   using Cfg = TcConfig<BT>;
   static bool configured = false;
   static int num_sms = 0;
@@ -742,10 +803,33 @@ static int launch_tc_persistent(const CUtensorMap& mw, const CUtensorMap& ma, co
     configured = true;
   }
   const int tiles_m = (M + BT - 1) / BT, tiles_n = (N + BLOCK_N_OUT - 1) / BLOCK_N_OUT;
-  const int num_tiles = tiles_m * tiles_n;
+  const int total = tiles_m * tiles_n;
+  // the tiles behind the last full wave: the narrowest token tile (from 64 tokens: below, the
+  // weight tile's trip through shared memory takes longer than the products) that leaves no
+  // more of them than there are CTAs
+  TcTail tail = {total, BT, 0, 0, 0, 1};
+  int num_tiles = total;
+  const int full = (total / num_sms) * num_sms;
+  if (full < total) {
+    const int n_first = full / tiles_m, t0_first = (full % tiles_m) * BT;
+    for (int bt = 64; bt < BT; bt += 16) {
+      const int count_first = (M - t0_first + bt - 1) / bt, per_n = (M + bt - 1) / bt;
+      const int cnt = count_first + (tiles_n - n_first - 1) * per_n;
+      if (cnt <= num_sms) {
+        tail = {full, bt, n_first, t0_first, count_first, per_n};
+        num_tiles = full + cnt;
+        break;
+      }
+    }
+  }
+  CUtensorMap ma_tail = ma;      // the same activations in boxes as tall as a narrow tile
+  if (tail.bt != BT) {
+    const int rc = make_map(&ma_tail, A, M, K, lda, tail.bt);
+    if (rc != RL_OK) return rc;
+  }
   const int grid = num_tiles < num_sms ? num_tiles : num_sms;
   cudaError_t e = rl_launch_pdl(gemm_tc_persistent_kernel<BT>, dim3(grid), dim3(TC_THREADS), (size_t)Cfg::SMEM_BYTES, stream,
-                                mw, ma, bias, out, out_mode, M, N, K, ldo, err, tiles_m, num_tiles);
+                                mw, ma, ma_tail, bias, out, out_mode, M, N, K, ldo, err, tiles_m, num_tiles, tail);
   if (e != cudaSuccess) {
     rl_set_error("rl_gemm_tc: launch of the persistent kernel failed: %s", cudaGetErrorString(e));
     return RL_ERR_CUDA;
@@ -901,9 +985,10 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* ou
     case 16: return launch_tc<16>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, fuse, stream);
     case 32: return launch_tc<32>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, fuse, stream);
     case 64: return launch_tc<64>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, fuse, stream);
-    case 128: return launch_tc_persistent<128>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, stream);
-    default: return launch_tc_persistent<256>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, stream);
+    default: break;
   }
+  if (bt == 128) return launch_tc_persistent<128>(mw, ma, A, lda, bias, out, out_mode, M, N, K, ldo, err, stream);
+  return launch_tc_persistent<256>(mw, ma, A, lda, bias, out, out_mode, M, N, K, ldo, err, stream);
 }
 
 extern "C" int rl_gemm_tc(const void* A, const void* W, const float* bias, void* out, int out_mode, int M, int N,
