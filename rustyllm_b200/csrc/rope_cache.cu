@@ -71,12 +71,15 @@ rope_kv_write_kernel(T* __restrict__ qkv, int ld, const int* __restrict__ positi
 
 // Fast path: bf16, half-split pairing over the whole head, head size a multiple of 16,
 // 16-byte aligned rows.  A thread rotates eight pairs (two 16-byte loads, two 16-byte
-// stores) or copies sixteen value elements.
+// stores) or copies sixteen value elements.  The token's sines and cosines are the same
+// for all its heads: the CTA computes them once into shared memory.
+#define ROPE_FAST_HEADS_PER_CTA 16
 __global__ void __launch_bounds__(ROPE_THREADS)
 rope_kv_write_bf16_half_kernel(__nv_bfloat16* __restrict__ qkv, int ld, const int* __restrict__ positions,
                                const int* __restrict__ slot_of_token, const int* __restrict__ page_table, int max_pages,
                                const float* __restrict__ inv_freq, int H, int G, int hd,
                                __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool) {
+  __shared__ float2 cs[128];                              // (cos, sin) of the token's hd / 2 <= 128 angles
   rl_pdl_trigger();
   rl_pdl_wait();
   const int m = blockIdx.x;
@@ -86,8 +89,14 @@ rope_kv_write_bf16_half_kernel(__nv_bfloat16* __restrict__ qkv, int ld, const in
   const int page = page_table[(size_t)slot * max_pages + pos / RL_PAGE];
   const size_t dst = ((size_t)page * G) * RL_PAGE * hd + (size_t)(pos % RL_PAGE) * hd;
   const int half = hd / 2, per_head = half / 8;          // groups of eight pairs a head
-  const int slot0 = blockIdx.y * ROPE_HEADS_PER_CTA;
-  const int nslots = min(ROPE_HEADS_PER_CTA, H + 2 * G - slot0);
+  const int slot0 = blockIdx.y * ROPE_FAST_HEADS_PER_CTA;
+  const int nslots = min(ROPE_FAST_HEADS_PER_CTA, H + 2 * G - slot0);
+  for (int i = threadIdx.x; i < half; i += ROPE_THREADS) {
+    float sn, c;
+    sincosf((float)pos * inv_freq[i], &sn, &c);
+    cs[i] = make_float2(c, sn);
+  }
+  __syncthreads();
   for (int idx = threadIdx.x; idx < nslots * per_head; idx += ROPE_THREADS) {
     const int hs = slot0 + idx / per_head;
     const int i = (idx % per_head) * 8;
@@ -108,9 +117,7 @@ rope_kv_write_bf16_half_kernel(__nv_bfloat16* __restrict__ qkv, int ld, const in
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const float2 a = __bfloat1622float2(l2[k]), b = __bfloat1622float2(h2[k]);
-      float s0, c0, s1, c1;
-      sincosf((float)pos * inv_freq[i + 2 * k], &s0, &c0);
-      sincosf((float)pos * inv_freq[i + 2 * k + 1], &s1, &c1);
+      const float c0 = cs[i + 2 * k].x, s0 = cs[i + 2 * k].y, c1 = cs[i + 2 * k + 1].x, s1 = cs[i + 2 * k + 1].y;
       ol[k] = __floats2bfloat162_rn(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
       oh[k] = __floats2bfloat162_rn(a.x * s0 + b.x * c0, a.y * s1 + b.y * c1);
     }
@@ -142,7 +149,9 @@ extern "C" int rl_rope_kv_write(void* qkv, int dtype, int ld, const int* positio
   const int threads = ROPE_THREADS;
   if (dtype == RL_BF16 && write_cache && !interleaved && rotary_dim == head_dim && head_dim % 16 == 0 && ld % 8 == 0 &&
       ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_pool & 15) == 0 && ((uintptr_t)v_pool & 15) == 0)
-    rl_launch_pdl(rope_kv_write_bf16_half_kernel, grid, threads, 0, stream, (__nv_bfloat16*)qkv, ld, positions,
+    rl_launch_pdl(rope_kv_write_bf16_half_kernel,
+                  dim3(num_tokens, (num_heads + 2 * num_kv_heads + ROPE_FAST_HEADS_PER_CTA - 1) / ROPE_FAST_HEADS_PER_CTA),
+                  threads, 0, stream, (__nv_bfloat16*)qkv, ld, positions,
                   slot_of_token, page_table, max_pages, inv_freq, num_heads, num_kv_heads, head_dim,
                   (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool);
   else if (dtype == RL_F32)
