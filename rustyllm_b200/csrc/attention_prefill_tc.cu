@@ -131,6 +131,23 @@ __device__ __forceinline__ float fa_exp2(float x) {       // one MUFU; 2^-inf = 
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// two floats an instruction (packed fp32 of sm_100) and a maximum of three
+__device__ __forceinline__ float2 fa_ffma2(float2 a, float2 b, float2 c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d)
+      : "l"(*reinterpret_cast<uint64_t*>(&a)), "l"(*reinterpret_cast<uint64_t*>(&b)), "l"(*reinterpret_cast<uint64_t*>(&c)));
+  return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float2 fa_fadd2(float2 a, float2 b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(*reinterpret_cast<uint64_t*>(&a)), "l"(*reinterpret_cast<uint64_t*>(&b)));
+  return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float fa_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 // the 256 softmax threads among themselves (barrier 1; barrier 0 is __syncthreads)
 __device__ __forceinline__ void fa_softmax_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 __device__ __forceinline__ void fa_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -349,7 +366,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int j = 0; j < HK; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sv[j]));
+        for (int j = 0; j < HK; j += 2) mx4[(j >> 1) & 3] = fa_max3(mx4[(j >> 1) & 3], __uint_as_float(sv[j]), __uint_as_float(sv[j + 1]));
         mx_own = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       }
       // the row's maximum: the two threads of a row exchange theirs (buffers take turns, so one
@@ -365,20 +382,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         m_used = mx;
       }
       const bool any_rescale = __any_sync(0xffffffffu, corr != 1.0f);
-      // probabilities, rounded to bf16 (the sum runs over the rounded values, the ones that are
-      // multiplied with V), packed in place: sv[0..31] then hold the thread's 64 bf16 values
+      // probabilities: exp2(score * scale - maximum), two scores an FMA; summed in float, rounded
+      // to bf16 for the product with V and packed in place (sv[0..31] then hold the thread's 64)
       const float m_sub = m_used == -INFINITY ? 0.f : m_used;
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      const float2 sc2 = make_float2(scale_log2e, scale_log2e), nm2 = make_float2(-m_sub, -m_sub);
+      float2 sum2[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
 #pragma unroll
       for (int j = 0; j < HK; j += 2) {
-        const float p0 = fa_exp2(fmaf(__uint_as_float(sv[j]), scale_log2e, -m_sub));
-        const float p1 = fa_exp2(fmaf(__uint_as_float(sv[j + 1]), scale_log2e, -m_sub));
-        __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-        const float2 pr = __bfloat1622float2(pb);
-        sum4[(j >> 1) & 3] += pr.x + pr.y;
+        const float2 t = fa_ffma2(make_float2(__uint_as_float(sv[j]), __uint_as_float(sv[j + 1])), sc2, nm2);
+        const float2 p2 = make_float2(fa_exp2(t.x), fa_exp2(t.y));
+        sum2[(j >> 1) & 3] = fa_fadd2(sum2[(j >> 1) & 3], p2);
+        __nv_bfloat162 pb = __floats2bfloat162_rn(p2.x, p2.y);
         sv[j >> 1] = *reinterpret_cast<uint32_t*>(&pb);
       }
-      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      const float2 s01 = fa_fadd2(sum2[0], sum2[1]), s23 = fa_fadd2(sum2[2], sum2[3]);
+      const float sum = (s01.x + s01.y) + (s23.x + s23.y);
       // O is only touched once the previous tile's P V has completed: waited for only if this
       // warp has a row to rescale (the barrier cannot have run ahead: the next P V needs our arrival)
       if (any_rescale && i > 0) {
