@@ -121,10 +121,15 @@ class Runner:
                     dtype: Union[str, torch.dtype] = "bfloat16", device: str = "cuda:0",
                     max_cache_tokens: Optional[int] = None, max_batch: int = 64,
                     max_context: Optional[int] = None, std: float = 0.02, norm_noise: bool = False,
-                    num_layers: Optional[int] = None) -> "Runner":
+                    num_layers: Optional[int] = None,
+                    storage_dtype: Union[str, torch.dtype, None] = None) -> "Runner":
         """Random weights drawn on the device from a configuration and a seed; no
         files.  ``num_layers`` overrides the number of layers (for measurements that
-        must fit in less memory or time; layer sizes stay as configured)."""
+        must fit in less memory or time; layer sizes stay as configured).
+        ``storage_dtype``: the dtype a checkpoint file would hold the values in (they are
+        rounded to it once); default bfloat16 for a bfloat16 run, float32 for a float32 run.
+        A float32 run with bfloat16 storage computes in 32-bit on exactly the weights of
+        the bfloat16 run of the same seed."""
         dev = torch.device(device)
         _require_cuda(dev)
         compute = parse_dtype(dtype)
@@ -135,7 +140,8 @@ class Runner:
         typed = arch.parse_config(cfg_dict)
         spec = arch.build_spec(typed)
         model = DecoderModel(spec, Runtime(dev, compute))
-        storage = torch.bfloat16 if compute == torch.bfloat16 else torch.float32
+        storage = parse_dtype(storage_dtype) if storage_dtype is not None else \
+            (torch.bfloat16 if compute == torch.bfloat16 else torch.float32)
         model.bind(random_parameters(model.param_specs(), seed, compute, dev, storage_dtype=storage,
                                      std=std, norm_noise=norm_noise))
         return cls(typed, cfg_dict, model,
