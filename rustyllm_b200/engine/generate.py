@@ -117,6 +117,8 @@ def generate_batch(engine, sampler, prompts: Sequence[Sequence[int]], options: G
     reason = [""] * B
     pos = [len(p) for p in prompts]
     slots: List[Optional[int]] = []
+    # the logits of a step are sampled from before the next step runs: no copy of them is needed
+    step = getattr(engine, "step_borrowed", engine.step)
     try:
         for _ in range(B):
             slots.append(engine.alloc_slot())
@@ -155,7 +157,7 @@ def generate_batch(engine, sampler, prompts: Sequence[Sequence[int]], options: G
             live = nxt
             if not live:
                 break
-            logits = engine.step([slots[i] for i in live], feed, "last")
+            logits = step([slots[i] for i in live], feed, "last")
             for i in live:
                 pos[i] += 1
             steps += 1

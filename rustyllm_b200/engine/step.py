@@ -191,7 +191,14 @@ class Engine:
                          list(q_lens), list(kv_lens), max(q_lens), max(kv_lens),
                          all(n == 1 for n in q_lens))
 
-    def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], want: Want = "last") -> Optional[torch.Tensor]:
+    def step_borrowed(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], want: Want = "last") -> Optional[torch.Tensor]:
+        """``step`` for a caller that is done with the logits before its next step (the
+        generation loop samples from them at once): a captured step then hands out the
+        graph's own output buffer instead of a copy."""
+        return self.step(slots, tokens, want, _borrow=True)
+
+    def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], want: Want = "last",
+             _borrow: bool = False) -> Optional[torch.Tensor]:
         """Run the given tokens of the given sequences as one batch from the cache.
 
         ``slots[b]`` holds sequence b, whose next tokens are ``tokens[b]`` (they take
@@ -220,7 +227,7 @@ class Engine:
                 g.graph.replay()
                 K.launch_count += g.launches
                 self.cache.commit(slots, ones)
-                return g.logits.clone()   # the graph's own buffer is overwritten by its next replay
+                return g.logits if _borrow else g.logits.clone()   # the graph's own buffer is overwritten by its next replay
             self._eager_decodes[B] = self._eager_decodes.get(B, 0) + 1
         packed, sizes, q_lens, kv_lens = self.build_step(slots, tokens, want)
         self.cache.prepare(slots, q_lens)

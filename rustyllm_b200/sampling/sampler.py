@@ -40,6 +40,20 @@ class Sampler:
         self.device = device
         self._floats = PinnedStaging(device, torch.float32) if device.type == "cuda" else None
         self._ints = PinnedStaging(device, torch.int32) if device.type == "cuda" else None
+        self._host_ids: Optional[torch.Tensor] = None      # pinned: the sampled ids come back through it
+        self._ids_copied = torch.cuda.Event() if device.type == "cuda" else None
+
+    def _to_host(self, ids: torch.Tensor) -> List[int]:
+        """The sampled ids on the host (waits for the kernels that produced them)."""
+        if self._ids_copied is None:
+            return ids.tolist()
+        n = ids.numel()
+        if self._host_ids is None or self._host_ids.numel() < n:
+            self._host_ids = torch.empty(max(n, 256), dtype=torch.int32, pin_memory=True)
+        self._host_ids[:n].copy_(ids, non_blocking=True)
+        self._ids_copied.record()
+        self._ids_copied.synchronize()
+        return self._host_ids[:n].tolist()
 
     @property
     def h2d_bytes(self) -> int:
@@ -73,7 +87,7 @@ class Sampler:
 
         if all(s.config.is_greedy for s in states):
             K.argmax(logits, out)
-            return out.tolist()
+            return self._to_host(out)
 
         def takes_top_k(c: SamplerConfig) -> bool:
             return not c.is_greedy and 1 < c.top_k < V
@@ -96,4 +110,4 @@ class Sampler:
             K.sample_candidates(logits, fd[0], fd[1], fd[2], out,
                                 topk, [states[b].config.top_k for b in topk], [states[b].config.top_p for b in topk],
                                 topp, [states[b].config.top_p for b in topp])
-        return out.tolist()
+        return self._to_host(out)
