@@ -92,9 +92,9 @@ def attention_decode(a) -> None:
     q = torch.randn(a.batch, (H + 2 * G) * hd, device=DEV).to(BF)
     out = torch.empty(a.batch, H * hd, device=DEV, dtype=BF)
     sp = a.splits or K.decode_splits(a.batch, G)
-    plan = K.decode_plan(slots, kv, 0, sp) if a.batch > 1 else None    # once a step, as the engine makes it
+    plan = K.decode_plan(slots, kv, 0, sp) if a.batch > 1 and not a.cluster else None    # once a step, as the engine makes it
     us = _time(lambda i: K.attention_decode(q, pools[i % layers][0], pools[i % layers][1], pt, slots, kv, out, H, G, hd,
-                                            1 / math.sqrt(hd), num_splits=sp, plan=plan), a.warmup, a.reps)
+                                            1 / math.sqrt(hd), num_splits=sp, plan=plan, cluster=a.cluster), a.warmup, a.reps)
     print(f"attention_decode B={a.batch} context={a.contexts or a.context} H={H} G={G} hd={hd} splits={sp}: "
           f"{us:.2f} us, {kv_bytes / us / 1e6:.2f} TB/s of cache")
 
@@ -163,6 +163,7 @@ def main(argv=None) -> int:
     p.add_argument("--head-dim", type=int, default=128); p.add_argument("--hidden", type=int, default=4096)
     p.add_argument("--intermediate", type=int, default=14336)
     p.add_argument("--greedy", action="store_true", help="sample: the argmax kernel")
+    p.add_argument("--cluster", action="store_true", help="attention-decode: the chunks of a sequence as one thread-block cluster (--splits 2, 4 or 8)")
     p.add_argument("--mma", action="store_true", help="attention-prefill: the mma.sync kernel also where tcgen05 applies")
     p.add_argument("--warmup", type=int, default=3); p.add_argument("--reps", type=int, default=20)
     p.add_argument("--graph", action="store_true", help="capture the timed launches in one CUDA graph: kernels that take "

@@ -30,6 +30,10 @@
 // no plan and the CTA writes the output; otherwise it writes its (max, sum, unnormalised
 // output) to scratch and a second kernel combines a sequence's chunks in chunk order.
 // Without a plan every sequence gets `splits` chunks (one sequence needs no dealing).
+// A third way needs no scratch and no second kernel: with 2, 4 or 8 equal chunks a sequence
+// the chunks' CTAs form a thread-block cluster, leave their (max, sum, output) in their own
+// shared memory, and every CTA combines its share of the output columns from all of them
+// through distributed shared memory, in chunk order.
 // (Working the plan out in every CTA, and letting the last CTA of a sequence do the
 // combining - found by an atomic ticket - were both measured and are slower: dependent
 // round trips to memory at the start and the end of a kernel that runs for 10 us.)
@@ -65,6 +69,22 @@ __device__ __forceinline__ void dec_wait() { asm volatile("cp.async.wait_group %
 __device__ __forceinline__ uint4 dec_lds16(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+// ---- thread-block cluster ----
+__device__ __forceinline__ uint32_t dec_cluster_size() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t dec_cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void dec_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the float at `p` (an address in this CTA's shared memory) in CTA `rank` of the cluster
+__device__ __forceinline__ float dec_peer_f32(const float* p, uint32_t rank) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  uint32_t ra;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
   return v;
 }
 
@@ -130,7 +150,8 @@ struct DecSmem {
   static constexpr int PIECES = HD / 8;                 // per lane and block: HD/16 of keys + HD/16 of values
   static constexpr int RING_BYTES = DEC_WARPS * DEC_STAGES * PIECES * 32 * 16;
   static constexpr int MERGE_BYTES = (DEC_WARPS * 16 * (HD + 4) + 2 * DEC_WARPS * 16) * 4;
-  static constexpr int BYTES = RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES;
+  static constexpr int RESULT_BYTES = (16 * HD + 2 * 16) * 4;      // the CTA's own (output, max, sum), read by its cluster
+  static constexpr int BYTES = RING_BYTES > MERGE_BYTES + RESULT_BYTES ? RING_BYTES : MERGE_BYTES + RESULT_BYTES;
 };
 
 template <int HD>
@@ -159,6 +180,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
   // which sequence, and which share of its keys
   int b = blockIdx.x, split = 0, num_splits = 1, len, cache_slot;
   const bool direct = plan == nullptr && even_splits == 1;   // one chunk per sequence: no scratch
+  const bool clustered = dec_cluster_size() > 1;          // the chunks of a sequence are the CTAs of a cluster
   if (plan == nullptr) {                                 // no plan: every sequence in `even_splits` chunks
     b = blockIdx.x / even_splits; split = blockIdx.x % even_splits; num_splits = even_splits;
     len = kv_lens[b]; cache_slot = seq_slots[b];
@@ -348,11 +370,37 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
     const int h = gkv * m + r;
     if (direct) {
       out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    } else if (clustered) {
+      float* c_o = reinterpret_cast<float*>(dec_smem + DecSmem<HD>::MERGE_BYTES);
+      c_o[r * HD + d] = O;
+      if (d == 0) { c_o[16 * HD + r] = M; c_o[16 * HD + 16 + r] = L; }
     } else {
       const size_t p = (size_t)blockIdx.x * H + h;         // partial results lie in grid order
       part_o[p * HD + d] = O;
       if (d == 0) { part_ml[2 * p] = M; part_ml[2 * p + 1] = L; }
     }
+  }
+  if (clustered) {
+    // every chunk of the sequence has its result in shared memory; this CTA finishes its share
+    // of the m x HD outputs, adding the chunks in their order
+    dec_cluster_sync();
+    const float* c_o = reinterpret_cast<const float*>(dec_smem + DecSmem<HD>::MERGE_BYTES);
+    const int per = (m * HD + num_splits - 1) / num_splits;
+    const int lo = split * per, hi = min(lo + per, m * HD);
+    for (int idx = lo + threadIdx.x; idx < hi; idx += DEC_WARPS * 32) {
+      const int r = idx / HD, d = idx % HD;
+      float M = -INFINITY;
+      for (int c = 0; c < num_splits; ++c) M = fmaxf(M, dec_peer_f32(c_o + 16 * HD + r, c));
+      float L = 0.f, O = 0.f;
+      for (int c = 0; c < num_splits; ++c) {
+        const float mc = dec_peer_f32(c_o + 16 * HD + r, c);
+        const float wgt = (mc > -INFINITY) ? exp2f(mc - M) : 0.f;
+        L += dec_peer_f32(c_o + 16 * HD + 16 + r, c) * wgt;
+        O += dec_peer_f32(c_o + r * HD + d, c) * wgt;
+      }
+      out[(size_t)b * ldo + (size_t)(gkv * m + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    }
+    dec_cluster_sync();      // nobody leaves while its shared memory may still be read
   }
 }
 
@@ -400,6 +448,33 @@ static int launch_decode(const void* q, int ldq, const void* k_pool, const void*
   const int4* entries = (const int4*)plan;                                   // null with one split
   const int2* seqs = plan ? (const int2*)(plan + 4 * (size_t)nchunk) : nullptr;
   dim3 grid(nchunk, G);
+  if (num_splits > 1 && part_o == nullptr) {
+    // no scratch: the chunks of a sequence are the CTAs of a cluster and combine through shared memory
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(DEC_WARPS * 32);
+    cfg.dynamicSmemBytes = DecSmem<HD>::BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (g_rl_pdl_enabled) {
+      attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[na].val.programmaticStreamSerializationAllowed = 1;
+      ++na;
+    }
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = num_splits; attr[na].val.clusterDim.y = 1; attr[na].val.clusterDim.z = 1;
+    ++na;
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_kernel<HD>,
+        (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table, max_pages,
+        seq_slots, kv_lens, (const int4*)nullptr, (__nv_bfloat16*)out, ldo, (float*)nullptr, (float*)nullptr, H, G,
+        scale * 1.4426950408889634f, window, num_splits);
+    RL_REQUIRE(e == cudaSuccess, "rl_attention_decode: cluster launch failed: %s", cudaGetErrorString(e));
+    RL_LAUNCH_CHECK("rl_attention_decode");
+    return RL_OK;
+  }
   rl_launch_pdl(attention_decode_kernel<HD>, grid, dim3(DEC_WARPS * 32), (size_t)DecSmem<HD>::BYTES, stream,
       (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table, max_pages,
       seq_slots, kv_lens, entries, (__nv_bfloat16*)out, ldo, part_o, part_ml, H, G, scale * 1.4426950408889634f, window,
@@ -456,7 +531,9 @@ extern "C" int rl_attention_decode_plan(const int* seq_slots, const int* kv_lens
 // scratch: rl_attention_decode_scratch_floats(...) floats (may be null with one split).
 // plan: what rl_attention_decode_plan made for these sequences, window and splits, or
 // null: then every sequence is cut into num_splits equal chunks whatever its length
-// (right for one sequence, or for sequences of like lengths).
+// (right for one sequence, or for sequences of like lengths).  Null scratch with 2, 4 or 8
+// splits and no plan: the chunks of a sequence run as a thread-block cluster and combine
+// through distributed shared memory (no scratch, no second kernel).
 extern "C" int rl_attention_decode(const void* q, int ldq, const void* k_pool, const void* v_pool,
                                    const int* page_table, int max_pages, const int* seq_slots, const int* kv_lens,
                                    void* out, int ldo, float* scratch, const int* plan, int num_seqs, int num_heads,
@@ -472,7 +549,8 @@ extern "C" int rl_attention_decode(const void* q, int ldq, const void* k_pool, c
              "rl_attention_decode: row strides too small or not a multiple of 8 elements");
   RL_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)k_pool & 15) == 0 && ((uintptr_t)v_pool & 15) == 0,
              "rl_attention_decode: q and the cache pools must be 16-byte aligned");
-  RL_REQUIRE(num_splits == 1 || scratch != nullptr, "rl_attention_decode: scratch is null with %d splits", num_splits);
+  RL_REQUIRE(num_splits == 1 || scratch != nullptr || (plan == nullptr && (num_splits == 2 || num_splits == 4 || num_splits == 8)),
+             "rl_attention_decode: without scratch the chunks combine as a cluster, which takes 2, 4 or 8 splits and no plan (got %d)", num_splits);
   RL_REQUIRE(plan == nullptr || ((uintptr_t)plan & 15) == 0, "rl_attention_decode: plan is not 16-byte aligned");
   RL_REQUIRE(window >= 0, "rl_attention_decode: negative window");
   if (num_seqs == 0) return RL_OK;

@@ -465,12 +465,13 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
                      seq_slots: torch.Tensor, kv_lens: torch.Tensor, out: torch.Tensor, num_heads: int,
                      num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
                      num_splits: Optional[int] = None, scratch: Optional[torch.Tensor] = None,
-                     plan: Optional[torch.Tensor] = None) -> None:
+                     plan: Optional[torch.Tensor] = None, cluster: bool = False) -> None:
     """One token per sequence over the bf16 cache, split over the context (tensor cores).
     q: [B, >= H*hd] bf16 (a view into the qkv buffer is fine); out: [B, H*hd] bf16.
     ``num_splits``: chunks per sequence; with a ``plan`` (from ``decode_plan`` with the
     same sequences, window and splits) that many on average, dealt to the sequences by
-    length."""
+    length.  ``cluster`` (2, 4 or 8 splits, no plan): the chunks of a sequence run as a
+    thread-block cluster and combine through shared memory - no scratch, one kernel."""
     _need(q, "q", torch.bfloat16, contiguous=False); _need(k_pool, "k_pool", torch.bfloat16)
     _need(v_pool, "v_pool", torch.bfloat16); _need(out, "out", torch.bfloat16)
     _need(page_table, "page_table", torch.int32); _need(seq_slots, "seq_slots", torch.int32)
@@ -479,8 +480,10 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     assert seq_slots.numel() == B and kv_lens.numel() == B and q.stride(1) == 1
     if num_splits is None:
         num_splits = decode_splits(B, num_kv_heads)
-    need = decode_scratch_floats(B, num_heads, head_dim, num_splits)
-    if num_splits > 1 and scratch is None:
+    if cluster:
+        assert plan is None and scratch is None and num_splits in (1, 2, 4, 8)
+    need = 0 if cluster else decode_scratch_floats(B, num_heads, head_dim, num_splits)
+    if num_splits > 1 and scratch is None and not cluster:
         scratch = torch.empty(need, dtype=torch.float32, device=q.device)
     if scratch is not None:
         _need(scratch, "scratch", torch.float32)
@@ -493,7 +496,7 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
         q.data_ptr(), ldq, k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr(), page_table.shape[1],
         seq_slots.data_ptr(), kv_lens.data_ptr(), out.data_ptr(), out.stride(0), _ptr(scratch), _ptr(plan), B,
         num_heads, num_kv_heads, head_dim, float(scale), int(window), int(num_splits), _stream()), "rl_attention_decode")
-    _count(2 if num_splits > 1 else 1)
+    _count(2 if num_splits > 1 and not cluster else 1)
 
 
 # ----------------------------------------------------------------------------- prefill attention
@@ -566,9 +569,14 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
     sequence boundaries (engine.step.StepState)."""
     if step.is_decode and attention_decode_supported(q.dtype, num_heads, num_kv_heads, head_dim):
         splits = decode_splits(q.shape[0], num_kv_heads)
+        if q.shape[0] == 1 and splits >= 8:
+            # one sequence: nothing to deal; eight equal chunks as one cluster, combined through shared memory
+            attention_decode(q, k_pool, v_pool, page_table, step.seq_slots, step.kv_lens, out,
+                             num_heads, num_kv_heads, head_dim, scale, window, num_splits=8, cluster=True)
+            return
         plan = None
         derived = getattr(step, "derived", None)     # what layers of one step share
-        if splits > 1 and q.shape[0] > 1 and derived is not None:     # one sequence: nothing to deal
+        if splits > 1 and q.shape[0] > 1 and derived is not None:
             key = ("decode_plan", int(window), splits)
             plan = derived.get(key)
             if plan is None:

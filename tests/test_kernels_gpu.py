@@ -507,6 +507,22 @@ def test_attention_decode_matches_plain(H, G, hd, splits, planned):
     torch.testing.assert_close(out.float(), simt.float(), rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("H,G,hd", [(32, 8, 128), (6, 2, 64), (16, 1, 128)])
+@pytest.mark.parametrize("splits", [2, 4, 8])
+def test_attention_decode_chunks_of_a_sequence_as_a_cluster(H, G, hd, splits):
+    """No scratch, one kernel: the chunks' CTAs combine through distributed shared memory."""
+    k = K()
+    lens = [1, 15, 64, 65, 200, 513, 1100]
+    for window in (0, 90):
+        case = _attention_case(torch.bfloat16, H, G, hd, [1] * len(lens), lens, window=window, seed=hd + splits)
+        q, kp, vp, pt, slots, kv_lens, ref = _decode_inputs(case)
+        out = torch.full((len(lens), H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        before = k.launch_count
+        k.attention_decode(q, kp, vp, pt, slots, kv_lens, out, H, G, hd, 1.0 / math.sqrt(hd), window, num_splits=splits, cluster=True)
+        assert k.launch_count - before == 1
+        torch.testing.assert_close(out.double().cpu(), ref, **_tol(torch.bfloat16))
+
+
 @pytest.mark.parametrize("splits,window", [(2, 0), (7, 0), (3, 100)])
 def test_attention_decode_deals_chunks_by_length(splits, window):
     """More sequences than a warp has lanes, one of them far longer than the rest: the
