@@ -107,7 +107,14 @@ def _check(code: int, name: str) -> None:
         raise KernelError(f"{name} failed ({code}): {msg}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current CUDA stream of the current device as a raw handle (asked for on every
+    launch: during graph capture it is the capturing stream)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
