@@ -12,8 +12,9 @@
 // fail; code that is handed only raw pointers and a stream and has no allocator to ask.
 // For them the scratch is a fixed array inside the library.
 //
-// What it does.  Exactly what rl_attention_decode does, with the same arguments minus
-// `scratch`.  It calls no cudaMalloc, cudaFree or other allocating routine.
+// What it does.  Exactly what rl_attention_decode does without a plan (every sequence in
+// num_splits equal chunks, a second kernel combines them), with the same arguments minus
+// `scratch` and `plan`.  It calls no cudaMalloc, cudaFree or other allocating routine.
 //
 // Limits and rules.
 //  * The built-in scratch holds RL_DECODE_STATIC_SCRATCH_FLOATS floats (4 MiB).  A call
