@@ -1,4 +1,4 @@
-// Prefill attention on the 5th-generation tensor cores (tcgen05), head size 128.
+// Prefill attention on the 5th-generation tensor cores (tcgen05), head sizes 64 and 128.
 //
 // Same math and the same packed, paged inputs as attention_prefill.cu (which stays the
 // kernel for head size 64 and is the restatement this one is tested against): causal
@@ -40,15 +40,18 @@ namespace {
 
 constexpr int TQ = 128;          // query rows per CTA
 constexpr int TK = 128;          // keys per tile = two pages
-constexpr int HD = 128;
 constexpr int FA_THREADS = 320;       // warp 0: TMA, warp 1: MMA, warps 2-9: softmax
 constexpr uint32_t FA_WAIT_LIMIT = 1u << 22;
 constexpr int KV_STAGES = 2;
 constexpr int HALF_BYTES = 128 * 64 * 2;               // [128 rows x 64 bf16], 16 KB
-constexpr int Q_BYTES = 2 * HALF_BYTES;                // 32 KB
-constexpr int KV_STAGE_BYTES = 4 * HALF_BYTES;         // K halves, V halves: 64 KB
-constexpr int FA_XCHG_BYTES = 3 * 2 * TQ * 4;          // row maxima (two tiles in turn) and row sums, one number a thread
-constexpr int FA_SMEM = Q_BYTES + KV_STAGES * KV_STAGE_BYTES + 1024 + 256 + FA_XCHG_BYTES;
+// sizes that depend on the head size HD (64 or 128): a head is HD / 64 halves of 64 dimensions
+template <int HD> struct FaSizes {
+  static constexpr int HALVES = HD / 64;
+  static constexpr int Q_BYTES = HALVES * HALF_BYTES;          // 16 or 32 KB
+  static constexpr int KV_STAGE_BYTES = 2 * HALVES * HALF_BYTES;  // K halves, then V halves: 32 or 64 KB
+  // + alignment slack, barriers, and the softmax threads' exchange: row maxima (two tiles in turn) and row sums
+  static constexpr int SMEM = Q_BYTES + KV_STAGES * KV_STAGE_BYTES + 1024 + 256 + 3 * 2 * TQ * 4;
+};
 constexpr float LAZY_LOG2 = 8.0f;                      // rescale O only when the maximum grew by more than 2^8
 
 __device__ __forceinline__ uint32_t fa_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -170,6 +173,7 @@ __host__ __device__ constexpr uint32_t fa_idesc(int m, int n, int b_mn) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+template <int HD>
 __global__ void __launch_bounds__(FA_THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ page_table, int max_pages,
@@ -179,7 +183,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   extern __shared__ uint8_t fa_smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)fa_smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* q_tile = smem;                                   // [2 halves][128 x 64]
-  uint8_t* kv_ring = smem + Q_BYTES;                        // [stage][K half0, K half1, V half0, V half1]
+  constexpr int HALVES = FaSizes<HD>::HALVES, Q_BYTES = FaSizes<HD>::Q_BYTES, KV_STAGE_BYTES = FaSizes<HD>::KV_STAGE_BYTES;
+  uint8_t* kv_ring = smem + Q_BYTES;                        // [stage][K halves, V halves]
   uint64_t* bars = (uint64_t*)(kv_ring + KV_STAGES * KV_STAGE_BYTES);
   uint64_t* q_full = bars;                 // 1
   uint64_t* k_full = bars + 1;             // [KV_STAGES] each: keys and values of a stage are
@@ -257,8 +262,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (lane == 0 && have_work) {
       // ---------------- TMA producer ----------------
       fa_expect_tx(fa_smem_u32(q_full), Q_BYTES);
-      fa_tma_2d(fa_smem_u32(q_tile), &map_q, fa_smem_u32(q_full), h * HD, row0 + qt0);
-      fa_tma_2d(fa_smem_u32(q_tile + HALF_BYTES), &map_q, fa_smem_u32(q_full), h * HD + 64, row0 + qt0);
+#pragma unroll
+      for (int half = 0; half < HALVES; ++half)
+        fa_tma_2d(fa_smem_u32(q_tile + half * HALF_BYTES), &map_q, fa_smem_u32(q_full), h * HD + 64 * half, row0 + qt0);
       // keys of tile i + 1 are asked for before the values of tile i: the keys' stage is free as
       // soon as S of two tiles back is done, the values' only when that tile's P V is
       auto load = [&](int i, bool values) -> bool {
@@ -273,11 +279,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int p1 = (2 * kt + 1) * RL_PAGE < kv_len ? pages[2 * kt + 1] : p0;   // beyond the sequence: any valid page (all masked)
         const int r0 = (p0 * G + gkv) * RL_PAGE, r1 = (p1 * G + gkv) * RL_PAGE;
         const uint32_t fb = fa_smem_u32(values ? &v_full[st] : &k_full[st]);
-        uint8_t* base = kv_ring + (size_t)st * KV_STAGE_BYTES + (values ? 2 * HALF_BYTES : 0);
+        uint8_t* base = kv_ring + (size_t)st * KV_STAGE_BYTES + (values ? HALVES * HALF_BYTES : 0);
         const CUtensorMap* map = values ? &map_v : &map_k;
-        fa_expect_tx(fb, 2 * HALF_BYTES);
+        fa_expect_tx(fb, HALVES * HALF_BYTES);
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {          // 64 head dimensions a half; 64 positions a page
+        for (int half = 0; half < HALVES; ++half) {     // 64 head dimensions a half; 64 positions a page
           fa_tma_2d(fa_smem_u32(base + half * HALF_BYTES), map, fb, 64 * half, r0);
           fa_tma_2d(fa_smem_u32(base + half * HALF_BYTES + 64 * 128), map, fb, 64 * half, r1);
         }
@@ -320,7 +326,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (!fa_wait(fa_smem_u32(&v_full[i % KV_STAGES]), (i / KV_STAGES) & 1, abort_flag)) { ok = false; break; }
         if (!fa_wait(fa_smem_u32(p_full), i & 1, abort_flag)) { ok = false; break; }
         fa_fence_after();
-        uint8_t* vbase = kv_ring + (size_t)(i % KV_STAGES) * KV_STAGE_BYTES + 2 * HALF_BYTES;
+        uint8_t* vbase = kv_ring + (size_t)(i % KV_STAGES) * KV_STAGE_BYTES + HALVES * HALF_BYTES;
 #pragma unroll
         for (int k = 0; k < TK / 16; ++k) {                 // 16 positions a step
           // P of this tile: 16 keys = 8 columns of packed bf16 pairs a step, in its S buffer
@@ -335,7 +341,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
   } else if (have_work) {
     // ---------------- softmax warps: two threads a query row, 64 keys each ----------------
-    constexpr int HK = TK / 2;                              // keys (and output columns) a thread
+    constexpr int HK = TK / 2;                              // keys a thread
+    constexpr int OC = HD / 2;                              // output columns a thread
     const int quarter = warp & 3, half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;                      // row of the tile = lane of tensor memory
     const int pos = start_pos + qt0 + r;                    // position of this row's query
@@ -405,9 +412,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         fa_fence_after();
         l_run *= corr;
 #pragma unroll 1
-        for (int c = 0; c < HK / 32; ++c) {               // this thread's half of the row of O
+        for (int c = 0; c < OC / 32; ++c) {               // this thread's half of the row of O
           uint32_t v[32];
-          const uint32_t o_addr = tmem_o + lane_addr + (uint32_t)(half * HK + c * 32);
+          const uint32_t o_addr = tmem_o + lane_addr + (uint32_t)(half * OC + c * 32);
           fa_ld32(o_addr, v);
           fa_wait_ld();
 #pragma unroll
@@ -439,11 +446,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (ok) {
       const float l_row = half == 0 ? l_run + x_sum[TQ + r] : x_sum[r] + l_run;    // keys 0-63 first, either way
       const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
-      __nv_bfloat16* orow = out + (size_t)(row0 + qt0 + r) * ldo + (size_t)h * HD + half * HK;
+      __nv_bfloat16* orow = out + (size_t)(row0 + qt0 + r) * ldo + (size_t)h * HD + half * OC;
 #pragma unroll 1
-      for (int c = 0; c < HK / 16; ++c) {
+      for (int c = 0; c < OC / 16; ++c) {
         uint32_t v[16];
-        fa_ld16(tmem_o + lane_addr + (uint32_t)(half * HK + c * 16), v);
+        fa_ld16(tmem_o + lane_addr + (uint32_t)(half * OC + c * 16), v);
         fa_wait_ld();
         if (r < rows_here) {
           uint32_t pk[8];
@@ -497,10 +504,10 @@ int fa_make_map(CUtensorMap* map, const void* base, long long rows, int cols, lo
 
 }  // namespace
 
-// 1 if the tcgen05 prefill kernel takes this shape: head size 128.
+// 1 if the tcgen05 prefill kernel takes this shape: head size 64 or 128.
 extern "C" int rl_attention_prefill_tc_supported(int num_heads, int num_kv_heads, int head_dim) {
   if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0) return 0;
-  return head_dim == 128;
+  return head_dim == 64 || head_dim == 128;
 }
 
 // Same contract as rl_attention_prefill, with num_tiles = sum over sequences of
@@ -513,7 +520,7 @@ extern "C" int rl_attention_prefill_tc(const void* q, int ldq, const void* k_poo
                                        int num_tokens, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim,
                                        float scale, int window, int* err, cudaStream_t stream) {
   RL_REQUIRE(rl_attention_prefill_tc_supported(num_heads, num_kv_heads, head_dim),
-             "rl_attention_prefill_tc: unsupported shape (heads %d, KV heads %d, head_dim %d): needs head_dim 128",
+             "rl_attention_prefill_tc: unsupported shape (heads %d, KV heads %d, head_dim %d): needs head_dim 64 or 128",
              num_heads, num_kv_heads, head_dim);
   RL_REQUIRE(num_seqs >= 0 && num_tiles >= 0 && num_tokens >= 0 && num_pages > 0 && num_heads <= 65535, "rl_attention_prefill_tc: bad sizes");
   RL_REQUIRE(ldq >= num_heads * head_dim && ldq % 8 == 0 && ldo >= num_heads * head_dim && ldo % 8 == 0,
@@ -524,8 +531,10 @@ extern "C" int rl_attention_prefill_tc(const void* q, int ldq, const void* k_poo
   if (num_seqs == 0 || num_tiles == 0) return RL_OK;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM);
-    RL_REQUIRE(e == cudaSuccess, "rl_attention_prefill_tc: cannot reserve %d bytes of shared memory: %s", FA_SMEM, cudaGetErrorString(e));
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FaSizes<128>::SMEM);
+    RL_REQUIRE(e == cudaSuccess, "rl_attention_prefill_tc: cannot reserve %d bytes of shared memory: %s", FaSizes<128>::SMEM, cudaGetErrorString(e));
+    e = cudaFuncSetAttribute(attention_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FaSizes<64>::SMEM);
+    RL_REQUIRE(e == cudaSuccess, "rl_attention_prefill_tc: cannot reserve %d bytes of shared memory: %s", FaSizes<64>::SMEM, cudaGetErrorString(e));
     configured = true;
   }
   CUtensorMap mq, mk, mv;
@@ -536,9 +545,13 @@ extern "C" int rl_attention_prefill_tc(const void* q, int ldq, const void* k_poo
   if (rc != RL_OK) return rc;
   rc = fa_make_map(&mv, v_pool, pool_rows, head_dim, head_dim, RL_PAGE);
   if (rc != RL_OK) return rc;
-  cudaError_t e = rl_launch_pdl(attention_prefill_tc_kernel, dim3(num_tiles, num_heads), dim3(FA_THREADS), (size_t)FA_SMEM, stream,
-                                mq, mk, mv, page_table, max_pages, cu_seqlens, seq_slots, kv_lens, num_seqs,
-                                (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, scale * 1.4426950408889634f, window, err);
+  cudaError_t e = head_dim == 128
+      ? rl_launch_pdl(attention_prefill_tc_kernel<128>, dim3(num_tiles, num_heads), dim3(FA_THREADS), (size_t)FaSizes<128>::SMEM, stream,
+                      mq, mk, mv, page_table, max_pages, cu_seqlens, seq_slots, kv_lens, num_seqs,
+                      (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, scale * 1.4426950408889634f, window, err)
+      : rl_launch_pdl(attention_prefill_tc_kernel<64>, dim3(num_tiles, num_heads), dim3(FA_THREADS), (size_t)FaSizes<64>::SMEM, stream,
+                      mq, mk, mv, page_table, max_pages, cu_seqlens, seq_slots, kv_lens, num_seqs,
+                      (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, scale * 1.4426950408889634f, window, err);
   if (e != cudaSuccess) {
     rl_set_error("rl_attention_prefill_tc: launch failed: %s", cudaGetErrorString(e));
     return RL_ERR_CUDA;

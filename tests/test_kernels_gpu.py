@@ -665,13 +665,13 @@ def test_attention_prefill_finds_one_far_key(far):
 
 
 # ----------------------------------------------------------------------------- prefill attention (tcgen05)
+@pytest.mark.parametrize("hd", [64, 128])
 @pytest.mark.parametrize("H,G", [(32, 8), (4, 4), (3, 1)])
 @pytest.mark.parametrize("lens_q,lens_kv", [([1, 5, 64, 65, 200], [1, 5, 64, 65, 200]),
                                             ([130, 1, 33, 64], [130, 300, 97, 128]),
                                             ([129], [129]), ([128, 256], [128, 256]), ([700], [700]), ([40], [1000])])
-def test_attention_prefill_tc_matches_plain(H, G, lens_q, lens_kv):
+def test_attention_prefill_tc_matches_plain(H, G, lens_q, lens_kv, hd):
     k = K()
-    hd = 128
     assert k.attention_prefill_tc_supported(torch.bfloat16, H, G, hd)
     case = _attention_case(torch.bfloat16, H, G, hd, lens_q, lens_kv, seed=H + len(lens_q) + lens_kv[0])
     q, kp, vp, pt, cu, slots, kv_lens, ref = _prefill_inputs(case, lens_q, lens_kv)
@@ -681,9 +681,10 @@ def test_attention_prefill_tc_matches_plain(H, G, lens_q, lens_kv):
     torch.testing.assert_close(out.double().cpu(), ref, **_tol(torch.bfloat16))
 
 
-def test_attention_prefill_tc_window_and_strided_queries():
+@pytest.mark.parametrize("hd", [64, 128])
+def test_attention_prefill_tc_window_and_strided_queries(hd):
     k = K()
-    H, G, hd, W = 4, 2, 128, 200
+    H, G, W = 4, 2, 200
     lens_q, lens_kv = [40, 350, 3], [40, 500, 300]
     case = _attention_case(torch.bfloat16, H, G, hd, lens_q, lens_kv, window=W, seed=4)
     q, kp, vp, pt, cu, slots, kv_lens, ref = _prefill_inputs(case, lens_q, lens_kv)
@@ -695,12 +696,13 @@ def test_attention_prefill_tc_window_and_strided_queries():
     torch.testing.assert_close(out.double().cpu(), ref, **_tol(torch.bfloat16))
 
 
+@pytest.mark.parametrize("hd", [64, 128])
 @pytest.mark.parametrize("far", [0, 63, 64, 127, 128, 300])
-def test_attention_prefill_tc_finds_one_far_key_and_rescales(far):
+def test_attention_prefill_tc_finds_one_far_key_and_rescales(far, hd):
     """Every query from position `far` on must return the value of key `far`: its score is far
     above the running maximum of the tiles before it, so the lazily kept maximum has to move
     and the accumulator has to be rescaled."""
-    H, G, hd, n = 4, 2, 128, 451
+    H, G, n = 4, 2, 451
 
     def craft(b, qb, kb, vb):
         direction = torch.ones(hd) / math.sqrt(hd)
