@@ -7,7 +7,8 @@ one B200.
 Prints ONE JSON line.  ``value``: decoded tokens a second at a batch of 8 (K single-token
 steps timed on the device with CUDA events after W warm-up steps).  ``e2e``: the same
 through ``Runner.generate`` (host token ids in, host token ids out; every step uploads
-its inputs from pinned memory and reads the sampled ids back).  ``prefill``: one step
+its inputs from pinned memory and reads the sampled ids back), K steps on the host's clock
+after W steps of the same generation.  ``prefill``: one step
 over a 2,048-token prompt.  ``roofline``: bytes a decode step must read (every weight
 it uses once, and the cache of the live sequences) over its time, against the measured
 copy bandwidth.  ``points``: decode at batch 1 and 64.
@@ -111,7 +112,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
-    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=24)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--batch", type=int, default=8)
@@ -217,14 +218,20 @@ def main():
             points[f"decode_b{b}"] = b * 1000.0 / pm
 
     # ---- end to end through the entry point ----
+    # One generation of warmup + steps + 1 tokens a sequence; the host's clock is read in the token
+    # callback, when the ids of a step are in the host's hands.  Like the device-timed arm it leaves
+    # `warmup` single-token steps untimed: the first steps after a prompt step run at the lower clocks
+    # the prompt step's power draw left behind.
     prompts = headline_prompts
-    opts = GenerationOptions(max_tokens=args.steps + 1, sampler=SamplerConfig(temperature=0.8), seed=1, ignore_eos=True)
-    runner.generate(prompts, GenerationOptions(max_tokens=args.warmup + 1, sampler=SamplerConfig(temperature=0.8),
-                                               seed=1, ignore_eos=True))
-    res = runner.generate(prompts, opts)
-    decode_s = res[0].stats.decode_time
-    steps_run = res[0].stats.steps - 1
-    e2e_value = args.batch * steps_run / decode_s
+    mk = lambda n: GenerationOptions(max_tokens=n, sampler=SamplerConfig(temperature=0.8), seed=1, ignore_eos=True)
+    runner.generate(prompts, mk(4))                   # captures the step for this batch size
+    stamps = []
+    def on_token(i, _tok):
+        if i == args.batch - 1:                       # the last sequence of a step's tokens
+            stamps.append(time.perf_counter())
+    runner.generate(prompts, mk(args.warmup + args.steps + 1), on_token=on_token)
+    assert len(stamps) == args.warmup + args.steps + 1
+    e2e_value = args.batch * args.steps / (stamps[args.warmup + args.steps] - stamps[args.warmup])
     # per single-token step: 7B+1 int32 (tokens, positions, slots, offsets, lengths, wanted rows)
     # and 3B float32 for the sampler (temperature, uniform, min_p), all from pinned memory
     h2d_per_step = (7 * args.batch + 1) * 4 + 3 * args.batch * 4
@@ -243,7 +250,9 @@ def main():
                    "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": "U[128,2048)",
                    "mean_context": round(ctx_tokens / args.batch, 1), "parallelism": "single GPU",
                    "l2": "inputs larger than L2 (15 GB of weights a step)", "peaks": peak_src,
-                   "decode": "CUDA graph per batch size"},
+                   "decode": "CUDA graph per batch size",
+                   "e2e_loop": "each step copies its integers from pinned memory and its sampled ids back; "
+                               "a step is queued before the host has read the previous step's ids"},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d_per_step),
                 "d2h_bytes_per_step": 4 * args.batch},
         "gpu_launches": launches,

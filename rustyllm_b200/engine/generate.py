@@ -14,6 +14,16 @@ the sequence and is cut from it.
 
 The loop only needs ``alloc_slot / free_slot / step`` of an engine and ``sample`` of
 a sampler, so its decisions are tested on the CPU against stand-ins.
+
+Running ahead.  The host learns a step's tokens only after the device has sampled
+them, and the device would wait meanwhile for the host to queue the next step.  Where
+the engine has ``step_fed_from_device`` and the sampler ``sample_begin``, the loop
+queues the next step - fed with the sampled ids where they lie on the device - before
+it waits for the ids, whenever no live sequence can end for a reason the host knows
+beforehand (its token count, its context).  A sequence that then turns out to have
+drawn a stop token has run one step too many: its logits are dropped and its slot is
+freed as usual, and the other sequences' rows are taken from that step.  Tokens,
+finish reasons and the order of ``on_token`` calls are those of the plain loop.
 """
 from __future__ import annotations
 
@@ -37,6 +47,7 @@ class GenerationOptions:
     stop_sequences: Sequence[Sequence[int]] = ()
     ignore_eos: bool = False            # benchmarks: run to max_tokens
     max_context: Optional[int] = None   # cap of the context (reference: --max-context)
+    run_ahead: bool = True              # queue a step before the host has read the previous one's tokens
 
     def validate(self) -> None:
         if self.max_tokens <= 0:
@@ -119,6 +130,8 @@ def generate_batch(engine, sampler, prompts: Sequence[Sequence[int]], options: G
     slots: List[Optional[int]] = []
     # the logits of a step are sampled from before the next step runs: no copy of them is needed
     step = getattr(engine, "step_borrowed", engine.step)
+    step_ahead = getattr(engine, "step_fed_from_device", None) if options.run_ahead else None
+    sample_begin = getattr(sampler, "sample_begin", None)
     try:
         for _ in range(B):
             slots.append(engine.alloc_slot())
@@ -128,8 +141,16 @@ def generate_batch(engine, sampler, prompts: Sequence[Sequence[int]], options: G
         steps = 1
         live = list(range(B))
         while live:
-            toks = sampler.sample(logits, [states[i] for i in live])
-            nxt, feed = [], []
+            ahead = None
+            if (step_ahead is not None and sample_begin is not None
+                    and all(len(out[i]) + 1 < options.max_tokens and pos[i] < cache_len[i] for i in live)):
+                # only a stop token or a stop sequence can end a sequence now: run the next step at once
+                pending = sample_begin(logits, [states[i] for i in live])
+                ahead = step_ahead([slots[i] for i in live], pending.device_ids)
+                toks = pending.wait()
+            else:
+                toks = sampler.sample(logits, [states[i] for i in live])
+            nxt, feed, kept_rows = [], [], []
             for row, i in enumerate(live):
                 tok = int(toks[row])
                 if tok in stop:
@@ -154,10 +175,15 @@ def generate_batch(engine, sampler, prompts: Sequence[Sequence[int]], options: G
                 else:
                     nxt.append(i)
                     feed.append([tok])
+                    kept_rows.append(row)
+            ran = len(live)
             live = nxt
             if not live:
                 break
-            logits = step([slots[i] for i in live], feed, "last")
+            if ahead is None:
+                logits = step([slots[i] for i in live], feed, "last")
+            else:
+                logits = ahead if len(live) == ran else ahead[kept_rows]
             for i in live:
                 pos[i] += 1
             steps += 1

@@ -77,14 +77,14 @@ class _DecodeGraph:
 
     def upload(self, tokens, starts, slots) -> int:
         """The integers of a single-token step from the host into ``static_in``; returns
-        the bytes copied."""
+        the bytes copied.  ``tokens`` None: the caller puts them there from the device."""
         B = self.num_seqs
         k = self._next
         self._next = (k + 1) % len(self._host)
         if self._in_use[k]:
             self._copied[k].synchronize()
         a = self._host_np[k]
-        a[0:B] = tokens
+        a[0:B] = 0 if tokens is None else tokens
         a[B:2 * B] = starts                       # position of the new token
         a[2 * B:3 * B] = slots                    # slot of each token
         a[3 * B:4 * B + 1] = self._rows           # token offsets: one token a sequence
@@ -196,6 +196,28 @@ class Engine:
         generation loop samples from them at once): a captured step then hands out the
         graph's own output buffer instead of a copy."""
         return self.step(slots, tokens, want, _borrow=True)
+
+    def step_fed_from_device(self, slots: Sequence[int], token_ids: torch.Tensor) -> Optional[torch.Tensor]:
+        """A single-token step of ``slots`` whose tokens are on the device already
+        (``token_ids``: int32 [len(slots)], as a sampler leaves them), queued without waiting
+        for them: the host may learn the ids while the step runs.  Ids a sampler wrote lie
+        inside the vocabulary, so nothing is checked.  Returns the logits of the last (only)
+        tokens in the captured step's own buffer, overwritten by its next run - or ``None``
+        when no captured step for this many sequences exists yet and nothing was run."""
+        B = len(slots)
+        g = self._graphs.get(B) if self.use_graphs else None
+        if g is None:
+            return None
+        if token_ids.dtype != torch.int32 or token_ids.numel() != B:
+            raise ValueError(f"token_ids must hold {B} int32 ids")
+        ones = [1] * B
+        self.cache.prepare(slots, ones)
+        self.h2d_bytes += g.upload(None, [self.cache.length(s) for s in slots], slots)
+        g.static_in[:B].copy_(token_ids, non_blocking=True)
+        g.graph.replay()
+        K.launch_count += g.launches
+        self.cache.commit(slots, ones)
+        return g.logits
 
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], want: Want = "last",
              _borrow: bool = False) -> Optional[torch.Tensor]:

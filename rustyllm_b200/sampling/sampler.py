@@ -43,17 +43,20 @@ class Sampler:
         self._host_ids: Optional[torch.Tensor] = None      # pinned: the sampled ids come back through it
         self._ids_copied = torch.cuda.Event() if device.type == "cuda" else None
 
-    def _to_host(self, ids: torch.Tensor) -> List[int]:
-        """The sampled ids on the host (waits for the kernels that produced them)."""
-        if self._ids_copied is None:
-            return ids.tolist()
+    def _copy_to_host(self, ids: torch.Tensor) -> None:
         n = ids.numel()
         if self._host_ids is None or self._host_ids.numel() < n:
             self._host_ids = torch.empty(max(n, 256), dtype=torch.int32, pin_memory=True)
         self._host_ids[:n].copy_(ids, non_blocking=True)
         self._ids_copied.record()
+
+    def _to_host(self, ids: torch.Tensor) -> List[int]:
+        """The sampled ids on the host (waits for the kernels that produced them)."""
+        if self._ids_copied is None:
+            return ids.tolist()
+        self._copy_to_host(ids)
         self._ids_copied.synchronize()
-        return self._host_ids[:n].tolist()
+        return self._host_ids[:ids.numel()].tolist()
 
     @property
     def h2d_bytes(self) -> int:
@@ -63,6 +66,18 @@ class Sampler:
         """logits: float32 [B, V] on the device (modified in place by the repeat
         penalty).  Draws one uniform from the generator of every row that is not
         greedy.  Returns host token ids."""
+        return self._to_host(self._sample_on_device(logits, states))
+
+    def sample_begin(self, logits: torch.Tensor, states: Sequence[SequenceSamplingState]) -> "PendingIds":
+        """``sample`` in two halves: the kernels and the copy to the host are queued here and
+        the ids are waited for in ``PendingIds.wait``, so that the caller can queue the next
+        step, fed from ``PendingIds.device_ids``, in between.  One pending result at a time."""
+        ids = self._sample_on_device(logits, states)
+        if self._ids_copied is not None:
+            self._copy_to_host(ids)
+        return PendingIds(self, ids)
+
+    def _sample_on_device(self, logits: torch.Tensor, states: Sequence[SequenceSamplingState]) -> torch.Tensor:
         B, V = logits.shape
         assert B == len(states)
         dev = logits.device
@@ -87,7 +102,7 @@ class Sampler:
 
         if all(s.config.is_greedy for s in states):
             K.argmax(logits, out)
-            return self._to_host(out)
+            return out
 
         def takes_top_k(c: SamplerConfig) -> bool:
             return not c.is_greedy and 1 < c.top_k < V
@@ -110,4 +125,19 @@ class Sampler:
             K.sample_candidates(logits, fd[0], fd[1], fd[2], out,
                                 topk, [states[b].config.top_k for b in topk], [states[b].config.top_p for b in topk],
                                 topp, [states[b].config.top_p for b in topp])
-        return self._to_host(out)
+        return out
+
+
+class PendingIds:
+    """Token ids that a sampler has queued: on the device now, on the host after ``wait``."""
+
+    def __init__(self, sampler: Sampler, device_ids: torch.Tensor):
+        self._sampler = sampler
+        self.device_ids = device_ids      # int32 [B]
+
+    def wait(self) -> List[int]:
+        s = self._sampler
+        if s._ids_copied is None:
+            return self.device_ids.tolist()
+        s._ids_copied.synchronize()
+        return s._host_ids[:self.device_ids.numel()].tolist()

@@ -95,6 +95,36 @@ def test_stop_tokens_and_batches_one_after_another(model_dirs):
     assert r.cache.free_pages == r.cache.num_pages and r.cache.slots.free_count == 2
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_ahead_of_the_host_generates_the_same_tokens(model_dirs, dtype):
+    """The loop queues a step before it has read the previous step's tokens; with stop tokens
+    that end sequences in the middle of a batch, filters and a repeat penalty, several batches
+    one after another, the tokens are those of the loop that waits every step."""
+    from rustyllm_b200 import GenerationOptions, Runner, SamplerConfig
+    from rustyllm_b200 import kernels as K
+    d, cfg = model_dirs["B"]
+    r, _ = Runner.from_path(d, dtype=dtype, max_cache_tokens=64 * 8, max_batch=4)
+    prompts = [random_tokens(384, n, 90 + n) for n in (4, 33, 9, 61, 2, 17, 26)]
+    for sampler in (SamplerConfig.greedy(), SamplerConfig(temperature=0.9),
+                    SamplerConfig(temperature=0.7, top_p=0.9, top_k=40, repeat_penalty=1.1)):
+        base = GenerationOptions(max_tokens=24, sampler=sampler, seed=5, run_ahead=False)
+        first = r.generate(prompts, base)
+        # stop tokens taken from what was generated: some sequences end early, at different steps
+        stops = tuple({first[1].token_ids[5], first[3].token_ids[11], first[5].token_ids[2]})
+        for stop_ids in ((), stops):
+            waits = r.generate(prompts, GenerationOptions(max_tokens=24, sampler=sampler, seed=5, run_ahead=False,
+                                                          stop_token_ids=stop_ids))
+            launches = K.launch_count
+            ahead = r.generate(prompts, GenerationOptions(max_tokens=24, sampler=sampler, seed=5, run_ahead=True,
+                                                          stop_token_ids=stop_ids))
+            assert [x.token_ids for x in ahead] == [x.token_ids for x in waits]
+            assert [x.finish_reason for x in ahead] == [x.finish_reason for x in waits]
+            assert K.launch_count > launches
+        assert any(x.finish_reason == "stop" for x in waits) and any(x.finish_reason == "length" for x in waits)
+        r.cache.check()
+        assert r.cache.free_pages == r.cache.num_pages and r.cache.slots.free_count == 4
+
+
 def test_random_weights_without_files_and_layer_override():
     from rustyllm_b200 import GenerationOptions, Runner, SamplerConfig
     r = Runner.from_config(TINY["B"]["config"], seed=3, dtype="bfloat16", max_cache_tokens=64 * 4, max_batch=2,

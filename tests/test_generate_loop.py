@@ -43,6 +43,36 @@ class PickSampler:
         return [int(x) for x in logits.tolist()]
 
 
+class AheadEngine(ScriptedEngine):
+    """Also takes a step whose tokens it is handed as a tensor (the device's copy of the ids)."""
+
+    def __init__(self, script, max_slots=8):
+        super().__init__(script, max_slots)
+        self.ahead_calls = 0
+
+    def step_fed_from_device(self, slots, token_ids):
+        if self.ahead_calls == 0:          # like the engine before it has captured a step
+            self.ahead_calls = 1
+            return None
+        self.ahead_calls += 1
+        return self.step(slots, [[int(t)] for t in token_ids.tolist()], "last")
+
+
+class Pending:
+    def __init__(self, ids):
+        self.device_ids = torch.tensor(ids, dtype=torch.int32)
+        self.waited = False
+
+    def wait(self):
+        self.waited = True
+        return self.device_ids.tolist()
+
+
+class AheadSampler(PickSampler):
+    def sample_begin(self, logits, states):
+        return Pending(self.sample(logits, states))
+
+
 def run(script, prompts, **opt):
     eng = ScriptedEngine(script)
     stop_ids = opt.pop("eos", (99,))
@@ -102,6 +132,55 @@ def test_context_limit_ends_a_sequence():
     assert res[0].finish_reason == "context"
     assert res[0].token_ids == [7, 7, 7]
     assert sum(len(t[0]) for _, t in eng.calls) == 5
+
+
+SCENARIOS = [
+    (lambda held: len(held), [[5, 6, 7]], dict(max_tokens=4)),
+    (lambda held: 99 if len(held) == 5 else 10 + len(held), [[1, 2, 3]], dict(max_tokens=10)),
+    (lambda held: 99 if len(held) - 1 >= held[0] else 50, [[3], [1], [2], [7], [5]], dict(max_tokens=6)),
+    (lambda held: 99 if len(held) - 1 >= held[0] else 50, [[6], [2], [9], [4]], dict(max_tokens=30)),
+    (lambda held: len(held), [[0, 0], [0]], dict(max_tokens=10, stop_sequences=[[4, 5]])),
+    (lambda held: 7, [[1, 2, 3], [1]], dict(max_tokens=10, max_seq_len=5)),
+    (lambda held: 42, [[1]], dict(max_tokens=3, stop_token_ids=(42,))),
+]
+
+
+@pytest.mark.parametrize("case", range(len(SCENARIOS)))
+def test_running_ahead_changes_no_token_reason_or_callback(case):
+    script, prompts, opt = SCENARIOS[case]
+    _, plain, seen_plain = run(script, prompts, **dict(opt))
+    opt = dict(opt)
+    stop_ids = opt.pop("eos", (99,))
+    max_seq = opt.pop("max_seq_len", 1000)
+    opts = GenerationOptions(sampler=SamplerConfig(temperature=0.5), **opt)
+    eng, seen = AheadEngine(script), []
+    res = generate_batch(eng, AheadSampler(), prompts, opts, [1] * len(prompts), stop_ids, max_seq,
+                         on_token=lambda i, t: seen.append((i, t)))
+    assert eng.held == {}, "every slot goes back, none twice"
+    assert [r.token_ids for r in res] == [r.token_ids for r in plain]
+    assert [r.finish_reason for r in res] == [r.finish_reason for r in plain]
+    assert seen == seen_plain
+    # and with running ahead switched off the engine is never asked for it
+    opts.run_ahead = False
+    eng2 = AheadEngine(script)
+    res2 = generate_batch(eng2, AheadSampler(), prompts, opts, [1] * len(prompts), stop_ids, max_seq)
+    assert eng2.ahead_calls == 0 and [r.token_ids for r in res2] == [r.token_ids for r in plain]
+
+
+def test_running_ahead_feeds_an_ended_sequence_once_more_and_no_further():
+    # sequence [p] draws its stop token after p tokens; only a stop token is unknown beforehand
+    script = lambda held: 99 if len(held) - 1 >= held[0] else 50
+    eng = AheadEngine(script)
+    opts = GenerationOptions(sampler=SamplerConfig.greedy(), max_tokens=30)
+    res = generate_batch(eng, AheadSampler(), [[4], [2]], opts, [1, 1], (99,), 1000)
+    assert [r.token_ids for r in res] == [[50] * 4, [50] * 2]
+    sizes = [len(c[0]) for c in eng.calls]
+    # prompt step; plain step (nothing captured yet); then steps run ahead: the one queued while
+    # sequence 1 drew its stop token still holds it, the next does not
+    assert sizes == [2, 2, 2, 2, 1, 1]
+    assert eng.calls[3][1][1] == [99]          # the dropped step was fed the stop token itself
+    assert eng.calls[5][1][0] == [99]          # and so was the last one, whose logits nobody reads
+    assert eng.ahead_calls == 5
 
 
 def test_options_are_validated_like_the_reference():
