@@ -10,14 +10,15 @@
 // reference's grouped scan does on the CPU and its Metal kernel
 // ``resident_gqa4_attention`` (src/metal_backend.m:542-592) does for groups of four.
 //
-// The kernel is bound by the read of the cache.  Every lane fetches exactly the 16-byte
-// pieces of keys and values that its own MMA fragments need: a dot product does not care
-// in which order its terms are added, so the head dimension (for Q.K) and the key index
-// and output column (for P.V) are assigned to fragment positions such that every lane's
-// share is contiguous in memory.  The pieces travel by cp.async into a ring in shared
-// memory that is private to each lane (no lane reads what another copied, so no barrier
-// is needed, and consecutive lanes hit consecutive banks): two blocks of 16 keys are in
-// flight per warp while a third is being multiplied.
+// The kernel is bound by the read of the cache, and the cache is read fastest in whole
+// lines: a block of 16 keys (and of 16 values) of one KV head is contiguous in its page, and
+// every cp.async instruction of a warp copies 512 consecutive bytes of it (with 64 bytes a
+// row and instruction, as the MMA fragments would have it, the same bytes arrive at three
+// quarters of the rate).  The copies land in a ring in shared memory that belongs to the
+// warp (so a warp barrier is all the synchronisation there is), 16-byte pieces XOR-swizzled
+// by their row so that ldmatrix reads the fragments without bank conflicts - keys as they
+// lie, values transposed: two blocks of 16 keys are in flight per warp while a third is
+// being multiplied.
 //
 // Grid: (chunks, KV heads); 4 warps per CTA take their chunk's 16-key blocks in turn.
 // The batch's sequences x `splits` chunks are dealt to the sequences in proportion to
@@ -51,9 +52,6 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ uint4 ldg16(const __nv_bfloat16* p) {
-  return __ldg(reinterpret_cast<const uint4*>(p));
-}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -66,10 +64,18 @@ __device__ __forceinline__ void dec_cp_async16(uint32_t dst, const void* src, in
 __device__ __forceinline__ void dec_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void dec_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-__device__ __forceinline__ uint4 dec_lds16(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
+// four 8x8 bf16 matrices, row addresses from lanes 8i .. 8i+7; register i = matrix i, lane (g, t)
+// holding row g, columns 2t, 2t+1 (`trans`: column g, rows 2t, 2t+1)
+__device__ __forceinline__ void dec_ldmatrix4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void dec_ldmatrix4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t ldg_pair(const __nv_bfloat16* p) {
+  return __ldg(reinterpret_cast<const uint32_t*>(p));
 }
 
 // ---- thread-block cluster ----
@@ -143,12 +149,14 @@ __global__ void attention_decode_plan_kernel(const int* __restrict__ seq_slots, 
   for (int x = base + lane; x < nchunk; x += 32) entries[x] = make_int4(-1, 0, 0, 0);
 }
 
-// shared memory of one CTA: the ring [warp][stage][piece][lane] of 16-byte pieces, reused
-// after the loop for the warps' (max, sum, output)
+// shared memory of one CTA: the ring [warp][stage][keys | values][16 rows][HD] of bf16 (16-byte
+// pieces swizzled within their row), reused after the loop for the warps' (max, sum, output)
 template <int HD>
 struct DecSmem {
-  static constexpr int PIECES = HD / 8;                 // per lane and block: HD/16 of keys + HD/16 of values
-  static constexpr int RING_BYTES = DEC_WARPS * DEC_STAGES * PIECES * 32 * 16;
+  static constexpr int ROW_BYTES = HD * 2;
+  static constexpr int TILE_BYTES = DEC_BLOCK * ROW_BYTES;          // 16 keys (or values) of one KV head
+  static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+  static constexpr int RING_BYTES = DEC_WARPS * DEC_STAGES * STAGE_BYTES;
   static constexpr int MERGE_BYTES = (DEC_WARPS * 16 * (HD + 4) + 2 * DEC_WARPS * 16) * 4;
   static constexpr int RESULT_BYTES = (16 * HD + 2 * 16) * 4;      // the CTA's own (output, max, sum), read by its cluster
   static constexpr int BYTES = RING_BYTES > MERGE_BYTES + RESULT_BYTES ? RING_BYTES : MERGE_BYTES + RESULT_BYTES;
@@ -164,7 +172,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
                         int window, int even_splits) {
   constexpr int NT = HD / 8;        // output n-tiles of 8 columns
   constexpr int KS = HD / 16;       // k-steps of the Q.K product
-  extern __shared__ __align__(16) uint8_t dec_smem[];
+  extern __shared__ __align__(128) uint8_t dec_smem[];
   float (*s_acc)[16][HD + 4] = reinterpret_cast<float (*)[16][HD + 4]>(dec_smem);
   float (*s_m)[16] = reinterpret_cast<float (*)[16]>(dec_smem + DEC_WARPS * 16 * (HD + 4) * 4);
   float (*s_l)[16] = s_m + DEC_WARPS;
@@ -207,31 +215,32 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
   const size_t page_stride = (size_t)G * RL_PAGE * HD;
   const size_t head_off = (size_t)gkv * RL_PAGE * HD;
 
-  // ring slot of piece p in stage st: lanes are consecutive, so loads and stores are conflict-free
-  constexpr int PIECES = DecSmem<HD>::PIECES;
-  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(dec_smem) +
-                        (uint32_t)(warp * DEC_STAGES * PIECES * 32 + lane) * 16;
-  auto slot = [&](int st, int p) { return ring + (uint32_t)((st * PIECES + p) * 32) * 16; };
-  // pieces 0 .. HD/16-1: keys (n-tile nt, 32-dimension chunk c); the rest: values (row r, group grp)
+  // A tile is 16 rows of HD bf16; the 16-byte piece `ch` of row `row` lies at
+  // row * ROW_BYTES + ((ch ^ (row & 7)) * 16).  A warp instruction copies 32 consecutive pieces.
+  constexpr int ROWB = DecSmem<HD>::ROW_BYTES, TILEB = DecSmem<HD>::TILE_BYTES, STAGEB = DecSmem<HD>::STAGE_BYTES;
+  constexpr int CH = HD / 8;                             // pieces a row
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(dec_smem) + (uint32_t)(warp * DEC_STAGES * STAGEB);
   auto issue = [&](int blk, int st, int page) {
     const int key0 = blk * DEC_BLOCK;
     const size_t base = (size_t)page * page_stride + head_off + (size_t)(key0 % RL_PAGE) * HD;
-    const __nv_bfloat16* kb = k_pool + base;
-    const __nv_bfloat16* vb = v_pool + base;
+    const __nv_bfloat16* kb = k_pool + base + 8 * lane;
+    const __nv_bfloat16* vb = v_pool + base + 8 * lane;
+    const uint32_t kd = ring + (uint32_t)(st * STAGEB), vd = kd + TILEB;
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-      for (int c = 0; c < HD / 32; ++c)
-        dec_cp_async16(slot(st, nt * (HD / 32) + c), kb + (size_t)(8 * nt + g) * HD + 8 * t + 32 * c, 16);
-    const int rows[4] = {2 * t, 2 * t + 1, 2 * t + 8, 2 * t + 9};
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int bytes = key0 + rows[r] < len ? 16 : 0;    // rows beyond the sequence may hold anything: zeros instead
-#pragma unroll
-      for (int grp = 0; grp < HD / 64; ++grp)
-        dec_cp_async16(slot(st, HD / 16 + r * (HD / 64) + grp), vb + (size_t)rows[r] * HD + 64 * grp + 8 * g, bytes);
+    for (int i = 0; i < TILEB / 512; ++i) {
+      const int piece = i * 32 + lane, row = piece / CH, ch = piece % CH;
+      const uint32_t off = (uint32_t)(row * ROWB + ((ch ^ (row & 7)) << 4));
+      dec_cp_async16(kd + off, kb + i * 256, 16);
+      // rows beyond the sequence may hold anything: zeros instead (their weights are zero)
+      dec_cp_async16(vd + off, vb + i * 256, key0 + row < len ? 16 : 0);
     }
   };
+  // ldmatrix row addresses of this lane within a tile.  Keys (as they lie): matrix lane/8 is piece
+  // 4c + lane/8 of keys 8nt + (lane & 7).  Values (transposed): matrix lane/8 is piece 2jp + lane/16
+  // of keys (lane & 7) + 8 * ((lane / 8) & 1).
+  const int swz = lane & 7;
+  const uint32_t k_row = (uint32_t)(swz * ROWB), k_piece = (uint32_t)(lane >> 3);
+  const uint32_t v_row = (uint32_t)((swz + 8 * ((lane >> 3) & 1)) * ROWB), v_piece = (uint32_t)(lane >> 4);
 
   {
     int first_pages[DEC_STAGES - 1];
@@ -249,18 +258,17 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
     }
   }
   // ---- Q fragments (after the first key/value copies are on their way): rows = the m heads
-  // of this KV head, columns permuted like the keys' ----
+  // of this KV head ----
   uint32_t qf[KS][4];
   {
-    const __nv_bfloat16* q0 = q + (size_t)b * ldq + (size_t)(gkv * m + g) * HD;
+    const __nv_bfloat16* q0 = q + (size_t)b * ldq + (size_t)(gkv * m + g) * HD + 2 * t;
     const __nv_bfloat16* q1 = q0 + (size_t)8 * HD;
 #pragma unroll
-    for (int c = 0; c < HD / 32; ++c) {
-      uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
-      if (g < m) lo = ldg16(q0 + 32 * c + 8 * t);
-      if (g + 8 < m) hi = ldg16(q1 + 32 * c + 8 * t);
-      qf[2 * c][0] = lo.x; qf[2 * c][1] = hi.x; qf[2 * c][2] = lo.y; qf[2 * c][3] = hi.y;
-      qf[2 * c + 1][0] = lo.z; qf[2 * c + 1][1] = hi.z; qf[2 * c + 1][2] = lo.w; qf[2 * c + 1][3] = hi.w;
+    for (int ks = 0; ks < KS; ++ks) {
+      qf[ks][0] = g < m ? ldg_pair(q0 + 16 * ks) : 0u;
+      qf[ks][1] = g + 8 < m ? ldg_pair(q1 + 16 * ks) : 0u;
+      qf[ks][2] = g < m ? ldg_pair(q0 + 16 * ks + 8) : 0u;
+      qf[ks][3] = g + 8 < m ? ldg_pair(q1 + 16 * ks + 8) : 0u;
     }
   }
 
@@ -273,13 +281,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
       if (ahead < blk_hi) issue(ahead, (it + DEC_STAGES - 1) % DEC_STAGES, __ldg(&pages[ahead * DEC_BLOCK / RL_PAGE]));
       dec_commit();
     }
-    dec_wait<DEC_STAGES - 1>();     // this lane's pieces of block `blk` have landed
-
-    uint4 vr[HD / 64][4];
-#pragma unroll
-    for (int r = 0; r < 4; ++r)
-#pragma unroll
-      for (int grp = 0; grp < HD / 64; ++grp) vr[grp][r] = dec_lds16(slot(st, HD / 16 + r * (HD / 64) + grp));
+    dec_wait<DEC_STAGES - 1>();     // this lane's pieces of block `blk` have landed,
+    __syncwarp();                   // and so have the other lanes'
+    const uint32_t kt = ring + (uint32_t)(st * STAGEB), vt = kt + TILEB;
 
     // scores S[16 heads x 16 keys] = Q . K^T
     float s[2][4];
@@ -288,9 +292,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
       s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
-        const uint4 kr = dec_lds16(slot(st, nt * (HD / 32) + c));
-        mma_bf16_16816(s[nt], qf[2 * c][0], qf[2 * c][1], qf[2 * c][2], qf[2 * c][3], kr.x, kr.y);
-        mma_bf16_16816(s[nt], qf[2 * c + 1][0], qf[2 * c + 1][1], qf[2 * c + 1][2], qf[2 * c + 1][3], kr.z, kr.w);
+        uint32_t kr[4];
+        dec_ldmatrix4(kr, kt + (uint32_t)(8 * nt * ROWB) + k_row + (((4 * c + k_piece) ^ swz) << 4));
+        mma_bf16_16816(s[nt], qf[2 * c][0], qf[2 * c][1], qf[2 * c][2], qf[2 * c][3], kr[0], kr[1]);
+        mma_bf16_16816(s[nt], qf[2 * c + 1][0], qf[2 * c + 1][1], qf[2 * c + 1][2], qf[2 * c + 1][3], kr[2], kr[3]);
       }
     }
     // mask keys outside [start, len), scale into the exp2 domain
@@ -322,20 +327,13 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
       pa[half] = pack_bf16(p00, p01);          // a0 / a1: keys 2t, 2t+1
       pa[2 + half] = pack_bf16(p10, p11);      // a2 / a3: keys 2t+8, 2t+9
     }
-    // output += P . V ; column c of n-tile j in 64-column group grp is dimension 64 grp + 8 c + j
+    // output += P . V ; n-tile j holds dimensions 8j .. 8j+7
 #pragma unroll
-    for (int grp = 0; grp < HD / 64; ++grp) {
-      const uint32_t* r0 = reinterpret_cast<const uint32_t*>(&vr[grp][0]);
-      const uint32_t* r1 = reinterpret_cast<const uint32_t*>(&vr[grp][1]);
-      const uint32_t* r2 = reinterpret_cast<const uint32_t*>(&vr[grp][2]);
-      const uint32_t* r3 = reinterpret_cast<const uint32_t*>(&vr[grp][3]);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
-        const uint32_t b0 = __byte_perm(r0[j >> 1], r1[j >> 1], sel);
-        const uint32_t b1 = __byte_perm(r2[j >> 1], r3[j >> 1], sel);
-        mma_bf16_16816(acc[grp * 8 + j], pa[0], pa[1], pa[2], pa[3], b0, b1);
-      }
+    for (int jp = 0; jp < NT / 2; ++jp) {
+      uint32_t vr[4];
+      dec_ldmatrix4_trans(vr, vt + v_row + (((2 * jp + v_piece) ^ swz) << 4));
+      mma_bf16_16816(acc[2 * jp], pa[0], pa[1], pa[2], pa[3], vr[0], vr[1]);
+      mma_bf16_16816(acc[2 * jp + 1], pa[0], pa[1], pa[2], pa[3], vr[2], vr[3]);
     }
   }
 
@@ -347,13 +345,11 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
     s_m[warp][g + 8] = m_run[1]; s_l[warp][g + 8] = l_run[1];
   }
 #pragma unroll
-  for (int grp = 0; grp < HD / 64; ++grp)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int d0 = 64 * grp + 16 * t + j, d1 = d0 + 8;
-      if (g < m) { s_acc[warp][g][d0] = acc[grp * 8 + j][0]; s_acc[warp][g][d1] = acc[grp * 8 + j][1]; }
-      if (g + 8 < m) { s_acc[warp][g + 8][d0] = acc[grp * 8 + j][2]; s_acc[warp][g + 8][d1] = acc[grp * 8 + j][3]; }
-    }
+  for (int j = 0; j < NT; ++j) {
+    const int d0 = 8 * j + 2 * t;
+    if (g < m) *reinterpret_cast<float2*>(&s_acc[warp][g][d0]) = make_float2(acc[j][0], acc[j][1]);
+    if (g + 8 < m) *reinterpret_cast<float2*>(&s_acc[warp][g + 8][d0]) = make_float2(acc[j][2], acc[j][3]);
+  }
   __syncthreads();
   for (int idx = threadIdx.x; idx < m * HD; idx += DEC_WARPS * 32) {
     const int r = idx / HD, d = idx % HD;
