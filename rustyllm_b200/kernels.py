@@ -442,9 +442,11 @@ def attention_decode_supported(dtype: torch.dtype, num_heads: int, num_kv_heads:
 
 def decode_splits(num_seqs: int, num_kv_heads: int) -> int:
     """Splits of the context per (sequence, KV head): enough CTAs for about one and a
-    half per SM, at most 16 (measured best at 1, 8 and 64 sequences of ~800 tokens).
-    Depends on the batch's size only, so that a captured step keeps its grid."""
-    return max(1, min(16, -(-3 * NUM_SMS // (2 * num_seqs * num_kv_heads))))
+    half per SM, at most 8 for a batch and 16 for one sequence (measured best at 1 to 64
+    sequences of 800 and 4,096 tokens).  Depends on the batch's size only, so that a
+    captured step keeps its grid."""
+    most = 16 if num_seqs == 1 else 8
+    return max(1, min(most, -(-3 * NUM_SMS // (2 * num_seqs * num_kv_heads))))
 
 
 def decode_scratch_floats(num_seqs: int, num_heads: int, head_dim: int, num_splits: int) -> int:
