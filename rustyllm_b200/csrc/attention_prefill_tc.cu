@@ -8,24 +8,30 @@
 // One CTA = 128 consecutive query tokens of one sequence and one query head.
 //   S = Q K^T   tcgen05.mma 128 x 128 x 128, Q and the key tile in shared memory (TMA,
 //               128-byte swizzle, K-major like the matrix products), S in tensor memory
-//               (two buffers: the next tile's scores are computed while this tile's
-//               are being exponentiated)
-//   softmax     eight warps, two threads a query row (= one lane of tensor memory; two
-//               warps may read the same lanes), 64 keys each: no shuffles, the two exchange
-//               their maxima through shared memory once a tile; running maximum kept lazily - the accumulator is only rescaled
-//               when the maximum has grown by more than 2^8, so most tiles skip the
-//               read-modify-write of O in tensor memory; P is written as bf16 over the
-//               first 64 columns of the S buffer it came from (tcgen05.st): it never
-//               touches shared memory
+//               (two buffers; a buffer is free for the scores of the tile after next as soon
+//               as its softmax threads have the scores in registers, so those are computed
+//               while this tile is being exponentiated)
+//   softmax     eight warps in two groups of four that take the key tiles in turn (even tiles,
+//               odd tiles), one thread a query row (= one lane of tensor memory) and tile, the
+//               row's 128 scores in registers.  The two warps that share a scheduler work on
+//               different tiles and are out of step: one's exponentials (the special-function
+//               unit, 16 a clock and SM, is what bounds the kernel) run under the other's loads,
+//               maxima and conversions.  The row's running maximum goes from a tile's thread to
+//               the next tile's through shared memory (one mbarrier a warp pair and tile parity)
+//               as soon as it is known, before the exponentials; it is kept lazily - the
+//               accumulator is only rescaled when the maximum has grown by more than 2^8, so most
+//               tiles skip the read-modify-write of O in tensor memory; each group sums its own
+//               tiles' probabilities and the two sums meet at the end; P is written as bf16 into
+//               a buffer of its own in tensor memory (64 columns a tile parity, tcgen05.st): it
+//               never touches shared memory
 //   O += P V    tcgen05.mma with P in tensor memory as A and the value tile as an
 //               MN-major B operand (values are stored [position][head_dim]); O stays in
-//               tensor memory over all key tiles.  The products of one thread run in the
-//               order they were issued, so the S of tile i + 2, which overwrites P of
-//               tile i, needs no barrier of its own
-// A key tile is two cache pages (128 positions).  Warp 0 feeds TMA, warp 1 issues MMAs,
-// warps 2-9 do the softmax and the final normalisation.  Every mbarrier wait is bounded; a
-// softmax warp whose wait ran out stops working but keeps arriving at the softmax warps'
-// own barrier until the loop ends, so that nobody waits there for ever.
+//               tensor memory over all key tiles
+// Tensor memory: S 0-255, O 256-.., P behind O (512 columns at head size 128).
+// A key tile is two cache pages (128 positions).  Warp 0 feeds TMA, warps 1 and 10 issue the two
+// products, warps 2-9 do the softmax and the final normalisation.  Every wait inside the loop is an mbarrier
+// wait and bounded; a softmax warp whose wait ran out leaves the loop and goes to the one named
+// barrier behind it, which every softmax warp reaches.
 //
 // Rows of a page beyond the sequence's length are never selected (their probabilities
 // are exactly 0), but they are multiplied: the cache pools must not hold NaN or Inf
@@ -40,17 +46,22 @@ namespace {
 
 constexpr int TQ = 128;          // query rows per CTA
 constexpr int TK = 128;          // keys per tile = two pages
-constexpr int FA_THREADS = 320;       // warp 0: TMA, warp 1: MMA, warps 2-9: softmax
+constexpr int FA_THREADS = 352;       // warp 0: TMA, warp 1: S = Q K^T, warps 2-9: softmax, warp 10: O += P V
+constexpr int FA_PV_WARP = 10;
 constexpr uint32_t FA_WAIT_LIMIT = 1u << 22;
-constexpr int KV_STAGES = 2;
 constexpr int HALF_BYTES = 128 * 64 * 2;               // [128 rows x 64 bf16], 16 KB
 // sizes that depend on the head size HD (64 or 128): a head is HD / 64 halves of 64 dimensions
 template <int HD> struct FaSizes {
   static constexpr int HALVES = HD / 64;
   static constexpr int Q_BYTES = HALVES * HALF_BYTES;          // 16 or 32 KB
-  static constexpr int KV_STAGE_BYTES = 2 * HALVES * HALF_BYTES;  // K halves, then V halves: 32 or 64 KB
-  // + alignment slack, barriers, and the softmax threads' exchange: row maxima (two tiles in turn) and row sums
-  static constexpr int SMEM = Q_BYTES + KV_STAGES * KV_STAGE_BYTES + 1024 + 256 + 3 * 2 * TQ * 4;
+  static constexpr int TILE_BYTES = HALVES * HALF_BYTES;       // a key tile or a value tile: 16 or 32 KB
+  // keys are asked for a tile further ahead than values: the scores of a tile are computed as soon as the
+  // buffer is free, a whole tile before its P V
+  static constexpr int K_STAGES = HD == 64 ? 4 : 3;
+  static constexpr int V_STAGES = HD == 64 ? 3 : 2;
+  // + alignment slack, barriers, and the softmax threads' exchange: running maxima (two tiles in turn), and the
+  // groups' last maxima and sums
+  static constexpr int SMEM = Q_BYTES + (K_STAGES + V_STAGES) * TILE_BYTES + 1024 + 512 + 3 * 2 * TQ * 4;
 };
 constexpr float LAZY_LOG2 = 8.0f;                      // rescale O only when the maximum grew by more than 2^8
 
@@ -183,37 +194,43 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   extern __shared__ uint8_t fa_smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)fa_smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* q_tile = smem;                                   // [2 halves][128 x 64]
-  constexpr int HALVES = FaSizes<HD>::HALVES, Q_BYTES = FaSizes<HD>::Q_BYTES, KV_STAGE_BYTES = FaSizes<HD>::KV_STAGE_BYTES;
-  uint8_t* kv_ring = smem + Q_BYTES;                        // [stage][K halves, V halves]
-  uint64_t* bars = (uint64_t*)(kv_ring + KV_STAGES * KV_STAGE_BYTES);
+  constexpr int HALVES = FaSizes<HD>::HALVES, Q_BYTES = FaSizes<HD>::Q_BYTES, TILE_BYTES = FaSizes<HD>::TILE_BYTES;
+  constexpr int K_STAGES = FaSizes<HD>::K_STAGES, V_STAGES = FaSizes<HD>::V_STAGES;
+  uint8_t* k_ring = smem + Q_BYTES;                         // [stage][halves]
+  uint8_t* v_ring = k_ring + K_STAGES * TILE_BYTES;         // [stage][halves]
+  uint64_t* bars = (uint64_t*)(v_ring + V_STAGES * TILE_BYTES);
   uint64_t* q_full = bars;                 // 1
-  uint64_t* k_full = bars + 1;             // [KV_STAGES] each: keys and values of a stage are
-  uint64_t* k_empty = k_full + KV_STAGES;  //   loaded and given back separately (the keys of a
-  uint64_t* v_full = k_empty + KV_STAGES;  //   tile are done with one product earlier than its
-  uint64_t* v_empty = v_full + KV_STAGES;  //   values, and wanted one product earlier)
-  uint64_t* s_full = v_empty + KV_STAGES;  // [2]
-  uint64_t* p_full = s_full + 2;           // 1
-  uint64_t* p_empty = p_full + 1;          // 1
-  uint64_t* o_full = p_empty + 1;          // 1
-  uint32_t* tmem_slot = (uint32_t*)(o_full + 1);
+  uint64_t* k_full = bars + 1;             // keys and values have rings of their own
+  uint64_t* k_empty = k_full + K_STAGES;
+  uint64_t* v_full = k_empty + K_STAGES;
+  uint64_t* v_empty = v_full + V_STAGES;
+  uint64_t* s_full = v_empty + V_STAGES;   // [2]
+  uint64_t* s_free = s_full + 2;           // [2]: the scores of a tile are in its threads' registers
+  uint64_t* p_full = s_free + 2;           // [2]: one a softmax group
+  uint64_t* pv_done = p_full + 2;          // [2]: the P V of a tile (by parity) has completed
+  uint64_t* o_full = pv_done + 2;          // 1
+  uint64_t* m_ready = o_full + 1;          // [tile parity][quarter]: the running maximum after a tile
+  uint32_t* tmem_slot = (uint32_t*)(m_ready + 8);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   int* s_seq = (int*)(tmem_slot + 2);
   int* s_tile = (int*)(tmem_slot + 3);
-  float* x_max = (float*)((uint8_t*)bars + 256);            // [tile parity][key half][row]
-  float* x_sum = x_max + 2 * 2 * TQ;                         // [key half][row]
+  float* m_shared = (float*)((uint8_t*)bars + 512);         // [tile parity][row]: running maximum after that tile
+  float* x_m = m_shared + 2 * TQ;                            // [group][row]: the maximum the group's sum is scaled by
+  float* x_sum = x_m + 2 * TQ;                               // [group][row]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   rl_pdl_trigger();
   if (threadIdx.x == 0) {
     fa_mbar_init(fa_smem_u32(q_full), 1);
-    for (int i = 0; i < KV_STAGES; ++i) {
-      fa_mbar_init(fa_smem_u32(&k_full[i]), 1); fa_mbar_init(fa_smem_u32(&k_empty[i]), 1);
-      fa_mbar_init(fa_smem_u32(&v_full[i]), 1); fa_mbar_init(fa_smem_u32(&v_empty[i]), 1);
-    }
+    for (int i = 0; i < K_STAGES; ++i) { fa_mbar_init(fa_smem_u32(&k_full[i]), 1); fa_mbar_init(fa_smem_u32(&k_empty[i]), 1); }
+    for (int i = 0; i < V_STAGES; ++i) { fa_mbar_init(fa_smem_u32(&v_full[i]), 1); fa_mbar_init(fa_smem_u32(&v_empty[i]), 1); }
     for (int i = 0; i < 2; ++i) fa_mbar_init(fa_smem_u32(&s_full[i]), 1);
-    fa_mbar_init(fa_smem_u32(p_full), 8);
-    fa_mbar_init(fa_smem_u32(p_empty), 1);
+    for (int i = 0; i < 2; ++i) {
+      fa_mbar_init(fa_smem_u32(&s_free[i]), 4); fa_mbar_init(fa_smem_u32(&p_full[i]), 4);
+      fa_mbar_init(fa_smem_u32(&pv_done[i]), 1);
+    }
+    for (int i = 0; i < 8; ++i) fa_mbar_init(fa_smem_u32(&m_ready[i]), 1);
     fa_mbar_init(fa_smem_u32(o_full), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -240,7 +257,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __syncthreads();
   fa_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s0 = tmem_base, tmem_o = tmem_base + 256;      // S buffers at columns 0 and 128, O at 256
+  // S buffers at columns 0 and 128, O at 256, the two P buffers (64 columns each) behind O
+  const uint32_t tmem_s0 = tmem_base, tmem_o = tmem_base + 256, tmem_p = tmem_base + 256 + HD;
   const int b = *s_seq;
   const bool have_work = b < num_seqs;      // the grid is sized exactly; defensive
   const int h = blockIdx.y, gkv = h / (H / G);
@@ -265,50 +283,51 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
       for (int half = 0; half < HALVES; ++half)
         fa_tma_2d(fa_smem_u32(q_tile + half * HALF_BYTES), &map_q, fa_smem_u32(q_full), h * HD + 64 * half, row0 + qt0);
-      // keys of tile i + 1 are asked for before the values of tile i: the keys' stage is free as
-      // soon as S of two tiles back is done, the values' only when that tile's P V is
-      auto load = [&](int i, bool values) -> bool {
-        const int kt = kt_begin + i, st = i % KV_STAGES;
-        const uint32_t phase = (i / KV_STAGES) & 1;
-        uint64_t* empty = values ? v_empty : k_empty;
-        if (i >= KV_STAGES && !fa_wait(fa_smem_u32(&empty[st]), phase ^ 1, abort_flag)) {
-          if (!*abort_flag) { *abort_flag = 1; atomicExch(err, 11); }
-          return false;
-        }
+      // keys and values have rings of their own: the keys' stage is free once the S of its tile
+      // is done, the values' once its P V is; whichever is free first is filled first
+      auto load = [&](int i, bool values) {
+        const int kt = kt_begin + i, st = i % (values ? V_STAGES : K_STAGES);
         const int p0 = pages[2 * kt];
         const int p1 = (2 * kt + 1) * RL_PAGE < kv_len ? pages[2 * kt + 1] : p0;   // beyond the sequence: any valid page (all masked)
         const int r0 = (p0 * G + gkv) * RL_PAGE, r1 = (p1 * G + gkv) * RL_PAGE;
         const uint32_t fb = fa_smem_u32(values ? &v_full[st] : &k_full[st]);
-        uint8_t* base = kv_ring + (size_t)st * KV_STAGE_BYTES + (values ? HALVES * HALF_BYTES : 0);
+        uint8_t* base = (values ? v_ring : k_ring) + (size_t)st * TILE_BYTES;
         const CUtensorMap* map = values ? &map_v : &map_k;
-        fa_expect_tx(fb, HALVES * HALF_BYTES);
+        fa_expect_tx(fb, TILE_BYTES);
 #pragma unroll
         for (int half = 0; half < HALVES; ++half) {     // 64 head dimensions a half; 64 positions a page
           fa_tma_2d(fa_smem_u32(base + half * HALF_BYTES), map, fb, 64 * half, r0);
           fa_tma_2d(fa_smem_u32(base + half * HALF_BYTES + 64 * 128), map, fb, 64 * half, r1);
         }
-        return true;
       };
-      bool ok = num_kt == 0 || load(0, false);
-      for (int i = 0; i < num_kt && ok; ++i) {
-        if (i + 1 < num_kt) ok = load(i + 1, false);
-        if (ok) ok = load(i, true);
+      auto stage_free = [&](uint64_t* empty, int stages, int i) -> bool {      // without waiting
+        return i < stages || fa_try_wait(fa_smem_u32(&empty[i % stages]), ((i / stages) & 1) ^ 1);
+      };
+      int nk = 0, nv = 0;
+      uint32_t idle = 0;
+      bool ok = true;
+      while (ok && nv < num_kt) {
+        bool moved = false;
+        if (nk < num_kt && stage_free(k_empty, K_STAGES, nk)) { load(nk, false); ++nk; moved = true; }
+        if (nv < nk && stage_free(v_empty, V_STAGES, nv)) { load(nv, true); ++nv; moved = true; }
+        if (moved) idle = 0;
+        else if (++idle > FA_WAIT_LIMIT || ((idle & 1023u) == 1023u && *abort_flag)) ok = false;
       }
+      if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(err, 11); }
     }
   } else if (warp == 1) {
     if (lane == 0 && have_work) {
-      // ---------------- MMA issuer ----------------
-      constexpr uint32_t idesc_s = fa_idesc(TQ, TK, 0);     // S = Q K^T : both K-major
-      constexpr uint32_t idesc_o = fa_idesc(TQ, HD, 1);     // O += P V  : V is MN-major
+      // ---------------- issuer of S = Q K^T ----------------
+      // The two products have a thread each, in different warps: issuing blocks while the tensor pipe
+      // is full, so with one thread the waits, commits and loop of one product would stand in the
+      // way of the other.  They need no order between them: every dependency is an mbarrier.
+      constexpr uint32_t idesc_s = fa_idesc(TQ, TK, 0);     // both K-major
       bool ok = fa_wait(fa_smem_u32(q_full), 0, abort_flag);
-      if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(err, 12); }
       auto issue_s = [&](int i) -> bool {                   // scores of tile i into S buffer i % 2
-        const int st = i % KV_STAGES, sb = i & 1;
-        if (!fa_wait(fa_smem_u32(&k_full[st]), (i / KV_STAGES) & 1, abort_flag)) return false;
-        // S buffer sb still holds P of tile i - 2; that tile's P V was issued before this and
-        // products run in the order of their issue
+        const int st = i % K_STAGES, sb = i & 1;
+        if (!fa_wait(fa_smem_u32(&k_full[st]), (i / K_STAGES) & 1, abort_flag)) return false;
         fa_fence_after();
-        uint8_t* base = kv_ring + (size_t)st * KV_STAGE_BYTES;
+        uint8_t* base = k_ring + (size_t)st * TILE_BYTES;
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint64_t da = fa_desc_kmajor(fa_smem_u32(q_tile + (k / 4) * HALF_BYTES)) + 2 * (k % 4);
@@ -316,105 +335,135 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           fa_mma(tmem_s0 + (uint32_t)(sb * TK), da, db, idesc_s, k > 0 ? 1u : 0u);
         }
         fa_commit(fa_smem_u32(&s_full[sb]));
-        fa_commit(fa_smem_u32(&k_empty[st]));               // the keys' half of the stage is free once S is done
+        fa_commit(fa_smem_u32(&k_empty[st]));               // the keys' stage is free once S is done
         return true;
       };
       if (ok && num_kt > 0) ok = issue_s(0);
+      if (ok && num_kt > 1) ok = issue_s(1);
+      for (int i = 0; i + 2 < num_kt && ok; ++i) {
+        // the scores of the tile after next, as soon as this tile's are in its threads' registers:
+        // they are computed while this tile and the next are being exponentiated
+        ok = fa_wait(fa_smem_u32(&s_free[i & 1]), (i >> 1) & 1, abort_flag);
+        if (ok) ok = issue_s(i + 2);
+      }
+      if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(err, 12); }
+    }
+  } else if (warp == FA_PV_WARP) {
+    if (lane == 0 && have_work) {
+      // ---------------- issuer of O += P V ----------------
+      constexpr uint32_t idesc_o = fa_idesc(TQ, HD, 1);     // P in tensor memory, V MN-major
+      bool ok = true;
       for (int i = 0; i < num_kt && ok; ++i) {
-        if (i + 1 < num_kt) ok = issue_s(i + 1);            // next tile's scores while this tile's softmax runs
-        if (!ok) break;
-        if (!fa_wait(fa_smem_u32(&v_full[i % KV_STAGES]), (i / KV_STAGES) & 1, abort_flag)) { ok = false; break; }
-        if (!fa_wait(fa_smem_u32(p_full), i & 1, abort_flag)) { ok = false; break; }
+        if (!fa_wait(fa_smem_u32(&v_full[i % V_STAGES]), (i / V_STAGES) & 1, abort_flag)) { ok = false; break; }
+        if (!fa_wait(fa_smem_u32(&p_full[i & 1]), (i >> 1) & 1, abort_flag)) { ok = false; break; }
         fa_fence_after();
-        uint8_t* vbase = kv_ring + (size_t)(i % KV_STAGES) * KV_STAGE_BYTES + HALVES * HALF_BYTES;
+        uint8_t* vbase = v_ring + (size_t)(i % V_STAGES) * TILE_BYTES;
 #pragma unroll
         for (int k = 0; k < TK / 16; ++k) {                 // 16 positions a step
-          // P of this tile: 16 keys = 8 columns of packed bf16 pairs a step, in its S buffer
+          // P of this tile: 16 keys = 8 columns of packed bf16 pairs a step, in the P buffer of its parity
           const uint64_t db = fa_desc_mnmajor(fa_smem_u32(vbase + k * 16 * 128), HALF_BYTES);
-          fa_mma_a_tmem(tmem_o, tmem_s0 + (uint32_t)((i & 1) * TK + 8 * k), db, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+          fa_mma_a_tmem(tmem_o, tmem_p + (uint32_t)((i & 1) * (TK / 2) + 8 * k), db, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
         }
-        fa_commit(fa_smem_u32(p_empty));                    // P and O are free again once these have completed
-        fa_commit(fa_smem_u32(&v_empty[i % KV_STAGES]));
+        fa_commit(fa_smem_u32(&pv_done[i & 1]));            // O, and this parity's P buffer, are free again once these have completed
+        fa_commit(fa_smem_u32(&v_empty[i % V_STAGES]));
       }
       if (ok) fa_commit(fa_smem_u32(o_full));
       else if (!*abort_flag) { *abort_flag = 1; atomicExch(err, 13); }
     }
   } else if (have_work) {
-    // ---------------- softmax warps: two threads a query row, 64 keys each ----------------
-    constexpr int HK = TK / 2;                              // keys a thread
-    constexpr int OC = HD / 2;                              // output columns a thread
-    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    // ---------------- softmax warps: group 0 takes the even key tiles, group 1 the odd ones ----------------
+    constexpr int OC = HD / 2;                              // output columns a thread writes at the end
+    const int quarter = warp & 3, grp = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;                      // row of the tile = lane of tensor memory
     const int pos = start_pos + qt0 + r;                    // position of this row's query
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    float m_used = -INFINITY, l_run = 0.f;                  // maximum the probabilities are scaled by; running sum (own keys)
+    float m_mine = -INFINITY, l_run = 0.f;                  // maximum this group's sum is scaled by; the sum
     bool ok = true;                                         // warp-uniform
-    for (int i = 0; i < num_kt; ++i) {
-      const int sb = i & 1, key0 = (kt_begin + i) * TK + half * HK;
-      if (ok) ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(&s_full[sb]), (i >> 1) & 1, abort_flag));
-      uint32_t sv[HK];
-      float mx_own = -INFINITY;
-      if (ok) {
-        fa_fence_after();
-        const uint32_t s_addr = tmem_s0 + lane_addr + (uint32_t)(sb * TK + half * HK);
-        // the thread's 64 scores into registers with one wait; everything below is straight-line
-        // code over them, so the scheduler has independent work to cover every latency
+    const float2 sc2 = make_float2(scale_log2e, scale_log2e);
+    for (int i = grp; i < num_kt && ok; i += 2) {
+      const int sb = grp, key0 = (kt_begin + i) * TK;       // S buffer = tile parity = group
+      ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(&s_full[sb]), (i >> 1) & 1, abort_flag));
+      if (!ok) break;
+      fa_fence_after();
+      const uint32_t s_addr = tmem_s0 + lane_addr + (uint32_t)(sb * TK);
+      // the row's 128 scores into registers with one wait; the S buffer is then free for the tile
+      // after next.  Everything below is straight-line code over the registers
+      uint32_t sa[TK];
 #pragma unroll
-        for (int c = 0; c < HK / 32; ++c) fa_ld32(s_addr + c * 32, sv + c * 32);
-        fa_wait_ld();
-        const bool need_mask = (kt_begin + i) * TK + TK - 1 > start_pos + qt0 || window > 0;
-        if (need_mask) {
+      for (int c = 0; c < TK / 32; ++c) fa_ld32(s_addr + 32 * c, sa + 32 * c);
+      fa_wait_ld();
+      fa_fence_before();
+      __syncwarp();
+      if (lane == 0) fa_arrive(fa_smem_u32(&s_free[sb]));
+      if (window > 0) {
 #pragma unroll
-          for (int j = 0; j < HK; ++j) {
-            const int key = key0 + j;
-            const bool vis = key <= pos && (window <= 0 || key > pos - window);
-            if (!vis) sv[j] = 0xff800000u;        // -inf
+        for (int j = 0; j < TK; ++j) {
+          const int key = key0 + j;
+          if (!(key <= pos && key > pos - window)) sa[j] = 0xff800000u;          // -inf
+        }
+      } else if (key0 + TK - 1 > start_pos + qt0) {
+        // the tile on the diagonal: key j of the tile is visible to this row if j <= lim.  Rows grow
+        // with the lane, so the 32-key chunks left of the warp's first row's limit need nothing
+        const int lim = pos - key0;
+        const int lim0 = __shfl_sync(0xffffffffu, lim, 0);
+#pragma unroll
+        for (int c = 0; c < TK / 32; ++c) {
+          if (32 * c + 31 > lim0) {
+#pragma unroll
+            for (int j = 32 * c; j < 32 * c + 32; ++j) sa[j] = j > lim ? 0xff800000u : sa[j];
           }
         }
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int j = 0; j < HK; j += 2) mx4[(j >> 1) & 3] = fa_max3(mx4[(j >> 1) & 3], __uint_as_float(sv[j]), __uint_as_float(sv[j + 1]));
-        mx_own = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      for (int j = 0; j < TK; j += 2) mx4[(j >> 1) & 3] = fa_max3(mx4[(j >> 1) & 3], __uint_as_float(sa[j]), __uint_as_float(sa[j + 1]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2e;
+      // the running maximum after the tile before (the other group's), and after this one: lazy, moved
+      // (with O and the sums rescaled) only when it grew by more than 2^8
+      float m_prev = -INFINITY;
+      if (i > 0) {
+        ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(&m_ready[((i - 1) & 1) * 4 + quarter]), ((i - 1) >> 1) & 1, abort_flag));
+        if (!ok) break;
+        m_prev = m_shared[((i - 1) & 1) * TQ + r];
       }
-      // the row's maximum: the two threads of a row exchange theirs (buffers take turns, so one
-      // barrier a tile is enough)
-      x_max[(sb * 2 + half) * TQ + r] = mx_own;
-      fa_softmax_sync();
-      if (!ok) continue;
-      const float mx = fmaxf(mx_own, x_max[(sb * 2 + (half ^ 1)) * TQ + r]) * scale_log2e;
-      // lazy maximum: move it (and rescale O and the sum) only when it grew by more than 2^8
-      float corr = 1.0f;
-      if (mx > m_used + LAZY_LOG2 || (m_used == -INFINITY && mx > -INFINITY)) {
-        corr = fa_exp2(m_used - mx);                          // 0 on the first visible tile
-        m_used = mx;
-      }
+      float m_now = m_prev;
+      if (mx > m_prev + LAZY_LOG2 || (m_prev == -INFINITY && mx > -INFINITY)) m_now = mx;
+      m_shared[(i & 1) * TQ + r] = m_now;
+      __syncwarp();
+      if (lane == 0) fa_arrive(fa_smem_u32(&m_ready[(i & 1) * 4 + quarter]));   // the next tile's threads may go on
+      const float corr = m_now != m_prev ? fa_exp2(m_prev - m_now) : 1.0f;       // 0 on the first visible tile
       const bool any_rescale = __any_sync(0xffffffffu, corr != 1.0f);
+      if (m_mine != m_now) { l_run *= fa_exp2(m_mine - m_now); m_mine = m_now; }
       // probabilities: exp2(score * scale - maximum), two scores an FMA; summed in float, rounded
-      // to bf16 for the product with V and packed in place (sv[0..31] then hold the thread's 64)
-      const float m_sub = m_used == -INFINITY ? 0.f : m_used;
-      const float2 sc2 = make_float2(scale_log2e, scale_log2e), nm2 = make_float2(-m_sub, -m_sub);
+      // to bf16 for the product with V and packed in place (sa[0..63] then hold the row's 128)
+      const float m_sub = m_now == -INFINITY ? 0.f : m_now;
+      const float2 nm2 = make_float2(-m_sub, -m_sub);
       float2 sum2[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
 #pragma unroll
-      for (int j = 0; j < HK; j += 2) {
-        const float2 t = fa_ffma2(make_float2(__uint_as_float(sv[j]), __uint_as_float(sv[j + 1])), sc2, nm2);
+      for (int j = 0; j < TK; j += 2) {
+        const float2 t = fa_ffma2(make_float2(__uint_as_float(sa[j]), __uint_as_float(sa[j + 1])), sc2, nm2);
         const float2 p2 = make_float2(fa_exp2(t.x), fa_exp2(t.y));
         sum2[(j >> 1) & 3] = fa_fadd2(sum2[(j >> 1) & 3], p2);
         __nv_bfloat162 pb = __floats2bfloat162_rn(p2.x, p2.y);
-        sv[j >> 1] = *reinterpret_cast<uint32_t*>(&pb);
+        sa[j >> 1] = *reinterpret_cast<uint32_t*>(&pb);
       }
-      const float2 s01 = fa_fadd2(sum2[0], sum2[1]), s23 = fa_fadd2(sum2[2], sum2[3]);
-      const float sum = (s01.x + s01.y) + (s23.x + s23.y);
-      // O is only touched once the previous tile's P V has completed: waited for only if this
-      // warp has a row to rescale (the barrier cannot have run ahead: the next P V needs our arrival)
+      // the P buffer of this parity is free once the P V of the tile two back has completed; the barriers
+      // take turns by tile parity, and this thread waited for the tile four back on the same one
+      if (i >= 2) {
+        ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(&pv_done[i & 1]), ((i - 2) >> 1) & 1, abort_flag));
+        if (!ok) break;
+      }
+      // O is only touched once the previous tile's P V has completed: waited for only if this warp has a
+      // row to rescale (the tile three back is done, as the one two back is; the barrier cannot have run
+      // ahead: the next P V needs our arrival)
       if (any_rescale && i > 0) {
-        ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(p_empty), (i - 1) & 1, abort_flag));
-        if (!ok) continue;
+        ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(&pv_done[(i - 1) & 1]), ((i - 1) >> 1) & 1, abort_flag));
+        if (!ok) break;
         fa_fence_after();
-        l_run *= corr;
 #pragma unroll 1
-        for (int c = 0; c < OC / 32; ++c) {               // this thread's half of the row of O
+        for (int c = 0; c < HD / 32; ++c) {               // the whole row of O
           uint32_t v[32];
-          const uint32_t o_addr = tmem_o + lane_addr + (uint32_t)(half * OC + c * 32);
+          const uint32_t o_addr = tmem_o + lane_addr + (uint32_t)(c * 32);
           fa_ld32(o_addr, v);
           fa_wait_ld();
 #pragma unroll
@@ -423,34 +472,39 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           fa_st16(o_addr + 16, *reinterpret_cast<uint32_t(*)[16]>(v + 16));
         }
       }
-      // P over the S buffer: this thread's 64 keys are columns 32 half .. 32 half + 31 (both threads of
-      // the row had their scores in registers before the barrier above)
-      {
-        const uint32_t p_addr = tmem_s0 + lane_addr + (uint32_t)(sb * TK + half * (HK / 2));
-        fa_st16(p_addr, *reinterpret_cast<uint32_t(*)[16]>(sv));
-        fa_st16(p_addr + 16, *reinterpret_cast<uint32_t(*)[16]>(sv + 16));
-        fa_wait_st();
-      }
-      l_run += sum;
+      fa_fence_after();
+      // 16 keys are 8 columns of packed pairs
+      const uint32_t p_addr = tmem_p + lane_addr + (uint32_t)(sb * (TK / 2));
+#pragma unroll
+      for (int c = 0; c < TK / 32; ++c) fa_st16(p_addr + 16 * c, *reinterpret_cast<uint32_t(*)[16]>(sa + 16 * c));
+      fa_wait_st();
+      const float2 s01 = fa_fadd2(sum2[0], sum2[1]), s23 = fa_fadd2(sum2[2], sum2[3]);
+      l_run += (s01.x + s01.y) + (s23.x + s23.y);
       // P is ready for the tensor cores
       fa_fence_before();
       __syncwarp();
-      if (lane == 0) fa_arrive(fa_smem_u32(p_full));
+      if (lane == 0) fa_arrive(fa_smem_u32(&p_full[grp]));
     }
     // ---- O / l -> out ----
     if (ok) ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(o_full), 0, abort_flag));
     if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(err, 14); }
-    x_sum[half * TQ + r] = l_run;
+    x_sum[grp * TQ + r] = l_run;
+    x_m[grp * TQ + r] = m_mine;
     fa_softmax_sync();
     fa_fence_after();
     if (ok) {
-      const float l_row = half == 0 ? l_run + x_sum[TQ + r] : x_sum[r] + l_run;    // keys 0-63 first, either way
+      // O is scaled by the last tile's maximum, the larger of the two groups'; sums in group order
+      const float m_other = x_m[(grp ^ 1) * TQ + r], l_other = x_sum[(grp ^ 1) * TQ + r];
+      const float m_fin = fmaxf(m_mine, m_other);
+      const float w_mine = m_mine == -INFINITY ? 0.f : fa_exp2(m_mine - m_fin);
+      const float w_other = m_other == -INFINITY ? 0.f : fa_exp2(m_other - m_fin);
+      const float l_row = grp == 0 ? l_run * w_mine + l_other * w_other : l_other * w_other + l_run * w_mine;
       const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
-      __nv_bfloat16* orow = out + (size_t)(row0 + qt0 + r) * ldo + (size_t)h * HD + half * OC;
+      __nv_bfloat16* orow = out + (size_t)(row0 + qt0 + r) * ldo + (size_t)h * HD + grp * OC;
 #pragma unroll 1
       for (int c = 0; c < OC / 16; ++c) {
         uint32_t v[16];
-        fa_ld16(tmem_o + lane_addr + (uint32_t)(half * OC + c * 16), v);
+        fa_ld16(tmem_o + lane_addr + (uint32_t)(grp * OC + c * 16), v);
         fa_wait_ld();
         if (r < rows_here) {
           uint32_t pk[8];
