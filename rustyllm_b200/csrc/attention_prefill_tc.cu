@@ -1,7 +1,7 @@
 // Prefill attention on the 5th-generation tensor cores (tcgen05), head sizes 64 and 128.
 //
-// Same math and the same packed, paged inputs as attention_prefill.cu (which stays the
-// kernel for head size 64 and is the restatement this one is tested against): causal
+// Same math and the same packed, paged inputs as attention_prefill.cu (the mma.sync kernel,
+// which this one is tested against): causal
 // grouped-query attention of the step's query tokens over their sequence's cached keys
 // and values, streaming softmax in float (SimonWaldherr/RustyLLM src/model.rs:7239-7294, 5807-5869).
 //
@@ -28,8 +28,10 @@
 //               MN-major B operand (values are stored [position][head_dim]); O stays in
 //               tensor memory over all key tiles
 // Tensor memory: S 0-255, O 256-.., P behind O (512 columns at head size 128).
-// A key tile is two cache pages (128 positions).  Warp 0 feeds TMA, warps 1 and 10 issue the two
-// products, warps 2-9 do the softmax and the final normalisation.  Every wait inside the loop is an mbarrier
+// A key tile is two cache pages (128 positions).  Warp 0 feeds TMA, warps 1 and 2 issue the two
+// products (a thread each: issuing blocks while the tensor pipe is full, and one thread's waits
+// and commits for one product would stand in the way of the other), warps 4-11 do the softmax and the final normalisation (with the registers that the
+// first four warps give up: setmaxnreg).  Every wait inside the loop is an mbarrier
 // wait and bounded; a softmax warp whose wait ran out leaves the loop and goes to the one named
 // barrier behind it, which every softmax warp reaches.
 //
@@ -46,8 +48,10 @@ namespace {
 
 constexpr int TQ = 128;          // query rows per CTA
 constexpr int TK = 128;          // keys per tile = two pages
-constexpr int FA_THREADS = 352;       // warp 0: TMA, warp 1: S = Q K^T, warps 2-9: softmax, warp 10: O += P V
-constexpr int FA_PV_WARP = 10;
+constexpr int FA_THREADS = 384;       // warp 0: TMA, warp 1: S = Q K^T, warp 2: O += P V, warp 3: idle, warps 4-11: softmax
+constexpr int FA_PV_WARP = 2;
+// registers a thread: the first warpgroup hands most of its share to the two softmax warpgroups
+constexpr int FA_REGS_FEED = 56, FA_REGS_SOFTMAX = 224;
 constexpr uint32_t FA_WAIT_LIMIT = 1u << 22;
 constexpr int HALF_BYTES = 128 * 64 * 2;               // [128 rows x 64 bf16], 16 KB
 // sizes that depend on the head size HD (64 or 128): a head is HD / 64 halves of 64 dimensions
@@ -276,245 +280,285 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   }
   const int num_kt = kt_end - kt_begin;
 
-  if (warp == 0) {
-    if (lane == 0 && have_work) {
-      // ---------------- TMA producer ----------------
-      fa_expect_tx(fa_smem_u32(q_full), Q_BYTES);
+  if (warp < 4) {
+    // ---- the feeding warps: a few registers are enough; the rest goes to the softmax warps ----
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FA_REGS_FEED));
+    if (warp == 0) {
+      if (lane == 0 && have_work) {
+        // ---------------- TMA producer ----------------
+        fa_expect_tx(fa_smem_u32(q_full), Q_BYTES);
 #pragma unroll
-      for (int half = 0; half < HALVES; ++half)
-        fa_tma_2d(fa_smem_u32(q_tile + half * HALF_BYTES), &map_q, fa_smem_u32(q_full), h * HD + 64 * half, row0 + qt0);
-      // keys and values have rings of their own: the keys' stage is free once the S of its tile
-      // is done, the values' once its P V is; whichever is free first is filled first
-      auto load = [&](int i, bool values) {
-        const int kt = kt_begin + i, st = i % (values ? V_STAGES : K_STAGES);
-        const int p0 = pages[2 * kt];
-        const int p1 = (2 * kt + 1) * RL_PAGE < kv_len ? pages[2 * kt + 1] : p0;   // beyond the sequence: any valid page (all masked)
-        const int r0 = (p0 * G + gkv) * RL_PAGE, r1 = (p1 * G + gkv) * RL_PAGE;
-        const uint32_t fb = fa_smem_u32(values ? &v_full[st] : &k_full[st]);
-        uint8_t* base = (values ? v_ring : k_ring) + (size_t)st * TILE_BYTES;
-        const CUtensorMap* map = values ? &map_v : &map_k;
-        fa_expect_tx(fb, TILE_BYTES);
+        for (int half = 0; half < HALVES; ++half)
+          fa_tma_2d(fa_smem_u32(q_tile + half * HALF_BYTES), &map_q, fa_smem_u32(q_full), h * HD + 64 * half, row0 + qt0);
+        // keys and values have rings of their own: the keys' stage is free once the S of its tile
+        // is done, the values' once its P V is; whichever is free first is filled first
+        auto load = [&](int i, bool values) {
+          const int kt = kt_begin + i, st = i % (values ? V_STAGES : K_STAGES);
+          const int p0 = pages[2 * kt];
+          const int p1 = (2 * kt + 1) * RL_PAGE < kv_len ? pages[2 * kt + 1] : p0;   // beyond the sequence: any valid page (all masked)
+          const int r0 = (p0 * G + gkv) * RL_PAGE, r1 = (p1 * G + gkv) * RL_PAGE;
+          const uint32_t fb = fa_smem_u32(values ? &v_full[st] : &k_full[st]);
+          uint8_t* base = (values ? v_ring : k_ring) + (size_t)st * TILE_BYTES;
+          const CUtensorMap* map = values ? &map_v : &map_k;
+          fa_expect_tx(fb, TILE_BYTES);
 #pragma unroll
-        for (int half = 0; half < HALVES; ++half) {     // 64 head dimensions a half; 64 positions a page
-          fa_tma_2d(fa_smem_u32(base + half * HALF_BYTES), map, fb, 64 * half, r0);
-          fa_tma_2d(fa_smem_u32(base + half * HALF_BYTES + 64 * 128), map, fb, 64 * half, r1);
-        }
-      };
-      auto stage_free = [&](uint64_t* empty, int stages, int i) -> bool {      // without waiting
-        return i < stages || fa_try_wait(fa_smem_u32(&empty[i % stages]), ((i / stages) & 1) ^ 1);
-      };
-      int nk = 0, nv = 0;
-      uint32_t idle = 0;
-      bool ok = true;
-      while (ok && nv < num_kt) {
-        bool moved = false;
-        if (nk < num_kt && stage_free(k_empty, K_STAGES, nk)) { load(nk, false); ++nk; moved = true; }
-        if (nv < nk && stage_free(v_empty, V_STAGES, nv)) { load(nv, true); ++nv; moved = true; }
-        if (moved) idle = 0;
-        else if (++idle > FA_WAIT_LIMIT || ((idle & 1023u) == 1023u && *abort_flag)) ok = false;
-      }
-      if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(err, 11); }
-    }
-  } else if (warp == 1) {
-    if (lane == 0 && have_work) {
-      // ---------------- issuer of S = Q K^T ----------------
-      // The two products have a thread each, in different warps: issuing blocks while the tensor pipe
-      // is full, so with one thread the waits, commits and loop of one product would stand in the
-      // way of the other.  They need no order between them: every dependency is an mbarrier.
-      constexpr uint32_t idesc_s = fa_idesc(TQ, TK, 0);     // both K-major
-      bool ok = fa_wait(fa_smem_u32(q_full), 0, abort_flag);
-      auto issue_s = [&](int i) -> bool {                   // scores of tile i into S buffer i % 2
-        const int st = i % K_STAGES, sb = i & 1;
-        if (!fa_wait(fa_smem_u32(&k_full[st]), (i / K_STAGES) & 1, abort_flag)) return false;
-        fa_fence_after();
-        uint8_t* base = k_ring + (size_t)st * TILE_BYTES;
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
-          const uint64_t da = fa_desc_kmajor(fa_smem_u32(q_tile + (k / 4) * HALF_BYTES)) + 2 * (k % 4);
-          const uint64_t db = fa_desc_kmajor(fa_smem_u32(base + (k / 4) * HALF_BYTES)) + 2 * (k % 4);
-          fa_mma(tmem_s0 + (uint32_t)(sb * TK), da, db, idesc_s, k > 0 ? 1u : 0u);
-        }
-        fa_commit(fa_smem_u32(&s_full[sb]));
-        fa_commit(fa_smem_u32(&k_empty[st]));               // the keys' stage is free once S is done
-        return true;
-      };
-      if (ok && num_kt > 0) ok = issue_s(0);
-      if (ok && num_kt > 1) ok = issue_s(1);
-      for (int i = 0; i + 2 < num_kt && ok; ++i) {
-        // the scores of the tile after next, as soon as this tile's are in its threads' registers:
-        // they are computed while this tile and the next are being exponentiated
-        ok = fa_wait(fa_smem_u32(&s_free[i & 1]), (i >> 1) & 1, abort_flag);
-        if (ok) ok = issue_s(i + 2);
-      }
-      if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(err, 12); }
-    }
-  } else if (warp == FA_PV_WARP) {
-    if (lane == 0 && have_work) {
-      // ---------------- issuer of O += P V ----------------
-      constexpr uint32_t idesc_o = fa_idesc(TQ, HD, 1);     // P in tensor memory, V MN-major
-      bool ok = true;
-      for (int i = 0; i < num_kt && ok; ++i) {
-        if (!fa_wait(fa_smem_u32(&v_full[i % V_STAGES]), (i / V_STAGES) & 1, abort_flag)) { ok = false; break; }
-        if (!fa_wait(fa_smem_u32(&p_full[i & 1]), (i >> 1) & 1, abort_flag)) { ok = false; break; }
-        fa_fence_after();
-        uint8_t* vbase = v_ring + (size_t)(i % V_STAGES) * TILE_BYTES;
-#pragma unroll
-        for (int k = 0; k < TK / 16; ++k) {                 // 16 positions a step
-          // P of this tile: 16 keys = 8 columns of packed bf16 pairs a step, in the P buffer of its parity
-          const uint64_t db = fa_desc_mnmajor(fa_smem_u32(vbase + k * 16 * 128), HALF_BYTES);
-          fa_mma_a_tmem(tmem_o, tmem_p + (uint32_t)((i & 1) * (TK / 2) + 8 * k), db, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
-        }
-        fa_commit(fa_smem_u32(&pv_done[i & 1]));            // O, and this parity's P buffer, are free again once these have completed
-        fa_commit(fa_smem_u32(&v_empty[i % V_STAGES]));
-      }
-      if (ok) fa_commit(fa_smem_u32(o_full));
-      else if (!*abort_flag) { *abort_flag = 1; atomicExch(err, 13); }
-    }
-  } else if (have_work) {
-    // ---------------- softmax warps: group 0 takes the even key tiles, group 1 the odd ones ----------------
-    constexpr int OC = HD / 2;                              // output columns a thread writes at the end
-    const int quarter = warp & 3, grp = (warp - 2) >> 2;
-    const int r = quarter * 32 + lane;                      // row of the tile = lane of tensor memory
-    const int pos = start_pos + qt0 + r;                    // position of this row's query
-    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    float m_mine = -INFINITY, l_run = 0.f;                  // maximum this group's sum is scaled by; the sum
-    bool ok = true;                                         // warp-uniform
-    const float2 sc2 = make_float2(scale_log2e, scale_log2e);
-    for (int i = grp; i < num_kt && ok; i += 2) {
-      const int sb = grp, key0 = (kt_begin + i) * TK;       // S buffer = tile parity = group
-      ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(&s_full[sb]), (i >> 1) & 1, abort_flag));
-      if (!ok) break;
-      fa_fence_after();
-      const uint32_t s_addr = tmem_s0 + lane_addr + (uint32_t)(sb * TK);
-      // the row's 128 scores into registers with one wait; the S buffer is then free for the tile
-      // after next.  Everything below is straight-line code over the registers
-      uint32_t sa[TK];
-#pragma unroll
-      for (int c = 0; c < TK / 32; ++c) fa_ld32(s_addr + 32 * c, sa + 32 * c);
-      fa_wait_ld();
-      fa_fence_before();
-      __syncwarp();
-      if (lane == 0) fa_arrive(fa_smem_u32(&s_free[sb]));
-      if (window > 0) {
-#pragma unroll
-        for (int j = 0; j < TK; ++j) {
-          const int key = key0 + j;
-          if (!(key <= pos && key > pos - window)) sa[j] = 0xff800000u;          // -inf
-        }
-      } else if (key0 + TK - 1 > start_pos + qt0) {
-        // the tile on the diagonal: key j of the tile is visible to this row if j <= lim.  Rows grow
-        // with the lane, so the 32-key chunks left of the warp's first row's limit need nothing
-        const int lim = pos - key0;
-        const int lim0 = __shfl_sync(0xffffffffu, lim, 0);
-#pragma unroll
-        for (int c = 0; c < TK / 32; ++c) {
-          if (32 * c + 31 > lim0) {
-#pragma unroll
-            for (int j = 32 * c; j < 32 * c + 32; ++j) sa[j] = j > lim ? 0xff800000u : sa[j];
+          for (int half = 0; half < HALVES; ++half) {     // 64 head dimensions a half; 64 positions a page
+            fa_tma_2d(fa_smem_u32(base + half * HALF_BYTES), map, fb, 64 * half, r0);
+            fa_tma_2d(fa_smem_u32(base + half * HALF_BYTES + 64 * 128), map, fb, 64 * half, r1);
           }
+        };
+        auto stage_free = [&](uint64_t* empty, int stages, int i) -> bool {      // without waiting
+          return i < stages || fa_try_wait(fa_smem_u32(&empty[i % stages]), ((i / stages) & 1) ^ 1);
+        };
+        int nk = 0, nv = 0;
+        uint32_t idle = 0;
+        bool ok = true;
+        while (ok && nv < num_kt) {
+          bool moved = false;
+          if (nk < num_kt && stage_free(k_empty, K_STAGES, nk)) { load(nk, false); ++nk; moved = true; }
+          if (nv < nk && stage_free(v_empty, V_STAGES, nv)) { load(nv, true); ++nv; moved = true; }
+          if (moved) idle = 0;
+          else if (++idle > FA_WAIT_LIMIT || ((idle & 1023u) == 1023u && *abort_flag)) ok = false;
         }
+        if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(err, 11); }
       }
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    } else if (warp == 1) {
+      if (lane == 0 && have_work) {
+        // ---------------- issuer of S = Q K^T ----------------
+        // The two products have a thread each, in different warps: issuing blocks while the tensor pipe
+        // is full, so with one thread the waits, commits and loop of one product would stand in the
+        // way of the other.  They need no order between them: every dependency is an mbarrier.
+        constexpr uint32_t idesc_s = fa_idesc(TQ, TK, 0);     // both K-major
+        bool ok = fa_wait(fa_smem_u32(q_full), 0, abort_flag);
+        auto issue_s = [&](int i) -> bool {                   // scores of tile i into S buffer i % 2
+          const int st = i % K_STAGES, sb = i & 1;
+          if (!fa_wait(fa_smem_u32(&k_full[st]), (i / K_STAGES) & 1, abort_flag)) return false;
+          fa_fence_after();
+          uint8_t* base = k_ring + (size_t)st * TILE_BYTES;
 #pragma unroll
-      for (int j = 0; j < TK; j += 2) mx4[(j >> 1) & 3] = fa_max3(mx4[(j >> 1) & 3], __uint_as_float(sa[j]), __uint_as_float(sa[j + 1]));
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2e;
-      // the running maximum after the tile before (the other group's), and after this one: lazy, moved
-      // (with O and the sums rescaled) only when it grew by more than 2^8
-      float m_prev = -INFINITY;
-      if (i > 0) {
-        ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(&m_ready[((i - 1) & 1) * 4 + quarter]), ((i - 1) >> 1) & 1, abort_flag));
-        if (!ok) break;
-        m_prev = m_shared[((i - 1) & 1) * TQ + r];
+          for (int k = 0; k < HD / 16; ++k) {
+            const uint64_t da = fa_desc_kmajor(fa_smem_u32(q_tile + (k / 4) * HALF_BYTES)) + 2 * (k % 4);
+            const uint64_t db = fa_desc_kmajor(fa_smem_u32(base + (k / 4) * HALF_BYTES)) + 2 * (k % 4);
+            fa_mma(tmem_s0 + (uint32_t)(sb * TK), da, db, idesc_s, k > 0 ? 1u : 0u);
+          }
+          fa_commit(fa_smem_u32(&s_full[sb]));
+          fa_commit(fa_smem_u32(&k_empty[st]));               // the keys' stage is free once S is done
+          return true;
+        };
+        if (ok && num_kt > 0) ok = issue_s(0);
+        if (ok && num_kt > 1) ok = issue_s(1);
+        for (int i = 0; i + 2 < num_kt && ok; ++i) {
+          // the scores of the tile after next, as soon as this tile's are in its threads' registers:
+          // they are computed while this tile and the next are being exponentiated
+          ok = fa_wait(fa_smem_u32(&s_free[i & 1]), (i >> 1) & 1, abort_flag);
+          if (ok) ok = issue_s(i + 2);
+        }
+        if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(err, 12); }
       }
-      float m_now = m_prev;
-      if (mx > m_prev + LAZY_LOG2 || (m_prev == -INFINITY && mx > -INFINITY)) m_now = mx;
-      m_shared[(i & 1) * TQ + r] = m_now;
-      __syncwarp();
-      if (lane == 0) fa_arrive(fa_smem_u32(&m_ready[(i & 1) * 4 + quarter]));   // the next tile's threads may go on
-      const float corr = m_now != m_prev ? fa_exp2(m_prev - m_now) : 1.0f;       // 0 on the first visible tile
-      const bool any_rescale = __any_sync(0xffffffffu, corr != 1.0f);
-      if (m_mine != m_now) { l_run *= fa_exp2(m_mine - m_now); m_mine = m_now; }
-      // probabilities: exp2(score * scale - maximum), two scores an FMA; summed in float, rounded
-      // to bf16 for the product with V and packed in place (sa[0..63] then hold the row's 128)
-      const float m_sub = m_now == -INFINITY ? 0.f : m_now;
-      const float2 nm2 = make_float2(-m_sub, -m_sub);
-      float2 sum2[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+    } else if (warp == FA_PV_WARP) {
+      if (lane == 0 && have_work) {
+        // ---------------- issuer of O += P V ----------------
+        constexpr uint32_t idesc_o = fa_idesc(TQ, HD, 1);     // P in tensor memory, V MN-major
+        bool ok = true;
+        for (int i = 0; i < num_kt && ok; ++i) {
+          if (!fa_wait(fa_smem_u32(&v_full[i % V_STAGES]), (i / V_STAGES) & 1, abort_flag)) { ok = false; break; }
+          if (!fa_wait(fa_smem_u32(&p_full[i & 1]), (i >> 1) & 1, abort_flag)) { ok = false; break; }
+          fa_fence_after();
+          uint8_t* vbase = v_ring + (size_t)(i % V_STAGES) * TILE_BYTES;
 #pragma unroll
-      for (int j = 0; j < TK; j += 2) {
-        const float2 t = fa_ffma2(make_float2(__uint_as_float(sa[j]), __uint_as_float(sa[j + 1])), sc2, nm2);
-        const float2 p2 = make_float2(fa_exp2(t.x), fa_exp2(t.y));
-        sum2[(j >> 1) & 3] = fa_fadd2(sum2[(j >> 1) & 3], p2);
-        __nv_bfloat162 pb = __floats2bfloat162_rn(p2.x, p2.y);
-        sa[j >> 1] = *reinterpret_cast<uint32_t*>(&pb);
+          for (int k = 0; k < TK / 16; ++k) {                 // 16 positions a step
+            // P of this tile: 16 keys = 8 columns of packed bf16 pairs a step, in the P buffer of its parity
+            const uint64_t db = fa_desc_mnmajor(fa_smem_u32(vbase + k * 16 * 128), HALF_BYTES);
+            fa_mma_a_tmem(tmem_o, tmem_p + (uint32_t)((i & 1) * (TK / 2) + 8 * k), db, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+          }
+          fa_commit(fa_smem_u32(&pv_done[i & 1]));            // O, and this parity's P buffer, are free again once these have completed
+          fa_commit(fa_smem_u32(&v_empty[i % V_STAGES]));
+        }
+        if (ok) fa_commit(fa_smem_u32(o_full));
+        else if (!*abort_flag) { *abort_flag = 1; atomicExch(err, 13); }
       }
-      // the P buffer of this parity is free once the P V of the tile two back has completed; the barriers
-      // take turns by tile parity, and this thread waited for the tile four back on the same one
-      if (i >= 2) {
-        ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(&pv_done[i & 1]), ((i - 2) >> 1) & 1, abort_flag));
-        if (!ok) break;
-      }
-      // O is only touched once the previous tile's P V has completed: waited for only if this warp has a
-      // row to rescale (the tile three back is done, as the one two back is; the barrier cannot have run
-      // ahead: the next P V needs our arrival)
-      if (any_rescale && i > 0) {
-        ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(&pv_done[(i - 1) & 1]), ((i - 1) >> 1) & 1, abort_flag));
+    }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(FA_REGS_SOFTMAX));
+    if (have_work) {
+      // ---------------- softmax warps: group 0 takes the even key tiles, group 1 the odd ones ----------------
+      constexpr int OC = HD / 2;                              // output columns a thread writes at the end
+      const int quarter = warp & 3, grp = (warp - 4) >> 2;
+      const int r = quarter * 32 + lane;                      // row of the tile = lane of tensor memory
+      const int pos = start_pos + qt0 + r;                    // position of this row's query
+      const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+      float m_mine = -INFINITY, l_run = 0.f;                  // maximum this group's sum is scaled by; the sum
+      bool ok = true;                                         // warp-uniform
+      const float2 sc2 = make_float2(scale_log2e, scale_log2e);
+      for (int i = grp; i < num_kt && ok; i += 2) {
+        const int sb = grp, key0 = (kt_begin + i) * TK;       // S buffer = tile parity = group
+        ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(&s_full[sb]), (i >> 1) & 1, abort_flag));
         if (!ok) break;
         fa_fence_after();
-#pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {               // the whole row of O
-          uint32_t v[32];
-          const uint32_t o_addr = tmem_o + lane_addr + (uint32_t)(c * 32);
-          fa_ld32(o_addr, v);
-          fa_wait_ld();
+        const uint32_t s_addr = tmem_s0 + lane_addr + (uint32_t)(sb * TK);
+        // the row's 128 scores into registers with one wait; the S buffer is then free for the tile
+        // after next.  Everything below is straight-line code over the registers
+        uint32_t sa[TK];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * corr);
-          fa_st16(o_addr, *reinterpret_cast<uint32_t(*)[16]>(v));
-          fa_st16(o_addr + 16, *reinterpret_cast<uint32_t(*)[16]>(v + 16));
-        }
-      }
-      fa_fence_after();
-      // 16 keys are 8 columns of packed pairs
-      const uint32_t p_addr = tmem_p + lane_addr + (uint32_t)(sb * (TK / 2));
-#pragma unroll
-      for (int c = 0; c < TK / 32; ++c) fa_st16(p_addr + 16 * c, *reinterpret_cast<uint32_t(*)[16]>(sa + 16 * c));
-      fa_wait_st();
-      const float2 s01 = fa_fadd2(sum2[0], sum2[1]), s23 = fa_fadd2(sum2[2], sum2[3]);
-      l_run += (s01.x + s01.y) + (s23.x + s23.y);
-      // P is ready for the tensor cores
-      fa_fence_before();
-      __syncwarp();
-      if (lane == 0) fa_arrive(fa_smem_u32(&p_full[grp]));
-    }
-    // ---- O / l -> out ----
-    if (ok) ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(o_full), 0, abort_flag));
-    if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(err, 14); }
-    x_sum[grp * TQ + r] = l_run;
-    x_m[grp * TQ + r] = m_mine;
-    fa_softmax_sync();
-    fa_fence_after();
-    if (ok) {
-      // O is scaled by the last tile's maximum, the larger of the two groups'; sums in group order
-      const float m_other = x_m[(grp ^ 1) * TQ + r], l_other = x_sum[(grp ^ 1) * TQ + r];
-      const float m_fin = fmaxf(m_mine, m_other);
-      const float w_mine = m_mine == -INFINITY ? 0.f : fa_exp2(m_mine - m_fin);
-      const float w_other = m_other == -INFINITY ? 0.f : fa_exp2(m_other - m_fin);
-      const float l_row = grp == 0 ? l_run * w_mine + l_other * w_other : l_other * w_other + l_run * w_mine;
-      const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
-      __nv_bfloat16* orow = out + (size_t)(row0 + qt0 + r) * ldo + (size_t)h * HD + grp * OC;
-#pragma unroll 1
-      for (int c = 0; c < OC / 16; ++c) {
-        uint32_t v[16];
-        fa_ld16(tmem_o + lane_addr + (uint32_t)(grp * OC + c * 16), v);
+        for (int c = 0; c < TK / 32; ++c) fa_ld32(s_addr + 32 * c, sa + 32 * c);
         fa_wait_ld();
-        if (r < rows_here) {
-          uint32_t pk[8];
+        fa_fence_before();
+        __syncwarp();
+        if (lane == 0) fa_arrive(fa_smem_u32(&s_free[sb]));
+        // The tile on the diagonal (no window) has code of its own, by 32-key chunks; every other tile
+        // runs straight-line code over all 128 scores, which the scheduler can reorder freely.
+        const bool diag = window <= 0 && key0 + TK - 1 > start_pos + qt0;     // warp-uniform
+        int live = TK / 32;                     // diagonal tile: chunks that some row of this warp sees
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (!diag) {
+          if (window > 0) {
 #pragma unroll
-          for (int j = 0; j < 16; j += 2) {
-            __nv_bfloat162 o2 = __floats2bfloat162_rn(__uint_as_float(v[j]) * inv, __uint_as_float(v[j + 1]) * inv);
-            pk[j >> 1] = *reinterpret_cast<uint32_t*>(&o2);
+            for (int j = 0; j < TK; ++j) {
+              const int key = key0 + j;
+              if (!(key <= pos && key > pos - window)) sa[j] = 0xff800000u;          // -inf
+            }
           }
-          *reinterpret_cast<uint4*>(orow + c * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-          *reinterpret_cast<uint4*>(orow + c * 16 + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+#pragma unroll
+          for (int j = 0; j < TK; j += 2) mx4[(j >> 1) & 3] = fa_max3(mx4[(j >> 1) & 3], __uint_as_float(sa[j]), __uint_as_float(sa[j + 1]));
+        } else {
+          // key j of the tile is visible to this row if j <= lim.  Rows grow with the lane, so the chunks
+          // left of the warp's first row's limit need no mask, and those right of its last row's limit
+          // are dropped whole: no maxima, no exponentials, P = 0
+          const int lim = pos - key0;
+          const int lim0 = __shfl_sync(0xffffffffu, lim, 0), lim31 = __shfl_sync(0xffffffffu, lim, 31);
+          live = lim31 < 0 ? 0 : min(TK / 32, (lim31 >> 5) + 1);
+#pragma unroll
+          for (int c = 0; c < TK / 32; ++c) {
+            if (c < live) {
+              if (32 * c + 31 > lim0) {
+#pragma unroll
+                for (int j = 32 * c; j < 32 * c + 32; ++j) sa[j] = j > lim ? 0xff800000u : sa[j];
+              }
+#pragma unroll
+              for (int j = 32 * c; j < 32 * c + 32; j += 2)
+                mx4[(j >> 1) & 3] = fa_max3(mx4[(j >> 1) & 3], __uint_as_float(sa[j]), __uint_as_float(sa[j + 1]));
+            }
+          }
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2e;
+        // the running maximum after the tile before (the other group's), and after this one: lazy, moved
+        // (with O and the sums rescaled) only when it grew by more than 2^8
+        float m_prev = -INFINITY;
+        if (i > 0) {
+          ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(&m_ready[((i - 1) & 1) * 4 + quarter]), ((i - 1) >> 1) & 1, abort_flag));
+          if (!ok) break;
+          m_prev = m_shared[((i - 1) & 1) * TQ + r];
+        }
+        float m_now = m_prev;
+        if (mx > m_prev + LAZY_LOG2 || (m_prev == -INFINITY && mx > -INFINITY)) m_now = mx;
+        m_shared[(i & 1) * TQ + r] = m_now;
+        __syncwarp();
+        if (lane == 0) fa_arrive(fa_smem_u32(&m_ready[(i & 1) * 4 + quarter]));   // the next tile's threads may go on
+        const float corr = m_now != m_prev ? fa_exp2(m_prev - m_now) : 1.0f;       // 0 on the first visible tile
+        const bool any_rescale = __any_sync(0xffffffffu, corr != 1.0f);
+        if (m_mine != m_now) { l_run *= fa_exp2(m_mine - m_now); m_mine = m_now; }
+        // probabilities: exp2(score * scale - maximum), two scores an FMA; summed in float, rounded
+        // to bf16 for the product with V and packed in place (sa[0..63] then hold the row's 128)
+        const float m_sub = m_now == -INFINITY ? 0.f : m_now;
+        const float2 nm2 = make_float2(-m_sub, -m_sub);
+        float2 sum2[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+        auto soft2 = [&](int j) {               // scores j, j + 1 -> probabilities, packed into sa[j / 2]
+          const float2 t = fa_ffma2(make_float2(__uint_as_float(sa[j]), __uint_as_float(sa[j + 1])), sc2, nm2);
+          const float2 p2 = make_float2(fa_exp2(t.x), fa_exp2(t.y));
+          sum2[(j >> 1) & 3] = fa_fadd2(sum2[(j >> 1) & 3], p2);
+          __nv_bfloat162 pb = __floats2bfloat162_rn(p2.x, p2.y);
+          sa[j >> 1] = *reinterpret_cast<uint32_t*>(&pb);
+        };
+        if (!diag) {
+#pragma unroll
+          for (int j = 0; j < TK; j += 2) {
+            const float2 t = fa_ffma2(make_float2(__uint_as_float(sa[j]), __uint_as_float(sa[j + 1])), sc2, nm2);
+            const float2 p2 = make_float2(fa_exp2(t.x), fa_exp2(t.y));
+            sum2[(j >> 1) & 3] = fa_fadd2(sum2[(j >> 1) & 3], p2);
+            __nv_bfloat162 pb = __floats2bfloat162_rn(p2.x, p2.y);
+            sa[j >> 1] = *reinterpret_cast<uint32_t*>(&pb);
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < TK / 32; ++c) {
+            if (c < live) {
+#pragma unroll
+              for (int j = 32 * c; j < 32 * c + 32; j += 2) soft2(j);
+            } else {
+#pragma unroll
+              for (int j = 16 * c; j < 16 * c + 16; ++j) sa[j] = 0u;
+            }
+          }
+        }
+        // the P buffer of this parity is free once the P V of the tile two back has completed; the barriers
+        // take turns by tile parity, and this thread waited for the tile four back on the same one
+        if (i >= 2) {
+          ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(&pv_done[i & 1]), ((i - 2) >> 1) & 1, abort_flag));
+          if (!ok) break;
+        }
+        // O is only touched once the previous tile's P V has completed: waited for only if this warp has a
+        // row to rescale (the tile three back is done, as the one two back is; the barrier cannot have run
+        // ahead: the next P V needs our arrival)
+        if (any_rescale && i > 0) {
+          ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(&pv_done[(i - 1) & 1]), ((i - 1) >> 1) & 1, abort_flag));
+          if (!ok) break;
+          fa_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {               // the whole row of O
+            uint32_t v[32];
+            const uint32_t o_addr = tmem_o + lane_addr + (uint32_t)(c * 32);
+            fa_ld32(o_addr, v);
+            fa_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * corr);
+            fa_st16(o_addr, *reinterpret_cast<uint32_t(*)[16]>(v));
+            fa_st16(o_addr + 16, *reinterpret_cast<uint32_t(*)[16]>(v + 16));
+          }
+        }
+        fa_fence_after();
+        // 16 keys are 8 columns of packed pairs
+        const uint32_t p_addr = tmem_p + lane_addr + (uint32_t)(sb * (TK / 2));
+#pragma unroll
+        for (int c = 0; c < TK / 32; ++c) fa_st16(p_addr + 16 * c, *reinterpret_cast<uint32_t(*)[16]>(sa + 16 * c));
+        fa_wait_st();
+        const float2 s01 = fa_fadd2(sum2[0], sum2[1]), s23 = fa_fadd2(sum2[2], sum2[3]);
+        l_run += (s01.x + s01.y) + (s23.x + s23.y);
+        // P is ready for the tensor cores
+        fa_fence_before();
+        __syncwarp();
+        if (lane == 0) fa_arrive(fa_smem_u32(&p_full[grp]));
+      }
+      // ---- O / l -> out ----
+      if (ok) ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(o_full), 0, abort_flag));
+      if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(err, 14); }
+      x_sum[grp * TQ + r] = l_run;
+      x_m[grp * TQ + r] = m_mine;
+      fa_softmax_sync();
+      fa_fence_after();
+      if (ok) {
+        // O is scaled by the last tile's maximum, the larger of the two groups'; sums in group order
+        const float m_other = x_m[(grp ^ 1) * TQ + r], l_other = x_sum[(grp ^ 1) * TQ + r];
+        const float m_fin = fmaxf(m_mine, m_other);
+        const float w_mine = m_mine == -INFINITY ? 0.f : fa_exp2(m_mine - m_fin);
+        const float w_other = m_other == -INFINITY ? 0.f : fa_exp2(m_other - m_fin);
+        const float l_row = grp == 0 ? l_run * w_mine + l_other * w_other : l_other * w_other + l_run * w_mine;
+        const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
+        __nv_bfloat16* orow = out + (size_t)(row0 + qt0 + r) * ldo + (size_t)h * HD + grp * OC;
+#pragma unroll 1
+        for (int c = 0; c < OC / 16; ++c) {
+          uint32_t v[16];
+          fa_ld16(tmem_o + lane_addr + (uint32_t)(grp * OC + c * 16), v);
+          fa_wait_ld();
+          if (r < rows_here) {
+            uint32_t pk[8];
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) {
+              __nv_bfloat162 o2 = __floats2bfloat162_rn(__uint_as_float(v[j]) * inv, __uint_as_float(v[j + 1]) * inv);
+              pk[j >> 1] = *reinterpret_cast<uint32_t*>(&o2);
+            }
+            *reinterpret_cast<uint4*>(orow + c * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            *reinterpret_cast<uint4*>(orow + c * 16 + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+          }
         }
       }
     }
