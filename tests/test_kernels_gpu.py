@@ -669,7 +669,10 @@ def test_attention_prefill_finds_one_far_key(far):
 @pytest.mark.parametrize("H,G", [(32, 8), (4, 4), (3, 1)])
 @pytest.mark.parametrize("lens_q,lens_kv", [([1, 5, 64, 65, 200], [1, 5, 64, 65, 200]),
                                             ([130, 1, 33, 64], [130, 300, 97, 128]),
-                                            ([129], [129]), ([128, 256], [128, 256]), ([700], [700]), ([40], [1000])])
+                                            ([129], [129]), ([128, 256], [128, 256]), ([700], [700]), ([40], [1000]),
+                                            # 18 key tiles, the query tiles not aligned with them: both of a query tile's
+                                            # last two key tiles are masked in part, and every ring and barrier wraps
+                                            ([1700], [2304])])
 def test_attention_prefill_tc_matches_plain(H, G, lens_q, lens_kv, hd):
     k = K()
     assert k.attention_prefill_tc_supported(torch.bfloat16, H, G, hd)
