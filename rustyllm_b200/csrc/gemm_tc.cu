@@ -457,8 +457,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   } else {
     // ---------------- epilogue: warps 2..5, each its quarter of the 128 lanes ----------------
     rl_pdl_wait();      // before this warp reads or writes global memory
-    if (fuse.scale_partials != nullptr)      // while the products still run
-      epilogue_row_scales<BT>(fuse, m0, M, K, warp & 3, lane, fuse_smem);
+    if constexpr (BT <= 64) {
+      if (fuse.scale_partials != nullptr)    // while the products still run
+        epilogue_row_scales<BT>(fuse, m0, M, K, warp & 3, lane, fuse_smem);
+    }
     if (out_mode == TC_OUT_ROPE_KV) {
       // position of every token of the tile and the row of the cache pools it is stored in
       int* tok_pos = (int*)(fuse_smem + BT);
@@ -923,17 +925,26 @@ extern "C" int rl_gemm_tc_supported(const void* A, const void* W, int M, int N, 
 
 static int token_tile(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
 
-// How many parts (1, 2, 4 or 8: the cluster size) the K range is cut into for M tokens:
-// the smallest that gives about two CTAs an SM, with at least four 64-wide K blocks a
-// part; products with 148 tiles or more, and token tiles above 64, are not split.
+// How many parts (1, 2, 4 or 8: the cluster size) the K range is cut into for M tokens.
+// Up to 64 tokens: the smallest that gives about two CTAs an SM, with at least four 64-wide
+// K blocks a part; products with 148 tiles or more are not split.  Above 64 tokens (one CTA
+// an SM): the largest that still fits one wave of 148 CTAs, if the tiles alone fill no more
+// than a quarter of it - a CTA cannot pull more than about 80 GB/s, so a product with few
+// tiles needs more CTAs to stream its weights (4,096 x 14,336 weights, 256 tokens: 74 us as
+// 32 tiles, 42 us in four parts each) - else the persistent kernel takes it unsplit (measured
+// equal or better from 48 tiles on).
 // A function of the shapes only, so a captured step keeps its grid.
 extern "C" int rl_gemm_tc_splits(int M, int N, int K) {
   const int bt = token_tile(M);
-  if (bt > 64) return 1;
   const int tiles = ((N + BLOCK_N_OUT - 1) / BLOCK_N_OUT) * ((M + bt - 1) / bt);
   const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
-  if (tiles >= 148) return 1;
   int splits = 1;
+  if (bt > 64) {
+    if (tiles * 4 > 148) return 1;
+    while (splits < 8 && tiles * splits * 2 <= 148 && total_kb / (splits * 2) >= 4) splits *= 2;
+    return splits;
+  }
+  if (tiles >= 148) return 1;
   while (splits < 8 && tiles * splits < 256 && total_kb / (splits * 2) >= 4) splits *= 2;
   return splits;
 }
@@ -970,7 +981,6 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* ou
              "rl_gemm_tc: a norm rides in the epilogue only for up to 64 tokens, got %d", M);
   const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
   int splits = force_splits > 0 ? force_splits : rl_gemm_tc_splits(M, N, K);
-  RL_REQUIRE(splits == 1 || bt <= 64, "rl_gemm_tc: K is split only for up to 64 tokens (the partial tile must fit the ring)");
   while (splits > 1 && (splits - 1) * ((total_kb + splits - 1) / splits) >= total_kb) splits /= 2;   // no part is empty
   RL_REQUIRE(out_mode != TC_OUT_ROPE_KV || (splits > 1 && bt <= 64),
              "rl_gemm_tc_qkv_rope: the rotation rides only in the cluster epilogue (up to 64 tokens, K in 2 or more parts); "
@@ -986,6 +996,10 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* ou
     case 32: return launch_tc<32>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, fuse, stream);
     case 64: return launch_tc<64>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, fuse, stream);
     default: break;
+  }
+  if (splits > 1) {       // few tiles of many tokens: the parts of a tile as a cluster, as for few tokens
+    if (bt == 128) return launch_tc<128>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, fuse, stream);
+    return launch_tc<256>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per, fuse, stream);
   }
   if (bt == 128) return launch_tc_persistent<128>(mw, ma, A, lda, bias, out, out_mode, M, N, K, ldo, err, stream);
   return launch_tc_persistent<256>(mw, ma, A, lda, bias, out, out_mode, M, N, K, ldo, err, stream);

@@ -76,7 +76,8 @@ def test_swiglu_interleaved(dtype, I):
 
 
 @pytest.mark.parametrize("M,N,K_,parts", [(1, 256, 128, 0), (8, 28672, 512, 0), (8, 1024, 4096, 8), (40, 400, 72, 0), (64, 512, 1024, 4),
-                                          (300, 344, 264, 0), (17, 130, 104, 2)])
+                                          (300, 344, 264, 0), (17, 130, 104, 2), (100, 640, 2048, 0), (130, 344, 1024, 4),
+                                          (256, 512, 512, 2)])
 def test_gemm_tc_swiglu_epilogue(M, N, K_, parts):
     k = K()
     a = _rand(M, K_, dtype=torch.bfloat16, seed=24)
@@ -173,7 +174,10 @@ def test_gemm_tc_all_modes(M, N, K_):
 
 
 @pytest.mark.parametrize("M,N,K_", [(1, 4096, 4096), (8, 6144, 4096), (8, 4096, 14336), (8, 512, 512), (64, 1024, 4096),
-                                    (33, 300, 1096), (16, 128, 256)])
+                                    (33, 300, 1096), (16, 128, 256),
+                                    # more than 64 tokens, few tiles: 128- and 256-token tiles in parts as well
+                                    (128, 4096, 4096), (100, 520, 2048), (200, 640, 1096), (256, 256, 1024), (300, 1100, 640),
+                                    (512, 4096, 4096)])
 def test_gemm_tc_split_k_is_deterministic_and_matches_the_unsplit_product(M, N, K_):
     k = K()
     a = _rand(M, K_, dtype=torch.bfloat16, seed=14)
@@ -197,8 +201,10 @@ def test_gemm_tc_split_k_is_deterministic_and_matches_the_unsplit_product(M, N, 
     out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
     k.gemm_tc(a, w, out, k.OUT_SAME)
     torch.testing.assert_close(out.double().cpu(), ref - bias.double().cpu() - res.double().cpu(), rtol=1e-2, atol=1e-2 * math.sqrt(K_))
-    if (M, N, K_) in [(1, 4096, 4096), (8, 6144, 4096), (8, 4096, 14336)]:
+    if (M, N, K_) in [(1, 4096, 4096), (8, 6144, 4096), (8, 4096, 14336), (128, 4096, 4096), (100, 520, 2048), (200, 640, 1096)]:
         assert k.gemm_tc_splits(M, N, K_) > 1
+    if (M, N, K_) == (512, 4096, 4096):
+        assert k.gemm_tc_splits(M, N, K_) == 1      # 64 tiles: the persistent kernel takes them whole
 
 
 @pytest.mark.parametrize("M,N,K_,parts", [(8, 384, 512, 0), (8, 384, 512, 1), (5, 200, 256, 4), (40, 136, 192, 2),
