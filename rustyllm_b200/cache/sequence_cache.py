@@ -25,9 +25,11 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..kernels import PAGE_SIZE
+from ..staging import PinnedStaging
 from .allocators import CacheFull, CacheMisuse, FreeList
 
 
@@ -91,6 +93,7 @@ class SequenceCache:
                  max_seq_len: Optional[int] = None):
         device = torch.device(device)
         self.device = device
+        self._staging: Optional[PinnedStaging] = None      # for page-table updates
         self.dtype = dtype
         self.page_size = PAGE_SIZE
         if max_tokens <= 0:
@@ -200,15 +203,18 @@ class SequenceCache:
 
     def _write_page_table(self, g: KVGroup, updates) -> None:
         """Record new pages in the host copy and in the device copy of the page table.
-        The device copy is written from a fresh host tensor each time (staged by the
-        driver before the call returns), so later changes to the host copy cannot
+        The device copy is written from a pinned buffer of a ring (a buffer is reused only
+        after the copy that read it has finished), so later changes on the host cannot
         reach a step that is already queued."""
-        t = torch.tensor(updates, dtype=torch.int64)
-        flat = t[:, 0] * self.max_pages_per_slot + t[:, 1]
-        vals = t[:, 2].to(torch.int32)
-        g.page_table_host.view(-1).index_copy_(0, flat, vals)
+        u = np.asarray(updates, dtype=np.int64)
+        flat = u[:, 0] * self.max_pages_per_slot + u[:, 1]
+        g.page_table_host.view(-1).numpy()[flat] = u[:, 2]
         if g.page_table is not g.page_table_host:
-            g.page_table.view(-1).index_copy_(0, flat.to(self.device), vals.to(self.device))
+            if self._staging is None:
+                self._staging = PinnedStaging(self.device, torch.int32)
+            n = flat.shape[0]
+            dev = self._staging.upload(np.concatenate([flat, u[:, 2]]))      # places, then pages, in one copy
+            g.page_table.view(-1).index_copy_(0, dev[:n].long(), dev[n:])
 
     def commit(self, slots: Sequence[int], counts: Sequence[int]) -> None:
         """The step ran: lengths grow; window groups release pages that fell out."""
