@@ -27,7 +27,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: the Llama-3.1-8B shape
+# the Llama-3.1-8B shape the headline numbers are quoted on
 LLAMA_8B = {
     "architectures": ["LlamaForCausalLM"], "model_type": "llama",
     "vocab_size": 128256, "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 32,
