@@ -186,6 +186,12 @@ class Runner:
     def step(self, slots, tokens, want="last"):
         return self.engine.step(slots, tokens, want)
 
+    def warm_up(self, batch_sizes: Sequence[int]) -> None:
+        """Capture the decode step for these batch sizes ahead of the first request."""
+        with self._generation_lock:
+            self.engine.warm_up(batch_sizes)
+            torch.cuda.synchronize(self.runtime.device)
+
     # ------------------------------------------------------------------ generation
     def generate(self, prompt: Union[Sequence[int], Sequence[Sequence[int]]],
                  options: Optional[GenerationOptions] = None,

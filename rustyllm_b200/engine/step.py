@@ -123,6 +123,24 @@ class Engine:
     def free_slot(self, slot: int) -> None:
         self.cache.free_slot(slot)
 
+    def warm_up(self, batch_sizes: Sequence[int]) -> None:
+        """Capture the single-token step for these batch sizes now instead of at their first
+        use in a generation (a capture takes a tenth of a second or more).  Needs that many
+        free slots and one page each; leaves the cache as it found it."""
+        if not self.use_graphs:
+            return
+        for B in sorted(set(int(b) for b in batch_sizes)):
+            if B <= 0 or B in self._graphs:
+                continue
+            slots = [self.alloc_slot() for _ in range(B)]
+            try:
+                self.step(slots, [[0]] * B, None)              # one token each, so that a length exists
+                while B not in self._graphs:                   # an eager step first, then the capture
+                    self.step(slots, [[0]] * B, "last")
+            finally:
+                for s in slots:
+                    self.free_slot(s)
+
     # ------------------------------------------------------------------ the step
     def build_step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], want: Want = "last"):
         """Validate on the host and lay out the step's integer inputs."""

@@ -125,6 +125,21 @@ def test_running_ahead_of_the_host_generates_the_same_tokens(model_dirs, dtype):
         assert r.cache.free_pages == r.cache.num_pages and r.cache.slots.free_count == 4
 
 
+def test_warm_up_captures_the_decode_steps_and_changes_no_token(model_dirs):
+    from rustyllm_b200 import GenerationOptions, Runner, SamplerConfig
+    d, cfg = model_dirs["A"]
+    prompts = [random_tokens(256, n, 20 + n) for n in (6, 19, 3)]
+    opts = GenerationOptions(max_tokens=7, sampler=SamplerConfig(temperature=0.8), seed=9)
+    cold, _ = Runner.from_path(d, dtype="bfloat16", max_cache_tokens=64 * 6, max_batch=3)
+    want = [r.token_ids for r in cold.generate(prompts, opts)]
+    warm, _ = Runner.from_path(d, dtype="bfloat16", max_cache_tokens=64 * 6, max_batch=3)
+    warm.warm_up([1, 2, 3, 3])
+    assert sorted(warm.engine._graphs) == [1, 2, 3]
+    warm.cache.check()
+    assert warm.cache.free_pages == warm.cache.num_pages and warm.cache.slots.free_count == 3
+    assert [r.token_ids for r in warm.generate(prompts, opts)] == want
+
+
 def test_random_weights_without_files_and_layer_override():
     from rustyllm_b200 import GenerationOptions, Runner, SamplerConfig
     r = Runner.from_config(TINY["B"]["config"], seed=3, dtype="bfloat16", max_cache_tokens=64 * 4, max_batch=2,
