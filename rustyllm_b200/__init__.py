@@ -5,7 +5,8 @@ after SimonWaldherr/RustyLLM's Llama dense decoder.
     runner, info = Runner.from_path("model_dir", dtype="bfloat16")
     result = runner.generate([1, 2, 3], GenerationOptions(max_tokens=8, sampler=SamplerConfig.greedy()))
 """
-from .config.llama import ConfigError, LlamaConfig, RopeScaling  # noqa: F401
+from .config.files import ConfigError  # noqa: F401
+from .config.llama import LlamaConfig, RopeScaling  # noqa: F401
 from .config.registry import (UnknownArchitecture, known_architectures, register_architecture,  # noqa: F401
                               resolve_architecture)
 from .config.spec import LayerSpec, ModelSpec, ParamSource, ParamSpec, PartSpec  # noqa: F401

@@ -12,8 +12,11 @@ Differences, all from the missing tokenizer: ``--prompt`` takes token ids (separ
 spaces or commas) and ``--stop`` takes a token id or a sequence of ids; generated ids
 are printed instead of text.  Added: ``--dtype`` (bfloat16 | float32), ``--random``
 (random weights from the model folder's config.json alone, or from a config.json path),
-``--prompt-file`` (one prompt of ids per line: a batch), ``--batch``, ``--prompt-len``
-for the benchmark with synthetic prompts.
+``--prompt-file`` (one prompt of ids per line: a batch), and for the benchmark with
+synthetic prompts ``--batch``, ``--prompt-len`` or ``--prompt-len-range lo,hi`` (lengths
+drawn uniformly from [lo, hi) with the seed).  ``--decode-tokens``, ``--context``, ``--runs``
+and ``--json`` are other spellings of ``--max-tokens``, ``--max-context``, ``--bench-runs``
+and ``--bench-json``.
 """
 from __future__ import annotations
 
@@ -44,7 +47,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="compute dtype (default: bfloat16)")
     p.add_argument("--prompt", "-p", help="input prompt as token ids, e.g. '1 15043 3186'")
     p.add_argument("--prompt-file", help="file with one prompt of token ids per line (a batch)")
-    p.add_argument("--max-tokens", "-n", type=int, default=256, help="Max tokens to generate (default: 256)")
+    p.add_argument("--max-tokens", "--decode-tokens", "-n", dest="max_tokens", type=int, default=256, help="Max tokens to generate (default: 256)")
     p.add_argument("--temp", "-t", type=float, default=0.7, help="Temperature (default: 0.7, 0=greedy)")
     p.add_argument("--top-p", type=float, default=1.0, help="Nucleus sampling threshold (default: 1 = off; reference: 0.9)")
     p.add_argument("--top-k", type=int, default=0, help="Top-K filtering (default: 0 = off; reference: 40)")
@@ -54,14 +57,15 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--seed", type=int, default=0, help="RNG seed (default: time-based)")
     p.add_argument("--stop", action="append", default=[], help="stop when this token id (or sequence of ids) is generated; repeatable")
     p.add_argument("--ignore-eos", action="store_true", help="do not stop at the model's end-of-sequence ids")
-    p.add_argument("--max-context", type=int, help="Cap runtime context/KV-cache length")
+    p.add_argument("--max-context", "--context", dest="max_context", type=int, help="Cap runtime context/KV-cache length")
     p.add_argument("--kv-cache-dtype", default="auto", choices=["auto", "f32", "bf16", "q8"], help="KV cache dtype (auto = the compute dtype)")
     p.add_argument("--batch", type=int, default=1, help="benchmark: sequences per batch with synthetic prompts")
     p.add_argument("--prompt-len", type=int, default=128, help="benchmark: synthetic prompt length")
+    p.add_argument("--prompt-len-range", metavar="LO,HI", help="benchmark: synthetic prompt lengths drawn uniformly from [LO, HI)")
     p.add_argument("--bench", action="store_true", help="Run a non-streaming generation benchmark")
-    p.add_argument("--bench-json", action="store_true", help="Run benchmark and emit machine-readable JSON")
+    p.add_argument("--bench-json", "--json", dest="bench_json", action="store_true", help="Run benchmark and emit machine-readable JSON")
     p.add_argument("--bench-output", action="store_true", help="Include generated ids for each benchmark run")
-    p.add_argument("--bench-runs", type=int, default=3, help="Number of benchmark runs (default: 3)")
+    p.add_argument("--bench-runs", "--runs", dest="bench_runs", type=int, default=3, help="Number of benchmark runs (default: 3)")
     p.add_argument("--kernel-bench", action="store_true", help="Run isolated kernel benchmark")
     p.add_argument("--kernel-bench-json", action="store_true", help="Emit isolated kernel benchmark JSON")
     p.add_argument("--kernel-bench-runs", type=int, default=25, help="Number of kernel benchmark runs (default: 25)")
@@ -95,7 +99,7 @@ def inspect(model_dir: str, list_tensors: bool) -> int:
     """Configuration, architecture and checkpoint compatibility, without loading weights
     (the reference's --inspect / --list-tensors over GGUF metadata)."""
     import torch
-    from .config.llama import read_config_json
+    from .config.files import read_config_json
     from .config.registry import resolve_architecture
     from .models.decoder import DecoderModel
     from .parts import Runtime
@@ -121,6 +125,22 @@ def inspect(model_dir: str, list_tensors: bool) -> int:
     except WeightsError as e:
         print(f"compatibility: NOT loadable\n{e}")
         return 1
+
+
+def synthetic_prompt_lengths(args, rnd) -> List[int]:
+    """Lengths of the benchmark's synthetic prompts: ``--batch`` times ``--prompt-len``, or drawn
+    uniformly from ``--prompt-len-range lo,hi`` (hi excluded) with the seeded generator."""
+    if not args.prompt_len_range:
+        if args.prompt_len <= 0:
+            raise SystemExit("--prompt-len must be greater than 0")
+        return [args.prompt_len] * args.batch
+    try:
+        lo, hi = (int(x) for x in args.prompt_len_range.replace(":", ",").split(","))
+    except ValueError:
+        raise SystemExit(f"--prompt-len-range wants two integers 'lo,hi', got {args.prompt_len_range!r}")
+    if not (0 < lo < hi):
+        raise SystemExit(f"--prompt-len-range needs 0 < lo < hi, got {lo},{hi}")
+    return [rnd.randrange(lo, hi) for _ in range(args.batch)]
 
 
 def _load(args, model_dir: str, max_batch: int):
@@ -266,7 +286,9 @@ def run_kernel_benchmark(runner, runs: int, as_json: bool) -> int:
         rows.append((f"attn_scan.ctx{ctx}", t, 2 * (ctx + 1) * att.G * att.hd * esz))
         eng.free_slot(s)
     if as_json:
-        print(json.dumps({"type": "llm-kernel-bench.v1", "model": runner.model_name(), "runs": runs, "layer": 0,
+        # the reference's envelope (src/main.rs:1672-1676): "type" names the record, "format" its layout
+        print(json.dumps({"type": "rusty-llm.kernel_benchmark", "format": "llm-kernel-bench.v1", "runtime": "rustyllm_b200",
+                          "model": runner.model_name(), "runs": runs, "layer": 0,
                           "rows": [{"name": n, "avg_us": t, "bytes": b, "gb_s": b / t / 1e3} for n, t, b in rows]}, indent=2))
     else:
         for n, t, b in rows:
@@ -309,7 +331,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         return run_kernel_benchmark(runner, args.kernel_bench_runs, args.kernel_bench_json)
     if prompts is None:
         V = runner.model.spec.vocab_size
-        prompts = [[rnd.randrange(V) for _ in range(args.prompt_len)] for _ in range(args.batch)]
+        prompts = [[rnd.randrange(V) for _ in range(n)] for n in synthetic_prompt_lengths(args, rnd)]
     if bench:
         return run_benchmark(runner, info, prompts, opts, args.bench_runs, args.bench_json, args.bench_output)
     single = len(prompts) == 1

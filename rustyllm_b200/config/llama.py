@@ -10,14 +10,10 @@ Every size the model uses lives here; nothing downstream hard-codes one.
 """
 from __future__ import annotations
 
-import json
-import os
 from dataclasses import dataclass, field
 from typing import Any, Mapping, Optional, Tuple
 
-
-class ConfigError(ValueError):
-    """A config.json that cannot describe a model of this architecture."""
+from .files import ConfigError, token_ids as _token_ids
 
 
 @dataclass(frozen=True)
@@ -69,17 +65,6 @@ def _opt_float(d: Mapping[str, Any], key: str, default: float) -> float:
     if isinstance(v, bool) or not isinstance(v, (int, float)):
         raise ConfigError(f"config key '{key}' must be a number, got {v!r}")
     return float(v)
-
-
-def _token_ids(d: Mapping[str, Any], key: str) -> Tuple[int, ...]:
-    v = d.get(key)
-    if v is None:
-        return ()
-    if isinstance(v, int) and not isinstance(v, bool):
-        return (v,)
-    if isinstance(v, (list, tuple)) and all(isinstance(t, int) and not isinstance(t, bool) for t in v):
-        return tuple(v)
-    raise ConfigError(f"config key '{key}' must be an integer or a list of integers, got {v!r}")
 
 
 def parse_rope_scaling(raw: Any) -> Optional[RopeScaling]:
@@ -255,17 +240,3 @@ class LlamaConfig:
         if self.eos_token_id:
             d["eos_token_id"] = self.eos_token_id[0] if len(self.eos_token_id) == 1 else list(self.eos_token_id)
         return d
-
-
-def read_config_json(model_dir: str) -> dict:
-    path = os.path.join(model_dir, "config.json")
-    if not os.path.isfile(path):
-        raise ConfigError(f"no config.json in {model_dir!r}")
-    with open(path, "r", encoding="utf-8") as f:
-        try:
-            d = json.load(f)
-        except json.JSONDecodeError as e:
-            raise ConfigError(f"{path}: not valid JSON ({e})") from e
-    if not isinstance(d, dict):
-        raise ConfigError(f"{path}: top level must be an object")
-    return d

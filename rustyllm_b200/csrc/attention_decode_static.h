@@ -35,8 +35,14 @@
 #define RL_DECODE_STATIC_SCRATCH_FLOATS (1u << 20)
 #define RL_DECODE_STATIC_MAX_DEVICES 64
 
-extern "C" int rl_attention_decode_static(const void* q, int ldq, const void* k_pool, const void* v_pool,
+#ifdef __cplusplus
+extern "C" {
+#endif
+int rl_attention_decode_static(const void* q, int ldq, const void* k_pool, const void* v_pool,
                                           const int* page_table, int max_pages, const int* seq_slots,
                                           const int* kv_lens, void* out, int ldo, int num_seqs, int num_heads,
                                           int num_kv_heads, int head_dim, float scale, int window, int num_splits,
                                           cudaStream_t stream);
+#ifdef __cplusplus
+}
+#endif

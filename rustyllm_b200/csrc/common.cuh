@@ -23,6 +23,7 @@ enum RlStatus {
 #define RL_PAGE 64
 
 void rl_set_error(const char* fmt, ...);
+int rl_num_sms();   // SMs of the current device (148 where no device can be asked)
 
 #define RL_REQUIRE(cond, ...)            \
   do {                                   \

@@ -218,14 +218,14 @@ extern "C" int rl_swiglu(const void* gate_up, void* out, int dtype, int num_toke
   if (num_tokens == 0) return RL_OK;
   const size_t total = (size_t)num_tokens * intermediate;
   const int threads = 256;
-  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  const int blocks = (int)((total + threads - 1) / threads < rl_num_sms() * 16 ? (total + threads - 1) / threads : rl_num_sms() * 16);
   if (dtype == RL_BF16 && interleaved && intermediate % 4 == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 7) == 0) {
     const size_t quads = total / 4;      // rows are contiguous: [M, 2I] in, [M, I] out
-    const int qblocks = (int)((quads + threads - 1) / threads < 148 * 16 ? (quads + threads - 1) / threads : 148 * 16);
+    const int qblocks = (int)((quads + threads - 1) / threads < rl_num_sms() * 16 ? (quads + threads - 1) / threads : rl_num_sms() * 16);
     rl_launch_pdl(swiglu_bf16_interleaved_kernel, qblocks, threads, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, quads);
   } else if (dtype == RL_BF16 && !interleaved && intermediate % 8 == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0) {
     const size_t vec = total / 8;
-    const int vblocks = (int)((vec + threads - 1) / threads < 148 * 16 ? (vec + threads - 1) / threads : 148 * 16);
+    const int vblocks = (int)((vec + threads - 1) / threads < rl_num_sms() * 16 ? (vec + threads - 1) / threads : rl_num_sms() * 16);
     rl_launch_pdl(swiglu_bf16x8_kernel, vblocks, threads, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, num_tokens, intermediate);
   } else if (dtype == RL_F32)
     rl_launch_pdl(swiglu_kernel<float>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out, num_tokens, intermediate, interleaved);
@@ -250,7 +250,7 @@ extern "C" int rl_convert(const void* in, int in_dtype, void* out, int out_dtype
   if (n == 0) return RL_OK;
   const int threads = 256;
   const long long want = (n + threads - 1) / threads;
-  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  const int blocks = (int)(want < rl_num_sms() * 16 ? want : rl_num_sms() * 16);
   if (in_dtype == RL_F32 && out_dtype == RL_BF16)
     convert_kernel<<<blocks, threads, 0, stream>>>((const float*)in, (__nv_bfloat16*)out, (size_t)n);
   else if (in_dtype == RL_BF16 && out_dtype == RL_F32)

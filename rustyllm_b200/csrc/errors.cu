@@ -26,6 +26,22 @@ extern "C" int rl_device_arch() {
   return major * 10 + minor;
 }
 
+// Number of SMs of the current device, asked once per device; grids and the choice of split
+// counts are sized by it.  Without a device (a build machine), the B200's 148.
+int rl_num_sms() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return 148; }
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) { cudaGetLastError(); return 148; }
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+extern "C" int rl_sm_count() { return rl_num_sms(); }
+
 int g_rl_pdl_enabled = 1;
 
 // Switch programmatic dependent launch on (1, default) or off (0) for all later launches.

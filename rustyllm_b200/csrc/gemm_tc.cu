@@ -794,16 +794,12 @@ static int launch_tc_persistent(const CUtensorMap& mw, const CUtensorMap& ma, co
                                 void* out, int out_mode, int M, int N, int K, int ldo, int* err, cudaStream_t stream) {
   using Cfg = TcConfig<BT>;
   static bool configured = false;
-  static int num_sms = 0;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     RL_REQUIRE(e == cudaSuccess, "rl_gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
-    int dev = 0;
-    cudaGetDevice(&dev);
-    e = cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-    RL_REQUIRE(e == cudaSuccess && num_sms > 0, "rl_gemm_tc: cannot read the number of SMs");
     configured = true;
   }
+  const int num_sms = rl_num_sms();
   const int tiles_m = (M + BT - 1) / BT, tiles_n = (N + BLOCK_N_OUT - 1) / BLOCK_N_OUT;
   const int total = tiles_m * tiles_n;
   // the tiles behind the last full wave: the narrowest token tile (from 64 tokens: below, the
@@ -938,13 +934,14 @@ extern "C" int rl_gemm_tc_splits(int M, int N, int K) {
   const int bt = token_tile(M);
   const int tiles = ((N + BLOCK_N_OUT - 1) / BLOCK_N_OUT) * ((M + bt - 1) / bt);
   const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+  const int sms = rl_num_sms();
   int splits = 1;
   if (bt > 64) {
-    if (tiles * 4 > 148) return 1;
-    while (splits < 8 && tiles * splits * 2 <= 148 && total_kb / (splits * 2) >= 4) splits *= 2;
+    if (tiles * 4 > sms) return 1;
+    while (splits < 8 && tiles * splits * 2 <= sms && total_kb / (splits * 2) >= 4) splits *= 2;
     return splits;
   }
-  if (tiles >= 148) return 1;
+  if (tiles >= sms) return 1;
   while (splits < 8 && tiles * splits < 256 && total_kb / (splits * 2) >= 4) splits *= 2;
   return splits;
 }

@@ -31,10 +31,9 @@ import time
 from dataclasses import dataclass, field
 from typing import Callable, List, Optional, Sequence
 
+from ..kernels import PAGE_SIZE
 from ..sampling.config import SamplerConfig
 from ..sampling.sampler import SequenceSamplingState
-
-PAGE = 64
 
 
 @dataclass
@@ -48,12 +47,15 @@ class GenerationOptions:
     ignore_eos: bool = False            # benchmarks: run to max_tokens
     max_context: Optional[int] = None   # cap of the context (reference: --max-context)
     run_ahead: bool = True              # queue a step before the host has read the previous one's tokens
+    prefill_step_tokens: int = 16384    # most prompt tokens one step runs (bounds the step's activation memory)
 
     def validate(self) -> None:
         if self.max_tokens <= 0:
             raise ValueError("max_tokens must be greater than 0.")
         if self.max_context is not None and self.max_context <= 0:
             raise ValueError("--max-context must be greater than 0.")
+        if self.prefill_step_tokens <= 0:
+            raise ValueError("prefill_step_tokens must be greater than 0.")
         self.sampler.validate()
         for s in self.stop_sequences:
             if len(s) == 0:
@@ -87,7 +89,7 @@ def _ends_with(seq: List[int], tail: Sequence[int]) -> bool:
 def pages_for(prompt_len: int, max_tokens: int) -> int:
     """Cache pages one request can come to hold: its prompt plus all but the last of
     its generated tokens (the last one is never fed back)."""
-    return -(-(prompt_len + max_tokens - 1) // PAGE)
+    return -(-(prompt_len + max_tokens - 1) // PAGE_SIZE)
 
 
 def plan_batches(prompt_lens: Sequence[int], max_tokens: int, max_batch: int, free_pages: int,
@@ -114,11 +116,63 @@ def plan_batches(prompt_lens: Sequence[int], max_tokens: int, max_batch: int, fr
     return batches
 
 
+def prompt_portions(prompt_lens: Sequence[int], step_tokens: int) -> List[List[tuple]]:
+    """Cut the prompts of a batch, in order, into steps of at most ``step_tokens`` tokens.
+    Each step is a list of ``(sequence, first token, one past the last token)``; a long prompt
+    goes on in the next step where the last one left it, and short prompts share a step."""
+    steps: List[List[tuple]] = []
+    cur: List[tuple] = []
+    room = step_tokens
+    for i, n in enumerate(prompt_lens):
+        at = 0
+        while at < n:
+            take = min(n - at, room)
+            cur.append((i, at, at + take))
+            at += take
+            room -= take
+            if room == 0:
+                steps.append(cur)
+                cur, room = [], step_tokens
+    if cur:
+        steps.append(cur)
+    return steps
+
+
+def run_prompts(engine, slots: Sequence[int], prompts: Sequence[Sequence[int]], step_tokens: int):
+    """The prompts of a batch through the step function, in as few steps as ``step_tokens``
+    allows; returns the logits at every prompt's last token, in the order of the batch.
+    (The reference feeds a prompt in chunks too and takes logits from its last token only,
+    ``prefill_prompt_tokens``, SimonWaldherr/RustyLLM src/runtime.rs:3368-3428.)"""
+    steps = prompt_portions([len(p) for p in prompts], step_tokens)
+    if len(steps) == 1:
+        return engine.step(list(slots), [list(p) for p in prompts], "last")
+    rows = [None] * len(prompts)
+    for portions in steps:
+        want = [[hi - lo - 1] if hi == len(prompts[i]) else [] for i, lo, hi in portions]
+        logits = engine.step([slots[i] for i, _, _ in portions], [list(prompts[i][lo:hi]) for i, lo, hi in portions],
+                             want if any(want) else None)
+        r = 0
+        for (i, _, _), w in zip(portions, want):
+            if w:
+                rows[i] = logits[r]
+                r += 1
+    return _stack_rows(rows)
+
+
+def _stack_rows(rows):
+    first = rows[0]
+    if hasattr(first, "new_empty"):        # device tensors: one [B, V] tensor, as a single step returns
+        import torch
+        return torch.stack(list(rows))
+    return list(rows)
+
+
 def generate_batch(engine, sampler, prompts: Sequence[Sequence[int]], options: GenerationOptions,
                    seeds: Sequence[int], stop_ids: Sequence[int], max_seq_len: int,
                    on_token: Optional[Callable[[int, int], None]] = None,
                    sync: Callable[[], None] = lambda: None) -> List[GenerationResult]:
-    """One batch: its prompts in one step, then one token per live sequence per step."""
+    """One batch: its prompts in one step (or, beyond ``options.prefill_step_tokens`` tokens, in
+    several), then one token per live sequence per step."""
     B = len(prompts)
     t_start = time.perf_counter()
     stop = set(() if options.ignore_eos else stop_ids) | set(options.stop_token_ids)
@@ -135,7 +189,7 @@ def generate_batch(engine, sampler, prompts: Sequence[Sequence[int]], options: G
     try:
         for _ in range(B):
             slots.append(engine.alloc_slot())
-        logits = engine.step(slots, [list(p) for p in prompts], "last")
+        logits = run_prompts(engine, slots, prompts, options.prefill_step_tokens)
         sync()
         t_prefill = time.perf_counter()
         steps = 1

@@ -11,6 +11,7 @@ tokenizer.
 from __future__ import annotations
 
 import os
+import sys
 import threading
 import time
 from dataclasses import dataclass
@@ -19,7 +20,7 @@ from typing import Any, Callable, Dict, List, Mapping, Optional, Sequence, Union
 import torch
 
 from ..cache.sequence_cache import SequenceCache
-from ..config.llama import read_config_json
+from ..config.files import read_config_json, read_generation_stop_ids
 from ..config.registry import resolve_architecture
 from .. import kernels
 from ..kernels import PAGE_SIZE
@@ -55,6 +56,7 @@ class LoadInfo:
     compatibility_time: float = 0.0  # names, shapes and dtypes against the model
     weights_time: float = 0.0        # copies to the device
     runner_time: float = 0.0         # cache and buffers
+    fp32_matrices: int = 0           # matrices kept in 32-bit in a bfloat16 run (slow products)
 
 
 def _require_cuda(device: torch.device) -> None:
@@ -67,8 +69,9 @@ def _require_cuda(device: torch.device) -> None:
 class Runner:
     def __init__(self, config: Any, config_dict: Mapping[str, Any], model: DecoderModel,
                  max_cache_tokens: int, max_batch: int, name: Optional[str] = None,
-                 kv_cache_dtype: Optional[torch.dtype] = None):
+                 kv_cache_dtype: Optional[torch.dtype] = None, extra_stop_ids: Sequence[int] = ()):
         self._config = config
+        self._extra_stop_ids = tuple(extra_stop_ids)
         self.config_dict = dict(config_dict)
         self.model = model
         self.runtime = model.runtime
@@ -85,9 +88,16 @@ class Runner:
     @classmethod
     def from_path(cls, path: str, dtype: Union[str, torch.dtype] = "bfloat16", device: str = "cuda:0",
                   max_cache_tokens: Optional[int] = None, max_batch: int = 64,
-                  max_context: Optional[int] = None):
-        """Load a model folder (config.json + model.safetensors).  Returns
-        ``(runner, load_info)``."""
+                  max_context: Optional[int] = None, keep_fp32_weights: bool = True):
+        """Load a model folder (config.json + model.safetensors; generation_config.json,
+        where there is one, adds its end-of-sequence ids to config.json's).  Returns
+        ``(runner, load_info)``.
+
+        ``keep_fp32_weights`` matters in a bfloat16 run only.  ``True`` (default): a matrix
+        the file stores in 32-bit stays 32-bit, and its products run in 32-bit on the CUDA
+        cores - many times slower than the tensor cores, so ``LoadInfo.fp32_matrices`` counts
+        them and a line on stderr says so.  ``False``: they are rounded to bfloat16 (nearest
+        even) like a bfloat16 file's would have been."""
         t0 = time.perf_counter()
         dev = torch.device(device)
         _require_cuda(dev)
@@ -102,18 +112,28 @@ class Runner:
         from ..weights.loader import check_checkpoint
         check_checkpoint(model.param_specs(), ckpt.entries, spec.ignored_tensors, path)
         t_compat = time.perf_counter()
-        tensors = load_parameters(model.param_specs(), ckpt, compute, dev, spec.ignored_tensors)
+        tensors = load_parameters(model.param_specs(), ckpt, compute, dev, spec.ignored_tensors,
+                                  keep_fp32=keep_fp32_weights)
         model.bind(tensors)
         torch.cuda.synchronize(dev)
         t_weights = time.perf_counter()
         size = ckpt.total_bytes
         ckpt.close()
         runner = cls(config, cfg_dict, model, cls._default_cache_tokens(spec, max_cache_tokens, max_batch, max_context),
-                     max_batch, name=os.path.basename(os.path.normpath(path)))
+                     max_batch, name=os.path.basename(os.path.normpath(path)),
+                     extra_stop_ids=read_generation_stop_ids(path, spec.vocab_size))
         t1 = time.perf_counter()
+        kept = 0
+        if compute != torch.float32:
+            kept = sum(1 for p, ps in model.param_specs().items()
+                       if ps.role in ("matrix", "table") and p in tensors and tensors[p].dtype == torch.float32)
+            if kept:
+                print(f"rustyllm_b200: {kept} matrices of {path!r} are stored in 32-bit and stay 32-bit in this "
+                      f"{dtype} run; their products run on the CUDA cores (keep_fp32_weights=False rounds them)",
+                      file=sys.stderr)
         info = LoadInfo(file_size_bytes=size, load_time=t1 - t0, parse_time=t_parse - t0,
                         compatibility_time=t_compat - t_parse, weights_time=t_weights - t_compat,
-                        runner_time=t1 - t_weights)
+                        runner_time=t1 - t_weights, fp32_matrices=kept)
         return runner, info
 
     @classmethod
@@ -172,8 +192,11 @@ class Runner:
 
     def stop_token_ids(self) -> Sequence[int]:
         """End-of-sequence ids of the model (the reference's ``is_stop_token``,
-        src/runtime.rs:3869-3892, asks its tokenizer; here config.json gives them)."""
-        return tuple(self.model.spec.eos_token_id)
+        src/runtime.rs:3869-3892, asks its tokenizer; here config.json gives them, together
+        with the folder's generation_config.json where it has one)."""
+        ids = list(self.model.spec.eos_token_id)
+        ids.extend(t for t in self._extra_stop_ids if t not in ids)
+        return tuple(ids)
 
     # ------------------------------------------------------------------ lower level
     def new_cache(self, max_tokens: int, max_slots: Optional[int] = None) -> SequenceCache:

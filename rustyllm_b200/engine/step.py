@@ -132,8 +132,10 @@ class Engine:
         for B in sorted(set(int(b) for b in batch_sizes)):
             if B <= 0 or B in self._graphs:
                 continue
-            slots = [self.alloc_slot() for _ in range(B)]
+            slots: List[int] = []
             try:
+                for _ in range(B):                             # one by one: a failure part-way frees those taken
+                    slots.append(self.alloc_slot())
                 self.step(slots, [[0]] * B, None)              # one token each, so that a length exists
                 while B not in self._graphs:                   # an eager step first, then the capture
                     self.step(slots, [[0]] * B, "last")

@@ -34,11 +34,12 @@ def main(argv=None) -> int:
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
+    from ..kernels import PAGE_SIZE
     from .runner import Runner   # late: building the kernels prints progress lines
     os.makedirs(args.out, exist_ok=True)
-    pages = -(-args.max_tokens // 64)
+    pages = -(-args.max_tokens // PAGE_SIZE)     # the cache's own unit is the 64 tokens the option counts in
     runner, _ = Runner.from_path(args.model, dtype=args.dtype, device=args.device,
-                                 max_cache_tokens=pages * 64, max_batch=min(max(pages, 1), 1024))
+                                 max_cache_tokens=pages * PAGE_SIZE, max_batch=min(max(pages, 1), 1024))
     engine = runner.engine
     slot_of: Dict[str, int] = {}
     dev = torch.device(args.device)

@@ -433,7 +433,18 @@ def gemm_tc_qkv_rope(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: 
 
 
 # ----------------------------------------------------------------------------- decode attention
-NUM_SMS = 148
+_num_sms = {}
+
+
+def num_sms() -> int:
+    """SMs of the current device, asked from the device once."""
+    dev = torch.cuda.current_device() if torch.cuda.is_available() else -1
+    if dev not in _num_sms:
+        lib = library()
+        lib.rl_sm_count.restype = _c_int
+        lib.rl_sm_count.argtypes = []
+        _num_sms[dev] = int(lib.rl_sm_count())
+    return _num_sms[dev]
 
 
 def attention_decode_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
@@ -446,7 +457,7 @@ def decode_splits(num_seqs: int, num_kv_heads: int) -> int:
     sequences of 800 and 4,096 tokens).  Depends on the batch's size only, so that a
     captured step keeps its grid."""
     most = 16 if num_seqs == 1 else 8
-    return max(1, min(most, -(-3 * NUM_SMS // (2 * num_seqs * num_kv_heads))))
+    return max(1, min(most, -(-3 * num_sms() // (2 * num_seqs * num_kv_heads))))
 
 
 def decode_scratch_floats(num_seqs: int, num_heads: int, head_dim: int, num_splits: int) -> int:
@@ -606,26 +617,34 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
                    num_heads, num_kv_heads, head_dim, scale, window)
 
 
-MAX_TOP_K = 1024
+from .sampling.config import MAX_TOP_K  # noqa: E402  (one definition, host side)
 
 
 def sample_candidates(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
-                      min_p: torch.Tensor, out: torch.Tensor, topk_rows, topk_k, topk_p, topp_rows, topp_p) -> None:
-    """Rows that sample from a candidate set.  ``topk_rows`` (host list of row indices)
-    with their ``topk_k`` and ``topk_p`` take the top-k path; ``topp_rows`` with
-    ``topp_p`` the top-p path over the whole vocabulary.  temperature / uniform /
-    min_p / out are indexed by logits row."""
+                      min_p: torch.Tensor, out: torch.Tensor,
+                      topk_rows: Optional[torch.Tensor], topk_k: Optional[torch.Tensor], topk_p: Optional[torch.Tensor],
+                      topp_rows: Optional[torch.Tensor], topp_p: Optional[torch.Tensor]) -> None:
+    """Rows that sample from a candidate set.  ``topk_rows`` (int32 row indices, on the
+    device) with their ``topk_k`` (int32, each at most ``MAX_TOP_K``) and ``topk_p`` (float32)
+    take the top-k path; ``topp_rows`` with ``topp_p`` the top-p path over the whole
+    vocabulary; ``None`` = no such rows.  temperature / uniform / min_p / out are indexed by
+    logits row."""
     _need(logits, "logits", torch.float32); _need(out, "out", torch.int32)
     _need(temperature, "temperature", torch.float32); _need(uniform, "uniform", torch.float32)
     _need(min_p, "min_p", torch.float32)
-    if any(k > MAX_TOP_K for k in topk_k):
-        raise KernelError(f"top_k up to {MAX_TOP_K} is supported on the device, got {max(topk_k)}")
-    dev = logits.device
-    i32 = lambda x: torch.tensor(list(x) or [0], dtype=torch.int32, device=dev)
-    f32 = lambda x: torch.tensor(list(x) or [0.0], dtype=torch.float32, device=dev)
-    rk, kk, pk, rp, pp = i32(topk_rows), i32(topk_k), f32(topk_p), i32(topp_rows), f32(topp_p)
-    _check(library().rl_sample_candidates(logits.data_ptr(), logits.shape[1], rk.data_ptr(), kk.data_ptr(), pk.data_ptr(),
-                                          len(topk_rows), rp.data_ptr(), pp.data_ptr(), len(topp_rows),
+    n_k = n_p = 0
+    if topk_rows is not None:
+        _need(topk_rows, "topk_rows", torch.int32); _need(topk_k, "topk_k", torch.int32); _need(topk_p, "topk_p", torch.float32)
+        n_k = topk_rows.numel()
+        assert topk_k.numel() == n_k and topk_p.numel() == n_k
+    if topp_rows is not None:
+        _need(topp_rows, "topp_rows", torch.int32); _need(topp_p, "topp_p", torch.float32)
+        n_p = topp_rows.numel()
+        assert topp_p.numel() == n_p
+    if n_k == 0 and n_p == 0:
+        return
+    _check(library().rl_sample_candidates(logits.data_ptr(), logits.shape[1], _ptr(topk_rows), _ptr(topk_k), _ptr(topk_p),
+                                          n_k, _ptr(topp_rows), _ptr(topp_p), n_p,
                                           temperature.data_ptr(), uniform.data_ptr(), min_p.data_ptr(), out.data_ptr(),
                                           _stream()), "rl_sample_candidates")
-    _count((1 if topk_rows else 0) + (1 if topp_rows else 0))
+    _count((1 if n_k else 0) + (1 if n_p else 0))

@@ -12,6 +12,7 @@ import math
 from dataclasses import dataclass
 
 RECENT_TOKEN_LIMIT = 64   # window of the repeat penalty, src/runtime.rs:493
+MAX_TOP_K = 1024          # the device's top-k kernel sorts its candidates in shared memory
 
 
 @dataclass
@@ -42,6 +43,11 @@ class SamplerConfig:
             raise ValueError("min_p must be in the range [0, 1).")
         if self.top_k < 0:
             raise ValueError("top_k must be >= 0.")
+        if self.top_k > MAX_TOP_K and not self.is_greedy:
+            # the reference takes any 0 < top_k < vocabulary (src/sampling.rs:87); here the candidate
+            # set is sorted on the device in shared memory, which bounds it.  Said before a generation
+            # starts rather than after its prompt step has run.
+            raise ValueError(f"top_k must be at most {MAX_TOP_K} (or 0 for no top-k filter), got {self.top_k}.")
 
     @property
     def is_greedy(self) -> bool:

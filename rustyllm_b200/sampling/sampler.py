@@ -109,22 +109,29 @@ class Sampler:
         topk = [b for b, s in enumerate(states) if takes_top_k(s.config)]
         topp = [b for b, s in enumerate(states)
                 if not s.config.is_greedy and not takes_top_k(s.config) and s.config.top_p < 1.0]
-        # one float upload: temperature | uniform | min_p
-        f = np.zeros((3, B), dtype=np.float32)
+        # one float upload: temperature | uniform | min_p | top-p of the top-k rows | top-p of the top-p rows
+        nk, np_ = len(topk), len(topp)
+        f = np.zeros(3 * B + nk + np_, dtype=np.float32)
         for b, s in enumerate(states):
             c = s.config
             greedy = c.is_greedy
-            f[0, b] = 0.0 if greedy else c.temperature
-            f[1, b] = 0.0 if greedy else s.rng.next_f32()
-            f[2, b] = c.min_p
+            f[b] = 0.0 if greedy else c.temperature
+            f[B + b] = 0.0 if greedy else s.rng.next_f32()
+            f[2 * B + b] = c.min_p
+        f[3 * B:3 * B + nk] = [states[b].config.top_p for b in topk]
+        f[3 * B + nk:] = [states[b].config.top_p for b in topp]
         fd = self._floats.upload(f)
+        temperature, uniform, min_p = fd[:B], fd[B:2 * B], fd[2 * B:3 * B]
         # every row goes through the softmax kernel (greedy rows are answered there too);
         # rows with a candidate set are then answered again by their own kernel
-        K.sample_temperature(logits, fd[0], fd[1], out, fd[2] if f[2].any() else None)
+        K.sample_temperature(logits, temperature, uniform, out, min_p if f[2 * B:3 * B].any() else None)
         if topk or topp:
-            K.sample_candidates(logits, fd[0], fd[1], fd[2], out,
-                                topk, [states[b].config.top_k for b in topk], [states[b].config.top_p for b in topk],
-                                topp, [states[b].config.top_p for b in topp])
+            # one int upload from pinned memory: rows of the top-k path | their k | rows of the top-p path
+            idx = self._ints.upload(np.asarray(topk + [states[b].config.top_k for b in topk] + topp, dtype=np.int32))
+            K.sample_candidates(logits, temperature, uniform, min_p, out,
+                                idx[:nk] if nk else None, idx[nk:2 * nk] if nk else None,
+                                fd[3 * B:3 * B + nk] if nk else None,
+                                idx[2 * nk:] if np_ else None, fd[3 * B + nk:] if np_ else None)
         return out
 
 

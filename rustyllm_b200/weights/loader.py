@@ -9,7 +9,8 @@ missing tensor (src/model.rs:3208), this loader collects everything that is wron
 ``WeightsError``.
 
 Run-time dtypes: matrices and tables take the compute dtype of the run, except
-that a tensor the file stores as 32-bit float stays 32-bit; vectors used in
+that a tensor the file stores as 32-bit float stays 32-bit (unless the caller asks
+for it to be rounded: ``keep_fp32=False``); vectors used in
 32-bit math (norm weights, biases) are always float32; integer tables are int32.
 Q/K/V and gate/up are concatenated along the rows so one matrix product serves
 each (the reference goes the other way and splits fused tensors by rows,
@@ -52,15 +53,17 @@ class WeightsError(ValueError):
         super().__init__("\n".join(lines))
 
 
-def runtime_dtype(role: str, file_dtype: torch.dtype, compute_dtype: torch.dtype) -> torch.dtype:
+def runtime_dtype(role: str, file_dtype: torch.dtype, compute_dtype: torch.dtype,
+                  keep_fp32: bool = True) -> torch.dtype:
     if role == "int_table":
         return torch.int32
     if role == "vector":
         return torch.float32
     if compute_dtype == torch.float32:
         return torch.float32
-    # reduced-precision run: a tensor stored in 32-bit (or wider) stays 32-bit
-    if file_dtype in (torch.float32, torch.float64):
+    # reduced-precision run: a tensor stored in 32-bit (or wider) stays 32-bit unless the
+    # caller asked for it to be rounded
+    if keep_fp32 and file_dtype in (torch.float32, torch.float64):
         return torch.float32
     return compute_dtype
 
@@ -111,8 +114,9 @@ def check_checkpoint(params: Mapping[str, ParamSpec], entries: Mapping[str, obje
 
 def load_parameters(params: Mapping[str, ParamSpec], checkpoint: Checkpoint,
                     compute_dtype: torch.dtype, device: torch.device,
-                    ignored: Iterable[str] = ()) -> Dict[str, torch.Tensor]:
-    """Check first, then copy: returns ``{parameter path: device tensor}``."""
+                    ignored: Iterable[str] = (), keep_fp32: bool = True) -> Dict[str, torch.Tensor]:
+    """Check first, then copy: returns ``{parameter path: device tensor}``.  ``keep_fp32``:
+    whether a matrix stored in 32-bit stays 32-bit in a reduced-precision run."""
     check_checkpoint(params, checkpoint.entries, ignored, checkpoint.model_dir)
     out: Dict[str, torch.Tensor] = {}
     aliases: List[Tuple[str, str]] = []
@@ -125,7 +129,7 @@ def load_parameters(params: Mapping[str, ParamSpec], checkpoint: Checkpoint,
         file_dtypes = {checkpoint.entries[s.name].dtype for s in ps.sources}
         widest = torch.float32 if (torch.float32 in file_dtypes or torch.float64 in file_dtypes) \
             else next(iter(file_dtypes))
-        dt = runtime_dtype(ps.role, widest, compute_dtype)
+        dt = runtime_dtype(ps.role, widest, compute_dtype, keep_fp32)
         dest = torch.empty(ps.shape, dtype=dt, device=device)
         for i, s in enumerate(ps.sources):
             t = checkpoint.tensor(s.name)

@@ -42,3 +42,19 @@ def test_inspect_and_list_tensors(model_dirs, capsys):
     out = capsys.readouterr().out
     assert "architecture: LlamaForCausalLM" in out and "compatibility: supported" in out
     assert "model.layers.2.mlp.down_proj.weight" in out and "hidden_size: 96" in out
+
+
+def test_benchmark_prompt_lengths_and_other_spellings():
+    import random
+    p = cli.build_parser()
+    a = p.parse_args(["m", "--json", "--runs", "2", "--batch", "16", "--prompt-len-range", "64,1024",
+                      "--decode-tokens", "256", "--context", "2048", "--seed", "3"])
+    assert a.bench_json and a.bench_runs == 2 and a.max_tokens == 256 and a.max_context == 2048
+    lens = cli.synthetic_prompt_lengths(a, random.Random(3))
+    assert len(lens) == 16 and all(64 <= n < 1024 for n in lens) and len(set(lens)) > 8
+    assert lens == cli.synthetic_prompt_lengths(a, random.Random(3))        # seeded
+    a = p.parse_args(["m", "--bench", "--batch", "3", "--prompt-len", "40"])
+    assert cli.synthetic_prompt_lengths(a, random.Random(1)) == [40, 40, 40]
+    for bad in ("5", "9,3", "0,4", "a,b"):
+        with pytest.raises(SystemExit):
+            cli.synthetic_prompt_lengths(p.parse_args(["m", "--bench", "--prompt-len-range", bad]), random.Random(1))

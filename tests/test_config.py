@@ -80,3 +80,24 @@ def test_round_trip_to_dict():
     for t in TINY.values():
         c = LlamaConfig.from_dict(t["config"])
         assert LlamaConfig.from_dict(c.to_dict()) == c
+
+
+def test_generation_config_adds_its_stop_ids(tmp_path):
+    """Instruction-tuned folders name their end-of-turn ids in generation_config.json."""
+    import json
+    from rustyllm_b200.config.files import read_config_json, read_generation_stop_ids
+    d = tmp_path / "m"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(dict(TINY["A"]["config"])))
+    assert read_config_json(str(d))["eos_token_id"] == 255
+    assert read_generation_stop_ids(str(d), 256) == ()            # no such file: nothing to add
+    (d / "generation_config.json").write_text(json.dumps({"eos_token_id": [255, 7, 9], "temperature": 0.6}))
+    assert read_generation_stop_ids(str(d), 256) == (255, 7, 9)
+    (d / "generation_config.json").write_text(json.dumps({"eos_token_id": 3}))
+    assert read_generation_stop_ids(str(d), 256) == (3,)
+    (d / "generation_config.json").write_text(json.dumps({"eos_token_id": 256}))
+    with pytest.raises(ConfigError, match="outside the vocabulary"):
+        read_generation_stop_ids(str(d), 256)
+    (d / "generation_config.json").write_text("[1, 2]")
+    with pytest.raises(ConfigError, match="object"):
+        read_generation_stop_ids(str(d), 256)

@@ -2,7 +2,8 @@
 import pytest
 import torch
 
-from rustyllm_b200.engine.generate import (GenerationOptions, generate_batch, pages_for, plan_batches)
+from rustyllm_b200.engine.generate import (GenerationOptions, generate_batch, pages_for, plan_batches,
+                                           prompt_portions)
 from rustyllm_b200.sampling.config import Rng, SamplerConfig
 
 
@@ -26,13 +27,15 @@ class ScriptedEngine:
         self.free.append(s)
 
     def step(self, slots, tokens, want):
-        assert want == "last"
         self.calls.append((list(slots), [list(t) for t in tokens]))
         rows = []
-        for s, t in zip(slots, tokens):
+        for b, (s, t) in enumerate(zip(slots, tokens)):
             self.held[s].extend(t)
-            rows.append(self.script(self.held[s]))
-        return torch.tensor(rows)
+            if want == "last" or (want is not None and want[b] == [len(t) - 1]):
+                rows.append(self.script(self.held[s]))
+            else:
+                assert want is None or want[b] == [], "a prompt portion wants its last token or nothing"
+        return torch.tensor(rows) if rows else None
 
 
 class PickSampler:
@@ -134,6 +137,34 @@ def test_context_limit_ends_a_sequence():
     assert sum(len(t[0]) for _, t in eng.calls) == 5
 
 
+def test_prompts_are_cut_into_steps_of_bounded_size():
+    assert prompt_portions([5, 3], 100) == [[(0, 0, 5), (1, 0, 3)]]
+    assert prompt_portions([5, 3], 4) == [[(0, 0, 4)], [(0, 4, 5), (1, 0, 3)]]
+    assert prompt_portions([2, 7, 1], 3) == [[(0, 0, 2), (1, 0, 1)], [(1, 1, 4)], [(1, 4, 7)], [(2, 0, 1)]]
+    for lens, n in (([64, 130, 1], 64), ([9, 9, 9], 1), ([1], 5)):
+        steps = prompt_portions(lens, n)
+        assert all(0 < sum(hi - lo for _, lo, hi in st) <= n for st in steps)
+        for i, total in enumerate(lens):      # every token once, in order
+            mine = [(lo, hi) for st in steps for j, lo, hi in st if j == i]
+            assert mine[0][0] == 0 and mine[-1][1] == total
+            assert all(a[1] == b[0] for a, b in zip(mine, mine[1:]))
+
+
+@pytest.mark.parametrize("step_tokens", [1, 2, 3, 64])
+def test_a_prompt_step_in_portions_changes_nothing(step_tokens):
+    script = lambda held: 99 if len(held) >= 9 else sum(held) % 50
+    prompts = [[5, 6, 7], [1], [2, 3, 4, 5, 6], [8, 8]]
+    _, whole, seen_whole = run(script, prompts, max_tokens=6)
+    eng, res, seen = run(script, prompts, max_tokens=6, prefill_step_tokens=step_tokens)
+    assert [r.token_ids for r in res] == [r.token_ids for r in whole]
+    assert [r.finish_reason for r in res] == [r.finish_reason for r in whole] and seen == seen_whole
+    fed = [sum(len(t) for t in c[1]) for c in eng.calls]
+    n_prompt_steps = -(-sum(len(p) for p in prompts) // step_tokens) if step_tokens < 11 else 1
+    assert all(f <= max(step_tokens, len(prompts)) for f in fed[:n_prompt_steps])
+    with pytest.raises(ValueError, match="prefill_step_tokens"):
+        GenerationOptions(prefill_step_tokens=0).validate()
+
+
 SCENARIOS = [
     (lambda held: len(held), [[5, 6, 7]], dict(max_tokens=4)),
     (lambda held: 99 if len(held) == 5 else 10 + len(held), [[1, 2, 3]], dict(max_tokens=10)),
@@ -194,6 +225,11 @@ def test_options_are_validated_like_the_reference():
         GenerationOptions(sampler=SamplerConfig(repeat_penalty=0.0)).validate()
     with pytest.raises(ValueError, match="temperature"):
         GenerationOptions(sampler=SamplerConfig(temperature=-1.0)).validate()
+    # the device sorts at most 1,024 candidates: said before a generation starts, not in its middle
+    with pytest.raises(ValueError, match="top_k must be at most 1024"):
+        GenerationOptions(sampler=SamplerConfig(top_k=1025)).validate()
+    GenerationOptions(sampler=SamplerConfig(top_k=1024)).validate()
+    GenerationOptions(sampler=SamplerConfig(temperature=0.0, top_k=5000)).validate()    # greedy: no candidate set
 
 
 def test_batches_are_cut_by_slots_and_by_pages():

@@ -133,6 +133,11 @@ def test_float32_file_in_a_bf16_run_stays_32_bit(tmp_path):
     p = load_parameters(model.param_specs(), Checkpoint(d), torch.bfloat16, CPU, spec.ignored_tensors)
     assert p["layers.0.mixer.wqkv"].dtype == torch.float32
     assert p["embedding.weight"].dtype == torch.float32
+    # rounded to the compute dtype only when asked (nearest even, as a bfloat16 file would hold them)
+    r = load_parameters(model.param_specs(), Checkpoint(d), torch.bfloat16, CPU, spec.ignored_tensors, keep_fp32=False)
+    assert r["layers.0.mixer.wqkv"].dtype == torch.bfloat16 and r["embedding.weight"].dtype == torch.bfloat16
+    assert torch.equal(r["embedding.weight"], p["embedding.weight"].to(torch.bfloat16))
+    assert r["layers.0.mixer_norm.weight"].dtype == torch.float32       # vectors stay 32-bit either way
 
 
 def test_random_folder_is_reproducible_and_seeded(tmp_path):
