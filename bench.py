@@ -117,6 +117,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true", help="only the batch given (no batch 1 / 64 points)")
+    ap.add_argument("--skip-cpu-baseline", action="store_true", help="do not time the CPU baseline (vs_baseline stays null)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -237,10 +238,26 @@ def main():
     h2d_per_step = (7 * args.batch + 1) * 4 + 3 * args.batch * 4
     kernels.check_device_errors()
 
+    # ---- the CPU baseline: this library's plain C++ float32 decoder at the same widths and depth ----
+    # The reference cannot be built here (no Rust toolchain) and publishes no number for this
+    # configuration, so the baseline is our own CPU restatement of its formulas, timed on this
+    # machine's host cores.  Like the reference it has no batching: its tokens a second are the same
+    # for one request or for eight one after another.
+    cpu = None
+    if not args.skip_cpu_baseline:
+        del runner, eng
+        torch.cuda.empty_cache()
+        try:
+            from rustyllm_b200 import baseline
+            cpu = baseline.time_decode(dict(cfg, num_hidden_layers=layers), distinct_layers=min(2, layers), context=4, tokens=4)
+        except Exception as e:      # a host without g++ or OpenMP: the GPU numbers stand without it
+            cpu = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+
     out = {
         "metric": "Llama-3.1-8B decode tok/s at batch 8 (bf16, random weights, context 4096)",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": (value / cpu["tokens_per_s"]) if cpu and "tokens_per_s" in cpu else None,
         "dtype": "bf16", "data": "synthetic (seeded random token ids, random-init weights N(0, 0.02))",
         "impl": "ours",
         "config": {"model": "Llama-3.1-8B shape", "layers": layers, "layers_of_config": full_layers,
@@ -260,6 +277,7 @@ def main():
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / peaks["hbm_gbs"]},
         "points": points,
+        "cpu_baseline": cpu,
         "clocks": clock_info,
     }
     print(json.dumps(out))
