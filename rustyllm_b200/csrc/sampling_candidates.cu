@@ -13,9 +13,10 @@
 //     nucleus is found by a radix selection on the weights' bit patterns with exact
 //     (fixed-point) bin sums: the smallest set of highest weights whose sum exceeds
 //     top_p * sum(all), ties at the boundary to the lower index; min-p then drops
-//     w < min_p.  The draw walks the kept tokens in index order (the reference walks
-//     them in descending weight; the distribution is the same, the token a given
-//     uniform maps to is not).
+//     w < min_p.  The draw walks the kept tokens by descending weight like the
+//     reference's, by the same selection run to the sum u * kept.  Sums are exact
+//     integers (2^-40 of the top weight) where the reference adds float32 in sorted
+//     order, so a uniform within float rounding of a boundary may map to the neighbour.
 #include <math.h>
 
 #include "common.cuh"
@@ -176,155 +177,160 @@ sample_topk_kernel(const float* __restrict__ logits, int vocab, const int* __res
 // ------------------------------------------------------------------ top-p over the vocabulary
 #define FX_ONE 1099511627776.0f   // 2^40: fixed-point scale of a weight in [0, 1]
 
-__global__ void __launch_bounds__(CAND_THREADS)
-sample_topp_kernel(const float* __restrict__ logits, int vocab, const int* __restrict__ rows,
-                   const float* __restrict__ temperature, const float* __restrict__ uniform,
-                   const float* __restrict__ min_p, const float* __restrict__ top_p, int* __restrict__ out) {
-  __shared__ unsigned long long hsum[256];
-  __shared__ uint32_t hcnt[256];
-  __shared__ float seg_sum[CAND_THREADS];
-  __shared__ int seg_eq[CAND_THREADS];
-  __shared__ float red[CAND_THREADS / 32];
-  __shared__ unsigned long long s_total, s_above;
-  __shared__ uint32_t s_prefix;
-  __shared__ int s_need_eq, s_seg;
-  __shared__ float s_max, s_kept, s_front;
-  const int row = rows[blockIdx.x];
-  const float* l = logits + (size_t)row * vocab;
+struct ToppShared {
+  unsigned long long hsum[256];
+  uint32_t hcnt[256];
+  int seg_eq[CAND_THREADS];
+  float red[CAND_THREADS / 32];
+  unsigned long long total, above, kept;
+  uint32_t prefix;
+  int need_eq;
+  float max;
+};
+
+// Walks the vocabulary's weights from the highest down (ties: lower index first) until their
+// running sum exceeds thr, without sorting: a radix selection on the weights' bit patterns,
+// 8 bits a pass, with exact fixed-point sums per bin.  Leaves in sh.prefix the weight (as
+// bits) of the token at which the sum crosses thr, in sh.need_eq which of the tokens of that
+// weight it is (1 = the first by index), in sh.above the sum of all greater weights.  If the
+// whole sum does not exceed thr, it is the last token of the order.  All threads call it.
+__device__ void topp_walk(const float* __restrict__ l, int vocab, float inv_temp, float mx,
+                          unsigned long long thr, ToppShared& sh) {
   const int tid = threadIdx.x;
-  const float inv_temp = 1.0f / temperature[row];
-  const float cut = min_p[row];
-
-  float mx = -INFINITY;
-  for (int i = tid; i < vocab; i += CAND_THREADS) mx = fmaxf(mx, cand_finite(l[i]) * inv_temp);
-  mx = rl_warp_max(mx);
-  if ((tid & 31) == 0) red[tid >> 5] = mx;
-  if (tid == 0) s_total = 0ull;
-  __syncthreads();
-  if (tid == 0) {
-    float t = red[0];
-    for (int w = 1; w < CAND_THREADS / 32; ++w) t = fmaxf(t, red[w]);
-    s_max = t;
-  }
-  __syncthreads();
-  mx = s_max;
-  if (!(mx > -INFINITY)) { if (tid == 0) out[row] = 0; return; }
-
-  // total weight, exactly (integer sums do not depend on the order)
-  unsigned long long mine = 0ull;
-  for (int i = tid; i < vocab; i += CAND_THREADS)
-    mine += (unsigned long long)(expf(cand_finite(l[i]) * inv_temp - mx) * FX_ONE);
-  atomicAdd(&s_total, mine);
-  __syncthreads();
-  const unsigned long long thr = (unsigned long long)((double)top_p[blockIdx.x] * (double)s_total);
-
-  // radix selection of the boundary weight: highest weights first until the sum exceeds thr
-  if (tid == 0) { s_prefix = 0; s_above = 0ull; }
+  if (tid == 0) { sh.prefix = 0; sh.above = 0ull; }
   uint32_t mask = 0;
   for (int pass = 0; pass < 4; ++pass) {
     const int shift = 24 - 8 * pass;
-    if (tid < 256) { hsum[tid] = 0ull; hcnt[tid] = 0u; }
+    if (tid < 256) { sh.hsum[tid] = 0ull; sh.hcnt[tid] = 0u; }
     __syncthreads();
-    const uint32_t prefix = s_prefix;
+    const uint32_t prefix = sh.prefix;
     for (int i = tid; i < vocab; i += CAND_THREADS) {
       const float w = expf(cand_finite(l[i]) * inv_temp - mx);
       const uint32_t key = __float_as_uint(w);      // w >= 0: bit order is value order
       if ((key & mask) == prefix) {
         const uint32_t b = (key >> shift) & 255u;
-        atomicAdd(&hsum[b], (unsigned long long)(w * FX_ONE));
-        atomicAdd(&hcnt[b], 1u);
+        atomicAdd(&sh.hsum[b], (unsigned long long)(w * FX_ONE));
+        atomicAdd(&sh.hcnt[b], 1u);
       }
     }
     __syncthreads();
     if (tid == 0) {
-      unsigned long long above = s_above;
+      unsigned long long above = sh.above;
       int chosen = -1, lowest = 0;
       for (int b = 255; b >= 0; --b) {
-        if (hcnt[b] == 0u) continue;
+        if (sh.hcnt[b] == 0u) continue;
         lowest = b;
-        if (above + hsum[b] > thr) { chosen = b; break; }
-        above += hsum[b];
+        if (above + sh.hsum[b] > thr) { chosen = b; break; }
+        above += sh.hsum[b];
       }
-      if (chosen < 0) { chosen = lowest; above -= hsum[lowest]; }   // rounding: everything is kept
-      s_above = above;
-      s_prefix = prefix | ((uint32_t)chosen << shift);
+      if (chosen < 0) { chosen = lowest; above -= sh.hsum[lowest]; }   // rounding: the whole order is walked
+      sh.above = above;
+      sh.prefix = prefix | ((uint32_t)chosen << shift);
       if (pass == 3) {
-        const float wT = __uint_as_float(s_prefix);
+        const float wT = __uint_as_float(sh.prefix);
         const unsigned long long fxT = (unsigned long long)(wT * FX_ONE);
-        long long n = (fxT == 0ull || thr < above) ? (long long)hcnt[chosen] : (long long)((thr - above) / fxT) + 1;
-        if (n > (long long)hcnt[chosen]) n = hcnt[chosen];
+        long long n = (fxT == 0ull || thr < above) ? (long long)sh.hcnt[chosen] : (long long)((thr - above) / fxT) + 1;
+        if (n > (long long)sh.hcnt[chosen]) n = sh.hcnt[chosen];
         if (n < 1) n = 1;
-        s_need_eq = (int)n;
+        sh.need_eq = (int)n;
       }
     }
     mask |= 255u << shift;
     __syncthreads();
   }
-  const uint32_t T = s_prefix;
-  const int need_eq = s_need_eq;
+}
 
-  // kept weights per contiguous segment, then the draw in index order
-  const int seg = (vocab + CAND_THREADS - 1) / CAND_THREADS;
-  const int lo = tid * seg, hi = min(lo + seg, vocab);
+// How many tokens of weight bits T lie in front of each thread's contiguous segment of the
+// vocabulary (so that "the n-th such token by index" can be told segment by segment).
+__device__ int topp_rank_of_segment(const float* __restrict__ l, int lo, int hi, float inv_temp, float mx, uint32_t T,
+                                    ToppShared& sh) {
+  const int tid = threadIdx.x;
   int eq = 0;
   for (int i = lo; i < hi; ++i)
     if (__float_as_uint(expf(cand_finite(l[i]) * inv_temp - mx)) == T) ++eq;
-  seg_eq[tid] = eq;
+  __syncthreads();
+  sh.seg_eq[tid] = eq;
   __syncthreads();
   if (tid == 0) {
     int c = 0;
-    for (int t = 0; t < CAND_THREADS; ++t) { const int e = seg_eq[t]; seg_eq[t] = c; c += e; }
+    for (int t = 0; t < CAND_THREADS; ++t) { const int e = sh.seg_eq[t]; sh.seg_eq[t] = c; c += e; }
   }
   __syncthreads();
-  const int rank0 = seg_eq[tid];
-  float sum = 0.f;
-  {
-    int rank = rank0;
-    for (int i = lo; i < hi; ++i) {
-      const float w = expf(cand_finite(l[i]) * inv_temp - mx);
-      const uint32_t key = __float_as_uint(w);
-      bool kept = key > T;
-      if (key == T) { kept = rank < need_eq; ++rank; }
-      if (kept && w >= cut) sum += w;
-    }
-  }
-  seg_sum[tid] = sum;
+  return sh.seg_eq[tid];
+}
+
+__global__ void __launch_bounds__(CAND_THREADS)
+sample_topp_kernel(const float* __restrict__ logits, int vocab, const int* __restrict__ rows,
+                   const float* __restrict__ temperature, const float* __restrict__ uniform,
+                   const float* __restrict__ min_p, const float* __restrict__ top_p, int* __restrict__ out) {
+  __shared__ ToppShared sh;
+  const int row = rows[blockIdx.x];
+  const float* l = logits + (size_t)row * vocab;
+  const int tid = threadIdx.x;
+  const float inv_temp = 1.0f / temperature[row];
+
+  float mx = -INFINITY;
+  for (int i = tid; i < vocab; i += CAND_THREADS) mx = fmaxf(mx, cand_finite(l[i]) * inv_temp);
+  mx = rl_warp_max(mx);
+  if ((tid & 31) == 0) sh.red[tid >> 5] = mx;
+  if (tid == 0) { sh.total = 0ull; sh.kept = 0ull; }
   __syncthreads();
   if (tid == 0) {
-    float total = 0.f;
-    for (int t = 0; t < CAND_THREADS; ++t) total += seg_sum[t];
-    s_kept = total;
-    const float r = uniform[row] * total;
-    float c = 0.f;
-    int chosen = -1, last = 0;
-    for (int t = 0; t < CAND_THREADS; ++t) {
-      if (seg_sum[t] > 0.f) last = t;
-      const float incl = c + seg_sum[t];
-      if (incl > r && seg_sum[t] > 0.f) { chosen = t; break; }
-      c = incl;
-    }
-    if (chosen < 0) { chosen = last; c -= seg_sum[last]; }
-    s_seg = chosen;
-    s_front = c;
+    float t = sh.red[0];
+    for (int w = 1; w < CAND_THREADS / 32; ++w) t = fmaxf(t, sh.red[w]);
+    sh.max = t;
   }
   __syncthreads();
-  if (!(s_kept > 0.f) || !isfinite(s_kept)) { if (tid == 0) out[row] = 0; return; }
-  if (tid == s_seg) {
-    const float r = uniform[row] * s_kept;
-    float c = s_front;
-    int rank = rank0, answer = -1, last = lo;
+  mx = sh.max;
+  if (!(mx > -INFINITY)) { if (tid == 0) out[row] = 0; return; }
+  // the highest weight is exp(0) = 1, so the reference's cut `w < min_p * w_max` is `w < min_p`
+  const float cut = min_p[row];
+
+  // total weight, exactly (integer sums do not depend on the order)
+  unsigned long long mine = 0ull;
+  for (int i = tid; i < vocab; i += CAND_THREADS)
+    mine += (unsigned long long)(expf(cand_finite(l[i]) * inv_temp - mx) * FX_ONE);
+  atomicAdd(&sh.total, mine);
+  __syncthreads();
+
+  // 1. the nucleus: the head of the order whose sum first exceeds top_p * total
+  topp_walk(l, vocab, inv_temp, mx, (unsigned long long)((double)top_p[blockIdx.x] * (double)sh.total), sh);
+  const uint32_t T = sh.prefix;
+  const int need_eq = sh.need_eq;
+  const int seg = (vocab + CAND_THREADS - 1) / CAND_THREADS;
+  const int lo = min(tid * seg, vocab), hi = min(lo + seg, vocab);
+  {
+    // its weight, exactly, without what min-p drops (tokens below the cut are its tail)
+    int rank = topp_rank_of_segment(l, lo, hi, inv_temp, mx, T, sh);
+    unsigned long long sum = 0ull;
     for (int i = lo; i < hi; ++i) {
       const float w = expf(cand_finite(l[i]) * inv_temp - mx);
       const uint32_t key = __float_as_uint(w);
       bool kept = key > T;
       if (key == T) { kept = rank < need_eq; ++rank; }
-      if (kept && w >= cut && w > 0.f) {
-        last = i;
-        c += w;
-        if (c > r) { answer = i; break; }
-      }
+      if (kept && w >= cut) sum += (unsigned long long)(w * FX_ONE);
     }
-    out[row] = answer >= 0 ? answer : last;
+    if (sum) atomicAdd(&sh.kept, sum);
+  }
+  __syncthreads();
+  const unsigned long long kept = sh.kept;
+  if (kept == 0ull) { if (tid == 0) out[row] = 0; return; }
+
+  // 2. the draw: the reference walks the kept tokens by descending weight until the running sum
+  // exceeds u * kept (src/sampling.rs:186-209) - the same walk as the nucleus's, to another sum.
+  // What it crosses at lies inside the kept head, because u * kept < kept.
+  unsigned long long r = (unsigned long long)((double)uniform[row] * (double)kept);
+  if (r >= kept) r = kept - 1;
+  topp_walk(l, vocab, inv_temp, mx, r, sh);
+  const uint32_t T2 = sh.prefix;
+  const int nth = sh.need_eq;
+  const int rank0 = topp_rank_of_segment(l, lo, hi, inv_temp, mx, T2, sh);
+  int rank = rank0;
+  for (int i = lo; i < hi; ++i) {
+    if (__float_as_uint(expf(cand_finite(l[i]) * inv_temp - mx)) == T2) {
+      ++rank;
+      if (rank == nth) { out[row] = i; break; }
+    }
   }
 }
 

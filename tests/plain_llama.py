@@ -132,15 +132,17 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     scale = 1.0 / math.sqrt(hd)
     out = torch.empty_like(q)
     t_idx = torch.arange(T)
-    allowed = t_idx[None, :] <= t_idx[:, None]
-    if window is not None and window > 0:
-        allowed &= t_idx[None, :] >= (t_idx[:, None] + 1 - window)
-    for h in range(H):
-        g = h // m
-        s = (q[:, h, :] @ k[:, g, :].T) * scale
-        s = s.masked_fill(~allowed, float("-inf"))
-        p = torch.softmax(s, dim=-1)
-        out[:, h, :] = p @ v[:, g, :]
+    for lo in range(0, T, 1024):          # query rows in blocks, only to bound the score matrix's memory
+        rows = t_idx[lo:lo + 1024]
+        allowed = t_idx[None, :] <= rows[:, None]
+        if window is not None and window > 0:
+            allowed &= t_idx[None, :] >= (rows[:, None] + 1 - window)
+        for h in range(H):
+            g = h // m
+            s = (q[lo:lo + 1024, h, :] @ k[:, g, :].T) * scale
+            s = s.masked_fill(~allowed, float("-inf"))
+            p = torch.softmax(s, dim=-1)
+            out[lo:lo + 1024, h, :] = p @ v[:, g, :]
     return out
 
 

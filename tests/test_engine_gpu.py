@@ -8,7 +8,7 @@ from gpu_helpers import assert_close_logits, load_runner, plain_logits, random_t
 
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
-CONFIGS = ["A", "B", "C", "D", "E"]
+CONFIGS = ["A", "B", "C", "D", "E", "H"]
 
 
 def _vocab(cfg):

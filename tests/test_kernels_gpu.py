@@ -396,6 +396,75 @@ def test_gemm_tc_qkv_rope_is_the_product_then_the_rotation_and_the_cache_write(M
     assert torch.equal(v_pool.permute(0, 2, 1, 3)[keep], v_before.permute(0, 2, 1, 3)[keep])
 
 
+def _llama3_inv_freq(hd, factor):
+    return P.rope_inv_freq(500000.0, hd, {"rope_type": "llama3", "factor": factor, "low_freq_factor": 1.0,
+                                          "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}).to(DEV)
+
+
+FAR_POSITIONS = [0, 4095, 4096, 4223, 4224, 8191, 8192, 8703]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,hd,factor,interleaved", [(8, 2, 128, 8.0, False), (8, 2, 64, 32.0, False), (3, 1, 128, 8.0, True)])
+def test_rope_kv_write_at_positions_in_the_thousands(dtype, H, G, hd, factor, interleaved):
+    """Positions up to 8,703 with the real models' rope constants: the angle is the float product
+    pos * inv_freq, whose sine needs an accurate range reduction there, and the slot's page table
+    is 137 entries long."""
+    k = K()
+    M = len(FAR_POSITIONS)
+    qkv = _rand(M, (H + 2 * G) * hd, dtype=dtype, seed=21)
+    positions = torch.tensor(FAR_POSITIONS, dtype=torch.int32, device=DEV)
+    slot_of_token = torch.full((M,), 1, dtype=torch.int32, device=DEV)
+    g = torch.Generator().manual_seed(5)
+    page_table = torch.stack([torch.zeros(137, dtype=torch.int64), torch.randperm(140, generator=g)[:137]]).to(torch.int32).to(DEV)
+    inv = _llama3_inv_freq(hd, factor)
+    k_pool, v_pool = _paged(G, hd, 140, dtype)
+    src = qkv.clone()
+    k.rope_kv_write(qkv, positions, slot_of_token, page_table, inv, H, G, hd, hd, interleaved, k_pool, v_pool)
+    x = src.double().cpu()
+    q, kk, v = x[:, :H * hd].view(M, H, hd), x[:, H * hd:(H + G) * hd].view(M, G, hd), x[:, (H + G) * hd:].view(M, G, hd)
+    sin, cos = P.rope_angles(positions.cpu(), inv.cpu())
+    f = P.apply_rope_interleaved if interleaved else P.apply_rope_half
+    q, kk = f(q, sin, cos), f(kk, sin, cos)
+    tol = _tol(dtype)
+    torch.testing.assert_close(qkv[:, :H * hd].double().cpu().view(M, H, hd), q, **tol)
+    for m, p in enumerate(FAR_POSITIONS):
+        page = int(page_table[1, p // PAGE]); off = p % PAGE
+        torch.testing.assert_close(k_pool[page, :, off].double().cpu(), kk[m], **tol)
+        assert torch.equal(v_pool[page, :, off].double().cpu(), v[m])
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_gemm_tc_qkv_rope_at_positions_in_the_thousands(interleaved):
+    k = K()
+    H, G, hd, K_ = 4, 2, 128, 1024
+    M = len(FAR_POSITIONS)
+    N = (H + 2 * G) * hd
+    a = _rand(M, K_, dtype=torch.bfloat16, seed=61, scale=1.0)
+    w = _rand(N, K_, dtype=torch.bfloat16, seed=62, scale=0.05)
+    assert k.gemm_tc_qkv_rope_supported(a, w, H, G, hd, hd)
+    positions = torch.tensor(FAR_POSITIONS, dtype=torch.int32, device=DEV)
+    slot_of_token = torch.full((M,), 1, dtype=torch.int32, device=DEV)
+    g = torch.Generator().manual_seed(6)
+    page_table = torch.stack([torch.zeros(137, dtype=torch.int64), torch.randperm(140, generator=g)[:137]]).to(torch.int32).to(DEV)
+    inv = _llama3_inv_freq(hd, 8.0)
+    k_pool, v_pool = _paged(G, hd, 140, torch.bfloat16)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    k.gemm_tc_qkv_rope(a, w, out, None, positions, slot_of_token, page_table, inv, interleaved, H, G, k_pool, v_pool)
+    k.check_device_errors()
+    y = a.double().cpu() @ w.double().cpu().T
+    q, kk, v = y[:, :H * hd].view(M, H, hd), y[:, H * hd:(H + G) * hd].view(M, G, hd), y[:, (H + G) * hd:].view(M, G, hd)
+    sin, cos = P.rope_angles(positions.cpu(), inv.cpu())
+    f = P.apply_rope_interleaved if interleaved else P.apply_rope_half
+    q, kk = f(q, sin, cos), f(kk, sin, cos)
+    tol = dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(out[:, :H * hd].double().cpu().view(M, H, hd), q, **tol)
+    for m, p in enumerate(FAR_POSITIONS):
+        page = int(page_table[1, p // PAGE]); off = p % PAGE
+        torch.testing.assert_close(k_pool[page, :, off].double().cpu(), kk[m], **tol)
+        torch.testing.assert_close(v_pool[page, :, off].double().cpu(), v[m], **tol)
+
+
 # ----------------------------------------------------------------------------- attention
 def _attention_case(dtype, H, G, hd, lens_q, lens_kv, window=0, seed=0, craft=None):
     """Builds a paged cache with scrambled pages for sequences of lens_kv tokens; the
@@ -729,6 +798,67 @@ def test_attention_prefill_tc_finds_one_far_key_and_rescales(far, hd):
     assert (ref[far + 1:] - want).abs().max() < 1e-3
 
 
+# ----------------------------------------------------------------------------- attention over thousands of keys
+def _far_key_craft(far, hd, gain=16.0):
+    def craft(b, qb, kb, vb):
+        direction = torch.ones(hd) / math.sqrt(hd)
+        qb[:] = (direction * gain).to(qb.dtype)
+        kb[:] = (kb.float() * 0.05).to(kb.dtype)
+        kb[far] = (direction * gain).to(kb.dtype)      # its score stands far above the thousands of others
+    return craft
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("n,far", [(4096, 0), (4096, 4095), (8704, 77), (8704, 8640)])
+def test_attention_decode_over_thousands_of_keys(n, far, hd):
+    """The contexts the benchmarks decode at: one key among 4,096 or 8,704 made to stand out, a
+    short sequence beside it; every way the engine runs it (one chunk, dealt chunks, a cluster)."""
+    k = K()
+    H, G = 8, 2
+    lens = [n, 33]
+    craft = _far_key_craft(far, hd)
+    case = _attention_case(torch.bfloat16, H, G, hd, [1, 1], lens, seed=n + far,
+                           craft=lambda b, qb, kb, vb: craft(b, qb, kb, vb) if b == 0 else None)
+    q, kp, vp, pt, slots, kv_lens, ref = _decode_inputs(case)
+    page = int(pt[int(slots[0]), far // PAGE]); v_far = vp[page, :, far % PAGE].double().cpu()
+    assert (ref[0:1] - v_far.repeat_interleave(H // G, dim=0).reshape(1, H * hd)).abs().max() < 2e-3
+    for splits, planned, cluster in ((1, False, False), (8, False, False), (8, True, False), (8, False, True)):
+        out = torch.full((2, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        plan = k.decode_plan(slots, kv_lens, 0, splits) if planned else None
+        k.attention_decode(q, kp, vp, pt, slots, kv_lens, out, H, G, hd, 1.0 / math.sqrt(hd), num_splits=splits,
+                           plan=plan, cluster=cluster)
+        torch.testing.assert_close(out.double().cpu(), ref, **_tol(torch.bfloat16))
+    simt = torch.empty(2, H * hd, dtype=torch.bfloat16, device=DEV)
+    k.attention_simt(q, kp, vp, pt, slots, (kv_lens - 1).to(torch.int32), simt, H, G, hd, 1.0 / math.sqrt(hd))
+    torch.testing.assert_close(simt.double().cpu(), ref, **_tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("lens_q,lens_kv,far", [([4096], [4096], 1), ([4096], [4096], 3900), ([600, 70], [8704, 70], 8100),
+                                                ([600, 70], [8704, 70], 5)])
+def test_attention_prefill_tc_over_thousands_of_keys(lens_q, lens_kv, far, hd):
+    """A whole prompt of 4,096 tokens, and a 600-token portion behind 8,104 cached positions."""
+    k = K()
+    H, G = 4, 2
+    craft = _far_key_craft(far, hd)
+    case = _attention_case(torch.bfloat16, H, G, hd, lens_q, lens_kv, seed=far + lens_kv[0],
+                           craft=lambda b, qb, kb, vb: craft(b, qb, kb, vb) if b == 0 else None)
+    q, kp, vp, pt, cu, slots, kv_lens, ref = _prefill_inputs(case, lens_q, lens_kv)
+    out = torch.full((q.shape[0], H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    k.attention_prefill_tc(q, kp, vp, pt, cu, slots, kv_lens, lens_q, out, H, G, hd, 1.0 / math.sqrt(hd))
+    k.check_device_errors()
+    torch.testing.assert_close(out.double().cpu(), ref, **_tol(torch.bfloat16))
+    # queries behind the far key return its value
+    first_q = lens_kv[0] - lens_q[0]
+    page = int(pt[int(slots[0]), far // PAGE]); v_far = vp[page, :, far % PAGE].double().cpu()
+    want = v_far.repeat_interleave(H // G, dim=0).reshape(1, H * hd)
+    lo = max(far + 1 - first_q, 0)
+    assert (ref[lo:lens_q[0]] - want).abs().max() < 2e-3
+    other = torch.empty_like(out)
+    k.attention_prefill(q, kp, vp, pt, cu, slots, kv_lens, lens_q, other, H, G, hd, 1.0 / math.sqrt(hd))
+    torch.testing.assert_close(other.double().cpu(), ref, **_tol(torch.bfloat16))
+
+
 # ----------------------------------------------------------------------------- sampling
 def test_argmax_first_maximum_wins_and_non_finite_is_skipped():
     k = K()
@@ -776,6 +906,73 @@ def test_temperature_sampling_follows_the_plain_sampler(V):
             assert lo <= float(u[i]) + slack and pre[got] >= float(u[i]) - slack and w[got] > 0, \
                 f"row {i} trial {trial}: {got} vs {want}"
             assert abs(got - want) < 64
+
+
+def _kept_candidates(logits, temperature, top_k, top_p, min_p):
+    """The reference's candidate set in float64: tokens by descending logit (ties: lower index),
+    the top-k head of it, min-p's head of that, top-p's head of that; with their weights."""
+    n = logits.shape[0]
+    v = np.where(np.isfinite(logits), logits, -np.inf).astype(np.float64)
+    order = np.lexsort((np.arange(n), -v))
+    if 0 < top_k < n:
+        order = order[:top_k]
+    w = np.exp((v[order] - v[order[0]]) / temperature)
+    total, limit = w.sum(), len(order)
+    if min_p > 0:
+        below = np.nonzero(w < min_p * w[0])[0]
+        limit = max(int(below[0]) if below.size else len(order), 1)
+    cutoff = limit
+    if top_p < 1.0:
+        over = np.nonzero(np.cumsum(w[:limit]) > top_p * total)[0]
+        cutoff = int(over[0]) + 1 if over.size else limit
+    return order[:cutoff], w[:cutoff]
+
+
+@pytest.mark.parametrize("V", [5000, 128256])
+def test_candidate_sampling_at_real_vocabularies_follows_the_plain_sampler(V):
+    """Top-k, top-p and min-p in every combination the options allow, at vocabularies far larger
+    than a thread block: the same generator seeds as the plain sampler, the same tokens.  Where
+    they differ, the uniform number must lie within float rounding of the boundary between the
+    two tokens' shares (the kernels add in another order than the reference's float32 loop)."""
+    from rustyllm_b200.sampling.config import SamplerConfig
+    from rustyllm_b200.sampling.sampler import Sampler, SequenceSamplingState
+    options = [dict(top_k=2), dict(top_k=40), dict(top_k=1024), dict(top_k=40, top_p=0.9), dict(top_k=40, min_p=0.05),
+               dict(top_k=1024, top_p=0.95, min_p=0.001), dict(top_p=0.9), dict(top_p=0.5, min_p=0.02), dict(top_p=0.99),
+               dict(top_p=0.9, top_k=40, repeat_penalty=1.1), dict(top_p=0.3), dict(top_p=0.999, min_p=0.0001)]
+    temps = [0.8, 1.3, 0.7]
+    rows = len(options)
+    g = torch.Generator().manual_seed(V)
+    base = torch.randn(rows, V, generator=g) * 3.0
+    base[1, 7] = float("-inf"); base[6, 11] = float("nan"); base[2, 100] = base[2, 200] = base[2].max() + 1.0   # a tie at the top
+    recent = torch.randint(0, V, (30,), generator=g).tolist()
+    configs = [SamplerConfig(temperature=temps[i % 3], **o) for i, o in enumerate(options)]
+    sampler = Sampler(torch.device(DEV))
+    states = [SequenceSamplingState(c, 500 + i, recent) for i, c in enumerate(configs)]
+    twins = [P.Rng(500 + i) for i in range(rows)]
+    differed = 0
+    for trial in range(8):
+        got = sampler.sample(base.clone().to(DEV), states)
+        for i, c in enumerate(configs):
+            u = twins[i].next_f32()
+
+            class Fixed:
+                def next_f32(self, v=u): return v
+            lg = base[i].numpy().copy()
+            want = P.sample(lg, c.temperature, Fixed(), c.top_k, c.top_p, c.min_p, c.repeat_penalty, recent=recent[-64:])
+            if got[i] == want:
+                continue
+            differed += 1
+            P.apply_repeat_penalty(lg, recent[-64:], c.repeat_penalty)
+            kept, w = _kept_candidates(lg, c.temperature, c.top_k, c.top_p, c.min_p)
+            where = np.nonzero(kept == got[i])[0]
+            assert where.size == 1, f"options {options[i]} trial {trial}: token {got[i]} is not among the {len(kept)} kept (plain: {want})"
+            j = int(where[0])
+            pre = np.cumsum(w) / w.sum()
+            slack = max(len(kept) * 2.0 ** -24, 1e-6)
+            assert (pre[j - 1] if j else 0.0) <= u + slack and pre[j] >= u - slack, \
+                f"options {options[i]} trial {trial}: {got[i]} (place {j}) vs {want}, u = {u}"
+    assert differed <= 4, f"{differed} of {8 * rows} draws differ from the plain sampler"
+
 
 
 def test_temperature_zero_rows_are_greedy_and_min_p_cuts():

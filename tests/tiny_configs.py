@@ -47,6 +47,33 @@ TINY = {
         "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 128,
         "max_position_embeddings": 512, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
         "tie_word_embeddings": False, "attention_bias": True}),
+    # E's widths with a long context and the rope constants of the real 8B model: positions in the
+    # thousands, where float rounding of pos * inv_freq and the length of a slot's page table show
+    "F": dict(seed=5, norm_noise=True, dtype="bfloat16", config={
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+        "vocab_size": 272, "hidden_size": 512, "intermediate_size": 640, "num_hidden_layers": 2,
+        "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 128,
+        "max_position_embeddings": 8768, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+        "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                         "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+        "tie_word_embeddings": False}),
+    # D's widths (head 64) with a long context and the rope constants of the real 1B model
+    "G": dict(seed=6, norm_noise=True, dtype="bfloat16", config={
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+        "vocab_size": 320, "hidden_size": 128, "intermediate_size": 192, "num_hidden_layers": 2,
+        "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
+        "max_position_embeddings": 8768, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+        "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                         "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+        "tie_word_embeddings": True}),
+    # 32 query heads on one KV head: more than the tensor-core decode attention groups (16), so
+    # single-token steps fall to the any-shape kernel while prompts take the tensor cores
+    "H": dict(seed=7, norm_noise=True, dtype="bfloat16", config={
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+        "vocab_size": 300, "hidden_size": 256, "intermediate_size": 320, "num_hidden_layers": 2,
+        "num_attention_heads": 32, "num_key_value_heads": 1, "head_dim": 64,
+        "max_position_embeddings": 512, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+        "tie_word_embeddings": False}),
 }
 
 
