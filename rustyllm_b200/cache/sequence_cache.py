@@ -11,8 +11,9 @@ sequence.  Here one pool serves every sequence of every batch:
   * a *slot* holds one sequence: its length, one row of each group's page table,
     and ``state_bytes`` of state that is zeroed when the slot is handed out;
   * a *group* is the storage of all layers with the same need (number of KV
-    heads, head size, all keys or a window of them).  It owns a pool
-    ``[layers, 2, pages, kv_heads, page_size, head_dim]`` and a page allocator;
+    heads, width of a key head and of a value head, all keys or a window of them).
+    It owns the keys ``[layers, pages, kv_heads, page_size, head_dim]``, the values
+    ``[layers, pages, kv_heads, page_size, value_dim]`` and a page allocator;
     page p of a slot holds positions ``[p*page_size, (p+1)*page_size)`` of every
     layer of the group.  A window group gives pages back once every position in
     them has left the window;
@@ -37,8 +38,17 @@ from .allocators import CacheFull, CacheMisuse, FreeList
 class KVNeed:
     """What one attention-like layer needs cached per position."""
     num_kv_heads: int
-    head_dim: int
+    head_dim: int                  # width of a key head
     window: Optional[int] = None   # None: all keys; W: only the last W positions are read
+    value_dim: Optional[int] = None  # width of a value head; None: the same as head_dim
+
+    def __post_init__(self):
+        if self.value_dim == self.head_dim:        # one way to say "the same": equal needs share a group
+            object.__setattr__(self, "value_dim", None)
+
+    @property
+    def v_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass(frozen=True)
@@ -57,8 +67,10 @@ class KVGroup:
         # zero-filled once: rows of a page beyond a sequence's length are never selected, but a
         # tensor-core attention kernel multiplies them by a probability of exactly 0, so they
         # must be finite (what earlier sequences left there is)
-        self.pool = torch.zeros((layers, 2, num_pages, need.num_kv_heads, PAGE_SIZE, need.head_dim),
+        self.keys = torch.zeros((layers, num_pages, need.num_kv_heads, PAGE_SIZE, need.head_dim),
                                 dtype=dtype, device=device)
+        self.values = torch.zeros((layers, num_pages, need.num_kv_heads, PAGE_SIZE, need.v_dim),
+                                  dtype=dtype, device=device)
         self.page_table_host = torch.zeros((max_slots, max_pages_per_slot), dtype=torch.int32)
         self.page_table = self.page_table_host if device.type == "cpu" else \
             torch.zeros((max_slots, max_pages_per_slot), dtype=torch.int32, device=device)
@@ -66,13 +78,16 @@ class KVGroup:
         self.slot_pages: List[List[int]] = [[] for _ in range(max_slots)]
 
     def k_pool(self, layer: int) -> torch.Tensor:
-        return self.pool[layer, 0]
+        return self.keys[layer]
 
     def v_pool(self, layer: int) -> torch.Tensor:
-        return self.pool[layer, 1]
+        return self.values[layer]
 
     def bytes_per_token(self) -> int:
-        return self.layers * 2 * self.need.num_kv_heads * self.need.head_dim * self.pool.element_size()
+        return self.layers * self.need.num_kv_heads * (self.need.head_dim + self.need.v_dim) * self.keys.element_size()
+
+    def memory_bytes(self) -> int:
+        return (self.keys.numel() + self.values.numel()) * self.keys.element_size()
 
     def pages_needed(self, slot: int, new_len: int) -> int:
         have = len(self.slot_pages[slot])
@@ -270,4 +285,4 @@ class SequenceCache:
                 raise CacheMisuse(f"{g.pages.held_count - len(seen)} held page(s) belong to no sequence")
 
     def memory_bytes(self) -> int:
-        return sum(g.pool.numel() * g.pool.element_size() for g in self.groups) + self.state.numel()
+        return sum(g.memory_bytes() for g in self.groups) + self.state.numel()

@@ -44,7 +44,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_pool,
                       const T* __restrict__ v_pool, const int* __restrict__ page_table, int max_pages,
                       const int* __restrict__ slot_of_token, const int* __restrict__ positions,
-                      T* __restrict__ out, int ldo, int H, int G, int hd, float scale, int window) {
+                      T* __restrict__ out, int ldo, int H, int G, int hd, int vd, float scale, int window) {
   __shared__ float qs[ATT_WARPS][ATT_MAX_HD];
   const int m = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -64,8 +64,8 @@ attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_
 #pragma unroll
   for (int e = 0; e < NE; ++e) acc[e] = 0.f;
   float run_max = -INFINITY, run_sum = 0.f;
-  const size_t head_off = (size_t)g * RL_PAGE * hd;
-  const size_t page_stride = (size_t)G * RL_PAGE * hd;
+  const size_t head_off = (size_t)g * RL_PAGE * hd, v_head_off = (size_t)g * RL_PAGE * vd;
+  const size_t page_stride = (size_t)G * RL_PAGE * hd, v_page_stride = (size_t)G * RL_PAGE * vd;
 
   for (int t0 = start; t0 <= pos; t0 += 32) {
     const int t = t0 + lane;
@@ -85,47 +85,50 @@ attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_
     for (int j = 0; j < n; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const int tj = t0 + j;
-      const T* vrow = v_pool + (size_t)pages[tj / RL_PAGE] * page_stride + head_off + (size_t)(tj % RL_PAGE) * hd;
+      const T* vrow = v_pool + (size_t)pages[tj / RL_PAGE] * v_page_stride + v_head_off + (size_t)(tj % RL_PAGE) * vd;
 #pragma unroll
       for (int e = 0; e < NE; ++e) {
         const int d = lane + 32 * e;
-        if (d < hd) acc[e] = fmaf(pj, rl_ld(vrow + d), acc[e]);
+        if (d < vd) acc[e] = fmaf(pj, rl_ld(vrow + d), acc[e]);
       }
     }
   }
   const float inv = 1.0f / run_sum;
-  T* orow = out + (size_t)m * ldo + (size_t)h * hd;
+  T* orow = out + (size_t)m * ldo + (size_t)h * vd;
 #pragma unroll
   for (int e = 0; e < NE; ++e) {
     const int d = lane + 32 * e;
-    if (d < hd) rl_st(orow + d, acc[e] * inv);
+    if (d < vd) rl_st(orow + d, acc[e] * inv);
   }
 }
 
-// q: [M, ldq] with head h at columns [h*hd, (h+1)*hd); out: [M, ldo] likewise.
-// k_pool/v_pool: [num_pages, G, RL_PAGE, hd] in the same dtype as q.
+// q: [M, ldq] with head h at columns [h*hd, (h+1)*hd); out: [M, ldo] with head h at columns
+// [h*vd, (h+1)*vd).  k_pool: [num_pages, G, RL_PAGE, hd], v_pool: [num_pages, G, RL_PAGE, vd]
+// (value heads may be narrower or wider than key heads: the reference keeps value_dim apart
+// from head_dim, src/model.rs:33, 67-69), both in the same dtype as q.
 extern "C" int rl_attention_simt(const void* q, int ldq, const void* k_pool, const void* v_pool,
                                  int dtype, const int* page_table, int max_pages,
                                  const int* slot_of_token, const int* positions, void* out, int ldo,
-                                 int num_tokens, int num_heads, int num_kv_heads, int head_dim,
+                                 int num_tokens, int num_heads, int num_kv_heads, int head_dim, int value_dim,
                                  float scale, int window, cudaStream_t stream) {
   RL_REQUIRE(num_tokens >= 0 && num_heads > 0 && num_kv_heads > 0, "rl_attention_simt: bad sizes");
   RL_REQUIRE(num_heads % num_kv_heads == 0, "rl_attention_simt: %d heads are no multiple of %d KV heads",
              num_heads, num_kv_heads);
   RL_REQUIRE(head_dim > 0 && head_dim <= ATT_MAX_HD && head_dim % 2 == 0,
              "rl_attention_simt: head_dim %d must be even and <= %d", head_dim, ATT_MAX_HD);
-  RL_REQUIRE(ldq >= num_heads * head_dim && ldo >= num_heads * head_dim, "rl_attention_simt: row strides too small");
+  RL_REQUIRE(value_dim > 0 && value_dim <= ATT_MAX_HD, "rl_attention_simt: value_dim %d must lie in (0, %d]", value_dim, ATT_MAX_HD);
+  RL_REQUIRE(ldq >= num_heads * head_dim && ldo >= num_heads * value_dim, "rl_attention_simt: row strides too small");
   RL_REQUIRE(window >= 0, "rl_attention_simt: negative window");
   if (num_tokens == 0) return RL_OK;
   dim3 grid(num_tokens, (num_heads + ATT_WARPS - 1) / ATT_WARPS);
   if (dtype == RL_F32)
     attention_simt_kernel<float><<<grid, ATT_WARPS * 32, 0, stream>>>(
         (const float*)q, ldq, (const float*)k_pool, (const float*)v_pool, page_table, max_pages,
-        slot_of_token, positions, (float*)out, ldo, num_heads, num_kv_heads, head_dim, scale, window);
+        slot_of_token, positions, (float*)out, ldo, num_heads, num_kv_heads, head_dim, value_dim, scale, window);
   else if (dtype == RL_BF16)
     attention_simt_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, 0, stream>>>(
         (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table,
-        max_pages, slot_of_token, positions, (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, head_dim, scale, window);
+        max_pages, slot_of_token, positions, (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, head_dim, value_dim, scale, window);
   else
     RL_REQUIRE(false, "rl_attention_simt: unknown dtype %d", dtype);
   RL_LAUNCH_CHECK("rl_attention_simt");

@@ -39,9 +39,9 @@ _SIGNATURES = {
     "rl_gemm_simt": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                      _c_int, _c_int, _c_void_p],
     "rl_rope_kv_write": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
-                         _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
+                         _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
     "rl_attention_simt": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
-                          _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
+                          _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
                           _c_void_p],
     "rl_repeat_penalty": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_float, _c_void_p],
     "rl_argmax": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
@@ -217,7 +217,11 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_mode: int
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slot_of_token: torch.Tensor,
                   page_table: torch.Tensor, inv_freq: torch.Tensor, num_heads: int, num_kv_heads: int,
                   head_dim: int, rotary_dim: int, interleaved: bool,
-                  k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor]) -> None:
+                  k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], value_dim: Optional[int] = None) -> None:
+    """Rotates the query and key heads of qkv ([M, H*hd + G*hd + G*vd]) in place and writes keys
+    and values at their tokens' places of the paged pools.  ``value_dim`` (default: head_dim)
+    is the width of a value head."""
+    vd = head_dim if value_dim is None else value_dim
     _need(qkv, "qkv"); _need(positions, "positions", torch.int32)
     _need(inv_freq, "inv_freq", torch.float32)
     M = qkv.shape[0]
@@ -225,21 +229,25 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slot_of_token: tor
         _need(k_pool, "k_pool", qkv.dtype); _need(v_pool, "v_pool", qkv.dtype)
         _need(slot_of_token, "slot_of_token", torch.int32); _need(page_table, "page_table", torch.int32)
         assert k_pool.shape[1:] == (num_kv_heads, page_size(), head_dim), k_pool.shape
+        assert v_pool.shape[1:] == (num_kv_heads, page_size(), vd), v_pool.shape
         max_pages = page_table.shape[1]
     else:
         max_pages = 0
     assert inv_freq.numel() >= rotary_dim // 2
     _check(library().rl_rope_kv_write(
         qkv.data_ptr(), _dt(qkv), qkv.stride(0), positions.data_ptr(), _ptr(slot_of_token), _ptr(page_table),
-        max_pages, inv_freq.data_ptr(), M, num_heads, num_kv_heads, head_dim, rotary_dim, int(interleaved),
+        max_pages, inv_freq.data_ptr(), M, num_heads, num_kv_heads, head_dim, vd, rotary_dim, int(interleaved),
         _ptr(k_pool), _ptr(v_pool), _stream()), "rl_rope_kv_write")
     _count()
 
 
 def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
                    slot_of_token: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
-                   num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
-    """q: [M, >= H*hd] (a view into the qkv buffer is fine), out: [M, H*hd]."""
+                   num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
+                   value_dim: Optional[int] = None) -> None:
+    """q: [M, >= H*hd] (a view into the qkv buffer is fine), out: [M, H*vd] where vd is
+    ``value_dim`` (default: head_dim), the width of a value head."""
+    vd = head_dim if value_dim is None else value_dim
     _need(q, "q", contiguous=False); _need(k_pool, "k_pool", q.dtype); _need(v_pool, "v_pool", q.dtype)
     _need(out, "out", q.dtype); _need(page_table, "page_table", torch.int32)
     _need(slot_of_token, "slot_of_token", torch.int32); _need(positions, "positions", torch.int32)
@@ -249,7 +257,7 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
     _check(library().rl_attention_simt(
         q.data_ptr(), ldq, k_pool.data_ptr(), v_pool.data_ptr(), _dt(q), page_table.data_ptr(),
         page_table.shape[1], slot_of_token.data_ptr(), positions.data_ptr(), out.data_ptr(), out.stride(0),
-        M, num_heads, num_kv_heads, head_dim, float(scale), int(window), _stream()), "rl_attention_simt")
+        M, num_heads, num_kv_heads, head_dim, vd, float(scale), int(window), _stream()), "rl_attention_simt")
     _count()
 
 
@@ -583,10 +591,16 @@ def attention_prefill_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
 # ----------------------------------------------------------------------------- attention dispatch
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
               step, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-              window: int = 0) -> None:
+              window: int = 0, value_dim: Optional[int] = None) -> None:
     """Attention of the step's tokens over the cache; picks the kernel for the
     dtype and the shape of the step.  ``step`` carries positions, slots and
-    sequence boundaries (engine.step.StepState)."""
+    sequence boundaries (engine.step.StepState).  Value heads of another width than the
+    key heads (``value_dim``) run on the any-shape kernel; the tensor-core kernels take
+    one width for both."""
+    if value_dim is not None and value_dim != head_dim:
+        attention_simt(q, k_pool, v_pool, page_table, step.slot_of_token, step.positions, out,
+                       num_heads, num_kv_heads, head_dim, scale, window, value_dim=value_dim)
+        return
     if step.is_decode and attention_decode_supported(q.dtype, num_heads, num_kv_heads, head_dim):
         splits = decode_splits(q.shape[0], num_kv_heads)
         if q.shape[0] == 1 and splits >= 8:

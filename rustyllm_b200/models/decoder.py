@@ -121,7 +121,7 @@ class DecoderModel:
     # ------------------------------------------------------------------ running
     def forward(self, step, cache: SequenceCache) -> torch.Tensor:
         """All tokens of the step through all scheduled layers: float32 [M, d]."""
-        x = self.embedding.forward(step.tokens)
+        x = self.embedding.forward(step)
         schedule = self.spec.schedule
         pending = None      # the next block's first norm, started by the block in front of it
         for pos, li in enumerate(schedule):

@@ -27,13 +27,17 @@ from .registry import build_part, register_mixer
 class GQAttention(Mixer):
     def __init__(self, runtime: Runtime, hidden_size: int, num_heads: int, num_kv_heads: int,
                  head_dim: int, position: PartSpec, names: Dict[str, str], bias: bool = False,
-                 window: Optional[int] = None):
+                 window: Optional[int] = None, value_dim: Optional[int] = None):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads are no multiple of {num_kv_heads} KV heads")
         if head_dim % 2 or not (0 < head_dim <= 256):
             raise ValueError(f"head_dim {head_dim} must be even and at most 256")
         if window is not None and window <= 0:
             raise ValueError("window must be > 0 or None")
+        vd = head_dim if value_dim is None else value_dim      # the reference keeps value_dim apart, src/model.rs:33, 67-69
+        if vd % 2 or not (0 < vd <= 256):
+            raise ValueError(f"value_dim {vd} must be even and at most 256")
+        self.vd = vd
         self.runtime = runtime
         self.d, self.H, self.G, self.hd = hidden_size, num_heads, num_kv_heads, head_dim
         self.bias = bias
@@ -44,22 +48,22 @@ class GQAttention(Mixer):
         self.wqkv = self.wo = self.bqkv = self.bo = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        d, H, G, hd, n = self.d, self.H, self.G, self.hd, self.names
+        d, H, G, hd, vd, n = self.d, self.H, self.G, self.hd, self.vd, self.names
         specs = {
             "wqkv": ParamSpec((ParamSource(n["q"] + ".weight", (H * hd, d)),
                                ParamSource(n["k"] + ".weight", (G * hd, d)),
-                               ParamSource(n["v"] + ".weight", (G * hd, d)))),
-            "wo": ParamSpec((ParamSource(n["o"] + ".weight", (d, H * hd)),)),
+                               ParamSource(n["v"] + ".weight", (G * vd, d)))),
+            "wo": ParamSpec((ParamSource(n["o"] + ".weight", (d, H * vd)),)),
         }
         if self.bias:
             specs["bqkv"] = ParamSpec((ParamSource(n["q"] + ".bias", (H * hd,)),
                                        ParamSource(n["k"] + ".bias", (G * hd,)),
-                                       ParamSource(n["v"] + ".bias", (G * hd,))), role="vector")
+                                       ParamSource(n["v"] + ".bias", (G * vd,))), role="vector")
             specs["bo"] = ParamSpec((ParamSource(n["o"] + ".bias", (d,)),), role="vector")
         return specs
 
     def kv_need(self) -> KVNeed:
-        return KVNeed(self.G, self.hd, self.window)
+        return KVNeed(self.G, self.hd, self.window, None if self.vd == self.hd else self.vd)
 
     folds_norms = True
 
@@ -67,15 +71,15 @@ class GQAttention(Mixer):
         return can_fold_norms(self.wqkv, self.runtime.compute_dtype, num_tokens)
 
     def forward(self, xn, residual: torch.Tensor, step, cache, then_norm=None):
-        H, G, hd = self.H, self.G, self.hd
+        H, G, hd, vd = self.H, self.G, self.hd, self.vd
         M = xn.shape[0]
         dt = xn.dtype
-        qkv = torch.empty((M, (H + 2 * G) * hd), dtype=dt, device=xn.device)
+        qkv = torch.empty((M, (H + G) * hd + G * vd), dtype=dt, device=xn.device)
         group, layer = cache.kv_group, cache.kv_layer
         k_pool, v_pool = group.k_pool(layer), group.v_pool(layer)
         pos = self.position
         x = xn.weighted if isinstance(xn, NormedInput) else xn
-        if (dt == torch.bfloat16 and self.wqkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16
+        if (dt == torch.bfloat16 and vd == hd and self.wqkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16
                 and K.gemm_tc_qkv_rope_supported(x, self.wqkv, H, G, hd, pos.rotary_dim)):
             # few tokens: rotation and cache write ride in the product's epilogue
             kw = dict(row_sumsq=xn.sumsq, row_eps=xn.eps) if isinstance(xn, NormedInput) else {}
@@ -86,8 +90,8 @@ class GQAttention(Mixer):
             linear(xn, self.wqkv, qkv, OUT_SAME, self.bqkv)
             K.rope_kv_write(qkv, step.positions, step.slot_of_token, group.page_table, pos.inv_freq, H, G, hd,
                             pos.rotary_dim, pos.interleaved,
-                            k_pool if cache.writes else None, v_pool if cache.writes else None)
-        attn = torch.empty((M, H * hd), dtype=dt, device=xn.device)
+                            k_pool if cache.writes else None, v_pool if cache.writes else None, value_dim=vd)
+        attn = torch.empty((M, H * vd), dtype=dt, device=xn.device)
         K.attention(qkv, k_pool, v_pool, group.page_table, step, attn, H, G, hd, self.scale,
-                    self.window or 0)
+                    self.window or 0, value_dim=vd)
         return linear(attn, self.wo, residual, OUT_ADD_F32, self.bo, then_norm=then_norm)

@@ -29,8 +29,11 @@ class TokenEmbedding(Part):
     def param_specs(self) -> Dict[str, ParamSpec]:
         return {"weight": ParamSpec((ParamSource(self.name, (self.V, self.d)),), role="table")}
 
-    def forward(self, tokens: torch.Tensor) -> torch.Tensor:
-        """tokens: int32 [M] -> float32 residual [M, d]."""
+    def forward(self, step) -> torch.Tensor:
+        """The step's tokens (``step.tokens``, int32 [M]) -> float32 residual [M, d].  An embedding
+        part is handed the whole step, so that one which also needs the tokens' positions (a
+        learned absolute position table) finds them in ``step.positions``."""
+        tokens = step.tokens
         x = torch.empty((tokens.numel(), self.d), dtype=torch.float32, device=tokens.device)
         K.embedding(self.weight, tokens, x, self.bad_token)
         return x

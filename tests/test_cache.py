@@ -42,8 +42,19 @@ def test_layers_with_equal_needs_share_a_group():
     c = _cache()
     assert len(c.groups) == 2
     assert c.entry_group == [(0, 0), (0, 1), (1, 0)]
-    assert c.groups[0].pool.shape == (2, 2, 8, 2, PAGE, 16)
-    assert c.groups[1].pool.shape == (1, 2, 8, 1, PAGE, 32)
+    assert c.groups[0].keys.shape == (2, 8, 2, PAGE, 16) and c.groups[0].values.shape == (2, 8, 2, PAGE, 16)
+    assert c.groups[1].keys.shape == (1, 8, 1, PAGE, 32)
+
+
+def test_value_heads_of_another_width_get_storage_of_their_own():
+    kv = [KVNeed(2, 16, None), KVNeed(2, 16, None, value_dim=8), KVNeed(2, 16, None, value_dim=8), KVNeed(2, 16, None, value_dim=16)]
+    c = SequenceCache(kv, [None] * 4, 64 * 4, torch.float32, "cpu")
+    assert len(c.groups) == 2 and c.entry_group[3][0] == c.entry_group[0][0]    # value_dim = head_dim is the plain need
+    wide = c.groups[c.entry_group[1][0]]
+    assert c.entry_group[1][0] == c.entry_group[2][0] != c.entry_group[0][0]
+    assert wide.keys.shape == (2, 4, 2, PAGE, 16) and wide.values.shape == (2, 4, 2, PAGE, 8)
+    assert wide.bytes_per_token() == 2 * 2 * (16 + 8) * 4
+    assert c.memory_bytes() >= wide.keys.numel() * 4 + wide.values.numel() * 4
 
 
 def test_pages_follow_lengths_and_come_back():

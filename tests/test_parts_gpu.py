@@ -179,7 +179,8 @@ def test_embedding_and_head_parts(dtype):
     table = _rand(307, 40, seed=1, dtype=dtype)
     emb.bind({"weight": table}); head.bind({"weight": table})
     ids = torch.tensor([306, 0, 5], dtype=torch.int32, device=DEV)
-    x = emb.forward(ids)
+    from types import SimpleNamespace
+    x = emb.forward(SimpleNamespace(tokens=ids))         # an embedding part is handed the step
     assert x.dtype == torch.float32 and torch.equal(x, table[ids.long()].float())
     xn = _rand(4, 40, seed=2, dtype=dtype)
     logits = head.forward(xn)

@@ -166,3 +166,130 @@ def test_routed_feed_forward_and_own_position_encoding_register_build_and_step()
         eng.free_slot(sl)
     r.cache.check()
     assert math.isfinite(float(whole.abs().max())) and whole.std() > 1e-3
+
+
+# ----------------------------------------------------------------------------- a learned position table, narrow value heads
+def _register_absolute():
+    from rustyllm_b200 import kernels as K
+    from rustyllm_b200.config.registry import register_architecture
+    from rustyllm_b200.config.spec import LayerSpec, ModelSpec, ParamSource, ParamSpec, PartSpec
+    from rustyllm_b200.parts import Part, register
+
+    @register("embedding", "toy_token_plus_position")
+    class ToyTokenPlusPosition(Part):
+        """x = E[token] + P[position]: a learned absolute position table.  The embedding part is
+        handed the step, so it finds the positions beside the tokens; both look-ups are the
+        framework's own gather kernel."""
+
+        def __init__(self, runtime, vocab_size, max_positions, hidden_size, name):
+            self.V, self.maxpos, self.d, self.name = vocab_size, max_positions, hidden_size, name
+            self.bad_token = torch.zeros(1, dtype=torch.int32, device=runtime.device)
+
+        def param_specs(self):
+            return {"weight": ParamSpec((ParamSource(self.name + ".tokens", (self.V, self.d)),), role="table"),
+                    "positions": ParamSpec((ParamSource(self.name + ".positions", (self.maxpos, self.d)),), role="table")}
+
+        def forward(self, step):
+            M = step.tokens.numel()
+            x = torch.empty((M, self.d), dtype=torch.float32, device=step.tokens.device)
+            p = torch.empty_like(x)
+            K.embedding(self.weight, step.tokens, x, self.bad_token)
+            K.embedding(self.positions, step.positions, p, self.bad_token)
+            return x.add_(p)
+
+    def spec(cfg):
+        d = cfg["hidden_size"]
+        def norm(n): return PartSpec("rms_norm", {"size": d, "eps": cfg["eps"], "name": n})
+        layers = []
+        for i in range(cfg["layers"]):
+            p = f"l{i}."
+            attn = PartSpec("gqa_attention", {
+                "hidden_size": d, "num_heads": cfg["heads"], "num_kv_heads": cfg["kv"], "head_dim": cfg["head_dim"],
+                "value_dim": cfg["value_dim"], "position": PartSpec("none", {"head_dim": cfg["head_dim"]}),
+                "names": {"q": p + "q", "k": p + "k", "v": p + "v", "o": p + "o"}})
+            ff = PartSpec("gated_mlp", {"hidden_size": d, "intermediate_size": cfg["inter"],
+                                        "names": {"gate": p + "g", "up": p + "u", "down": p + "d"}})
+            layers.append(LayerSpec(PartSpec("pre_norm"), attn, norm(p + "n1"), ff, norm(p + "n2")))
+        return ModelSpec("ToyAbsoluteForCausalLM", cfg["vocab_size"], d, cfg["max_positions"],
+                         PartSpec("toy_token_plus_position", {"vocab_size": cfg["vocab_size"], "max_positions": cfg["max_positions"],
+                                                              "hidden_size": d, "name": "emb"}),
+                         tuple(layers), tuple(range(cfg["layers"])), norm("nf"),
+                         PartSpec("lm_head", {"vocab_size": cfg["vocab_size"], "hidden_size": d, "name": "head"}))
+
+    register_architecture(("ToyAbsoluteForCausalLM",), dict, spec)
+
+
+ABS = {"architectures": ["ToyAbsoluteForCausalLM"], "vocab_size": 53, "max_positions": 200, "hidden_size": 48, "inter": 72,
+       "heads": 6, "kv": 2, "head_dim": 16, "value_dim": 10, "eps": 1e-5, "layers": 2}
+
+
+def _restated_absolute(model, tokens):
+    c = ABS
+    hd, vd, H, G = c["head_dim"], c["value_dim"], c["heads"], c["kv"]
+    f = lambda t: t.detach().to(F64).cpu()
+    T = len(tokens)
+    x = f(model.embedding.weight)[torch.tensor(tokens)] + f(model.embedding.positions)[:T]
+    scale = 1.0 / math.sqrt(hd)
+    for blk in model.blocks:
+        xn = P.rms_norm(x, f(blk.mixer_norm.weight), c["eps"])
+        qkv = xn @ f(blk.mixer.wqkv).T
+        q = qkv[:, :H * hd].view(T, H, hd)
+        k = qkv[:, H * hd:(H + G) * hd].view(T, G, hd)
+        v = qkv[:, (H + G) * hd:].view(T, G, vd)
+        a = torch.empty(T, H, vd, dtype=F64)
+        mask = torch.tril(torch.ones(T, T, dtype=torch.bool))
+        for h in range(H):
+            g = h // (H // G)
+            s = (q[:, h] @ k[:, g].T * scale).masked_fill(~mask, float("-inf"))
+            a[:, h] = torch.softmax(s, -1) @ v[:, g]
+        x = x + a.reshape(T, H * vd) @ f(blk.mixer.wo).T
+        xn = P.rms_norm(x, f(blk.feed_forward_norm.weight), c["eps"])
+        gu = xn @ f(blk.feed_forward.wgu).T
+        # a bfloat16 run keeps gate and up rows in turn, a 32-bit run one block after the other
+        gate, up = (gu[:, 0::2], gu[:, 1::2]) if blk.feed_forward.interleaved else (gu[:, :c["inter"]], gu[:, c["inter"]:])
+        x = x + P.swiglu(gate, up) @ f(blk.feed_forward.wdown).T
+    return P.rms_norm(x, f(model.final_norm.weight), c["eps"]) @ f(model.head.weight).T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_learned_positions_and_narrow_value_heads_register_build_and_step(dtype):
+    """An architecture registered from here whose embedding adds a learned absolute position
+    table (no rotation at all) and whose value heads (10) are narrower than its key heads (16):
+    value storage of its own width in the cache, the any-shape attention kernel, whole prompts
+    and token by token, against the float64 restatement above."""
+    _register_absolute()
+    from rustyllm_b200 import Runner
+    r = Runner.from_config(ABS, seed=13, dtype=dtype, storage_dtype="bfloat16", max_cache_tokens=64 * 8, max_batch=3, std=0.05)
+    m = r.model
+    assert type(m.embedding).__name__ == "ToyTokenPlusPosition" and m.embedding.positions.shape == (200, 48)
+    assert m.blocks[0].mixer.wqkv.shape == (6 * 16 + 2 * 16 + 2 * 10, 48) and m.blocks[0].mixer.wo.shape == (48, 60)
+    g = r.cache.groups[0]
+    assert g.keys.shape[-1] == 16 and g.values.shape[-1] == 10
+    eng = r.engine
+    gen = torch.Generator().manual_seed(2)
+    seqs = [torch.randint(0, 53, (n,), generator=gen).tolist() for n in (150, 9, 70)]
+    want = torch.cat([_restated_absolute(m, s) for s in seqs])
+    from gpu_helpers import assert_close_logits         # the engine tests' bounds, relative to a row's scale
+    slots = [eng.alloc_slot() for _ in seqs]
+    whole = eng.step(slots, seqs, "all")
+    for s in slots:
+        eng.free_slot(s)
+    assert_close_logits(whole, want, dtype, "toy absolute, whole")
+    slots = [eng.alloc_slot() for _ in seqs]
+    cut = [120, 3, 66]
+    a = eng.step(slots, [s[:n] for s, n in zip(seqs, cut)], "all")
+    rows, o = {}, 0
+    for i, n in enumerate(cut):
+        rows[i] = [a[o:o + n]]; o += n
+    fed = list(cut)
+    while any(fed[i] < len(seqs[i]) for i in range(3)):
+        live = [i for i in range(3) if fed[i] < len(seqs[i])]
+        out = eng.step([slots[i] for i in live], [[seqs[i][fed[i]]] for i in live], "last")
+        for row, i in enumerate(live):
+            rows[i].append(out[row:row + 1]); fed[i] += 1
+    stepped = torch.cat(rows[0] + rows[1] + rows[2])
+    assert_close_logits(stepped, want, dtype, "toy absolute, prompt step then single tokens")
+    for sl in slots:
+        eng.free_slot(sl)
+    r.cache.check()
+    assert int(m.embedding.bad_token.item()) == 0
