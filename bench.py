@@ -178,6 +178,13 @@ def main():
             eng.free_slot(s)
         return ms, launches, mean_ctx
 
+    def point(batch, ms, ctx_tokens):
+        """One decode measurement as a record: tokens a second, the step's time, the mean context of
+        its sequences and the fraction of the copy bandwidth its bytes (weights + live cache) reach."""
+        gbs = (weight_bytes + ctx_tokens * kv_bytes_per_token) / (ms * 1e-3) / 1e9
+        return {"value": batch * 1000.0 / ms, "ms_per_step": round(ms, 4), "mean_context": round(ctx_tokens / batch, 1),
+                "gb_s": round(gbs, 1), "frac": round(gbs / peaks["hbm_gbs"], 4)}
+
     clocks = ClockSampler()
     clocks.start()
     headline_prompts = draw_prompts(args.batch)      # the device-timed and the end-to-end arm decode the same batch
@@ -212,11 +219,12 @@ def main():
                "frac": pre_flops / (pms * 1e-3) / (peaks["bf16_tflops"] * 1e12)}
 
     # ---- batch 1 and 64 ----
-    points = {}
+    points, point_details = {}, {}
     if not args.skip_points:
         for b in (1, 64):
-            pm, _, _ = time_decode(b, max(8, args.steps // 2), args.warmup)
+            pm, _, pctx = time_decode(b, max(8, args.steps // 2), args.warmup)
             points[f"decode_b{b}"] = b * 1000.0 / pm
+            point_details[f"decode_b{b}"] = point(b, pm, pctx)
 
     # ---- end to end through the entry point ----
     # One generation of warmup + steps + 1 tokens a sequence; the host's clock is read in the token
@@ -230,9 +238,21 @@ def main():
     def on_token(i, _tok):
         if i == args.batch - 1:                       # the last sequence of a step's tokens
             stamps.append(time.perf_counter())
+    t_gen = time.perf_counter()
     runner.generate(prompts, mk(args.warmup + args.steps + 1), on_token=on_token)
     assert len(stamps) == args.warmup + args.steps + 1
     e2e_value = args.batch * args.steps / (stamps[args.warmup + args.steps] - stamps[args.warmup])
+    # the same generation from its first decoded token on (the steps right behind the prompt step
+    # run at the clocks that step's power draw left behind), and with the prompt step included
+    e2e_from_first = args.batch * (args.warmup + args.steps) / (stamps[-1] - stamps[0])
+    e2e_with_prompt = args.batch * (args.warmup + args.steps + 1) / (stamps[-1] - t_gen)
+    # the reference's default sampler (top-k 40, top-p 0.9, repeat penalty 1.1; src/sampling.rs:30-52)
+    # instead of plain temperature sampling: the path a user of the reference's defaults gets
+    ref_s = SamplerConfig.reference_defaults()
+    stamps_ref = []
+    runner.generate(prompts, GenerationOptions(max_tokens=args.warmup + args.steps + 1, sampler=ref_s, seed=1, ignore_eos=True),
+                    on_token=lambda i, _t: stamps_ref.append(time.perf_counter()) if i == args.batch - 1 else None)
+    e2e_ref_sampler = args.batch * args.steps / (stamps_ref[args.warmup + args.steps] - stamps_ref[args.warmup])
     # per single-token step: 7B+1 int32 (tokens, positions, slots, offsets, lengths, wanted rows)
     # and 3B float32 for the sampler (temperature, uniform, min_p), all from pinned memory
     h2d_per_step = (7 * args.batch + 1) * 4 + 3 * args.batch * 4
@@ -271,12 +291,16 @@ def main():
                    "e2e_loop": "each step copies its integers from pinned memory and its sampled ids back; "
                                "a step is queued before the host has read the previous step's ids"},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d_per_step),
-                "d2h_bytes_per_step": 4 * args.batch},
+                "d2h_bytes_per_step": 4 * args.batch,
+                "window": f"steps {args.warmup + 1} to {args.warmup + args.steps} of one generation, as the device-timed arm",
+                "from_first_decoded_token": e2e_from_first, "with_prompt_step": e2e_with_prompt,
+                "reference_default_sampler": e2e_ref_sampler},
         "gpu_launches": launches,
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / peaks["hbm_gbs"]},
         "points": points,
+        "point_details": dict(point_details, **{f"decode_b{args.batch}": point(args.batch, ms, ctx_tokens)}),
         "cpu_baseline": cpu,
         "clocks": clock_info,
     }

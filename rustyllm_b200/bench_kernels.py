@@ -1,7 +1,7 @@
 """Times one kernel of the library alone, at a chosen shape, on random data.
 
     python -m rustyllm_b200.bench_kernels gemm --m 8 --n 28672 --k 4096 [--mode same|f32|add|swiglu] [--parts 0]
-    python -m rustyllm_b200.bench_kernels attention-decode --batch 8 --context 800 [--splits 0] [--contexts 1761,1350,159]
+    python -m rustyllm_b200.bench_kernels attention-decode --batch 8 --context 800 [--splits 0] [--contexts 1761,1350,159 | --context-range 128,2048]
     python -m rustyllm_b200.bench_kernels attention-prefill --tokens 2048
     python -m rustyllm_b200.bench_kernels rmsnorm | swiglu | rope --m 8
     python -m rustyllm_b200.bench_kernels sample --m 8 --n 128256 [--greedy]
@@ -83,6 +83,10 @@ def _cache(batch: int, context: int, G: int, hd: int, layers: int):
 def attention_decode(a) -> None:
     H, G, hd = a.heads, a.kv_heads, a.head_dim
     lens = [int(x) for x in a.contexts.split(",")] if a.contexts else [a.context] * a.batch
+    if a.context_range:                      # seeded uniform draw, as the benchmarks' prompts
+        lo, hi = (int(x) for x in a.context_range.split(","))
+        g = torch.Generator().manual_seed(0)
+        lens = torch.randint(lo, hi, (a.batch,), generator=g).tolist()
     a.batch, a.context = len(lens), max(lens)
     kv_bytes = sum(lens) * G * hd * 2 * 2
     layers = max(2, min(8, int(300e6 // kv_bytes) + 1))
@@ -95,7 +99,7 @@ def attention_decode(a) -> None:
     plan = K.decode_plan(slots, kv, 0, sp) if a.batch > 1 and not a.cluster else None    # once a step, as the engine makes it
     us = _time(lambda i: K.attention_decode(q, pools[i % layers][0], pools[i % layers][1], pt, slots, kv, out, H, G, hd,
                                             1 / math.sqrt(hd), num_splits=sp, plan=plan, cluster=a.cluster), a.warmup, a.reps)
-    print(f"attention_decode B={a.batch} context={a.contexts or a.context} H={H} G={G} hd={hd} splits={sp}: "
+    print(f"attention_decode B={a.batch} context={a.contexts or a.context_range or a.context} (mean {sum(lens) / len(lens):.0f}) H={H} G={G} hd={hd} splits={sp}: "
           f"{us:.2f} us, {kv_bytes / us / 1e6:.2f} TB/s of cache")
 
 
@@ -158,6 +162,7 @@ def main(argv=None) -> int:
     p.add_argument("--mode", default="same", choices=["same", "f32", "add", "swiglu"]); p.add_argument("--parts", type=int, default=0)
     p.add_argument("--batch", type=int, default=8); p.add_argument("--context", type=int, default=800)
     p.add_argument("--contexts", default="", help="attention-decode: comma-separated lengths, one per sequence (instead of --batch/--context)")
+    p.add_argument("--context-range", default="", help="attention-decode: LO,HI - lengths drawn uniformly from [LO, HI) with a fixed seed")
     p.add_argument("--splits", type=int, default=0); p.add_argument("--tokens", type=int, default=2048)
     p.add_argument("--heads", type=int, default=32); p.add_argument("--kv-heads", type=int, default=8)
     p.add_argument("--head-dim", type=int, default=128); p.add_argument("--hidden", type=int, default=4096)

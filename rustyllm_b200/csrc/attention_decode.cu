@@ -28,8 +28,9 @@
 // pieces and the CTAs carry equal loads.  The plan depends on the lengths only, so one
 // plan serves every layer of a step; the grid depends on the batch's size only (a
 // captured step keeps it while the lengths change).  With one chunk per sequence there is
-// no plan and the CTA writes the output; otherwise it writes its (max, sum, unnormalised
-// output) to scratch and a second kernel combines a sequence's chunks in chunk order.
+// no plan and the CTA writes the output; otherwise a sequence of one chunk is still written by
+// its CTA, and the chunks of a longer one write their (max, sum, unnormalised output) to
+// scratch and a second kernel combines them in chunk order.
 // Without a plan every sequence gets `splits` chunks (one sequence needs no dealing).
 // A third way needs no scratch and no second kernel: with 2, 4 or 8 equal chunks a sequence
 // the chunks' CTAs form a thread-block cluster, leave their (max, sum, output) in their own
@@ -187,7 +188,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
   const int m = H / G;                                   // query heads per KV head (<= 16)
   // which sequence, and which share of its keys
   int b = blockIdx.x, split = 0, num_splits = 1, len, cache_slot;
-  const bool direct = plan == nullptr && even_splits == 1;   // one chunk per sequence: no scratch
   const bool clustered = dec_cluster_size() > 1;          // the chunks of a sequence are the CTAs of a cluster
   if (plan == nullptr) {                                 // no plan: every sequence in `even_splits` chunks
     b = blockIdx.x / even_splits; split = blockIdx.x % even_splits; num_splits = even_splits;
@@ -197,6 +197,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
     if (e.x < 0) return;                                 // spare chunk
     b = e.x; split = e.y & 0xffff; num_splits = e.y >> 16; len = e.z; cache_slot = e.w;
   }
+  // a sequence that is one chunk (always so without splits; with a plan, the short ones beside
+  // long ones) is finished here: no scratch, nothing for the combining kernel to do
+  const bool direct = num_splits == 1;
   const int start = (window > 0 && len - window > 0) ? len - window : 0;
   const int* pages = page_table + (size_t)cache_slot * max_pages;
 
@@ -413,6 +416,7 @@ __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o
     first = fc.x; count = fc.y;
   }
   rl_pdl_wait();
+  if (count == 1) return;        // written by its only chunk
   float M = -INFINITY;
   for (int s = 0; s < count; ++s) M = fmaxf(M, part_ml[2 * ((size_t)(first + s) * H + h)]);
   for (int d = threadIdx.x; d < HD; d += blockDim.x) {

@@ -194,7 +194,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ page_table, int max_pages,
                             const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slots,
                             const int* __restrict__ kv_lens, int num_seqs, __nv_bfloat16* __restrict__ out, int ldo,
-                            int H, int G, float scale_log2e, int window, int* __restrict__ err) {
+                            int H, int G, float scale_log2e, int window, int* __restrict__ err,
+                            const int* __restrict__ tile_order) {
   extern __shared__ uint8_t fa_smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)fa_smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* q_tile = smem;                                   // [2 halves][128 x 64]
@@ -247,15 +248,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   rl_pdl_wait();       // everything below reads what earlier kernels of the step wrote
-  // ---- which sequence and which of its 128-row query tiles (heaviest first) ----
+  // ---- which sequence and which of its 128-row query tiles.  The grid is (heads, tiles) and
+  // blocks start in the order of the grid: with the caller's table the tiles come by falling
+  // number of keys, all heads of the heaviest tile first, so the last blocks to start are the
+  // lightest; without it, the tiles of the step in reverse (right for one sequence) ----
   if (threadIdx.x == 32) {
-    int t = (int)(gridDim.x - 1 - blockIdx.x), b = 0;
-    for (; b < num_seqs; ++b) {
-      const int tiles = (cu_seqlens[b + 1] - cu_seqlens[b] + TQ - 1) / TQ;
-      if (t < tiles) break;
-      t -= tiles;
+    if (tile_order != nullptr) {
+      *s_seq = tile_order[2 * blockIdx.y]; *s_tile = tile_order[2 * blockIdx.y + 1];
+    } else {
+      int t = (int)(gridDim.y - 1 - blockIdx.y), b = 0;
+      for (; b < num_seqs; ++b) {
+        const int tiles = (cu_seqlens[b + 1] - cu_seqlens[b] + TQ - 1) / TQ;
+        if (t < tiles) break;
+        t -= tiles;
+      }
+      *s_seq = b; *s_tile = t;
     }
-    *s_seq = b; *s_tile = t;
   }
   fa_fence_before();
   __syncthreads();
@@ -265,7 +273,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const uint32_t tmem_s0 = tmem_base, tmem_o = tmem_base + 256, tmem_p = tmem_base + 256 + HD;
   const int b = *s_seq;
   const bool have_work = b < num_seqs;      // the grid is sized exactly; defensive
-  const int h = blockIdx.y, gkv = h / (H / G);
+  const int h = blockIdx.x, gkv = h / (H / G);
   int row0 = 0, q_len = 0, kv_len = 0, qt0 = 0, rows_here = 0, kt_begin = 0, kt_end = 0, start_pos = 0;
   const int* pages = page_table;
   if (have_work) {
@@ -610,17 +618,19 @@ extern "C" int rl_attention_prefill_tc_supported(int num_heads, int num_kv_heads
 
 // Same contract as rl_attention_prefill, with num_tiles = sum over sequences of
 // ceil(tokens / 128), num_pages = pages in the cache pools, and err = device int that is set
-// non-zero if a bounded wait in the kernel ran out.  The pools must hold finite values
+// non-zero if a bounded wait in the kernel ran out.  tile_order (may be null): num_tiles pairs
+// (sequence, tile of the sequence), every tile of the step once, in the order the blocks should
+// start in (heaviest first).  The pools must hold finite values
 // everywhere (see the note at the top of this file).
 extern "C" int rl_attention_prefill_tc(const void* q, int ldq, const void* k_pool, const void* v_pool, int num_pages,
                                        const int* page_table, int max_pages, const int* cu_seqlens,
                                        const int* seq_slots, const int* kv_lens, int num_seqs, int num_tiles,
                                        int num_tokens, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim,
-                                       float scale, int window, int* err, cudaStream_t stream) {
+                                       float scale, int window, int* err, const int* tile_order, cudaStream_t stream) {
   RL_REQUIRE(rl_attention_prefill_tc_supported(num_heads, num_kv_heads, head_dim),
              "rl_attention_prefill_tc: unsupported shape (heads %d, KV heads %d, head_dim %d): needs head_dim 64 or 128",
              num_heads, num_kv_heads, head_dim);
-  RL_REQUIRE(num_seqs >= 0 && num_tiles >= 0 && num_tokens >= 0 && num_pages > 0 && num_heads <= 65535, "rl_attention_prefill_tc: bad sizes");
+  RL_REQUIRE(num_seqs >= 0 && num_tiles >= 0 && num_tokens >= 0 && num_pages > 0 && num_tiles <= 65535, "rl_attention_prefill_tc: bad sizes");
   RL_REQUIRE(ldq >= num_heads * head_dim && ldq % 8 == 0 && ldo >= num_heads * head_dim && ldo % 8 == 0,
              "rl_attention_prefill_tc: row strides must be multiples of 8 elements and hold all heads");
   RL_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)k_pool & 15) == 0 && ((uintptr_t)v_pool & 15) == 0,
@@ -644,12 +654,12 @@ extern "C" int rl_attention_prefill_tc(const void* q, int ldq, const void* k_poo
   rc = fa_make_map(&mv, v_pool, pool_rows, head_dim, head_dim, RL_PAGE);
   if (rc != RL_OK) return rc;
   cudaError_t e = head_dim == 128
-      ? rl_launch_pdl(attention_prefill_tc_kernel<128>, dim3(num_tiles, num_heads), dim3(FA_THREADS), (size_t)FaSizes<128>::SMEM, stream,
+      ? rl_launch_pdl(attention_prefill_tc_kernel<128>, dim3(num_heads, num_tiles), dim3(FA_THREADS), (size_t)FaSizes<128>::SMEM, stream,
                       mq, mk, mv, page_table, max_pages, cu_seqlens, seq_slots, kv_lens, num_seqs,
-                      (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, scale * 1.4426950408889634f, window, err)
-      : rl_launch_pdl(attention_prefill_tc_kernel<64>, dim3(num_tiles, num_heads), dim3(FA_THREADS), (size_t)FaSizes<64>::SMEM, stream,
+                      (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, scale * 1.4426950408889634f, window, err, tile_order)
+      : rl_launch_pdl(attention_prefill_tc_kernel<64>, dim3(num_heads, num_tiles), dim3(FA_THREADS), (size_t)FaSizes<64>::SMEM, stream,
                       mq, mk, mv, page_table, max_pages, cu_seqlens, seq_slots, kv_lens, num_seqs,
-                      (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, scale * 1.4426950408889634f, window, err);
+                      (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, scale * 1.4426950408889634f, window, err, tile_order);
   if (e != cudaSuccess) {
     rl_set_error("rl_attention_prefill_tc: launch failed: %s", cudaGetErrorString(e));
     return RL_ERR_CUDA;

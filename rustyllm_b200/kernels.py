@@ -57,7 +57,7 @@ _SIGNATURES = {
     "rl_attention_prefill_supported": [_c_int, _c_int, _c_int],
     "rl_attention_prefill_tc": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
                                 _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float,
-                                _c_int, _c_void_p, _c_void_p],
+                                _c_int, _c_void_p, _c_void_p, _c_void_p],
     "rl_attention_prefill_tc_supported": [_c_int, _c_int, _c_int],
     "rl_gemm_tc_supported": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int],
     "rl_gemm_tc": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -66,7 +66,7 @@ _SIGNATURES = {
     "rl_gemm_tc_qkv_rope_supported": [_c_int, _c_int, _c_int, _c_int, _c_int, _c_int],
     "rl_gemm_tc_qkv_rope": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                             _c_void_p, _c_int, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int,
-                            _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
+                            _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
 }
 
 
@@ -397,8 +397,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_mode: int,
 def gemm_tc_qkv_rope_supported(a: torch.Tensor, w: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
                                rotary_dim: int) -> bool:
     """Whether the QKV product of these operands can carry the rotary encoding and the cache
-    write in its epilogue (head size 128 rotated whole, up to 64 tokens, a product that is
-    split over K)."""
+    write in its epilogue (head size 128 or 64 rotated whole, up to 64 tokens, a product that
+    is split over K)."""
     if not gemm_tc_supported(a, w, None) or w.shape[0] != (num_heads + 2 * num_kv_heads) * head_dim:
         return False
     return bool(library().rl_gemm_tc_qkv_rope_supported(a.shape[0], num_heads, num_kv_heads, head_dim, rotary_dim, a.shape[1]))
@@ -411,20 +411,23 @@ def gemm_tc_qkv_rope(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: 
                      row_sumsq: Optional[torch.Tensor] = None, row_eps: float = 0.0) -> None:
     """qkv = a @ w.T (+ bias) with rotary encoding of the query and key heads and the write of
     keys and values into the paged cache, all in the product's epilogue.  Of ``out``
-    [M, (H + 2G) * 128] bf16 only the query heads are written; keys and values go to the
-    pools (``None``: nowhere).  ``row_sumsq`` / ``row_eps``: as in ``gemm_tc``."""
+    [M, (H + 2G) * head_dim] bf16 only the query heads are written; keys and values go to the
+    pools (``None``: nowhere).  The head size (128 or 64) follows from ``w``'s rows.
+    ``row_sumsq`` / ``row_eps``: as in ``gemm_tc``."""
     _need(a, "a", torch.bfloat16, contiguous=False); _need(w, "w", torch.bfloat16); _need(out, "out", torch.bfloat16, contiguous=False)
     _need(positions, "positions", torch.int32); _need(slot_of_token, "slot_of_token", torch.int32)
     _need(page_table, "page_table", torch.int32); _need(inv_freq, "inv_freq", torch.float32)
     M, K = a.shape
-    assert w.shape == ((num_heads + 2 * num_kv_heads) * 128, K) and out.shape == (M, w.shape[0]) and out.stride(1) == 1
-    assert positions.numel() == M and slot_of_token.numel() == M and inv_freq.numel() == 64
+    hd = w.shape[0] // (num_heads + 2 * num_kv_heads)
+    assert hd in (64, 128) and w.shape == ((num_heads + 2 * num_kv_heads) * hd, K)
+    assert out.shape == (M, w.shape[0]) and out.stride(1) == 1
+    assert positions.numel() == M and slot_of_token.numel() == M and inv_freq.numel() == hd // 2
     if bias is not None:
         _need(bias, "bias", torch.float32)
         assert bias.numel() == w.shape[0]
     if k_pool is not None:
         _need(k_pool, "k_pool", torch.bfloat16); _need(v_pool, "v_pool", torch.bfloat16)
-        assert k_pool.shape[1:] == (num_kv_heads, PAGE_SIZE, 128) and v_pool.shape == k_pool.shape
+        assert k_pool.shape[1:] == (num_kv_heads, PAGE_SIZE, hd) and v_pool.shape == k_pool.shape
     pieces = 0
     if row_sumsq is not None:
         _need(row_sumsq, "row_sumsq", torch.float32)
@@ -435,7 +438,7 @@ def gemm_tc_qkv_rope(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: 
     _check(library().rl_gemm_tc_qkv_rope(
         a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), M, K, lda, ldo, _tc_error_word(a.device).data_ptr(),
         _ptr(row_sumsq), pieces, float(row_eps), positions.data_ptr(), slot_of_token.data_ptr(), page_table.data_ptr(),
-        page_table.shape[1], inv_freq.data_ptr(), 1 if interleaved else 0, num_heads, num_kv_heads,
+        page_table.shape[1], inv_freq.data_ptr(), 1 if interleaved else 0, num_heads, num_kv_heads, hd,
         _ptr(k_pool), _ptr(v_pool), _stream()), "rl_gemm_tc_qkv_rope")
     _count()
 
@@ -462,10 +465,14 @@ def attention_decode_supported(dtype: torch.dtype, num_heads: int, num_kv_heads:
 def decode_splits(num_seqs: int, num_kv_heads: int) -> int:
     """Splits of the context per (sequence, KV head): enough CTAs for about one and a
     half per SM, at most 8 for a batch and 16 for one sequence (measured best at 1 to 64
-    sequences of 800 and 4,096 tokens).  Depends on the batch's size only, so that a
+    sequences of 800 and 4,096 tokens), and at least 2 for a batch, so that its chunks are
+    dealt by length: beside short sequences a long one is then cut in pieces (64 sequences of
+    256 to 8,700 tokens: 115 us as one chunk each, 95 us dealt), and a sequence that remains
+    one chunk costs nothing more for it.  Depends on the batch's size only, so that a
     captured step keeps its grid."""
     most = 16 if num_seqs == 1 else 8
-    return max(1, min(most, -(-3 * num_sms() // (2 * num_seqs * num_kv_heads))))
+    least = 1 if num_seqs == 1 else 2
+    return max(least, min(most, -(-3 * num_sms() // (2 * num_seqs * num_kv_heads))))
 
 
 def decode_scratch_floats(num_seqs: int, num_heads: int, head_dim: int, num_splits: int) -> int:
@@ -561,6 +568,20 @@ def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
 PREFILL_TC_QTILE = 128
 
 
+def prefill_tile_order(q_lens, kv_lens, device) -> torch.Tensor:
+    """For the tcgen05 prefill attention: the step's 128-query tiles as (sequence, tile of the
+    sequence) pairs by falling number of keys (a tile attends to its sequence's cached prefix and
+    to the step's tokens up to its own last one), int32 [tiles, 2] on the device.  Made once a
+    step from the host's copies of the lengths and used by every layer."""
+    items = []
+    for b, (nq, nkv) in enumerate(zip(q_lens, kv_lens)):
+        first = nkv - nq
+        for t in range(-(-nq // PREFILL_TC_QTILE)):
+            items.append((-(first + min(nq, (t + 1) * PREFILL_TC_QTILE)), b, t))
+    items.sort()
+    return torch.tensor([[b, t] for _, b, t in items], dtype=torch.int32).to(device, non_blocking=True)
+
+
 def attention_prefill_tc_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
     return dtype == torch.bfloat16 and bool(library().rl_attention_prefill_tc_supported(num_heads, num_kv_heads, head_dim))
 
@@ -568,9 +589,10 @@ def attention_prefill_tc_supported(dtype: torch.dtype, num_heads: int, num_kv_he
 def attention_prefill_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
                          cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, kv_lens: torch.Tensor, q_lens,
                          out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                         window: int = 0) -> None:
-    """The same as ``attention_prefill`` on tcgen05 tensor cores (head size 128).  The cache pools
-    must hold finite values everywhere (the cache zero-fills them when it allocates them)."""
+                         window: int = 0, tile_order: Optional[torch.Tensor] = None) -> None:
+    """The same as ``attention_prefill`` on tcgen05 tensor cores (head size 64 or 128).  The cache
+    pools must hold finite values everywhere (the cache zero-fills them when it allocates them).
+    ``tile_order``: what ``prefill_tile_order`` made for this step (the blocks then start heaviest first)."""
     _need(q, "q", torch.bfloat16, contiguous=False); _need(k_pool, "k_pool", torch.bfloat16)
     _need(v_pool, "v_pool", torch.bfloat16); _need(out, "out", torch.bfloat16)
     _need(page_table, "page_table", torch.int32); _need(cu_seqlens, "cu_seqlens", torch.int32)
@@ -579,12 +601,15 @@ def attention_prefill_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
     assert cu_seqlens.numel() == B + 1 and seq_slots.numel() == B and kv_lens.numel() == B
     assert q.shape[0] == sum(q_lens) and q.stride(1) == 1
     tiles = sum(-(-n // PREFILL_TC_QTILE) for n in q_lens)
+    if tile_order is not None:
+        _need(tile_order, "tile_order", torch.int32)
+        assert tile_order.numel() == 2 * tiles
     ldq = q.stride(0) if q.shape[0] > 1 else max(q.stride(0), num_heads * head_dim)
     _check(library().rl_attention_prefill_tc(
         q.data_ptr(), ldq, k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0], page_table.data_ptr(),
         page_table.shape[1], cu_seqlens.data_ptr(), seq_slots.data_ptr(), kv_lens.data_ptr(), B, tiles, q.shape[0],
         out.data_ptr(), out.stride(0), num_heads, num_kv_heads, head_dim, float(scale), int(window),
-        _tc_error_word(q.device).data_ptr(), _stream()), "rl_attention_prefill_tc")
+        _tc_error_word(q.device).data_ptr(), _ptr(tile_order), _stream()), "rl_attention_prefill_tc")
     _count()
 
 
@@ -620,8 +645,14 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
         return
     if not step.is_decode and attention_prefill_tc_supported(q.dtype, num_heads, num_kv_heads, head_dim) \
             and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0:
+        order = None
+        derived = getattr(step, "derived", None)
+        if derived is not None and len(step.q_lens) > 1:     # one sequence: the kernel's own reverse order is the heaviest first
+            order = derived.get("prefill_tile_order")
+            if order is None:
+                order = derived["prefill_tile_order"] = prefill_tile_order(step.q_lens, step.kv_lens_host, q.device)
         attention_prefill_tc(q, k_pool, v_pool, page_table, step.cu_seqlens, step.seq_slots, step.kv_lens,
-                             step.q_lens, out, num_heads, num_kv_heads, head_dim, scale, window)
+                             step.q_lens, out, num_heads, num_kv_heads, head_dim, scale, window, tile_order=order)
         return
     if not step.is_decode and attention_prefill_supported(q.dtype, num_heads, num_kv_heads, head_dim):
         attention_prefill(q, k_pool, v_pool, page_table, step.cu_seqlens, step.seq_slots, step.kv_lens,

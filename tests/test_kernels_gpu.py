@@ -340,27 +340,27 @@ def test_rope_kv_write(dtype, H, G, hd, rot, interleaved):
     assert torch.equal(v_pool.permute(0, 2, 1, 3)[keep], v_before.permute(0, 2, 1, 3)[keep])
 
 
+@pytest.mark.parametrize("hd", [128, 64])
 @pytest.mark.parametrize("interleaved", [False, True])
 @pytest.mark.parametrize("M,H,G,K_,normed,store", [(1, 3, 1, 1024, False, True), (8, 3, 1, 1024, True, True),
                                                   (11, 2, 2, 2048, False, True), (33, 4, 2, 512, True, True),
-                                                  (11, 3, 1, 1024, False, False)])
-def test_gemm_tc_qkv_rope_is_the_product_then_the_rotation_and_the_cache_write(M, H, G, K_, normed, store, interleaved):
+                                                  (11, 3, 1, 1024, False, False), (64, 32, 8, 2048, True, True)])
+def test_gemm_tc_qkv_rope_is_the_product_then_the_rotation_and_the_cache_write(M, H, G, K_, normed, store, interleaved, hd):
     """The QKV product with rotation and cache write in its epilogue, against float64:
     product, (finished norm,) bias, rotation of query and key heads, keys and values at
     their tokens' places of the paged cache, nothing else in the pools touched."""
     k = K()
-    hd = 128
-    N = (H + 2 * G) * hd
+    N = (H + 2 * G) * hd              # head size 64: two heads a tile of 128 columns; 5 heads leave the last tile half empty
     x = _rand(M, K_, seed=51, scale=2.0)
     g = _rand(K_, seed=52) * 0.3 + 1.0
     a = (x * g).to(torch.bfloat16) if normed else x.to(torch.bfloat16)
     w = _rand(N, K_, dtype=torch.bfloat16, seed=53, scale=0.05)
     bias = _rand(N, seed=54, scale=0.5)
     assert k.gemm_tc_qkv_rope_supported(a, w, H, G, hd, hd)
-    assert not k.gemm_tc_qkv_rope_supported(a, w, H, G, hd, 64)          # partial rotation: the separate kernel
-    positions = torch.tensor(([0, 1, 63, 64, 65, 200, 5, 6, 7, 130, 131] * 3)[:M], dtype=torch.int32, device=DEV)
-    slot_of_token = torch.tensor(([0, 0, 0, 0, 0, 0, 2, 2, 2, 2, 2] + [1] * 11 + [3] * 11)[:M], dtype=torch.int32, device=DEV)
-    page_table = torch.tensor([[7, 3, 1, 9], [10, 11, 12, 13], [2, 8, 4, 5], [14, 15, 16, 17]], dtype=torch.int32, device=DEV)
+    assert not k.gemm_tc_qkv_rope_supported(a, w, H, G, hd, hd // 2)     # partial rotation: the separate kernel
+    positions = torch.tensor(([0, 1, 63, 64, 65, 200, 5, 6, 7, 130, 131] * 3 + list(range(31)))[:M], dtype=torch.int32, device=DEV)
+    slot_of_token = torch.tensor(([0, 0, 0, 0, 0, 0, 2, 2, 2, 2, 2] + [1] * 11 + [3] * 11 + [4] * 31)[:M], dtype=torch.int32, device=DEV)
+    page_table = torch.tensor([[7, 3, 1, 9], [10, 11, 12, 13], [2, 8, 4, 5], [14, 15, 16, 17], [0, 6, 6, 6]], dtype=torch.int32, device=DEV)
     inv = torch.tensor([1.0 / (10000.0 ** (2 * i / hd)) for i in range(hd // 2)], device=DEV)
     k_pool, v_pool = _paged(G, hd, 18, torch.bfloat16)
     k_before, v_before = k_pool.clone(), v_pool.clone()
