@@ -119,8 +119,24 @@ class DecoderModel:
                              max_slots=max_slots, max_seq_len=max_seq_len)
 
     # ------------------------------------------------------------------ running
+    use_native = True      # run the step's launch chain in native code where the model consists of parts it knows
+
+    def native_for(self, cache: SequenceCache):
+        """The native executor of this model on ``cache`` (csrc/decoder_forward.cu), or ``None``
+        if a part of the model is not one it knows: then the Python parts launch the same kernels."""
+        if not self.use_native:
+            return None
+        made = getattr(self, "_native", None)
+        if made is None or made[0] is not cache:
+            from .. import native
+            made = self._native = (cache, native.NativeDecoder(self, cache) if native.eligible(self, cache) else None)
+        return made[1]
+
     def forward(self, step, cache: SequenceCache) -> torch.Tensor:
         """All tokens of the step through all scheduled layers: float32 [M, d]."""
+        nat = self.native_for(cache)
+        if nat is not None:
+            return nat.forward(step)
         x = self.embedding.forward(step)
         schedule = self.spec.schedule
         pending = None      # the next block's first norm, started by the block in front of it
@@ -146,5 +162,8 @@ class DecoderModel:
         """Final norm and head at the wanted rows only: float32 [len(rows), V]
         (the reference computes the head for the last prompt token only,
         src/runtime.rs:3405-3427)."""
+        made = getattr(self, "_native", None)
+        if self.use_native and made is not None and made[1] is not None:
+            return made[1].logits(x, rows)
         xn = self.final_norm.forward(x, self.runtime.compute_dtype, rows)
         return self.head.forward(xn)

@@ -176,6 +176,7 @@ def test_folded_norms_save_launches_and_give_the_norm_kernels_results(model_dirs
     for mode, limit in (("folded", linear.FOLD_NORMS_UP_TO), ("kernels", 0)):
         monkeypatch.setattr(linear, "FOLD_NORMS_UP_TO", limit)
         r = load_runner(d, "bfloat16")
+        monkeypatch.setattr(type(r.model), "use_native", False)      # the Python parts read the limit; the native executor has its own
         s = r.engine.alloc_slot()
         before = kernels.launch_count
         out[mode] = r.engine.step([s], [toks], "all")
@@ -184,3 +185,37 @@ def test_folded_norms_save_launches_and_give_the_norm_kernels_results(model_dirs
         assert_close_logits(out[mode], ref, "bfloat16", f"{name} {mode}")
     assert launches["kernels"] - launches["folded"] == 2 * cfg["num_hidden_layers"] - 1
     assert not torch.equal(out["folded"], out["kernels"])      # the other order of roundings shows
+
+
+@pytest.mark.parametrize("name", ["B", "C", "D", "E", "F", "H"])
+def test_native_executor_and_python_parts_launch_the_same_chain(model_dirs, name, monkeypatch):
+    """The step's launch chain in native code (csrc/decoder_forward.cu) against the Python parts:
+    the same kernels with the same arguments, so the same bits - for a packed prompt step of
+    unequal lengths, a step of few tokens (norms folded into the products), a mixed step and
+    single-token steps, eager and captured."""
+    from rustyllm_b200 import Runner, kernels
+    d, cfg = model_dirs[name]
+    V = _vocab(cfg)
+    seqs = [random_tokens(V, n, 700 + i) for i, n in enumerate([150, 9, 70])]
+    out = {}
+    for mode in ("native", "python"):
+        monkeypatch.setattr("rustyllm_b200.models.decoder.DecoderModel.use_native", mode == "native")
+        r, _ = Runner.from_path(d, dtype="bfloat16", max_cache_tokens=64 * 12, max_batch=4)
+        eng = r.engine
+        assert (r.model.native_for(r.cache) is not None) == (mode == "native")
+        slots = [eng.alloc_slot() for _ in seqs]
+        before = kernels.launch_count
+        got = [eng.step(slots, [s[:n] for s, n in zip(seqs, (140, 3, 64))], "all")]          # 207 tokens: norm kernels
+        got.append(eng.step(slots[1:], [seqs[1][3:8], seqs[2][64:69]], "all"))               # 10 tokens: folded norms
+        got.append(eng.step(slots, [seqs[0][140:149], seqs[1][8:9], seqs[2][69:70]], "last"))   # mixed
+        for _ in range(3):                                                                    # eager, then captured
+            got.append(eng.step([slots[0]], [[seqs[0][149]]], "last"))
+            eng.cache.lengths[slots[0]] -= 1                                                  # feed the same position again
+        out[mode] = (torch.cat(got), kernels.launch_count - before)
+        for s in slots:
+            eng.free_slot(s)
+        kernels.check_device_errors()
+    assert torch.equal(out["native"][0], out["python"][0])
+    assert out["native"][1] == out["python"][1], "both count the same launches"
+    ref = plain_logits(d, seqs[0])
+    assert_close_logits(out["native"][0][:140], ref[:140], "bfloat16", f"{name} native prompt")
