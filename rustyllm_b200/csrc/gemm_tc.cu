@@ -47,14 +47,18 @@
 
 #include "tc_device.cuh"
 
-template <int BT>
+// DEEP (few tokens only): two CTAs an SM with rings half as deep again, for products whose whole
+// grid fits two CTAs an SM.  A CTA streams at (bytes it has in flight) / latency, so a grid that
+// leaves SMs half empty is the faster the more each of its CTAs has in flight - and the more
+// weights it has asked for before the kernel in front of it has finished.
+template <int BT, bool DEEP = false>
 struct TcConfig {
   static constexpr int STAGE_BYTES = (BLOCK_N_OUT + BT) * BLOCK_K * 2;
   // few tokens: the product streams weights, three stages a CTA and three or four CTAs an
   // SM keep more loads in flight than one deep ring; many tokens: one CTA, a deep ring
-  static constexpr int RING_BYTES_MAX = BT <= 64 ? 73728 : 196608;
+  static constexpr int RING_BYTES_MAX = BT <= 64 ? (DEEP ? 110592 : 73728) : 196608;
   static constexpr int STAGES = (RING_BYTES_MAX / STAGE_BYTES) < 8 ? (RING_BYTES_MAX / STAGE_BYTES) : 8;
-  static constexpr int MIN_CTAS = BT <= 64 ? 3 : 1;
+  static constexpr int MIN_CTAS = BT <= 64 ? (DEEP ? 2 : 3) : 1;
   static constexpr int TMEM_COLS = BT < 32 ? 32 : BT;
   static constexpr int FUSE_FLOATS = 3 * BT;       // the tile's row scales; its tokens' positions and cache rows
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + FUSE_FLOATS * 4;
@@ -173,12 +177,12 @@ __device__ __forceinline__ void tile_epilogue(uint32_t tmem_acc, int quarter, in
 
 // BT: tokens per CTA (MMA N).  Grid: (parts * ceil(N_out / 128), ceil(M_tokens / BT)) in
 // clusters of `parts` CTAs along x; the CTA's rank in its cluster is its part of K.
-template <int BT>
-__global__ void __launch_bounds__(TC_THREADS, TcConfig<BT>::MIN_CTAS)
+template <int BT, bool DEEP>
+__global__ void __launch_bounds__(TC_THREADS, TcConfig<BT, DEEP>::MIN_CTAS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                const float* __restrict__ bias, void* __restrict__ out, int out_mode, int M, int N, int K,
                int ldo, int* __restrict__ err, int kb_per_split, const TcFuse fuse) {
-  using Cfg = TcConfig<BT>;
+  using Cfg = TcConfig<BT, DEEP>;
   extern __shared__ uint8_t smem_raw[];
   // tiles need 1024-byte alignment for the 128-byte swizzle pattern
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -599,14 +603,14 @@ int tc_make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, 
   return RL_OK;
 }
 
-template <int BT>
-static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, void* out, int out_mode,
+template <int BT, bool DEEP>
+static int launch_tc_as(const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, void* out, int out_mode,
                      int M, int N, int K, int ldo, int* err, int splits, int kb_per_split, const TcFuse& fuse,
                      cudaStream_t stream) {
-  using Cfg = TcConfig<BT>;
+  using Cfg = TcConfig<BT, DEEP>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BT, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     RL_REQUIRE(e == cudaSuccess, "rl_gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
     configured = true;
   }
@@ -631,12 +635,34 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, const float* 
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BT>, mw, ma, bias, out, out_mode, M, N, K, ldo, err, kb_per_split, fuse);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BT, DEEP>, mw, ma, bias, out, out_mode, M, N, K, ldo, err, kb_per_split, fuse);
   if (e != cudaSuccess) {
     rl_set_error("rl_gemm_tc: launch failed (%d parts): %s", splits, cudaGetErrorString(e));
     return RL_ERR_CUDA;
   }
   return RL_OK;
+}
+
+static int g_deep_rings = 1;
+// 1 (default): the deep-ring variant where it was measured to pay; 0: never (for measurements)
+extern "C" void rl_set_deep_rings(int enabled) { g_deep_rings = enabled ? 1 : 0; }
+
+// The deep-ring variant where the whole grid fits two CTAs an SM (up to 64 tokens) and the product
+// is not split over K, or the step has more than 32 tokens.  Measured on whole decode steps of the
+// 8B shape (ms a step, rings off / on for every such product / on by this rule): one sequence
+// 3.03 / 2.96 / 2.95, 8 sequences 3.18 / 3.23 / 3.18, 64 sequences 5.49 / 5.34 / 5.34.  With few
+// tokens the split products (QKV, O, down) lose more by leaving no room for the next kernel's
+// CTAs, which load their first weights while this one still runs, than their own rings gain.
+template <int BT>
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, void* out, int out_mode,
+                     int M, int N, int K, int ldo, int* err, int splits, int kb_per_split, const TcFuse& fuse,
+                     cudaStream_t stream) {
+  if constexpr (BT <= 64) {
+    const long long ctas = (long long)splits * ((N + BLOCK_N_OUT - 1) / BLOCK_N_OUT) * ((M + BT - 1) / BT);
+    if (g_deep_rings && (splits == 1 || BT == 64) && ctas <= 2LL * rl_num_sms())
+      return launch_tc_as<BT, true>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per_split, fuse, stream);
+  }
+  return launch_tc_as<BT, false>(mw, ma, bias, out, out_mode, M, N, K, ldo, err, splits, kb_per_split, fuse, stream);
 }
 
 // 1 if the tensor-core kernel takes these operands: TMA needs 16-byte aligned bases
