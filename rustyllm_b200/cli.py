@@ -207,7 +207,18 @@ def run_benchmark(runner, info, prompts, opts, runs: int, as_json: bool, with_ou
         if not as_json:
             print(f"run {run + 1}: prompt {p} tok, generated {g} tok, prefill {row['prefill_tok_s']:.1f} tok/s, "
                   f"decode {row['decode_tok_s']:.2f} tok/s")
-    summary = {"avg_prompt_tokens": tp / runs, "avg_generated_tokens": tg / runs, "avg_prefill_ms": tpre * 1e3 / runs,
+    # what a decode step has to read: every matrix once (the embedding table only where it is also the
+    # head) and the cache of the live sequences at their mean length over the run
+    m = runner.model
+    weights = m.parameter_bytes()
+    if m.head.weight.data_ptr() != m.embedding.weight.data_ptr():
+        weights -= m.embedding.weight.numel() * m.embedding.weight.element_size()
+    per_token = sum(g.bytes_per_token() for g in runner.cache.groups)
+    mean_live = tp / runs + tg / runs / 2.0
+    step_bytes = weights + per_token * mean_live
+    steps_s = (tg / len(prompts)) / max(tdec, 0.001)            # every sequence decodes one token a step
+    summary = {"decode_step_bytes": step_bytes, "decode_gb_s": step_bytes * steps_s / 1e9,
+               "avg_prompt_tokens": tp / runs, "avg_generated_tokens": tg / runs, "avg_prefill_ms": tpre * 1e3 / runs,
                "avg_decode_ms": tdec * 1e3 / runs, "avg_total_ms": ttot * 1e3 / runs, "avg_wall_ms": twall * 1e3 / runs,
                "aggregate_prefill_tok_s": tp / max(tpre, 0.001), "aggregate_decode_tok_s": tg / max(tdec, 0.001)}
     if as_json:
