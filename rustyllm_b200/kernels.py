@@ -36,6 +36,7 @@ _SIGNATURES = {
     "rl_rmsnorm": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_float, _c_void_p],
     "rl_swiglu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "rl_convert": [_c_void_p, _c_int, _c_void_p, _c_int, _c_ll, _c_void_p],
+    "rl_random_fill": [_c_void_p, _c_int, _c_ll, ctypes.c_ulonglong, _c_float, _c_float, _c_void_p],
     "rl_gemm_simt": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                      _c_int, _c_int, _c_void_p],
     "rl_rope_kv_write": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
@@ -188,6 +189,16 @@ def convert(src: torch.Tensor, dst: torch.Tensor) -> None:
     _need(src, "src"); _need(dst, "dst")
     assert src.numel() == dst.numel()
     _check(library().rl_convert(src.data_ptr(), _dt(src), dst.data_ptr(), _dt(dst), src.numel(), _stream()), "rl_convert")
+    _count()
+
+
+def random_fill(out: torch.Tensor, seed: int, mean: float, std: float) -> None:
+    """out[i] = mean + std * z_i with z_i the library's reproducible near-normal number i of
+    ``seed`` (csrc/random_fill.cu): the same values as ``weights.random_init.normal_values``
+    computes on the host, bit for bit."""
+    _need(out, "out")
+    _check(library().rl_random_fill(out.data_ptr(), _dt(out), out.numel(), int(seed) & ((1 << 64) - 1), float(mean), float(std),
+                                    _stream()), "rl_random_fill")
     _count()
 
 

@@ -28,6 +28,18 @@ def _tol(dtype):
     return dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-5)
 
 
+# ----------------------------------------------------------------------------- random weights
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("mean", [0.0, 1.0])
+def test_random_fill_gives_the_hosts_numbers_bit_for_bit(dtype, mean):
+    from rustyllm_b200.weights.random_init import normal_values
+    n, seed = 100003, (1 << 62) + 12345
+    out = torch.empty(n, dtype=dtype, device=DEV)
+    K().random_fill(out, seed, mean, 0.02)
+    host = torch.from_numpy(normal_values(seed, n, mean, 0.02)).to(dtype)
+    assert torch.equal(out.cpu(), host)
+
+
 # ----------------------------------------------------------------------------- elementwise
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_embedding_gathers_rows_and_flags_bad_ids(dtype):

@@ -102,3 +102,31 @@ def test_engines_at_real_widths(name):
     assert 2e-3 < noise < 3e-2, f"{name}: rounding noise of the plain implementation {noise:.2e} is not what this test was sized for"
     assert rms <= 1.25 * noise, f"{name}: bf16 engine rms error {rms:.2e} of a row's scale, rounding noise alone is {noise:.2e}"
     assert worst <= 6.5 * noise, f"{name}: bf16 engine worst error {worst:.2e}, rounding noise (rms) is {noise:.2e}"
+
+
+def test_a_written_folder_and_a_drawn_model_of_one_seed_are_the_same_model(tmp_path):
+    """Llama-3.1-8B's widths, two layers: the folder that ``write_random_model`` writes for a seed,
+    loaded by name (concatenated Q/K/V, interleaved gate and up rows at an intermediate size of
+    14,336), against the model ``Runner.from_config`` draws on the device for the same seed: the
+    same tensors bit for bit, hence the same logits.  (The drawn model is held to the plain
+    implementation above; this carries that to the loader at real widths.)"""
+    from rustyllm_b200 import Runner, write_random_model
+    cfg = dict(architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=1536, num_hidden_layers=2,
+               max_position_embeddings=1024, rms_norm_eps=1e-5, torch_dtype="bfloat16", **SHAPES["llama31_8b"])
+    d = write_random_model(str(tmp_path / "m"), cfg, seed=5, dtype="bfloat16", device="cuda:0")
+    loaded, info = Runner.from_path(d, dtype="bfloat16", max_cache_tokens=64 * 8, max_batch=2)
+    drawn = Runner.from_config(cfg, seed=5, dtype="bfloat16", max_cache_tokens=64 * 8, max_batch=2)
+    assert info.fp32_matrices == 0
+    for a, b in zip(loaded.model.blocks, drawn.model.blocks):
+        for name in ("wqkv", "wo"):
+            assert torch.equal(getattr(a.mixer, name), getattr(b.mixer, name)), name
+        for name in ("wgu", "wdown"):
+            assert torch.equal(getattr(a.feed_forward, name), getattr(b.feed_forward, name)), name
+    assert torch.equal(loaded.model.embedding.weight, drawn.model.embedding.weight)
+    toks = random_tokens(cfg["vocab_size"], 70, 3)
+    out = []
+    for r in (loaded, drawn):
+        s = r.engine.alloc_slot()
+        out.append(r.engine.step([s], [toks], "all"))
+        r.engine.free_slot(s)
+    assert torch.equal(out[0], out[1])

@@ -159,3 +159,32 @@ def test_random_folder_is_reproducible_and_seeded(tmp_path):
     nw = Checkpoint(n).tensor("model.norm.weight").float()
     assert 0.9 < nw.mean().item() < 1.1 and nw.std().item() > 0.005
     assert torch.all(ca.tensor("model.norm.weight").float() == 1.0)
+
+
+def test_random_numbers_are_a_function_of_seed_and_index_alone():
+    """The generator behind random weights: integer arithmetic and two float operations, so the
+    host code here and the device kernel give the same bits (the device half is a GPU test)."""
+    import numpy as np
+    from rustyllm_b200.weights.random_init import _tensor_seed, normal_values
+    v = normal_values(12345, 1 << 16, 0.0, 0.02)
+    assert v.dtype == np.float32 and abs(float(v.mean())) < 3e-4 and abs(float(v.std()) - 0.02) < 3e-4
+    assert float(np.abs(v).max()) <= 6 * 0.02
+    # literal values: element 0 of seed 12345 is the sum of the twelve 16-bit fields of three splitmix64 outputs
+    def sm(x):
+        m = (1 << 64) - 1
+        z = (x + 0x9E3779B97F4A7C15) & m
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & m
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & m
+        return z ^ (z >> 31)
+    for i in (0, 1, 77):
+        total = 0
+        for r in range(3):
+            h = sm(12345 + 3 * i + r)
+            total += (h & 0xffff) + ((h >> 16) & 0xffff) + ((h >> 32) & 0xffff) + (h >> 48)
+        assert v[i] == np.float32(total - 393210) * (np.float32(0.02) * np.float32(1 / 65536))
+    # part of a tensor is the beginning of the whole; another seed, other numbers; mean 1 for norm weights
+    assert np.array_equal(normal_values(12345, 100, 0.0, 0.02), v[:100])
+    assert not np.array_equal(normal_values(12346, 100, 0.0, 0.02), v[:100])
+    w = normal_values(7, 1000, 1.0, 0.02)
+    assert abs(float(w.mean()) - 1.0) < 3e-3
+    assert _tensor_seed(1, "a") != _tensor_seed(1, "b") != _tensor_seed(2, "b")
