@@ -73,9 +73,119 @@ gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ W, const float* 
   }
 }
 
+// Few tokens (up to 64), float operands: the product is a single pass over W, so what counts is
+// how many of its bytes are on their way at any time and how many warps an SM has to hide the
+// latency of a chain of dependent FFMAs.  A CTA of four warps takes 32 weight rows; 16-byte
+// asynchronous copies fill a ring of four stages of 64 k-values (8 KB of W a stage, the tokens'
+// slice of A beside it; 39 to 100 KB a CTA, five to two CTAs an SM); thread (lane, warp) holds
+// weight row `lane` and the tokens [warp * TM, (warp + 1) * TM) and reads its row four k-values
+// a load (rows 68 floats apart: no bank conflicts), the tokens' values as broadcasts.  Each
+// output element is still the chain fmaf(a[k], w[k], acc) over k = 0, 1, 2, ...: bit-equal to
+// the tiled kernel below.
+constexpr int STREAM_BN = 32, STREAM_BK = 64, STREAM_STAGES = 4, STREAM_WS = STREAM_BK + 4, STREAM_MAX_M = 64;
+template <int TM> constexpr int stream_smem() { return STREAM_STAGES * (STREAM_BN * STREAM_WS + 4 * TM * STREAM_BK) * 4; }
+
+__device__ __forceinline__ void stream_copy16(float* dst, const float* src, bool live) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  const int bytes = live ? 16 : 0;         // 0: the sixteen bytes are filled with zeros, nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+
+template <int TM>
+__global__ void __launch_bounds__(128)
+gemm_simt_stream_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
+                        void* __restrict__ out, int out_mode, int M, int N, int K, int lda, int ldo) {
+  extern __shared__ __align__(16) float stream_ring[];
+  float* Wt = stream_ring;                                                 // [STAGES][BN][WS]
+  float* At = stream_ring + STREAM_STAGES * STREAM_BN * STREAM_WS;          // [STAGES][4 TM][BK]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int n0 = blockIdx.x * STREAM_BN;
+  const int num_kb = (K + STREAM_BK - 1) / STREAM_BK;
+  auto fill = [&](int kb) {
+    const int s = kb % STREAM_STAGES, k0 = kb * STREAM_BK;
+    float* wt = Wt + s * STREAM_BN * STREAM_WS;
+    float* at = At + s * (4 * TM) * STREAM_BK;
+#pragma unroll
+    for (int i = 0; i < (STREAM_BN * STREAM_BK / 4) / 128; ++i) {
+      const int idx = tid + i * 128, r = idx / (STREAM_BK / 4), c = idx % (STREAM_BK / 4);
+      const bool live = n0 + r < N && k0 + 4 * c < K;
+      stream_copy16(wt + r * STREAM_WS + 4 * c, live ? W + (size_t)(n0 + r) * K + k0 + 4 * c : W, live);
+    }
+    for (int idx = tid; idx < 4 * TM * (STREAM_BK / 4); idx += 128) {
+      const int r = idx / (STREAM_BK / 4), c = idx % (STREAM_BK / 4);
+      const bool live = r < M && k0 + 4 * c < K;
+      stream_copy16(at + r * STREAM_BK + 4 * c, live ? A + (size_t)r * lda + k0 + 4 * c : A, live);
+    }
+  };
+  for (int kb = 0; kb < STREAM_STAGES - 1; ++kb) {
+    if (kb < num_kb) fill(kb);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  float acc[TM];
+#pragma unroll
+  for (int i = 0; i < TM; ++i) acc[i] = 0.f;
+  for (int kb = 0; kb < num_kb; ++kb) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(STREAM_STAGES - 2) : "memory");
+    __syncthreads();                       // stage kb has arrived for every thread; stage kb - 1 has been read by all
+    if (kb + STREAM_STAGES - 1 < num_kb) fill(kb + STREAM_STAGES - 1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const int s = kb % STREAM_STAGES;
+    const float* wt = Wt + s * STREAM_BN * STREAM_WS + lane * STREAM_WS;
+    const float* at = At + s * (4 * TM) * STREAM_BK + warp * TM * STREAM_BK;
+#pragma unroll 4
+    for (int k = 0; k < STREAM_BK; k += 4) {
+      const float4 w = *reinterpret_cast<const float4*>(wt + k);
+#pragma unroll
+      for (int i = 0; i < TM; ++i) {
+        const float4 a = *reinterpret_cast<const float4*>(at + i * STREAM_BK + k);
+        acc[i] = fmaf(a.x, w.x, acc[i]);
+        acc[i] = fmaf(a.y, w.y, acc[i]);
+        acc[i] = fmaf(a.z, w.z, acc[i]);
+        acc[i] = fmaf(a.w, w.w, acc[i]);
+      }
+    }
+  }
+  const int gn = n0 + lane;
+  if (gn >= N) return;
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int gm = warp * TM + i;
+    if (gm >= M) continue;
+    float v = acc[i];
+    if (bias) v += bias[gn];
+    const size_t o = (size_t)gm * ldo + gn;
+    if (out_mode == RL_OUT_ADD_F32) ((float*)out)[o] += v;
+    else ((float*)out)[o] = v;             // float operands: "same" and "float" are one
+  }
+}
+
+template <int TM>
+static int launch_gemm_simt_stream(const float* A, const float* W, const float* bias, void* out, int out_mode, int M, int N,
+                                   int K, int lda, int ldo, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_simt_stream_kernel<TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, stream_smem<TM>());
+    RL_REQUIRE(e == cudaSuccess, "rl_gemm_simt: cannot reserve %d bytes of shared memory: %s", stream_smem<TM>(), cudaGetErrorString(e));
+    configured = true;
+  }
+  gemm_simt_stream_kernel<TM><<<(N + STREAM_BN - 1) / STREAM_BN, 128, stream_smem<TM>(), stream>>>(A, W, bias, out, out_mode, M, N, K, lda, ldo);
+  RL_LAUNCH_CHECK("rl_gemm_simt");
+  return RL_OK;
+}
+
 template <typename T>
 static int launch_gemm_simt(const T* A, const T* W, const float* bias, void* out, int out_mode, int M,
                             int N, int K, int lda, int ldo, cudaStream_t stream) {
+  if constexpr (sizeof(T) == 4) {
+    // few tokens, rows that 16-byte copies can fetch: the streaming kernel
+    if (M <= STREAM_MAX_M && K % 4 == 0 && lda % 4 == 0 && (((uintptr_t)A | (uintptr_t)W) & 15) == 0) {
+      if (M <= 4) return launch_gemm_simt_stream<1>(A, W, bias, out, out_mode, M, N, K, lda, ldo, stream);
+      if (M <= 8) return launch_gemm_simt_stream<2>(A, W, bias, out, out_mode, M, N, K, lda, ldo, stream);
+      if (M <= 16) return launch_gemm_simt_stream<4>(A, W, bias, out, out_mode, M, N, K, lda, ldo, stream);
+      if (M <= 32) return launch_gemm_simt_stream<8>(A, W, bias, out, out_mode, M, N, K, lda, ldo, stream);
+      return launch_gemm_simt_stream<16>(A, W, bias, out, out_mode, M, N, K, lda, ldo, stream);
+    }
+  }
   if (M > 64) {
     dim3 grid((N + 127) / 128, (M + 127) / 128);
     gemm_simt_kernel<T, 128, 128, 8, 8, 8><<<grid, 256, 0, stream>>>(A, W, bias, out, out_mode, M, N, K, lda, ldo);

@@ -643,6 +643,7 @@ static int launch_tc_as(const CUtensorMap& mw, const CUtensorMap& ma, const floa
   return RL_OK;
 }
 
+
 static int g_deep_rings = 1;
 // 1 (default): the deep-ring variant where it was measured to pay; 0: never (for measurements)
 extern "C" void rl_set_deep_rings(int enabled) { g_deep_rings = enabled ? 1 : 0; }
@@ -679,11 +680,13 @@ static int token_tile(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64
 // How many parts (1, 2, 4 or 8: the cluster size) the K range is cut into for M tokens.
 // Up to 64 tokens: the smallest that gives about two CTAs an SM, with at least four 64-wide
 // K blocks a part; products with 148 tiles or more are not split.  Above 64 tokens (one CTA
-// an SM): the largest that still fits one wave of 148 CTAs, if the tiles alone fill no more
-// than a quarter of it - a CTA cannot pull more than about 80 GB/s, so a product with few
-// tiles needs more CTAs to stream its weights (4,096 x 14,336 weights, 256 tokens: 74 us as
-// 32 tiles, 42 us in four parts each) - else the persistent kernel takes it unsplit (measured
-// equal or better from 48 tiles on).
+// an SM): the largest that still fits one wave of 148 CTAs - one SM cannot pull more than
+// about 100 GB/s, so a product with few tiles needs more CTAs to stream its weights (4,096 x
+// 14,336 weights, 256 tokens: 80 us as 32 tiles, 43 us in four parts each) - but with more
+// than a quarter of a wave of 256-token tiles, two parts pay only if K is long (4,096 x 14,336
+// weights, 512 tokens: 88 us unsplit, 74 us in two parts; 4,096 x 4,096: 32 us and 35 us;
+// 128-token tiles, 6,144 x 4,096: 26 us and 20 us).  From half a wave of tiles on the
+// persistent kernel takes the product unsplit.
 // A function of the shapes only, so a captured step keeps its grid.
 extern "C" int rl_gemm_tc_splits(int M, int N, int K) {
   const int bt = token_tile(M);
@@ -692,8 +695,8 @@ extern "C" int rl_gemm_tc_splits(int M, int N, int K) {
   const int sms = rl_num_sms();
   int splits = 1;
   if (bt > 64) {
-    if (tiles * 4 > sms) return 1;
     while (splits < 8 && tiles * splits * 2 <= sms && total_kb / (splits * 2) >= 4) splits *= 2;
+    if (splits == 2 && tiles * 4 > sms && bt > 128 && total_kb < 96) splits = 1;
     return splits;
   }
   if (tiles >= sms) return 1;
