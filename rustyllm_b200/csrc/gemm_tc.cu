@@ -699,7 +699,14 @@ extern "C" int rl_gemm_tc_splits(int M, int N, int K) {
     if (splits == 2 && tiles * 4 > sms && bt > 128 && total_kb < 96) splits = 1;
     return splits;
   }
-  if (tiles >= sms) return 1;
+  // up to 64 tokens (three CTAs an SM).  From a sweep over the products of the three shapes measured
+  // here (us at 8 tokens, unsplit / 2 / 4 / 8 parts): 48 tiles 19.8 / 14.3 / 11.2 / 10.6; 96 tiles
+  // 21.3 / 19.1 / 18.1 / 21.0; 128 tiles 13.4 / 15.1 / 15.7 / 19.9; 172 tiles 33.5 / 29.4 / 32.6 / 36.2;
+  // 224 tiles 37.5 / 42.8 / 42.7 / 45.6.  So: nearly a CTA an SM already - unsplit; a little more than
+  // one wave of SMs - two parts, which still run together as one wave of three CTAs an SM (whole
+  // steps of the Llama-2-7B shape: one sequence 2.75 -> 2.68 ms, sixteen 3.60 -> 3.58 ms).
+  if (tiles >= sms) return (tiles * 2 <= sms * 12 / 5 && total_kb >= 8) ? 2 : 1;
+  if (tiles * 8 >= sms * 7) return 1;
   while (splits < 8 && tiles * splits < 256 && total_kb / (splits * 2) >= 4) splits *= 2;
   return splits;
 }
