@@ -344,14 +344,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         bv.x = nn < N ? bias[nn] : 0.f; bv.y = nn + 1 < N ? bias[nn + 1] : 0.f;
         bv.z = nn + 2 < N ? bias[nn + 2] : 0.f; bv.w = nn + 3 < N ? bias[nn + 3] : 0.f;
       }
-      for (int j = split + num_splits * cg; j < cols; j += num_splits * 4) {
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        const uint32_t off = (uint32_t)((j * BLOCK_N_OUT + r4) * 4);
-        for (int sp = 0; sp < num_splits; ++sp) {
-          const float4 t = dsmem_ld4(dsmem_addr(red_local + off, (uint32_t)sp));
-          v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+      // Four columns a warp at a time, every load of the four (the parts' sums through the cluster's
+      // shared memory, the residual's old values) issued before the first is used: with 128 or 256
+      // token columns a tile this loop is bound by the latency of its loads, not their number.
+      constexpr int U = BT > 128 ? 8 : BT > 64 ? 4 : 1;
+      const bool add_vec = out_mode == TC_OUT_ADD_F32 && vec_ok;
+      const int step = num_splits * 4;
+      for (int j0 = split + num_splits * cg; j0 < cols; j0 += step * U) {
+        float4 v[U], old[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int j = j0 + u * step;
+          v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          old[u] = v[u];
+          if (U > 1 && add_vec && j < cols) old[u] = __ldcg(reinterpret_cast<const float4*>((const float*)out + (size_t)(m0 + j) * ldo + nn));
         }
-        tc_finish_column<BT>(v, j, r4, et & 31, n0, m0, N, ldo, bv, out, out_mode, fuse, fuse_smem, vec_ok);
+        for (int sp = 0; sp < num_splits; ++sp) {       // parts are added in the order 0, 1, 2, ...
+          float4 t[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const int j = j0 + u * step;
+            t[u] = j < cols ? dsmem_ld4(dsmem_addr(red_local + (uint32_t)((j * BLOCK_N_OUT + r4) * 4), (uint32_t)sp))
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) { v[u].x += t[u].x; v[u].y += t[u].y; v[u].z += t[u].z; v[u].w += t[u].w; }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int j = j0 + u * step;
+          if (j < cols)
+            tc_finish_column<BT>(v[u], j, r4, et & 31, n0, m0, N, ldo, bv, out, out_mode, fuse, fuse_smem, vec_ok,
+                                 U > 1 && add_vec, old[u]);
+        }
       }
     }
     __syncwarp();
@@ -682,11 +707,13 @@ static int token_tile(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64
 // K blocks a part; products with 148 tiles or more are not split.  Above 64 tokens (one CTA
 // an SM): the largest that still fits one wave of 148 CTAs - one SM cannot pull more than
 // about 100 GB/s, so a product with few tiles needs more CTAs to stream its weights (4,096 x
-// 14,336 weights, 256 tokens: 80 us as 32 tiles, 43 us in four parts each) - but with more
-// than a quarter of a wave of 256-token tiles, two parts pay only if K is long (4,096 x 14,336
-// weights, 512 tokens: 88 us unsplit, 74 us in two parts; 4,096 x 4,096: 32 us and 35 us;
-// 128-token tiles, 6,144 x 4,096: 26 us and 20 us).  From half a wave of tiles on the
-// persistent kernel takes the product unsplit.
+// 14,336 weights, 256 tokens: 74 us as 32 tiles, 37 us in four parts each; 512 tokens: 80 us
+// unsplit, 58 us in two parts; 4,096 x 4,096, 512 tokens: 29 us and 26 us) - but two parts of
+// 256-token tiles that fill no more than two thirds of the SMs gain nothing over the unsplit
+// tiles unless K is long (6,144 x 4,096, 256 tokens: 25 us and 26 us; 128-token tiles, 128
+// tokens: 23 us and 18 us).  From half a wave of tiles on the persistent kernel takes the
+// product unsplit.  Cluster sizes that are no power of two were measured too and lose: clusters
+// of three do not all fit the GPCs at once (48 tiles in three parts: 41 us).
 // A function of the shapes only, so a captured step keeps its grid.
 extern "C" int rl_gemm_tc_splits(int M, int N, int K) {
   const int bt = token_tile(M);
@@ -696,7 +723,7 @@ extern "C" int rl_gemm_tc_splits(int M, int N, int K) {
   int splits = 1;
   if (bt > 64) {
     while (splits < 8 && tiles * splits * 2 <= sms && total_kb / (splits * 2) >= 4) splits *= 2;
-    if (splits == 2 && tiles * 4 > sms && bt > 128 && total_kb < 96) splits = 1;
+    if (splits == 2 && tiles * 3 <= sms && bt > 128 && total_kb < 96) splits = 1;
     return splits;
   }
   // up to 64 tokens (three CTAs an SM).  From a sweep over the products of the three shapes measured
@@ -732,8 +759,7 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* ou
   RL_REQUIRE(out_mode >= 0 && out_mode <= 4, "rl_gemm_tc: unknown output mode %d", out_mode);
   RL_REQUIRE(out_mode != TC_OUT_SWIGLU || N % 2 == 0, "rl_gemm_tc: the SwiGLU epilogue needs an even number of weight rows, got %d", N);
   RL_REQUIRE(ldo >= (out_mode == TC_OUT_SWIGLU ? N / 2 : N) && err != nullptr, "rl_gemm_tc: bad output stride or null error word");
-  RL_REQUIRE(force_splits == 0 || force_splits == 1 || force_splits == 2 || force_splits == 4 || force_splits == 8,
-             "rl_gemm_tc: the number of K parts must be 1, 2, 4 or 8, got %d", force_splits);
+  RL_REQUIRE(force_splits >= 0 && force_splits <= 8, "rl_gemm_tc: the number of K parts must be 1 to 8 (0: chosen from the shapes), got %d", force_splits);
   RL_REQUIRE(scale_partials == nullptr || fuse.scale_count > 0, "rl_gemm_tc: row scales without their sums");
   RL_REQUIRE(norm_weight == nullptr || (out_mode == TC_OUT_ADD_F32 && fuse.norm_out != nullptr && fuse.norm_partials != nullptr && fuse.ld_norm >= N),
              "rl_gemm_tc: the norm for the next product needs the add-into-residual mode, its two outputs and ld_norm >= N");
@@ -743,7 +769,7 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* ou
              "rl_gemm_tc: a norm rides in the epilogue only for up to 64 tokens, got %d", M);
   const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
   int splits = force_splits > 0 ? force_splits : rl_gemm_tc_splits(M, N, K);
-  while (splits > 1 && (splits - 1) * ((total_kb + splits - 1) / splits) >= total_kb) splits /= 2;   // no part is empty
+  while (splits > 1 && (splits - 1) * ((total_kb + splits - 1) / splits) >= total_kb) --splits;   // no part is empty
   RL_REQUIRE(out_mode != TC_OUT_ROPE_KV || (splits > 1 && bt <= 64),
              "rl_gemm_tc_qkv_rope: the rotation rides only in the cluster epilogue (up to 64 tokens, K in 2 or more parts); "
              "M=%d N=%d K=%d give %d part(s)", M, N, K, splits);
@@ -786,7 +812,7 @@ extern "C" int rl_gemm_tc_qkv_rope_supported(int M, int num_heads, int num_kv_he
   const int N = (num_heads + 2 * num_kv_heads) * head_dim;
   const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
   int splits = rl_gemm_tc_splits(M, N, K);
-  while (splits > 1 && (splits - 1) * ((total_kb + splits - 1) / splits) >= total_kb) splits /= 2;
+  while (splits > 1 && (splits - 1) * ((total_kb + splits - 1) / splits) >= total_kb) --splits;
   return splits > 1;
 }
 

@@ -203,10 +203,12 @@ int tc_make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, 
 // float, added into the float residual (with the start of the next norm), SwiGLU of
 // interleaved gate / up rows, or rotary encoding with the write into the paged cache.
 // fuse_smem: [0, BT) row scales, then the tokens' positions and cache rows (rotary mode).
+// have_old, old_residual (add mode with vec_ok only): the four residual values, if already loaded.
 template <int BT>
 __device__ __forceinline__ void tc_finish_column(float4 v, int j, int r4, int lane32, int n0, int m0, int N, int ldo,
                                                  float4 bv, void* __restrict__ out, int out_mode, const TcFuse& fuse,
-                                                 const float* fuse_smem, bool vec_ok) {
+                                                 const float* fuse_smem, bool vec_ok, bool have_old = false,
+                                                 float4 old_residual = make_float4(0.f, 0.f, 0.f, 0.f)) {
   const int nn = n0 + r4;
   const int et = lane32;          // lane within the warp
   do {
@@ -277,7 +279,8 @@ __device__ __forceinline__ void tc_finish_column(float4 v, int j, int r4, int la
           } else if (out_mode == TC_OUT_F32) {
             *reinterpret_cast<float4*>((float*)out + o) = v;
           } else {
-            float4 old = *reinterpret_cast<const float4*>((float*)out + o);
+            // (the caller may have fetched the residual's values already, with other columns' loads)
+            float4 old = have_old ? old_residual : *reinterpret_cast<const float4*>((float*)out + o);
             old.x += v.x; old.y += v.y; old.z += v.z; old.w += v.w;
             *reinterpret_cast<float4*>((float*)out + o) = old;
             v = old;

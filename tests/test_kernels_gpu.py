@@ -189,7 +189,7 @@ def test_gemm_tc_all_modes(M, N, K_):
                                     (33, 300, 1096), (16, 128, 256),
                                     # more than 64 tokens, few tiles: 128- and 256-token tiles in parts as well
                                     (128, 4096, 4096), (100, 520, 2048), (200, 640, 1096), (256, 256, 1024), (300, 1100, 640),
-                                    (512, 4096, 4096)])
+                                    (512, 4096, 4096), (700, 4096, 1024)])
 def test_gemm_tc_split_k_is_deterministic_and_matches_the_unsplit_product(M, N, K_):
     k = K()
     a = _rand(M, K_, dtype=torch.bfloat16, seed=14)
@@ -216,7 +216,9 @@ def test_gemm_tc_split_k_is_deterministic_and_matches_the_unsplit_product(M, N, 
     if (M, N, K_) in [(1, 4096, 4096), (8, 6144, 4096), (8, 4096, 14336), (128, 4096, 4096), (100, 520, 2048), (200, 640, 1096)]:
         assert k.gemm_tc_splits(M, N, K_) > 1
     if (M, N, K_) == (512, 4096, 4096):
-        assert k.gemm_tc_splits(M, N, K_) == 1      # 64 tiles: the persistent kernel takes them whole
+        assert k.gemm_tc_splits(M, N, K_) == 2      # 64 tiles of 256 tokens: two parts fill most of the SMs
+    if (M, N, K_) == (700, 4096, 1024):
+        assert k.gemm_tc_splits(M, N, K_) == 1      # 96 tiles: the persistent kernel takes them whole
 
 
 @pytest.mark.parametrize("M,N,K_,parts", [(8, 384, 512, 0), (8, 384, 512, 1), (5, 200, 256, 4), (40, 136, 192, 2),
