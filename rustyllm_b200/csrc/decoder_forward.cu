@@ -122,7 +122,7 @@ int attention(const RlLayerDesc& L, const RlRunDesc& R, const RlStepDesc& S, Ste
   if (same && S.is_decode && rl_attention_decode_supported(H, G, hd)) {
     const int splits = decode_splits(S.B, G);
     ++g_launches;
-    if (S.B == 1 && splits >= 8)        // one sequence: eight equal chunks as one cluster, combined through shared memory
+    if (S.B == 1 && splits >= 8 && !S.long_context)      // one sequence: eight equal chunks as one cluster, combined through shared memory
       return rl_attention_decode(B.qkv, ldq, R.k_pool, R.v_pool, R.page_table, R.max_pages, S.seq_slots, S.kv_lens, B.attn, H * hd,
                                  nullptr, nullptr, S.B, H, G, hd, L.scale, L.window, 8, stream);
     const int* plan = nullptr;

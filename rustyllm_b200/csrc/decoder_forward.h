@@ -56,6 +56,7 @@ struct RlStepDesc {
   const int* kv_lens;
   int tiles_tc, tiles_mma;      // query tiles of 128 and of 64 tokens over the step's sequences
   const int* tile_order;        // for the tcgen05 prefill attention (may be null)
+  int long_context;             // the longest sequence holds more tokens than one cluster of chunks serves well
 };
 
 #ifdef __cplusplus

@@ -42,6 +42,9 @@ class StepState:
     # device data that parts derive from the step and that holds for all layers (a part
     # that needs, say, a work plan of the sequences makes it once and leaves it here)
     derived: Dict[object, object] = field(default_factory=dict)
+    # the longest sequence holds more than kernels.LONG_CONTEXT tokens.  A part may choose another
+    # launch shape by it: captured steps are kept per (number of sequences, this flag).
+    long_context: bool = False
 
 
 Want = Union[str, None, Sequence[Sequence[int]]]
@@ -52,12 +55,12 @@ class _DecodeGraph:
     the step's integers from ``static_in`` and leave logits in ``logits``; everything
     they read beyond that (page tables, cache pools, weights) keeps its address."""
 
-    def __init__(self, engine: "Engine", num_seqs: int):
+    def __init__(self, engine: "Engine", num_seqs: int, long_context: bool = False):
         B = num_seqs
         self.num_seqs = B
         dev = engine.device
         self.static_in = torch.zeros(7 * B + 1, dtype=torch.int32, device=dev)
-        st = engine.step_state(self.static_in, (B, B, B), [1] * B, [1] * B)
+        st = engine.step_state(self.static_in, (B, B, B), [1] * B, [K.LONG_CONTEXT + 1 if long_context else 1] * B)
         before = K.launch_count
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
@@ -113,8 +116,8 @@ class Engine:
         self._staging = PinnedStaging(self.device) if self.device.type == "cuda" else None
         self.h2d_bytes = 0
         self.use_graphs = use_graphs and self.device.type == "cuda" and model.graph_capturable
-        self._graphs = {}          # num_seqs -> _DecodeGraph
-        self._eager_decodes = {}   # num_seqs -> eager single-token steps run so far
+        self._graphs = {}          # (num_seqs, long context) -> _DecodeGraph
+        self._eager_decodes = {}   # (num_seqs, long context) -> eager single-token steps run so far
 
     # ------------------------------------------------------------------ slots
     def alloc_slot(self) -> int:
@@ -130,14 +133,14 @@ class Engine:
         if not self.use_graphs:
             return
         for B in sorted(set(int(b) for b in batch_sizes)):
-            if B <= 0 or B in self._graphs:
+            if B <= 0 or (B, False) in self._graphs:
                 continue
             slots: List[int] = []
             try:
                 for _ in range(B):                             # one by one: a failure part-way frees those taken
                     slots.append(self.alloc_slot())
                 self.step(slots, [[0]] * B, None)              # one token each, so that a length exists
-                while B not in self._graphs:                   # an eager step first, then the capture
+                while (B, False) not in self._graphs:          # an eager step first, then the capture
                     self.step(slots, [[0]] * B, "last")
             finally:
                 for s in slots:
@@ -209,7 +212,7 @@ class Engine:
         rows = take(W)
         return StepState(M, B, tokens, positions, slot_of_token, cu, seq_slots, kv, rows,
                          list(q_lens), list(kv_lens), max(q_lens), max(kv_lens),
-                         all(n == 1 for n in q_lens))
+                         all(n == 1 for n in q_lens), long_context=max(kv_lens) > K.LONG_CONTEXT)
 
     def step_borrowed(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], want: Want = "last") -> Optional[torch.Tensor]:
         """``step`` for a caller that is done with the logits before its next step (the
@@ -225,14 +228,15 @@ class Engine:
         tokens in the captured step's own buffer, overwritten by its next run - or ``None``
         when no captured step for this many sequences exists yet and nothing was run."""
         B = len(slots)
-        g = self._graphs.get(B) if self.use_graphs else None
+        starts = [self.cache.length(s) for s in slots]
+        g = self._graphs.get((B, max(starts) + 1 > K.LONG_CONTEXT)) if self.use_graphs and B > 0 else None
         if g is None:
             return None
         if token_ids.dtype != torch.int32 or token_ids.numel() != B:
             raise ValueError(f"token_ids must hold {B} int32 ids")
         ones = [1] * B
         self.cache.prepare(slots, ones)
-        self.h2d_bytes += g.upload(None, [self.cache.length(s) for s in slots], slots)
+        self.h2d_bytes += g.upload(None, starts, slots)
         g.static_in[:B].copy_(token_ids, non_blocking=True)
         g.graph.replay()
         K.launch_count += g.launches
@@ -253,9 +257,11 @@ class Engine:
         decode = (self.use_graphs and B > 0 and len(tokens) == B and isinstance(want, str) and want == "last"
                   and all(len(t) == 1 for t in tokens))
         if decode:
-            g = self._graphs.get(B)
-            if g is None and self._eager_decodes.get(B, 0) >= 1:
-                g = self._graphs[B] = _DecodeGraph(self, B)
+            starts = [self.cache.length(s) for s in slots]
+            key = (B, max(starts) + 1 > K.LONG_CONTEXT)
+            g = self._graphs.get(key)
+            if g is None and self._eager_decodes.get(key, 0) >= 1:
+                g = self._graphs[key] = _DecodeGraph(self, B, key[1])
             if g is not None:
                 # the short way for the step that generation repeats: same checks, same layout
                 # of the integers as build_step, no intermediate arrays
@@ -265,12 +271,12 @@ class Engine:
                     raise ValueError(f"token id {bad} lies outside the vocabulary [0, {self.vocab_size})")
                 ones = [1] * B
                 self.cache.prepare(slots, ones)
-                self.h2d_bytes += g.upload(toks, [self.cache.length(s) for s in slots], slots)
+                self.h2d_bytes += g.upload(toks, starts, slots)
                 g.graph.replay()
                 K.launch_count += g.launches
                 self.cache.commit(slots, ones)
                 return g.logits if _borrow else g.logits.clone()   # the graph's own buffer is overwritten by its next replay
-            self._eager_decodes[B] = self._eager_decodes.get(B, 0) + 1
+            self._eager_decodes[key] = self._eager_decodes.get(key, 0) + 1
         packed, sizes, q_lens, kv_lens = self.build_step(slots, tokens, want)
         self.cache.prepare(slots, q_lens)
         if self._staging is not None:

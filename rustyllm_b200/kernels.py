@@ -473,6 +473,14 @@ def attention_decode_supported(dtype: torch.dtype, num_heads: int, num_kv_heads:
     return dtype == torch.bfloat16 and bool(library().rl_attention_decode_supported(num_heads, num_kv_heads, head_dim))
 
 
+# One sequence alone: up to this many cached tokens its eight chunks run as one cluster that
+# combines through shared memory (one kernel; 6.0 us against 7.9 us at 1,024 tokens, equal at
+# 4,096); beyond, sixteen chunks and the combining kernel (32,768 tokens: 30 us against 52 us;
+# 131,072: 95 us against 198 us - 64 CTAs cannot keep the memory busy).  A captured step keeps
+# its grid, so the step carries on which side of this it lies (``StepState.long_context``).
+LONG_CONTEXT = 6144
+
+
 def decode_splits(num_seqs: int, num_kv_heads: int) -> int:
     """Splits of the context per (sequence, KV head): enough CTAs for about one and a
     half per SM, at most 8 for a batch and 16 for one sequence (measured best at 1 to 64
@@ -639,7 +647,7 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
         return
     if step.is_decode and attention_decode_supported(q.dtype, num_heads, num_kv_heads, head_dim):
         splits = decode_splits(q.shape[0], num_kv_heads)
-        if q.shape[0] == 1 and splits >= 8:
+        if q.shape[0] == 1 and splits >= 8 and not getattr(step, "long_context", False):
             # one sequence: nothing to deal; eight equal chunks as one cluster, combined through shared memory
             attention_decode(q, k_pool, v_pool, page_table, step.seq_slots, step.kv_lens, out,
                              num_heads, num_kv_heads, head_dim, scale, window, num_splits=8, cluster=True)

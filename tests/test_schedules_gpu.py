@@ -79,6 +79,30 @@ def test_a_sequence_pushed_to_position_8700(model_dirs, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["F", "G"])
+def test_one_sequence_decoding_across_the_long_context_mark(model_dirs, name, dtype):
+    """A sequence alone, single tokens from position 6,100 to 6,199: up to ``kernels.LONG_CONTEXT``
+    cached tokens its attention runs as one cluster of eight chunks, beyond as sixteen chunks and a
+    combining kernel, each side with a captured step of its own."""
+    from rustyllm_b200 import kernels
+    assert 6100 < kernels.LONG_CONTEXT < 6190
+    d, cfg = model_dirs[name]
+    long = random_tokens(cfg["vocab_size"], 8704, 41)
+    ref = plain_logits(d, long)
+    r = _runner(d, dtype, 64 * 100, 1)
+    eng = r.engine
+    s = eng.alloc_slot()
+    for at in range(0, 6100, 3050):
+        eng.step([s], [long[at:at + 3050]], None)
+    got = [eng.step([s], [[t]], "last") for t in long[6100:6200]]
+    assert_close_logits(torch.cat(got), ref[6100:6200], dtype, f"{name} single tokens from 6,100 to 6,199")
+    if eng.use_graphs:
+        assert sorted(eng._graphs) == [(1, False), (1, True)]
+    eng.free_slot(s)
+    r.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["F", "B"])
 def test_a_batch_of_64_unequal_sequences_then_another_in_their_slots(model_dirs, name, dtype):
     """64 prompts of 1 to 600 tokens (B: to 244) in one packed step, ten single-token steps
