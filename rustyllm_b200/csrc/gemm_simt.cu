@@ -173,6 +173,79 @@ static int launch_gemm_simt_stream(const float* A, const float* W, const float* 
   return RL_OK;
 }
 
+// Many tokens, float operands with rows that 16-byte loads can fetch: the classic register tile.
+// 256 threads own 8 x 8 outputs each of a 128 x 128 tile (two groups of four rows and of four
+// columns, 64 apart, so that shared memory is read 16 bytes a time without conflicts); a
+// thread fetches one 16-byte piece of A and one of W for the next 8 k-values into registers
+// while the current ones are multiplied, and stores them transposed ([k][row]) into the other
+// of two buffers.  Every output element is still the chain fmaf(a[k], w[k], acc), k = 0, 1, 2, ...
+__global__ void __launch_bounds__(256)
+gemm_simt_big_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
+                     void* __restrict__ out, int out_mode, int M, int N, int K, int lda, int ldo) {
+  constexpr int BM = 128, BN = 128, BK = 8, LD = BM + 4;
+  __shared__ __align__(16) float As[2][BK][LD];
+  __shared__ __align__(16) float Ws[2][BK][LD];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int lr = tid >> 1, lk = (tid & 1) * 4;             // this thread's piece of a tile: row lr, k-values lk .. lk + 3
+  const bool a_row = m0 + lr < M, w_row = n0 + lr < N;
+  const float* ap = A + (size_t)(a_row ? m0 + lr : 0) * lda + lk;
+  const float* wp = W + (size_t)(w_row ? n0 + lr : 0) * K + lk;
+  auto fetch = [&](int k0, float4& a, float4& w) {
+    const bool live = k0 + lk < K;                          // K is a multiple of 4: a piece is whole or beyond the end
+    a = (a_row && live) ? *reinterpret_cast<const float4*>(ap + k0) : make_float4(0.f, 0.f, 0.f, 0.f);
+    w = (w_row && live) ? *reinterpret_cast<const float4*>(wp + k0) : make_float4(0.f, 0.f, 0.f, 0.f);
+  };
+  auto stash = [&](int buf, const float4& a, const float4& w) {
+    As[buf][lk + 0][lr] = a.x; As[buf][lk + 1][lr] = a.y; As[buf][lk + 2][lr] = a.z; As[buf][lk + 3][lr] = a.w;
+    Ws[buf][lk + 0][lr] = w.x; Ws[buf][lk + 1][lr] = w.y; Ws[buf][lk + 2][lr] = w.z; Ws[buf][lk + 3][lr] = w.w;
+  };
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+  float4 na, nw;
+  fetch(0, na, nw);
+  stash(0, na, nw);
+  __syncthreads();
+  const int num_kb = (K + BK - 1) / BK;
+  for (int kb = 0; kb < num_kb; ++kb) {
+    const int buf = kb & 1;
+    if (kb + 1 < num_kb) fetch((kb + 1) * BK, na, nw);
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4]);
+      const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][k][64 + ty * 4]);
+      const float4 b0 = *reinterpret_cast<const float4*>(&Ws[buf][k][tx * 4]);
+      const float4 b1 = *reinterpret_cast<const float4*>(&Ws[buf][k][64 + tx * 4]);
+      const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    if (kb + 1 < num_kb) stash(buf ^ 1, na, nw);            // the other buffer was last read an iteration ago
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int gm = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + i - 4);
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int gn = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + j - 4);
+      if (gn >= N) continue;
+      float v = acc[i][j];
+      if (bias) v += bias[gn];
+      const size_t o = (size_t)gm * ldo + gn;
+      if (out_mode == RL_OUT_ADD_F32) ((float*)out)[o] += v;
+      else ((float*)out)[o] = v;
+    }
+  }
+}
+
 template <typename T>
 static int launch_gemm_simt(const T* A, const T* W, const float* bias, void* out, int out_mode, int M,
                             int N, int K, int lda, int ldo, cudaStream_t stream) {
@@ -184,6 +257,12 @@ static int launch_gemm_simt(const T* A, const T* W, const float* bias, void* out
       if (M <= 16) return launch_gemm_simt_stream<4>(A, W, bias, out, out_mode, M, N, K, lda, ldo, stream);
       if (M <= 32) return launch_gemm_simt_stream<8>(A, W, bias, out, out_mode, M, N, K, lda, ldo, stream);
       return launch_gemm_simt_stream<16>(A, W, bias, out, out_mode, M, N, K, lda, ldo, stream);
+    }
+    if (M > STREAM_MAX_M && K % 4 == 0 && lda % 4 == 0 && (((uintptr_t)A | (uintptr_t)W) & 15) == 0) {
+      dim3 grid((N + 127) / 128, (M + 127) / 128);
+      gemm_simt_big_kernel<<<grid, 256, 0, stream>>>(A, W, bias, out, out_mode, M, N, K, lda, ldo);
+      RL_LAUNCH_CHECK("rl_gemm_simt");
+      return RL_OK;
     }
   }
   if (M > 64) {
