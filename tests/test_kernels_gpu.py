@@ -989,6 +989,48 @@ def test_candidate_sampling_at_real_vocabularies_follows_the_plain_sampler(V):
 
 
 
+@pytest.mark.parametrize("V", [5000, 128256])
+def test_candidate_sampling_with_thousands_of_equal_logits(V):
+    """Rows whose boundary classes are large: all logits equal, logits rounded to halves (classes of
+    thousands of identical keys), two values in turn, a few thousand equal finite logits among
+    -inf.  The selection then refines a class down to all 32 bits and tells its tokens apart by
+    index; the answers follow the plain sampler as in the test above."""
+    from rustyllm_b200.sampling.config import SamplerConfig
+    from rustyllm_b200.sampling.sampler import Sampler, SequenceSamplingState
+    g = torch.Generator().manual_seed(V + 1)
+    flat = torch.zeros(V)
+    halves = (torch.randn(V, generator=g) * 3.0 * 2).round() / 2
+    two = torch.where(torch.arange(V) % 2 == 0, torch.tensor(1.0), torch.tensor(0.5))
+    few = torch.full((V,), float("-inf")); few[torch.randperm(V, generator=g)[:3000]] = 2.0
+    dists = [flat, halves, two, few]
+    options = [dict(top_k=40), dict(top_k=1024, top_p=0.9), dict(top_p=0.9), dict(top_p=0.5, min_p=0.5), dict(top_k=2)]
+    rows = [(d, o) for d in dists for o in options]
+    base = torch.stack([d for d, _ in rows])
+    configs = [SamplerConfig(temperature=0.9, **o) for _, o in rows]
+    sampler = Sampler(torch.device(DEV))
+    states = [SequenceSamplingState(c, 900 + i, []) for i, c in enumerate(configs)]
+    twins = [P.Rng(900 + i) for i in range(len(rows))]
+    for trial in range(6):
+        got = sampler.sample(base.clone().to(DEV), states)
+        for i, c in enumerate(configs):
+            u = twins[i].next_f32()
+
+            class Fixed:
+                def next_f32(self, v=u): return v
+            lg = base[i].numpy().copy()
+            want = P.sample(lg, c.temperature, Fixed(), c.top_k, c.top_p, c.min_p, c.repeat_penalty, recent=[])
+            if got[i] == want:
+                continue
+            kept, w = _kept_candidates(lg, c.temperature, c.top_k, c.top_p, c.min_p)
+            where = np.nonzero(kept == got[i])[0]
+            assert where.size == 1, f"row {i} {rows[i][1]} trial {trial}: token {got[i]} is not among the {len(kept)} kept (plain: {want})"
+            j = int(where[0])
+            pre = np.cumsum(w) / w.sum()
+            slack = max(len(kept) * 2.0 ** -24, 1e-6)
+            assert (pre[j - 1] if j else 0.0) <= u + slack and pre[j] >= u - slack, \
+                f"row {i} {rows[i][1]} trial {trial}: {got[i]} (place {j}) vs {want}, u = {u}"
+
+
 def test_temperature_zero_rows_are_greedy_and_min_p_cuts():
     k = K()
     logits = torch.tensor([[1.0, 5.0, 2.0, 4.9], [10.0, 9.5, 3.0, 1.0]], device=DEV)
