@@ -122,9 +122,11 @@ class Sampler:
         f[3 * B + nk:] = [states[b].config.top_p for b in topp]
         fd = self._floats.upload(f)
         temperature, uniform, min_p = fd[:B], fd[B:2 * B], fd[2 * B:3 * B]
-        # every row goes through the softmax kernel (greedy rows are answered there too);
-        # rows with a candidate set are then answered again by their own kernel
-        K.sample_temperature(logits, temperature, uniform, out, min_p if f[2 * B:3 * B].any() else None)
+        # rows without a candidate set (greedy rows among them) are answered by the softmax kernel,
+        # which takes every row of the batch (the others' answers are overwritten below); it is
+        # left out when every row has a candidate set
+        if nk + np_ < B:
+            K.sample_temperature(logits, temperature, uniform, out, min_p if f[2 * B:3 * B].any() else None)
         if topk or topp:
             # one int upload from pinned memory: rows of the top-k path | their k | rows of the top-p path
             idx = self._ints.upload(np.asarray(topk + [states[b].config.top_k for b in topk] + topp, dtype=np.int32))
