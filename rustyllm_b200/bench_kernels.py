@@ -4,7 +4,7 @@
     python -m rustyllm_b200.bench_kernels attention-decode --batch 8 --context 800 [--splits 0] [--contexts 1761,1350,159 | --context-range 128,2048]
     python -m rustyllm_b200.bench_kernels attention-prefill --tokens 2048
     python -m rustyllm_b200.bench_kernels rmsnorm | swiglu | rope --m 8
-    python -m rustyllm_b200.bench_kernels sample --m 8 --n 128256 [--greedy]
+    python -m rustyllm_b200.bench_kernels sample --m 8 --n 128256 [--greedy | --top-k 40 --top-p 0.9 | --top-p 0.9]
 
 Each run launches the kernel ``--reps`` times after ``--warmup`` launches, rotating over
 several copies of the big operand so that the 126 MB L2 cannot serve it, times the
@@ -126,6 +126,16 @@ def sample(a) -> None:
     logits = [torch.randn(rows, V, device=DEV) * 3 for _ in range(copies)]
     out = torch.empty(rows, dtype=torch.int32, device=DEV)
     temps = torch.full((rows,), 0.8, device=DEV); u = torch.rand(rows, device=DEV)
+    if a.top_k > 0 or a.top_p < 1.0:          # the candidate kernels: top-k (with top-p inside it) or top-p alone
+        idx = torch.arange(rows, dtype=torch.int32, device=DEV)
+        pp = torch.full((rows,), a.top_p, device=DEV); zero = torch.zeros(rows, device=DEV)
+        if a.top_k > 0:
+            kk = torch.full((rows,), a.top_k, dtype=torch.int32, device=DEV)
+            us = _time(lambda i: K.sample_candidates(logits[i % copies], temps, u, zero, out, idx, kk, pp, None, None), a.warmup, a.reps)
+        else:
+            us = _time(lambda i: K.sample_candidates(logits[i % copies], temps, u, zero, out, None, None, None, idx, pp), a.warmup, a.reps)
+        print(f"sample_candidates rows={rows} vocab={V} top_k={a.top_k} top_p={a.top_p}: {us:.2f} us")
+        return
     if a.greedy:
         us = _time(lambda i: K.argmax(logits[i % copies], out), a.warmup, a.reps)
     else:
@@ -168,6 +178,8 @@ def main(argv=None) -> int:
     p.add_argument("--head-dim", type=int, default=128); p.add_argument("--hidden", type=int, default=4096)
     p.add_argument("--intermediate", type=int, default=14336)
     p.add_argument("--greedy", action="store_true", help="sample: the argmax kernel")
+    p.add_argument("--top-k", type=int, default=0, help="sample: the top-k kernel with this k (and --top-p inside it)")
+    p.add_argument("--top-p", type=float, default=1.0, help="sample: nucleus threshold; without --top-k the top-p kernel over the whole vocabulary")
     p.add_argument("--cluster", action="store_true", help="attention-decode: the chunks of a sequence as one thread-block cluster (--splits 2, 4 or 8)")
     p.add_argument("--mma", action="store_true", help="attention-prefill: the mma.sync kernel also where tcgen05 applies")
     p.add_argument("--warmup", type=int, default=3); p.add_argument("--reps", type=int, default=20)
