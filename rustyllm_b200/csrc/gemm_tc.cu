@@ -742,7 +742,7 @@ extern "C" int rl_gemm_tc_splits(int M, int N, int K) {
 // ldo, bf16 (out_mode 0) or float (1 store, 2 add); out_mode 3: W's rows are (gate_0, up_0,
 // gate_1, ...) and out is bf16 [M, N/2] = silu(gate) * up.  err: device int, set non-zero if a
 // bounded wait inside the kernel ran out.  force_splits: 0 = number of K parts chosen
-// from the shapes; 1, 2, 4 or 8 = as given (for measurements).
+// from the shapes; 1 to 8 = as given (for measurements; the rule itself picks powers of two).
 // RMSNorm folded in, both optional (null = not):
 //  scale_partials [M, scale_count] float: A is `x * norm weight`, not yet divided by the rms
 //    of x; the sums of squares of x's rows come in scale_count pieces a row, and row m of

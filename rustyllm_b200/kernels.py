@@ -367,7 +367,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_mode: int,
     """out = a @ w.T (+ bias) on the tensor cores (tcgen05).  a: [M, K] bf16, w: [N, K] bf16;
     out: bf16 (OUT_SAME) or float32 (OUT_F32 store, OUT_ADD_F32 add), or, with OUT_SWIGLU,
     bf16 [M, N/2] = silu(even columns) * odd columns of the product.  force_splits: 0 = the
-    kernel's own choice of K parts; 1, 2, 4, 8 = as given.
+    kernel's own choice of K parts; 1 to 8 = as given.
 
     An RMSNorm around the product can ride along.  ``row_sumsq`` [M, pieces] float32 with
     ``row_eps``: ``a`` holds ``x * norm weight`` and row m of the product is multiplied by
