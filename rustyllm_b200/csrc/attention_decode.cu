@@ -417,9 +417,34 @@ __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o
   }
   rl_pdl_wait();
   if (count == 1) return;        // written by its only chunk
+  constexpr int FAST = 16;       // chunks whose loads are all requested before the first is used
+  const int d = threadIdx.x;     // the block has HD threads or 64 (then two dimensions a thread)
+  if (count <= FAST && (int)blockDim.x == HD) {
+    // one trip to L2 instead of two in a row (the maxima, then the outputs): this kernel is all latency
+    float2 ml[FAST];
+    float o[FAST];
+#pragma unroll
+    for (int s = 0; s < FAST; ++s) {
+      const size_t p = (size_t)(first + (s < count ? s : 0)) * H + h;
+      ml[s] = s < count ? __ldcg(reinterpret_cast<const float2*>(part_ml + 2 * p)) : make_float2(-INFINITY, 0.f);
+      o[s] = s < count ? __ldcg(part_o + p * HD + d) : 0.f;
+    }
+    float M = -INFINITY;
+#pragma unroll
+    for (int s = 0; s < FAST; ++s) M = fmaxf(M, ml[s].x);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int s = 0; s < FAST; ++s) {       // in chunk order, as below
+      const float wgt = (ml[s].x > -INFINITY) ? exp2f(ml[s].x - M) : 0.f;
+      L += ml[s].y * wgt;
+      O += o[s] * wgt;
+    }
+    out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    return;
+  }
   float M = -INFINITY;
   for (int s = 0; s < count; ++s) M = fmaxf(M, part_ml[2 * ((size_t)(first + s) * H + h)]);
-  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+  for (int dd = threadIdx.x; dd < HD; dd += blockDim.x) {
     float L = 0.f, O = 0.f;
 #pragma unroll 4
     for (int s = 0; s < count; ++s) {
@@ -427,9 +452,9 @@ __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o
       const float ms = part_ml[2 * p];
       const float wgt = (ms > -INFINITY) ? exp2f(ms - M) : 0.f;
       L += part_ml[2 * p + 1] * wgt;
-      O += part_o[p * HD + d] * wgt;
+      O += part_o[p * HD + dd] * wgt;
     }
-    out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    out[(size_t)b * ldo + (size_t)h * HD + dd] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
   }
 }
 
@@ -481,7 +506,7 @@ static int launch_decode(const void* q, int ldq, const void* k_pool, const void*
       num_splits);
   RL_LAUNCH_CHECK("rl_attention_decode");
   if (num_splits > 1) {
-    rl_launch_pdl(attention_decode_combine_kernel<HD>, dim3(H, B), dim3(HD >= 128 ? 128 : 64), 0, stream,
+    rl_launch_pdl(attention_decode_combine_kernel<HD>, dim3(H, B), dim3(HD), 0, stream,
                   (const float*)part_o, (const float*)part_ml, seqs, num_splits, (__nv_bfloat16*)out, ldo, H);
     RL_LAUNCH_CHECK("rl_attention_decode (combine)");
   }
