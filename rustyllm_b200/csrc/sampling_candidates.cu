@@ -57,10 +57,11 @@ __device__ __forceinline__ uint32_t cand_class(uint32_t key, int pbits) { return
 // stretch's tokens.
 #define CAND_UNROLL 8
 __device__ __forceinline__ int cand_stretch(int vocab) { return ((vocab + 31) / 32 + 31) / 32 * 32; }
+// (the tokens [first, last) of the row; first a multiple of 128)
 template <typename F>
-__device__ __forceinline__ void cand_scan(const float* __restrict__ l, int vocab, F&& f) {
+__device__ __forceinline__ void cand_scan_range(const float* __restrict__ l, int vocab, int first, int last, F&& f) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int per = cand_stretch(vocab), lo = min(warp * per, vocab), hi = min(lo + per, vocab);
+  const int per = cand_stretch(last - first), lo = min(first + warp * per, last), hi = min(lo + per, last);
   if ((vocab & 3) == 0 && (((uintptr_t)l) & 15) == 0) {
     // rows that 16-byte loads can fetch: four tokens a lane and load (per is a multiple of 32, so
     // lo is one of 4; order within a stretch: not ascending, which these passes do not need)
@@ -93,6 +94,8 @@ __device__ __forceinline__ void cand_scan(const float* __restrict__ l, int vocab
     }
   }
 }
+template <typename F>
+__device__ __forceinline__ void cand_scan(const float* __restrict__ l, int vocab, F&& f) { cand_scan_range(l, vocab, 0, vocab, f); }
 // The same walk for passes that tell tokens apart by index: g(i, l[i], live) is called by all 32
 // lanes together for every 32 consecutive tokens (live: i lies in the row), in ascending order.
 template <typename G>
@@ -231,6 +234,36 @@ struct TopkShared {
   uint32_t need;
 };
 
+// A row of a large vocabulary is the work of up to eight CTAs (one cluster; as many as leave every
+// CTA of the launch an SM of its own): each takes its share of the row in the passes (a pass is
+// bound by instruction issue: some 25 instructions a token), the first CTA adds the histograms
+// through distributed shared memory, finds the boundary and tells the others; all of them append
+// their tokens to the first CTA's list, which sorts and draws.  8 rows of 128,256 logits, top-k 40:
+// 40 us with one CTA a row, 19 us with eight; 16 rows: 31 us with eight, 24 us with four; 64 rows:
+// 42 us with one, 32 us with two, 68 us with eight (two waves).
+__device__ __forceinline__ uint32_t cc_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cc_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the address of `p` (in this CTA's shared memory) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t cc_map(const void* p, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"((uint32_t)__cvta_generic_to_shared(p)), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ uint32_t cc_ld(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void cc_st(uint32_t addr, uint32_t v) { asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
+__device__ __forceinline__ uint32_t cc_add(uint32_t addr, uint32_t v) {
+  uint32_t old;
+  asm volatile("atom.shared::cluster.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(addr), "r"(v) : "memory");
+  return old;
+}
+
+template <int CL>      // CTAs a row: 1, or 2, 4 or 8 as one cluster
 __global__ void __launch_bounds__(CAND_THREADS)
 sample_topk_kernel(const float* __restrict__ logits, int vocab, const int* __restrict__ rows,
                    const float* __restrict__ temperature, const float* __restrict__ uniform,
@@ -238,10 +271,17 @@ sample_topk_kernel(const float* __restrict__ logits, int vocab, const int* __res
                    const float* __restrict__ top_p, int* __restrict__ out) {
   extern __shared__ __align__(16) uint8_t cand_smem[];
   TopkShared& sh = *reinterpret_cast<TopkShared*>(cand_smem);
-  const int row = rows[blockIdx.x];
+  const int which = blockIdx.x / CL;
+  const uint32_t crank = CL > 1 ? cc_rank() : 0u;
+  const int row = rows[which];
   const float* l = logits + (size_t)row * vocab;
-  const int K = min(min(top_k[blockIdx.x], CAND_MAX_K), vocab);
+  const int K = min(min(top_k[which], CAND_MAX_K), vocab);
   const int tid = threadIdx.x;
+  // this CTA's part of the row in the passes (whole multiples of 128 tokens)
+  const int part = CL > 1 ? ((vocab + CL - 1) / CL + 127) / 128 * 128 : vocab;
+  const int p_lo = min((int)crank * part, vocab), p_hi = min(p_lo + part, vocab);
+  if (tid == 0) sh.count = 0;             // (the first CTA's is the list's; set before the first cluster barrier)
+
   // 1. the class of keys the K-th largest lies in
   uint32_t prefix = 0u, need = (uint32_t)K, class_cnt = 0u;
   int pbits = 0;
@@ -249,41 +289,71 @@ sample_topk_kernel(const float* __restrict__ logits, int vocab, const int* __res
     const int nb = level < 2 ? 12 : 8, nbins = 1 << nb, shift = 32 - pbits - nb;
     for (int i = tid; i < nbins; i += CAND_THREADS) sh.cnt[i] = 0u;
     __syncthreads();
-    cand_scan(l, vocab, [&](int, float v) {
+    cand_scan_range(l, vocab, p_lo, p_hi, [&](int, float v) {
       const uint32_t key = ord_key(cand_finite(v));
       if (pbits == 0 || cand_class(key, pbits) == prefix) cand_count(sh.cnt, (key >> shift) & (uint32_t)(nbins - 1));
     });
     __syncthreads();
-    cand_find_boundary(sh.cnt, nullptr, nbins, need, 0ull, sh.bd);
-    need -= sh.bd.above_cnt;
-    prefix = (prefix << nb) | (uint32_t)sh.bd.bin;
+    if (CL > 1) {
+      cc_sync();                          // every CTA's histogram is complete
+      if (crank == 0) {
+        for (int i = tid; i < nbins; i += CAND_THREADS) {
+          uint32_t v[CL];
+#pragma unroll
+          for (int r = 1; r < CL; ++r) v[r] = cc_ld(cc_map(&sh.cnt[i], (uint32_t)r));
+          uint32_t c = sh.cnt[i];
+#pragma unroll
+          for (int r = 1; r < CL; ++r) c += v[r];
+          sh.cnt[i] = c;
+        }
+        __syncthreads();
+      }
+    }
+    if (crank == 0) cand_find_boundary(sh.cnt, nullptr, nbins, need, 0ull, sh.bd);
+    uint32_t b_bin, b_above, b_cnt;
+    if (CL > 1) {
+      cc_sync();                          // the boundary is known; the others' histograms have been read
+      b_bin = cc_ld(cc_map(&sh.bd.bin, 0u)); b_above = cc_ld(cc_map(&sh.bd.above_cnt, 0u)); b_cnt = cc_ld(cc_map(&sh.bd.bin_cnt, 0u));
+    } else {
+      b_bin = (uint32_t)sh.bd.bin; b_above = sh.bd.above_cnt; b_cnt = sh.bd.bin_cnt;
+    }
+    need -= b_above;
+    prefix = (prefix << nb) | b_bin;
     pbits += nb;
-    class_cnt = sh.bd.bin_cnt;
-    __syncthreads();                      // everyone has read the boundary before the next level writes it
+    class_cnt = b_cnt;
+    if (CL > 1) cc_sync(); else __syncthreads();     // everyone has read the boundary before the next level writes it
     if (class_cnt <= CAND_CAP || pbits == 32) break;
   }
   // need >= 1 tokens of the class belong to the set, all tokens of higher classes do (K - need of them)
 
-  // 2. gather: higher classes whole; the boundary class whole if it is small (the sort puts its
-  // best first), else - all its keys are equal - its `need` lowest indices
+  // 2. gather into the (first CTA's) list: higher classes whole; the boundary class whole if it is
+  // small (the sort puts its best first), else - all its keys are equal - its `need` lowest indices
   const bool whole = class_cnt <= CAND_CAP;
   const int n_above = K - (int)need;
-  if (tid == 0) sh.count = 0;
-  __syncthreads();
-  int eq = 0;                              // (not whole) this lane's tokens of the boundary class
-  cand_scan(l, vocab, [&](int i, float v) {
+  const uint32_t a_count = CL > 1 ? cc_map(&sh.count, 0u) : 0u, a_key = CL > 1 ? cc_map(&sh.lkey[0], 0u) : 0u,
+                 a_idx = CL > 1 ? cc_map(&sh.lidx[0], 0u) : 0u;
+  cand_scan_range(l, vocab, p_lo, p_hi, [&](int i, float v) {
     const uint32_t key = ord_key(cand_finite(v));
     const uint32_t cls = cand_class(key, pbits);
     if (cls > prefix || (whole && cls == prefix)) {
-      const int slot = atomicAdd(&sh.count, 1);
-      sh.lkey[slot] = key; sh.lidx[slot] = i;
-    } else if (cls == prefix) {
-      ++eq;
+      if (CL > 1) {
+        const uint32_t slot = cc_add(a_count, 1u);
+        cc_st(a_key + 4u * slot, key); cc_st(a_idx + 4u * slot, (uint32_t)i);
+      } else {
+        const int slot = atomicAdd(&sh.count, 1);
+        sh.lkey[slot] = key; sh.lidx[slot] = i;
+      }
     }
   });
+  if (CL > 1) {
+    cc_sync();                            // the list is complete; the other CTAs are done
+    if (crank != 0) return;
+  }
   const int list_n = n_above + (whole ? (int)class_cnt : (int)need);
   if (!whole) {
-    // all keys of the class are equal: its `need` lowest indices
+    // all keys of the class are equal: its `need` lowest indices (the whole row, by this CTA)
+    int eq = 0;
+    cand_scan(l, vocab, [&](int, float v) { if (ord_key(cand_finite(v)) == prefix) ++eq; });
     int rank = cand_warp_prefix((int)__reduce_add_sync(0xffffffffu, (unsigned)eq), sh.seg_eq);
     cand_scan_ordered(l, vocab, [&](int i, float v, bool live) {
       const bool is = live && ord_key(cand_finite(v)) == prefix;
@@ -328,7 +398,7 @@ sample_topk_kernel(const float* __restrict__ logits, int vocab, const int* __res
     int cutoff = limit;
     float kept = 0.f;
     for (int j = 0; j < limit; ++j) kept += w[j];
-    const float tp = top_p[blockIdx.x];
+    const float tp = top_p[which];
     if (tp < 1.0f) {
       float c = 0.f;
       const float thr = tp * sum;
@@ -572,12 +642,36 @@ extern "C" int rl_sample_candidates(const float* logits, int vocab, const int* r
   if (num_topk > 0) {
     static bool configured_k = false;
     if (!configured_k) {
-      cudaError_t e = cudaFuncSetAttribute(sample_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(TopkShared));
+      cudaError_t e = cudaFuncSetAttribute(sample_topk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(TopkShared));
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(sample_topk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(TopkShared));
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(sample_topk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(TopkShared));
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(sample_topk_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(TopkShared));
       RL_REQUIRE(e == cudaSuccess, "rl_sample_candidates: cannot reserve %d bytes of shared memory: %s", (int)sizeof(TopkShared), cudaGetErrorString(e));
       configured_k = true;
     }
-    sample_topk_kernel<<<num_topk, CAND_THREADS, sizeof(TopkShared), stream>>>(logits, vocab, rows_topk, temperature, uniform,
-                                                                               min_p, top_k, top_p_k, out);
+    // CTAs a row: the most that leave each CTA of the launch an SM of its own (clusters of eight
+    // only while they fill no more than half of the SMs: sixteen of them no longer find room at once)
+    const int sms = rl_num_sms();
+    const int cl = vocab < 16384 ? 1 : num_topk * 16 <= sms ? 8 : num_topk * 4 <= sms ? 4 : num_topk * 2 <= sms ? 2 : 1;
+    if (cl > 1) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(cl * num_topk);
+      cfg.blockDim = dim3(CAND_THREADS);
+      cfg.dynamicSmemBytes = sizeof(TopkShared);
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = cl; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      cudaError_t e = cl == 8 ? cudaLaunchKernelEx(&cfg, sample_topk_kernel<8>, logits, vocab, rows_topk, temperature, uniform, min_p, top_k, top_p_k, out)
+                    : cl == 4 ? cudaLaunchKernelEx(&cfg, sample_topk_kernel<4>, logits, vocab, rows_topk, temperature, uniform, min_p, top_k, top_p_k, out)
+                              : cudaLaunchKernelEx(&cfg, sample_topk_kernel<2>, logits, vocab, rows_topk, temperature, uniform, min_p, top_k, top_p_k, out);
+      RL_REQUIRE(e == cudaSuccess, "rl_sample_candidates (top-k): launch failed: %s", cudaGetErrorString(e));
+    } else {
+      sample_topk_kernel<1><<<num_topk, CAND_THREADS, sizeof(TopkShared), stream>>>(logits, vocab, rows_topk, temperature, uniform,
+                                                                                    min_p, top_k, top_p_k, out);
+    }
     RL_LAUNCH_CHECK("rl_sample_candidates (top-k)");
   }
   if (num_topp > 0) {
