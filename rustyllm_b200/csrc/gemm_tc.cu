@@ -769,7 +769,8 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* ou
              "rl_gemm_tc: a norm rides in the epilogue only for up to 64 tokens, got %d", M);
   const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
   int splits = force_splits > 0 ? force_splits : rl_gemm_tc_splits(M, N, K);
-  while (splits > 1 && (splits - 1) * ((total_kb + splits - 1) / splits) >= total_kb) --splits;   // no part is empty
+  while (splits > 1 && (splits - 1) * ((total_kb + splits - 1) / splits) >= total_kb)                // no part is empty
+    splits = (splits & (splits - 1)) == 0 ? splits / 2 : splits - 1;                                 // (a power of two stays one)
   RL_REQUIRE(out_mode != TC_OUT_ROPE_KV || (splits > 1 && bt <= 64),
              "rl_gemm_tc_qkv_rope: the rotation rides only in the cluster epilogue (up to 64 tokens, K in 2 or more parts); "
              "M=%d N=%d K=%d give %d part(s)", M, N, K, splits);
@@ -812,7 +813,7 @@ extern "C" int rl_gemm_tc_qkv_rope_supported(int M, int num_heads, int num_kv_he
   const int N = (num_heads + 2 * num_kv_heads) * head_dim;
   const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
   int splits = rl_gemm_tc_splits(M, N, K);
-  while (splits > 1 && (splits - 1) * ((total_kb + splits - 1) / splits) >= total_kb) --splits;
+  while (splits > 1 && (splits - 1) * ((total_kb + splits - 1) / splits) >= total_kb) splits /= 2;
   return splits > 1;
 }
 
