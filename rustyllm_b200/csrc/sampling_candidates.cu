@@ -423,6 +423,7 @@ sample_topk_kernel(const float* __restrict__ logits, int vocab, const int* __res
 #define FX_ONE 1099511627776.0f   // 2^40: fixed-point scale of a weight in [0, 1]
 
 struct ToppShared {
+  uint32_t limb[4][CAND_BINS];    // a histogram's sums while it is being made: four limbs of 11 bits (see topp_add)
   uint32_t cnt[CAND_BINS];        // histogram of a deeper level
   cand_u64 sum[CAND_BINS];
   uint32_t cnt1[CAND_BINS];       // the first level's, made once and used by both walks
@@ -441,18 +442,37 @@ struct ToppShared {
 
 __device__ __forceinline__ cand_u64 cand_fx(float w) { return (cand_u64)(w * FX_ONE); }
 
+// Exact sums of a histogram's bins without 64-bit shared-memory atomics (which took 140 of this
+// kernel's 200 us): a weight's fixed-point value (at most 2^40) is added limb by limb, 11 bits
+// each, into four 32-bit arrays - a limb's sum over a vocabulary of up to two million tokens
+// stays below 2^32 - and the bins' 64-bit sums are put together afterwards.  Zero limbs are skipped.
+__device__ __forceinline__ void topp_add(uint32_t (*limb)[CAND_BINS], uint32_t bin, cand_u64 fx) {
+  const uint32_t l0 = (uint32_t)fx & 2047u, l1 = (uint32_t)(fx >> 11) & 2047u, l2 = (uint32_t)(fx >> 22) & 2047u, l3 = (uint32_t)(fx >> 33);
+  if (l0) atomicAdd(&limb[0][bin], l0);
+  if (l1) atomicAdd(&limb[1][bin], l1);
+  if (l2) atomicAdd(&limb[2][bin], l2);
+  if (l3) atomicAdd(&limb[3][bin], l3);
+}
+__device__ __forceinline__ void topp_clear(uint32_t (*limb)[CAND_BINS], uint32_t* cnt, int nbins) {
+  for (int i = threadIdx.x; i < nbins; i += CAND_THREADS) { cnt[i] = 0u; limb[0][i] = limb[1][i] = limb[2][i] = limb[3][i] = 0u; }
+}
+__device__ __forceinline__ void topp_sums(uint32_t (*limb)[CAND_BINS], cand_u64* sum, int nbins) {
+  for (int i = threadIdx.x; i < nbins; i += CAND_THREADS)
+    sum[i] = (cand_u64)limb[0][i] + ((cand_u64)limb[1][i] << 11) + ((cand_u64)limb[2][i] << 22) + ((cand_u64)limb[3][i] << 33);
+}
+
 // The first level's histogram of the row's weights: counts and exact sums by the top 12 bits.
 __device__ void topp_level1(const float* __restrict__ l, int vocab, float inv_temp, float mx, ToppShared& sh) {
-  const int tid = threadIdx.x;
-  for (int i = tid; i < CAND_BINS; i += CAND_THREADS) { sh.cnt1[i] = 0u; sh.sum1[i] = 0ull; }
+  topp_clear(sh.limb, sh.cnt1, CAND_BINS);
   __syncthreads();
   cand_scan(l, vocab, [&](int, float v) {
     const float w = expf(cand_finite(v) * inv_temp - mx);
     const uint32_t bin = __float_as_uint(w) >> 20;     // w >= 0: bit order is value order
     cand_count(sh.cnt1, bin);
-    const cand_u64 fx = cand_fx(w);
-    if (fx) atomicAdd(&sh.sum1[bin], fx);
+    topp_add(sh.limb, bin, cand_fx(w));
   });
+  __syncthreads();
+  topp_sums(sh.limb, sh.sum1, CAND_BINS);
   __syncthreads();
 }
 
@@ -471,7 +491,7 @@ __device__ void topp_walk(const float* __restrict__ l, int vocab, float inv_temp
   __syncthreads();
   while (class_cnt > CAND_CAP && pbits < 32) {
     const int nb = pbits < 24 ? 12 : 8, nbins = 1 << nb, shift = 32 - pbits - nb;
-    for (int i = tid; i < nbins; i += CAND_THREADS) { sh.cnt[i] = 0u; sh.sum[i] = 0ull; }
+    topp_clear(sh.limb, sh.cnt, nbins);
     __syncthreads();
     cand_scan(l, vocab, [&](int, float v) {
       const float w = expf(cand_finite(v) * inv_temp - mx);
@@ -479,10 +499,11 @@ __device__ void topp_walk(const float* __restrict__ l, int vocab, float inv_temp
       if (cand_class(key, pbits) == prefix) {
         const uint32_t bin = (key >> shift) & (uint32_t)(nbins - 1);
         cand_count(sh.cnt, bin);
-        const cand_u64 fx = cand_fx(w);
-        if (fx) atomicAdd(&sh.sum[bin], fx);
+        topp_add(sh.limb, bin, cand_fx(w));
       }
     });
+    __syncthreads();
+    topp_sums(sh.limb, sh.sum, nbins);
     __syncthreads();
     // what is left of the threshold inside this class; beyond its whole sum: the class's last token
     cand_find_boundary(sh.cnt, sh.sum, nbins, 0u, thr >= above ? thr - above : 0ull, sh.bd);
