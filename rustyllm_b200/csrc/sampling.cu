@@ -77,8 +77,13 @@ extern "C" int rl_repeat_penalty(float* logits, int rows, int vocab, const int* 
 }
 
 // ------------------------------------------------------------------ cluster helpers
-#define SAMPLE_CLUSTER 8
+#define SAMPLE_CLUSTER 8      // CTAs a row at most (the launch chooses 1, 2, 4 or 8: sample_cluster_for)
 
+__device__ __forceinline__ uint32_t sample_cluster_size() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
 __device__ __forceinline__ uint32_t sample_cluster_rank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -98,7 +103,8 @@ __device__ __forceinline__ uint32_t sample_peer_u32(const void* p, uint32_t rank
 // this CTA's share [lo, hi) of a row: whole multiples of 1024 entries, so that each warp's
 // part of it starts on a multiple of 32
 __device__ __forceinline__ void sample_slice(int vocab, int* lo, int* hi, int* per_warp) {
-  const int slice = ((vocab + SAMPLE_CLUSTER - 1) / SAMPLE_CLUSTER + SAMPLE_THREADS - 1) / SAMPLE_THREADS * SAMPLE_THREADS;
+  const int ncta = (int)sample_cluster_size();
+  const int slice = ((vocab + ncta - 1) / ncta + SAMPLE_THREADS - 1) / SAMPLE_THREADS * SAMPLE_THREADS;
   *lo = min((int)sample_cluster_rank() * slice, vocab);
   *hi = min(*lo + slice, vocab);
   *per_warp = slice / (SAMPLE_THREADS / 32);
@@ -140,7 +146,7 @@ __device__ int cluster_argmax(const float* __restrict__ l, int vocab) {
   sample_cluster_sync();
   int result = -1;
   if (threadIdx.x == 0 && sample_cluster_rank() == 0) {
-    for (uint32_t r = 1; r < SAMPLE_CLUSTER; ++r)
+    for (uint32_t r = 1; r < sample_cluster_size(); ++r)
       argmax_combine(bv, bi, __uint_as_float(sample_peer_u32(&cta_v, r)), (int)sample_peer_u32(&cta_i, r));
     result = (bi == 0x7fffffff) ? 0 : bi;   // nothing finite: token 0
   }
@@ -150,20 +156,30 @@ __device__ int cluster_argmax(const float* __restrict__ l, int vocab) {
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
-  const int row = blockIdx.x / SAMPLE_CLUSTER;
+  const int row = blockIdx.x / (int)sample_cluster_size();
   const int r = cluster_argmax(logits + (size_t)row * vocab, vocab);
   if (r >= 0) out[row] = r;
 }
 
+// CTAs a row: eight while they fill no more than half of the SMs, else the most (4, 2, 1) that leave
+// every CTA of the launch an SM of its own - a CTA has 1,024 threads, two fit an SM, and 64 rows of
+// eight CTAs ran as two waves (temperature sampling of 64 rows of 128,256 logits: 51 us, as two CTAs a
+// row 42 us; 256 rows: 173 and 121 us; argmax of 256 rows: 53 and 26 us).  Small vocabularies: one CTA.
+static int sample_cluster_for(int rows, int vocab) {
+  const int sms = rl_num_sms();
+  return vocab < 16384 ? 1 : rows * 16 <= sms ? 8 : rows * 4 <= sms ? 4 : rows * 2 <= sms ? 2 : 1;
+}
+
 static cudaError_t sample_launch_cluster(void (*kernel)(const float*, int, int*), int rows, cudaStream_t stream,
                                          const float* logits, int vocab, int* out) {
+  const int cl = sample_cluster_for(rows, vocab);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(rows * SAMPLE_CLUSTER);
+  cfg.gridDim = dim3(rows * cl);
   cfg.blockDim = dim3(SAMPLE_THREADS);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = SAMPLE_CLUSTER; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  attr[0].val.clusterDim.x = cl; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, logits, vocab, out);
@@ -190,7 +206,8 @@ sample_temperature_kernel(const float* __restrict__ logits, int vocab, const flo
   __shared__ float range_sum[NW];
   __shared__ float red[NW];
   __shared__ float cta_max, cta_sum;
-  const int row = blockIdx.x / SAMPLE_CLUSTER;
+  const uint32_t ncta = sample_cluster_size();
+  const int row = blockIdx.x / (int)ncta;
   const uint32_t rank = sample_cluster_rank();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float* l = logits + (size_t)row * vocab;
@@ -219,7 +236,7 @@ sample_temperature_kernel(const float* __restrict__ logits, int vocab, const flo
   }
   sample_cluster_sync();                                       // barrier 1
   mx = -INFINITY;
-  for (uint32_t r = 0; r < SAMPLE_CLUSTER; ++r) mx = fmaxf(mx, __uint_as_float(sample_peer_u32(&cta_max, r)));
+  for (uint32_t r = 0; r < ncta; ++r) mx = fmaxf(mx, __uint_as_float(sample_peer_u32(&cta_max, r)));
   if (!(mx > -INFINITY)) {  // nothing finite
     if (threadIdx.x == 0 && rank == 0) out[row] = 0;
     sample_cluster_sync();
@@ -247,7 +264,7 @@ sample_temperature_kernel(const float* __restrict__ logits, int vocab, const flo
   float totals[SAMPLE_CLUSTER];
   float total = 0.f;
 #pragma unroll
-  for (uint32_t r = 0; r < SAMPLE_CLUSTER; ++r) { totals[r] = __uint_as_float(sample_peer_u32(&cta_sum, r)); total += totals[r]; }
+  for (uint32_t r = 0; r < SAMPLE_CLUSTER; ++r) { totals[r] = r < ncta ? __uint_as_float(sample_peer_u32(&cta_sum, r)) : 0.f; if (r < ncta) total += totals[r]; }
   sample_cluster_sync();                                       // barrier 3: shared memory of peers is not read below
   if (!isfinite(total) || total <= 0.f) {  // src/sampling.rs:112-119: fall back to the best index
     const int r = cluster_argmax(l, vocab);
@@ -259,7 +276,7 @@ sample_temperature_kernel(const float* __restrict__ logits, int vocab, const flo
   int chosen_cta = -1;
 #pragma unroll
   for (int c = 0; c < SAMPLE_CLUSTER; ++c) {
-    if (chosen_cta < 0) {
+    if (chosen_cta < 0 && c < (int)ncta) {
       const float incl = before + totals[c];
       if (incl > r && totals[c] > 0.f) chosen_cta = c; else before = incl;
     }
@@ -318,13 +335,14 @@ extern "C" int rl_sample_temperature(const float* logits, int rows, int vocab, c
                                      cudaStream_t stream) {
   RL_REQUIRE(rows >= 0 && vocab > 0, "rl_sample_temperature: bad sizes rows=%d vocab=%d", rows, vocab);
   if (rows == 0) return RL_OK;
+  const int cl = sample_cluster_for(rows, vocab);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(rows * SAMPLE_CLUSTER);
+  cfg.gridDim = dim3(rows * cl);
   cfg.blockDim = dim3(SAMPLE_THREADS);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = SAMPLE_CLUSTER; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  attr[0].val.clusterDim.x = cl; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, sample_temperature_kernel, logits, vocab, temperature, uniform, min_p, out);
