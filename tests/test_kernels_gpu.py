@@ -1031,6 +1031,51 @@ def test_candidate_sampling_with_thousands_of_equal_logits(V):
                 f"row {i} {rows[i][1]} trial {trial}: {got[i]} (place {j}) vs {want}, u = {u}"
 
 
+@pytest.mark.parametrize("rows", [5, 30, 60, 90])
+def test_top_k_rows_in_clusters_of_every_size(rows):
+    """The top-k kernel gives a row of a large vocabulary to a cluster of 8, 4 or 2 CTAs or to one
+    CTA, by the number of rows of the call; the temperature and argmax kernels likewise.  Every
+    row of every such call against the plain sampler."""
+    from rustyllm_b200.sampling.config import SamplerConfig
+    from rustyllm_b200.sampling.sampler import Sampler, SequenceSamplingState
+    V = 20000
+    g = torch.Generator().manual_seed(rows)
+    base = torch.randn(rows, V, generator=g) * 3.0
+    kinds = [dict(top_k=40, top_p=0.9), dict(), dict(temperature=0.0), dict(top_k=7, min_p=0.05)]
+    configs = [SamplerConfig(**{"temperature": 0.8, **kinds[i % 4]}) for i in range(rows)]
+    sampler = Sampler(torch.device(DEV))
+    states = [SequenceSamplingState(c, 70 + i, []) for i, c in enumerate(configs)]
+    twins = [P.Rng(70 + i) for i in range(rows)]
+    differed = 0
+    for trial in range(2):
+        got = sampler.sample(base.clone().to(DEV), states)
+        for i, c in enumerate(configs):
+            if c.is_greedy:
+                assert got[i] == int(base[i].argmax())
+                continue
+            u = twins[i].next_f32()
+
+            class Fixed:
+                def next_f32(self, v=u): return v
+            lg = base[i].numpy().copy()
+            want = P.sample(lg, c.temperature, Fixed(), c.top_k, c.top_p, c.min_p, c.repeat_penalty, recent=[])
+            if got[i] == want:
+                continue
+            differed += 1
+            if c.top_k > 0:
+                kept, w = _kept_candidates(lg, c.temperature, c.top_k, c.top_p, c.min_p)
+            else:                     # the whole vocabulary in index order, as the reference walks it
+                kept = np.arange(V)
+                w = np.exp((lg.astype(np.float64) - lg.max()) / c.temperature)
+            where = np.nonzero(kept == got[i])[0]
+            assert where.size == 1, f"row {i} {kinds[i % 4]}: token {got[i]} is not among the {len(kept)} kept (plain: {want})"
+            j = int(where[0])
+            pre = np.cumsum(w) / w.sum()
+            slack = max(len(kept) * 2.0 ** -24, 1e-6)
+            assert (pre[j - 1] if j else 0.0) <= u + slack and pre[j] >= u - slack, f"row {i}: {got[i]} vs {want}, u = {u}"
+    assert differed <= max(2, rows // 10)
+
+
 def test_temperature_zero_rows_are_greedy_and_min_p_cuts():
     k = K()
     logits = torch.tensor([[1.0, 5.0, 2.0, 4.9], [10.0, 9.5, 3.0, 1.0]], device=DEV)
