@@ -164,7 +164,7 @@ argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out
 // CTAs a row: eight while they fill no more than half of the SMs, else the most (4, 2, 1) that leave
 // every CTA of the launch an SM of its own - a CTA has 1,024 threads, two fit an SM, and 64 rows of
 // eight CTAs ran as two waves (temperature sampling of 64 rows of 128,256 logits: 51 us, as two CTAs a
-// row 42 us; 256 rows: 173 and 121 us; argmax of 256 rows: 53 and 26 us).  Small vocabularies: one CTA.
+// row 26 us; 256 rows: 173 and 66 us; argmax of 256 rows: 53 and 26 us).  Small vocabularies: one CTA.
 static int sample_cluster_for(int rows, int vocab) {
   const int sms = rl_num_sms();
   return vocab < 16384 ? 1 : rows * 16 <= sms ? 8 : rows * 4 <= sms ? 4 : rows * 2 <= sms ? 2 : 1;
@@ -203,9 +203,14 @@ sample_temperature_kernel(const float* __restrict__ logits, int vocab, const flo
                           const float* __restrict__ uniform, const float* __restrict__ min_p,
                           int* __restrict__ out) {
   constexpr int NW = SAMPLE_THREADS / 32;
-  __shared__ float range_sum[NW];
+  // The row is summed in SAMPLE_CLUSTER parts of NW ranges each, whatever the number of CTAs the
+  // launch gave it (a CTA takes SAMPLE_CLUSTER / ncta parts in turn): every sum below is the same
+  // additions in the same order for 1, 2, 4 and 8 CTAs a row, so a row's draw does not depend on
+  // how many rows the call has.
+  __shared__ float range_sum[SAMPLE_CLUSTER][NW];
+  __shared__ float part_sum[SAMPLE_CLUSTER];
   __shared__ float red[NW];
-  __shared__ float cta_max, cta_sum;
+  __shared__ float cta_max;
   const uint32_t ncta = sample_cluster_size();
   const int row = blockIdx.x / (int)ncta;
   const uint32_t rank = sample_cluster_rank();
@@ -219,8 +224,10 @@ sample_temperature_kernel(const float* __restrict__ logits, int vocab, const flo
   }
   const float inv_temp = 1.0f / temp;
   const float cut = min_p ? min_p[row] : 0.f;
-  int lo, hi, per_warp;
-  sample_slice(vocab, &lo, &hi, &per_warp);
+  const int part = ((vocab + SAMPLE_CLUSTER - 1) / SAMPLE_CLUSTER + SAMPLE_THREADS - 1) / SAMPLE_THREADS * SAMPLE_THREADS;
+  const int per_warp = part / NW;                 // tokens a range
+  const int ppc = SAMPLE_CLUSTER / (int)ncta;     // parts a CTA
+  const int lo = min((int)rank * ppc * part, vocab), hi = min(lo + ppc * part, vocab);
 
   // 1. maximum of the scaled finite logits: this CTA's share, then the cluster's
   float mx = -INFINITY;
@@ -243,28 +250,34 @@ sample_temperature_kernel(const float* __restrict__ logits, int vocab, const flo
     return;
   }
 
-  // 2. weights, summed over one contiguous range of the vocabulary per warp
-  const int wlo = min(lo + warp * per_warp, hi), whi = min(wlo + per_warp, hi);
-  float mine = 0.f;
+  // 2. weights, summed over one contiguous range of the vocabulary per warp and part
+  for (int q = 0; q < ppc; ++q) {
+    const int plo = min(lo + q * part, hi);
+    const int wlo = min(plo + warp * per_warp, hi), whi = min(min(wlo + per_warp, plo + part), hi);
+    float mine = 0.f;
 #pragma unroll 8
-  for (int i = wlo + lane; i < whi; i += 32) {
-    const float w = expf(finite_or_neg_inf(l[i]) * inv_temp - mx);
-    if (w >= cut) mine += w;
+    for (int i = wlo + lane; i < whi; i += 32) {
+      const float w = expf(finite_or_neg_inf(l[i]) * inv_temp - mx);
+      if (w >= cut) mine += w;
+    }
+    for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+    if (lane == 0) range_sum[q][warp] = mine;
   }
-  for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
-  if (lane == 0) range_sum[warp] = mine;
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if ((int)threadIdx.x < ppc) {
     float t = 0.f;
-    for (int w = 0; w < NW; ++w) t += range_sum[w];
-    cta_sum = t;
+    for (int w = 0; w < NW; ++w) t += range_sum[threadIdx.x][w];
+    part_sum[threadIdx.x] = t;
   }
   sample_cluster_sync();                                       // barrier 2
-  // every thread walks the CTAs' totals (the same additions in the same order everywhere)
+  // every thread walks the parts' totals (the same additions in the same order everywhere)
   float totals[SAMPLE_CLUSTER];
   float total = 0.f;
 #pragma unroll
-  for (uint32_t r = 0; r < SAMPLE_CLUSTER; ++r) { totals[r] = r < ncta ? __uint_as_float(sample_peer_u32(&cta_sum, r)) : 0.f; if (r < ncta) total += totals[r]; }
+  for (int p = 0; p < SAMPLE_CLUSTER; ++p) {
+    totals[p] = __uint_as_float(sample_peer_u32(&part_sum[p % ppc], (uint32_t)(p / ppc)));
+    total += totals[p];
+  }
   sample_cluster_sync();                                       // barrier 3: shared memory of peers is not read below
   if (!isfinite(total) || total <= 0.f) {  // src/sampling.rs:112-119: fall back to the best index
     const int r = cluster_argmax(l, vocab);
@@ -273,15 +286,15 @@ sample_temperature_kernel(const float* __restrict__ logits, int vocab, const flo
   }
   const float r = uniform[row] * total;
   float before = 0.f;       // sum in front of the chosen part
-  int chosen_cta = -1;
+  int chosen_part = -1;
 #pragma unroll
-  for (int c = 0; c < SAMPLE_CLUSTER; ++c) {
-    if (chosen_cta < 0 && c < (int)ncta) {
-      const float incl = before + totals[c];
-      if (incl > r && totals[c] > 0.f) chosen_cta = c; else before = incl;
+  for (int p = 0; p < SAMPLE_CLUSTER; ++p) {
+    if (chosen_part < 0) {
+      const float incl = before + totals[p];
+      if (incl > r && totals[p] > 0.f) chosen_part = p; else before = incl;
     }
   }
-  if (chosen_cta < 0) {
+  if (chosen_part < 0) {
     // rounding left r at or above the total: the last kept candidate (src/sampling.rs:210)
     if (threadIdx.x == 0 && rank == 0) {
       int last = vocab - 1;  // without a cut the reference answers n - 1 (src/sampling.rs:211)
@@ -293,20 +306,23 @@ sample_temperature_kernel(const float* __restrict__ logits, int vocab, const flo
     }
     return;
   }
-  if ((int)rank != chosen_cta) return;
+  if ((int)rank != chosen_part / ppc) return;
+  const int q = chosen_part % ppc;
   int chosen = -1;
   for (int w = 0; w < NW; ++w) {
-    const float incl = before + range_sum[w];
-    if (incl > r && range_sum[w] > 0.f) { chosen = w; break; }
+    const float incl = before + range_sum[q][w];
+    if (incl > r && range_sum[q][w] > 0.f) { chosen = w; break; }
     before = incl;
   }
-  if (chosen < 0) {          // the CTA's total said "in here", the walk over its ranges "not yet": its last range that kept anything
-    for (int w = NW - 1; w >= 0; --w) if (range_sum[w] > 0.f) { chosen = w; break; }
+  if (chosen < 0) {          // the part's total said "in here", the walk over its ranges "not yet": its last range that kept anything
+    for (int w = NW - 1; w >= 0; --w) if (range_sum[q][w] > 0.f) { chosen = w; break; }
     before = -INFINITY;      // the walk below then never passes r and ends at the range's last kept entry
   }
   if (warp != chosen) return;
   // 3. the chosen warp walks its range, 32 entries at a time, to the entry where the
   // running sum passes r
+  const int plo = min(lo + q * part, hi);
+  const int wlo = min(plo + warp * per_warp, hi), whi = min(min(wlo + per_warp, plo + part), hi);
   float c = before;
   int last_kept = wlo;
   for (int i0 = wlo; i0 < whi; i0 += 32) {

@@ -1076,6 +1076,28 @@ def test_top_k_rows_in_clusters_of_every_size(rows):
     assert differed <= max(2, rows // 10)
 
 
+def test_a_rows_draw_does_not_depend_on_how_many_rows_the_call_has():
+    """The temperature kernel gives a row 8, 4, 2 or 1 CTAs by the number of rows of the call and
+    sums the row in the same eight parts either way: the same logits and the same uniform number
+    give the same token in calls of 1, 12, 40 and 80 rows, bit for bit the same sums."""
+    k = K()
+    V = 128256
+    g = torch.Generator().manual_seed(11)
+    row = (torch.randn(V, generator=g) * 3.0).to(DEV)
+    answers = []
+    for u in (0.013, 0.37, 0.5, 0.93, 0.999999):
+        per_call = []
+        for rows in (1, 12, 40, 80):
+            logits = row.repeat(rows, 1).contiguous()
+            out = torch.empty(rows, dtype=torch.int32, device=DEV)
+            k.sample_temperature(logits, torch.full((rows,), 0.8, device=DEV), torch.full((rows,), u, device=DEV), out)
+            assert (out == out[0]).all()
+            per_call.append(int(out[0]))
+        assert len(set(per_call)) == 1, f"u = {u}: {per_call}"
+        answers.append(per_call[0])
+    assert len(set(answers)) > 2
+
+
 def test_temperature_zero_rows_are_greedy_and_min_p_cuts():
     k = K()
     logits = torch.tensor([[1.0, 5.0, 2.0, 4.9], [10.0, 9.5, 3.0, 1.0]], device=DEV)
