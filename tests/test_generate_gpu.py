@@ -95,6 +95,32 @@ def test_stop_tokens_and_batches_one_after_another(model_dirs):
     assert r.cache.free_pages == r.cache.num_pages and r.cache.slots.free_count == 2
 
 
+@pytest.mark.parametrize("name,cache_tokens,max_batch", [("A", 64 * 6, 3), ("B", 64 * 16, 5), ("B", 64 * 40, 16)])
+def test_many_random_requests_through_a_small_cache(model_dirs, name, cache_tokens, max_batch):
+    """Dozens of requests of random lengths and a random token budget through caches far too small
+    for them at once: batches follow one another, sequences end early (tiny B stops at two ids),
+    slots and pages are taken again.  Greedy in 32-bit, every sequence token for token as the
+    plain loop makes it; the cache is whole afterwards."""
+    import random
+    from rustyllm_b200 import GenerationOptions, Runner, SamplerConfig
+    d, cfg = model_dirs[name]
+    pc, pw = _plain(d)
+    V, maxpos = cfg["vocab_size"], cfg["max_position_embeddings"]
+    eos = cfg.get("eos_token_id")
+    stop = eos if isinstance(eos, list) else [eos]
+    rng = random.Random(cache_tokens)
+    r, _ = Runner.from_path(d, dtype="float32", max_cache_tokens=cache_tokens, max_batch=max_batch)
+    for _ in range(2):
+        n, budget = rng.randrange(4, 24), rng.randrange(1, 28)
+        prompts = [random_tokens(V, rng.randrange(1, min(maxpos - 30, cache_tokens // 2)), rng.randrange(1 << 30)) for _ in range(n)]
+        res = r.generate(prompts, GenerationOptions(max_tokens=budget, sampler=SamplerConfig.greedy(), seed=3))
+        for p, got in zip(prompts, res):
+            want = P.generate(pc, pw, p, min(budget, maxpos - len(p)), temperature=0.0, stop_ids=stop)
+            assert got.token_ids == want, f"a prompt of {len(p)} tokens among {n} requests"
+        r.cache.check()
+        assert r.cache.free_pages == r.cache.num_pages
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_running_ahead_of_the_host_generates_the_same_tokens(model_dirs, dtype):
     """The loop queues a step before it has read the previous step's tokens; with stop tokens
