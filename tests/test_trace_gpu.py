@@ -89,3 +89,56 @@ def test_replay_three_cuts(model_dirs, tmp_path, name, dtype):
         got = read_step(out_dir, step, V)
         ref = torch.cat([plain_logits(d, reqs[rid])[pos] for rid, pos in exp])
         assert_close_logits(got, ref, dtype, f"{name} step {step}")
+
+
+@pytest.mark.parametrize("name", ["C", "E"])
+def test_replay_of_a_random_trace(model_dirs, tmp_path, name):
+    """Batches drawn at random, one after another: 1 to 8 requests of 1 to 300 prompt tokens and 0 to
+    39 further tokens each, logits wanted at random places of the prompts and at four decoded tokens
+    in five, requests that end with their prompt, steps in which nothing is wanted; the cache sized
+    to the token exactly (the most that live requests hold, each rounded up to 64).  Both dtypes."""
+    import random
+    d, cfg = model_dirs[name]
+    V, maxpos = cfg["vocab_size"], cfg["max_position_embeddings"]
+    rng = random.Random(len(name) + V)
+    steps, expect, reqs, sn, peak = [], {}, {}, 0, 0
+    for batch in range(3):
+        ids = [f"b{batch}r{i}" for i in range(rng.randrange(1, 9))]
+        lens = {r: rng.randrange(1, min(300, maxpos - 45)) for r in ids}
+        decs = {r: rng.randrange(0, 40) for r in ids}
+        for r in ids:
+            reqs[r] = random_tokens(V, lens[r] + decs[r], rng.randrange(1 << 30))
+        peak = max(peak, sum(-(-(lens[r] + decs[r]) // 64) * 64 for r in ids))
+        entries, exp = [], []
+        for r in ids:
+            want = sorted(rng.sample(range(lens[r]), rng.randrange(0, min(4, lens[r]) + 1)))
+            entries.append({"id": r, "tokens": reqs[r][:lens[r]], "want": want})
+            if want:
+                exp.append((r, want))
+        steps.append({"step": sn, "entries": entries, "end": [r for r in ids if decs[r] == 0]})
+        if exp:
+            expect[sn] = exp
+        sn += 1
+        fed, live = dict(lens), [r for r in ids if decs[r] > 0]
+        while live:
+            entries, exp, end = [], [], []
+            for r in live:
+                want = [0] if rng.random() < 0.8 else []
+                entries.append({"id": r, "tokens": [reqs[r][fed[r]]], "want": want})
+                if want:
+                    exp.append((r, [fed[r]]))
+                fed[r] += 1
+                if fed[r] == len(reqs[r]):
+                    end.append(r)
+            steps.append({"step": sn, "entries": entries, "end": end})
+            if exp:
+                expect[sn] = exp
+            sn += 1
+            live = [r for r in live if fed[r] < len(reqs[r])]
+    for dtype in ("float32", "bfloat16"):
+        out_dir = str(tmp_path / dtype)
+        run_trace(d, dtype, steps, out_dir, max_tokens=peak)
+        for step, exp in expect.items():
+            got = read_step(out_dir, step, V)
+            ref = torch.cat([plain_logits(d, reqs[r])[pos] for r, pos in exp])
+            assert_close_logits(got, ref, dtype, f"{name} step {step}")
