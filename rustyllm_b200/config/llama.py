@@ -178,6 +178,12 @@ class LlamaConfig:
                 rope_theta = float(rope_params["rope_theta"])
             if scaling_raw is None:
                 scaling_raw = rope_params
+        # keys of other architectures that would change the arithmetic if they meant anything here:
+        # refused rather than ignored
+        if d.get("partial_rotary_factor") not in (None, 1, 1.0):
+            raise ConfigError(f"partial_rotary_factor = {d['partial_rotary_factor']!r}: this architecture rotates the whole head")
+        if d.get("sliding_window") is not None:
+            raise ConfigError(f"sliding_window = {d['sliding_window']!r}: this architecture attends to the whole context")
         dtype = d.get("torch_dtype", d.get("dtype", "bfloat16"))
         if dtype not in ("bfloat16", "float32", "float16"):
             raise ConfigError(f"torch_dtype {dtype!r} is not one of bfloat16, float32, float16")

@@ -101,3 +101,11 @@ def test_generation_config_adds_its_stop_ids(tmp_path):
     (d / "generation_config.json").write_text("[1, 2]")
     with pytest.raises(ConfigError, match="object"):
         read_generation_stop_ids(str(d), 256)
+
+
+def test_keys_of_other_architectures_that_would_change_the_arithmetic_are_refused():
+    base = dict(vocab_size=32, hidden_size=16, intermediate_size=24, num_hidden_layers=1, num_attention_heads=2)
+    assert LlamaConfig.from_dict(dict(base, partial_rotary_factor=1.0, sliding_window=None, use_cache=True)).head_dim == 8
+    for extra in (dict(partial_rotary_factor=0.5), dict(sliding_window=4096)):
+        with pytest.raises(ConfigError):
+            LlamaConfig.from_dict(dict(base, **extra))
