@@ -14,10 +14,12 @@
 // neighbouring entries a load; then the ranges' totals in index order), so a row's
 // answer does not depend on the other rows.
 //
-// A row is the work of a thread-block cluster of 8 CTAs, an eighth of the vocabulary
-// each, so that enough loads are in flight to read a row of 128 K logits in a few
-// microseconds; the CTAs exchange their maxima and sums through distributed shared
-// memory.  Every path through a kernel passes the same cluster barriers in all CTAs.
+// A row is the work of a thread-block cluster of up to 8 CTAs (8 while the call's rows leave
+// room for that, else 4, 2 or 1), each with its share of the vocabulary, so that enough loads
+// are in flight to read a row of 128 K logits in a few microseconds; the CTAs exchange their
+// maxima and sums through distributed shared memory.  The sums are taken over the same eight
+// parts of the row whatever the number of CTAs, so a row's draw is the same in a call of one
+// row and of a hundred.  Every path through a kernel passes the same cluster barriers in all CTAs.
 #include <math.h>
 
 #include "common.cuh"
