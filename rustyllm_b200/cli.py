@@ -69,6 +69,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--kernel-bench", action="store_true", help="Run isolated kernel benchmark")
     p.add_argument("--kernel-bench-json", action="store_true", help="Emit isolated kernel benchmark JSON")
     p.add_argument("--kernel-bench-runs", type=int, default=25, help="Number of kernel benchmark runs (default: 25)")
+    p.add_argument("--kernel-bench-layer", type=int, default=0, help="Transformer layer to benchmark (default: 0)")
+    p.add_argument("--ubatch", type=int, default=None, help="Logical prefill microbatch/chunk size: most prompt tokens one step runs (default: 16384)")
     p.add_argument("--verbose", "-v", action="store_true", help="Print startup timing details")
     p.add_argument("--inspect", action="store_true", help="Inspect config and checkpoint compatibility without loading weights")
     p.add_argument("--list-tensors", action="store_true", help="Print the checkpoint's tensor inventory and exit")
@@ -91,6 +93,8 @@ def _options(args):
     opts = GenerationOptions(max_tokens=args.max_tokens, sampler=sampler, seed=args.seed, stop_token_ids=tuple(stop_ids),
                              stop_sequences=tuple(tuple(s) for s in stop_seqs), ignore_eos=args.ignore_eos,
                              max_context=args.max_context)
+    if args.ubatch is not None:
+        opts.prefill_step_tokens = args.ubatch
     opts.validate()
     return opts
 
@@ -237,26 +241,38 @@ def run_benchmark(runner, info, prompts, opts, runs: int, as_json: bool, with_ou
     return 0
 
 
-def run_kernel_benchmark(runner, runs: int, as_json: bool) -> int:
+def run_kernel_benchmark(runner, runs: int, as_json: bool, layer_index: int = 0) -> int:
     """``--kernel-bench``: per-operation time of one layer at one token, in the spirit of the
     reference's rows (attn_qkv.fused, attn_rope.qk, attn_scan.ctx*, ffn_gate_up.fused,
     ffn_activation.silu_mul, output; src/runtime.rs:2639-2815), with bytes and GB/s."""
     import torch
     from . import kernels as K
-    blk = runner.model.blocks[0]
+    if not 0 <= layer_index < len(runner.model.blocks):
+        raise SystemExit(f"--kernel-bench-layer {layer_index}: the model has layers 0 to {len(runner.model.blocks) - 1}")
+    blk = runner.model.blocks[layer_index]
     att, ff = blk.mixer, blk.feed_forward
     dev, dt = runner.runtime.device, runner.runtime.compute_dtype
     esz = 2 if dt == torch.bfloat16 else 4
     d = runner.model.spec.hidden_size
 
     def timed(fn):
+        """Microseconds a call on the device: the runs are captured in one CUDA graph and replayed,
+        so that the host's time to launch does not stand in for kernels of a few microseconds."""
         for _ in range(3):
             fn()
+        torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(runs):
-            fn()
-        e1.record()
+        stream = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(graph, stream=stream):
+                for _ in range(runs):
+                    fn()
+            graph.replay()
+            stream.synchronize()
+            e0.record(stream)
+            graph.replay()
+            e1.record(stream)
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) * 1e3 / runs
 
@@ -288,7 +304,7 @@ def run_kernel_benchmark(runner, runs: int, as_json: bool) -> int:
             break
         s = eng.alloc_slot()
         eng.step([s], [[1] * ctx], None)
-        group, layer = runner.cache.kv_entry(0)
+        group, layer = runner.cache.kv_entry(layer_index)
         st = eng.step_state(torch.tensor([1, ctx, s, 0, 1, s, ctx + 1, 0], dtype=torch.int32, device=dev), (1, 1, 1), [1], [ctx + 1])
         runner.cache.prepare([s], [1])
         q = torch.randn(1, qkv.shape[1], device=dev).to(dt)
@@ -299,7 +315,7 @@ def run_kernel_benchmark(runner, runs: int, as_json: bool) -> int:
     if as_json:
         # the reference's envelope (src/main.rs:1672-1676): "type" names the record, "format" its layout
         print(json.dumps({"type": "rusty-llm.kernel_benchmark", "format": "llm-kernel-bench.v1", "runtime": "rustyllm_b200",
-                          "model": runner.model_name(), "runs": runs, "layer": 0,
+                          "model": runner.model_name(), "runs": runs, "layer": layer_index,
                           "rows": [{"name": n, "avg_us": t, "bytes": b, "gb_s": b / t / 1e3} for n, t, b in rows]}, indent=2))
     else:
         for n, t, b in rows:
@@ -339,7 +355,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         return 2
     runner, info = _load(args, model_dir, max_batch=max(args.batch, len(prompts) if prompts else 1))
     if kbench:
-        return run_kernel_benchmark(runner, args.kernel_bench_runs, args.kernel_bench_json)
+        return run_kernel_benchmark(runner, args.kernel_bench_runs, args.kernel_bench_json, args.kernel_bench_layer)
     if prompts is None:
         V = runner.model.spec.vocab_size
         prompts = [[rnd.randrange(V) for _ in range(n)] for n in synthetic_prompt_lengths(args, rnd)]
