@@ -45,7 +45,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--model", help="same as the positional model folder")
     p.add_argument("--random", action="store_true", help="random weights from the folder's config.json (no safetensors needed)")
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="compute dtype (default: bfloat16)")
-    p.add_argument("--prompt", "-p", help="input prompt as token ids, e.g. '1 15043 3186'")
+    p.add_argument("--prompt", "--prompt-ids", "-p", dest="prompt", help="input prompt as token ids, e.g. '1 15043 3186' or 1,15043,3186")
     p.add_argument("--prompt-file", help="file with one prompt of token ids per line (a batch)")
     p.add_argument("--max-tokens", "--decode-tokens", "-n", dest="max_tokens", type=int, default=256, help="Max tokens to generate (default: 256)")
     p.add_argument("--temp", "-t", type=float, default=0.7, help="Temperature (default: 0.7, 0=greedy)")
