@@ -43,8 +43,11 @@ class StepState:
     # that needs, say, a work plan of the sequences makes it once and leaves it here)
     derived: Dict[object, object] = field(default_factory=dict)
     # the longest sequence holds more than kernels.LONG_CONTEXT tokens.  A part may choose another
-    # launch shape by it: captured steps are kept per (number of sequences, this flag).
+    # launch shape by it: captured steps are kept per (number of sequences, this flag, the next).
     long_context: bool = False
+    # how far the longest sequence lies above the mean of all (kernels.length_spread: 0 equal,
+    # 1 near, 2 far); 2 where nobody said: the choice that is right for any lengths
+    length_spread: int = 2
 
 
 Want = Union[str, None, Sequence[Sequence[int]]]
@@ -55,12 +58,12 @@ class _DecodeGraph:
     the step's integers from ``static_in`` and leave logits in ``logits``; everything
     they read beyond that (page tables, cache pools, weights) keeps its address."""
 
-    def __init__(self, engine: "Engine", num_seqs: int, long_context: bool = False):
+    def __init__(self, engine: "Engine", num_seqs: int, long_context: bool = False, length_spread: int = 2):
         B = num_seqs
         self.num_seqs = B
         dev = engine.device
         self.static_in = torch.zeros(7 * B + 1, dtype=torch.int32, device=dev)
-        st = engine.step_state(self.static_in, (B, B, B), [1] * B, [K.LONG_CONTEXT + 1 if long_context else 1] * B)
+        st = engine.step_state(self.static_in, (B, B, B), [1] * B, [1] * B, lengths_class=(long_context, length_spread))
         before = K.launch_count
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
@@ -104,9 +107,9 @@ class _DecodeGraph:
 class Engine:
     """A model with its cache and the step function over them.
 
-    ``use_graphs``: single-token steps are captured once per batch size in a CUDA graph
-    and replayed (the first such step of a size runs eagerly, so every kernel has been
-    launched once before it is captured)."""
+    ``use_graphs``: single-token steps are captured once per batch size and class of the
+    sequences' lengths (``lengths_class``) in a CUDA graph and replayed (the first such step
+    of a kind runs eagerly, so every kernel has been launched once before it is captured)."""
 
     def __init__(self, model: DecoderModel, cache: SequenceCache, use_graphs: bool = True):
         self.model = model
@@ -116,8 +119,8 @@ class Engine:
         self._staging = PinnedStaging(self.device) if self.device.type == "cuda" else None
         self.h2d_bytes = 0
         self.use_graphs = use_graphs and self.device.type == "cuda" and model.graph_capturable
-        self._graphs = {}          # (num_seqs, long context) -> _DecodeGraph
-        self._eager_decodes = {}   # (num_seqs, long context) -> eager single-token steps run so far
+        self._graphs = {}          # (num_seqs, long context, length spread) -> _DecodeGraph
+        self._eager_decodes = {}   # (num_seqs, long context, length spread) -> eager single-token steps run so far
 
     # ------------------------------------------------------------------ slots
     def alloc_slot(self) -> int:
@@ -133,20 +136,21 @@ class Engine:
         if not self.use_graphs:
             return
         for B in sorted(set(int(b) for b in batch_sizes)):
-            if B <= 0 or (B, False) in self._graphs:
+            classes = [(False, spread) for spread in ((0,) if B == 1 else (0, 1, 2))]
+            if B <= 0 or all((B,) + c in self._graphs for c in classes):
                 continue
             slots: List[int] = []
             try:
                 for _ in range(B):                             # one by one: a failure part-way frees those taken
                     slots.append(self.alloc_slot())
                 self.step(slots, [[0]] * B, None)              # one token each, so that a length exists
-                while (B, False) not in self._graphs:          # an eager step first, then the capture
-                    self.step(slots, [[0]] * B, "last")
+                for c in classes:                              # the launches of every class of lengths a batch can have
+                    while (B,) + c not in self._graphs:        # an eager step first, then the capture
+                        self.step(slots, [[0]] * B, "last", _lengths_class=c)
             finally:
                 for s in slots:
                     self.free_slot(s)
 
-    # ------------------------------------------------------------------ the step
     def build_step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], want: Want = "last"):
         """Validate on the host and lay out the step's integer inputs."""
         B = len(slots)
@@ -199,8 +203,15 @@ class Engine:
             np.asarray(rows, dtype=np.int32)])
         return packed, (M, B, len(rows)), q_lens, kv_lens
 
-    def step_state(self, packed_dev: torch.Tensor, sizes, q_lens, kv_lens) -> StepState:
+    @staticmethod
+    def lengths_class(kv_lens: Sequence[int]):
+        """What of the sequences' lengths a kernel's launch shape may depend on (``StepState.long_context``,
+        ``StepState.length_spread``); captured steps are kept by it."""
+        return max(kv_lens) > K.LONG_CONTEXT, K.length_spread(kv_lens)
+
+    def step_state(self, packed_dev: torch.Tensor, sizes, q_lens, kv_lens, lengths_class=None) -> StepState:
         M, B, W = sizes
+        long_context, spread = lengths_class if lengths_class is not None else self.lengths_class(kv_lens)
         o = 0
         def take(n):
             nonlocal o
@@ -212,7 +223,7 @@ class Engine:
         rows = take(W)
         return StepState(M, B, tokens, positions, slot_of_token, cu, seq_slots, kv, rows,
                          list(q_lens), list(kv_lens), max(q_lens), max(kv_lens),
-                         all(n == 1 for n in q_lens), long_context=max(kv_lens) > K.LONG_CONTEXT)
+                         all(n == 1 for n in q_lens), long_context=long_context, length_spread=spread)
 
     def step_borrowed(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], want: Want = "last") -> Optional[torch.Tensor]:
         """``step`` for a caller that is done with the logits before its next step (the
@@ -229,7 +240,7 @@ class Engine:
         when no captured step for this many sequences exists yet and nothing was run."""
         B = len(slots)
         starts = [self.cache.length(s) for s in slots]
-        g = self._graphs.get((B, max(starts) + 1 > K.LONG_CONTEXT)) if self.use_graphs and B > 0 else None
+        g = self._graphs.get((B,) + self.lengths_class([n + 1 for n in starts])) if self.use_graphs and B > 0 else None
         if g is None:
             return None
         if token_ids.dtype != torch.int32 or token_ids.numel() != B:
@@ -244,7 +255,7 @@ class Engine:
         return g.logits
 
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], want: Want = "last",
-             _borrow: bool = False) -> Optional[torch.Tensor]:
+             _borrow: bool = False, _lengths_class=None) -> Optional[torch.Tensor]:
         """Run the given tokens of the given sequences as one batch from the cache.
 
         ``slots[b]`` holds sequence b, whose next tokens are ``tokens[b]`` (they take
@@ -258,10 +269,10 @@ class Engine:
                   and all(len(t) == 1 for t in tokens))
         if decode:
             starts = [self.cache.length(s) for s in slots]
-            key = (B, max(starts) + 1 > K.LONG_CONTEXT)
+            key = (B,) + (_lengths_class or self.lengths_class([n + 1 for n in starts]))
             g = self._graphs.get(key)
             if g is None and self._eager_decodes.get(key, 0) >= 1:
-                g = self._graphs[key] = _DecodeGraph(self, B, key[1])
+                g = self._graphs[key] = _DecodeGraph(self, B, key[1], key[2])
             if g is not None:
                 # the short way for the step that generation repeats: same checks, same layout
                 # of the integers as build_step, no intermediate arrays
@@ -284,7 +295,7 @@ class Engine:
         else:
             dev = torch.from_numpy(packed).to(self.device)
         self.h2d_bytes += packed.nbytes
-        st = self.step_state(dev, sizes, q_lens, kv_lens)
+        st = self.step_state(dev, sizes, q_lens, kv_lens, _lengths_class)
         x = self.model.forward(st, self.cache)
         self.cache.commit(slots, q_lens)
         if sizes[2] == 0:

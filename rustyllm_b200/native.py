@@ -45,7 +45,7 @@ class RlModelDesc(ctypes.Structure):
 class RlStepDesc(ctypes.Structure):
     _fields_ = [("M", _i), ("B", _i), ("is_decode", _i), ("tokens", _vp), ("positions", _vp), ("slot_of_token", _vp),
                 ("cu_seqlens", _vp), ("seq_slots", _vp), ("kv_lens", _vp), ("tiles_tc", _i), ("tiles_mma", _i),
-                ("tile_order", _vp), ("long_context", _i)]
+                ("tile_order", _vp), ("long_context", _i), ("length_spread", _i)]
 
 
 def _matrix_ok(w: Optional[torch.Tensor]) -> bool:
@@ -149,7 +149,8 @@ class NativeDecoder:
                         seq_slots=step.seq_slots.data_ptr(), kv_lens=step.kv_lens.data_ptr(),
                         tiles_tc=sum(-(-n // K.PREFILL_TC_QTILE) for n in step.q_lens),
                         tiles_mma=sum(-(-n // K.PREFILL_QTILE) for n in step.q_lens),
-                        tile_order=None if order is None else order.data_ptr(), long_context=int(step.long_context))
+                        tile_order=None if order is None else order.data_ptr(), long_context=int(step.long_context),
+                        length_spread=int(step.length_spread))
         rc = self.lib.rl_decoder_forward(self._desc_ptr, ctypes.addressof(sd), x.data_ptr(), work.data_ptr(), nbytes,
                                          self._err.data_ptr(), self.model.embedding.bad_token.data_ptr(), K._stream())
         K._check(rc, "rl_decoder_forward")

@@ -255,3 +255,15 @@ def test_rng_matches_the_reference_generator():
     assert r.next_f32() == (s >> 40) / 2**24
     vals = [Rng(12345).next_f32() for _ in range(3)]
     assert vals[0] == vals[1] == vals[2] and 0.0 <= vals[0] < 1.0
+
+
+def test_classes_of_a_batchs_lengths():
+    """Equal (the longest within 16 tokens of the mean), near (within 768) and far; one sequence is
+    always equal.  A step's launches may depend on the class, so captured steps are kept by it."""
+    from rustyllm_b200 import kernels as K
+    assert K.length_spread([1]) == 0 and K.length_spread([100000]) == 0
+    assert K.length_spread([500, 500, 500]) == 0
+    assert K.length_spread([516, 500, 500, 500]) == 0          # 12 above the mean of 504
+    assert K.length_spread([532, 500]) == 0 and K.length_spread([534, 500]) == 1
+    assert K.length_spread([2036, 500]) == 1 and K.length_spread([2038, 500]) == 2
+    assert K.length_spread([1] * 63 + [781]) == 1 and K.length_spread([1] * 63 + [782]) == 2

@@ -97,9 +97,53 @@ def test_one_sequence_decoding_across_the_long_context_mark(model_dirs, name, dt
     got = [eng.step([s], [[t]], "last") for t in long[6100:6200]]
     assert_close_logits(torch.cat(got), ref[6100:6200], dtype, f"{name} single tokens from 6,100 to 6,199")
     if eng.use_graphs:
-        assert sorted(eng._graphs) == [(1, False), (1, True)]
+        assert sorted(eng._graphs) == [(1, False, 0), (1, True, 0)]
     eng.free_slot(s)
     r.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,batch", [("F", 5), ("G", 16)])
+def test_batches_of_equal_near_and_far_lengths_take_their_own_decode_steps(model_dirs, name, batch, dtype):
+    """Batches whose lengths are equal, near one another (within 768 tokens of their mean) and far
+    apart decode through captured steps of their own: with equal chunks a sequence (a cluster, one
+    kernel a layer) where that serves them, with chunks dealt by length and a combining kernel
+    where not.  5 sequences have 8 chunks each, a cluster's size, so the near batch clusters too;
+    16 have 7, rounded to 4 in a cluster, which only a batch of equal lengths takes."""
+    from rustyllm_b200 import kernels
+    d, cfg = model_dirs[name]
+    V, layers, G = cfg["vocab_size"], cfg["num_hidden_layers"], cfg["num_key_value_heads"]
+    steps = 5
+    batches = {0: [300] * batch,
+               1: [150 + (450 * i) // (batch - 1) for i in range(batch)],
+               2: [2400] + [40 + i for i in range(batch - 1)]}
+    r = _runner(d, dtype, max(sum(-(-(n + steps) // 64) * 64 for n in lens) for lens in batches.values()), batch)
+    eng = r.engine
+    launches = {}
+    for spread, lens in batches.items():
+        assert kernels.length_spread([n + 1 for n in lens]) == spread == kernels.length_spread([n + steps for n in lens])
+        seqs = [random_tokens(V, n + steps, 50 * spread + i) for i, n in enumerate(lens)]
+        refs = [plain_logits(d, q) for q in seqs]
+        slots = [eng.alloc_slot() for _ in lens]
+        first = eng.step(slots, [q[:n] for q, n in zip(seqs, lens)], "last")
+        assert_close_logits(first, torch.stack([refs[b][n - 1] for b, n in enumerate(lens)]), dtype, f"{name} spread {spread}: prompts")
+        for t in range(steps):
+            before = kernels.launch_count
+            out = eng.step(slots, [[q[n + t]] for q, n in zip(seqs, lens)], "last")
+            launches[spread] = kernels.launch_count - before
+            assert_close_logits(out, torch.stack([refs[b][n + t] for b, n in enumerate(lens)]), dtype,
+                                f"{name} spread {spread}: single token {t}")
+        for sl in slots:
+            eng.free_slot(sl)
+    r.cache.check()
+    kernels.check_device_errors()
+    if eng.use_graphs:
+        assert sorted(eng._graphs) == [(batch, False, 0), (batch, False, 1), (batch, False, 2)]
+    if dtype == "bfloat16":
+        cluster = {spread: kernels.decode_cluster_size(batch, G, False, spread) for spread in (0, 1, 2)}
+        assert cluster == ({0: 8, 1: 8, 2: 0} if batch == 5 else {0: 4, 1: 0, 2: 0})
+        dealt = launches[2]                         # a plan a step and a combining kernel a layer more than a cluster
+        assert [launches[c] for c in (0, 1)] == [dealt - (layers + 1 if cluster[c] else 0) for c in (0, 1)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
