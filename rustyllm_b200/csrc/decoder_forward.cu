@@ -102,19 +102,23 @@ int decode_splits(int num_seqs, int num_kv_heads) {
   return s;
 }
 
-// The size of the cluster (2, 4 or 8) if the chunks of every sequence are to run as one, else 0: the
-// chunks are then dealt to the sequences by their lengths and combined by a second kernel.  Equal
-// chunks a sequence cost a kernel less (about 2.5 us a layer) and lose where sequences are unequal:
-// one sequence alone takes eight up to the long-context mark; several take the largest power of two
-// within their splits if their lengths are equal (spread 0), or within 768 tokens of their mean
-// (spread 1) with nothing lost to the rounding, and if the grid stays within two CTAs an SM
-// (kernels.decode_cluster_size is the same rule; measured on whole steps of 2 to 32 sequences).
+// How the decode attention cuts the sequences of a step: 8, 4 or 2 = so many equal chunks a sequence
+// as one cluster; 1 = every sequence whole in one CTA; 0 = chunks dealt to the sequences by their
+// lengths and combined by a second kernel.  Equal chunks cost a kernel less (about 2.5 us a layer)
+// and lose where sequences are unequal.  One sequence alone takes eight up to the long-context mark.
+// Several whose lengths are equal (spread 0) or within 768 tokens of their mean (spread 1): where two
+// chunks a sequence no longer fit two CTAs an SM (a second wave of clusters costs more than it
+// brings), every sequence whole; else the largest power of two within their splits - for spread 1
+// only if nothing is lost to the rounding.  (kernels.decode_cluster_size is the same rule;
+// measured on whole steps of 2 to 64 sequences.)
 int decode_cluster(int num_seqs, int num_kv_heads, int splits, int long_context, int length_spread) {
   if (num_seqs == 1) return (splits >= 8 && !long_context) ? 8 : 0;
   if (splits < 2 || length_spread > 1) return 0;
+  const int slots = 2 * rl_num_sms();
+  if (num_seqs * num_kv_heads * 2 > slots) return 1;
   const int size = splits >= 8 ? 8 : splits >= 4 ? 4 : 2;
   if (length_spread == 1 && size != splits) return 0;
-  return num_seqs * num_kv_heads * size <= 2 * rl_num_sms() ? size : 0;
+  return num_seqs * num_kv_heads * size <= slots ? size : 0;
 }
 
 bool can_fold(const RlLinear& l, int M) {
@@ -138,7 +142,7 @@ int attention(const RlLayerDesc& L, const RlRunDesc& R, const RlStepDesc& S, Ste
     const int splits = decode_splits(S.B, G);
     ++g_launches;
     const int cluster = decode_cluster(S.B, G, splits, S.long_context, S.length_spread);
-    if (cluster > 0)       // equal chunks a sequence as one cluster, combined through shared memory: one kernel, no plan
+    if (cluster > 0)       // equal chunks a sequence as one cluster, combined through shared memory (or no chunks): one kernel, no plan
       return rl_attention_decode(B.qkv, ldq, R.k_pool, R.v_pool, R.page_table, R.max_pages, S.seq_slots, S.kv_lens, B.attn, H * hd,
                                  nullptr, nullptr, S.B, H, G, hd, L.scale, L.window, cluster, stream);
     const int* plan = nullptr;

@@ -510,24 +510,31 @@ def length_spread(kv_lens: Sequence[int]) -> int:
 
 
 def decode_cluster_size(num_seqs: int, num_kv_heads: int, long_context: bool, spread: int) -> int:
-    """The size of the cluster (2, 4 or 8) if the chunks of every sequence are to run as one,
-    else 0.  One sequence alone: eight chunks up to the long-context mark.  Several: the largest
-    power of two within ``decode_splits`` if their lengths are equal (class 0), or near (class 1)
-    with nothing lost to the rounding, and if the grid stays within two CTAs an SM.  Whole decode
-    steps of the 8B shape, 1,024 tokens a sequence, cluster against dealt chunks: 8 sequences
-    3.10 against 3.18 ms, 16: 3.30 / 3.38, 2: 2.91 / 2.95, 6: 3.04 / 3.12; lengths 1,024 +- 30 %:
-    8: 3.13 / 3.19, 16: 3.36 / 3.42, but 4 (7 splits rounded to 4): 3.07 / 3.04, so those stay
-    dealt; the longest 80 % above the mean: 3.15 / 3.17, about even; beyond that the longest
-    sequence's few CTAs would finish last."""
+    """How the decode attention cuts the sequences of a step: 8, 4 or 2 = so many equal chunks a
+    sequence as one cluster; 1 = every sequence whole in one CTA; 0 = chunks dealt by length and
+    a combining kernel.  One sequence alone: eight chunks up to the long-context mark.  Several
+    whose lengths are equal (class 0) or near (class 1): where two chunks a sequence no longer fit
+    two CTAs an SM, every sequence whole; else the largest power of two within ``decode_splits``
+    - for class 1 only if nothing is lost to the rounding.  Whole decode steps of the 8B shape,
+    1,024 tokens a sequence, against dealt chunks: 2 sequences 2.91 / 2.95 ms, 6: 3.04 / 3.12,
+    8: 3.10 / 3.18, 16: 3.30 / 3.38, 20: 3.57 / 3.84, 32: 3.81 / 4.05, 64: 4.93 / 5.23; lengths
+    1,024 +- 30 %: 8: 3.13 / 3.19, 16: 3.36 / 3.42, 32: 3.84 / 4.06, 64: 5.05 / 5.20, but 4
+    sequences (7 splits rounded to 4): 3.07 / 3.04, so those stay dealt; with the longest 80 %
+    above the mean the two are about even, and beyond, the longest sequence's few CTAs would
+    finish last.  (A cluster of two at 20 sequences, 320 CTAs for 296 places: 17.7 us against
+    10.9 us whole at 512 tokens.)"""
     splits = decode_splits(num_seqs, num_kv_heads)
     if num_seqs == 1:
         return 8 if splits >= 8 and not long_context else 0
     if splits < 2 or spread > 1:
         return 0
+    places = 2 * num_sms()
+    if num_seqs * num_kv_heads * 2 > places:
+        return 1
     size = 8 if splits >= 8 else 4 if splits >= 4 else 2
     if spread == 1 and size != splits:
         return 0
-    return size if num_seqs * num_kv_heads * size <= 2 * num_sms() else 0
+    return size if num_seqs * num_kv_heads * size <= places else 0
 
 
 def decode_scratch_floats(num_seqs: int, num_heads: int, head_dim: int, num_splits: int) -> int:
@@ -686,9 +693,10 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
         cluster = decode_cluster_size(q.shape[0], num_kv_heads, getattr(step, "long_context", False),
                                       getattr(step, "length_spread", 2))
         if cluster:
-            # nothing to deal: equal chunks a sequence as one cluster, combined through shared memory
+            # nothing to deal: equal chunks a sequence as one cluster, combined through shared memory,
+            # or every sequence whole
             attention_decode(q, k_pool, v_pool, page_table, step.seq_slots, step.kv_lens, out,
-                             num_heads, num_kv_heads, head_dim, scale, window, num_splits=cluster, cluster=True)
+                             num_heads, num_kv_heads, head_dim, scale, window, num_splits=cluster, cluster=cluster > 1)
             return
         plan = None
         derived = getattr(step, "derived", None)     # what layers of one step share

@@ -103,13 +103,15 @@ def test_one_sequence_decoding_across_the_long_context_mark(model_dirs, name, dt
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name,batch", [("F", 5), ("G", 16)])
+@pytest.mark.parametrize("name,batch", [("F", 5), ("G", 16), ("F", 80)])
 def test_batches_of_equal_near_and_far_lengths_take_their_own_decode_steps(model_dirs, name, batch, dtype):
     """Batches whose lengths are equal, near one another (within 768 tokens of their mean) and far
     apart decode through captured steps of their own: with equal chunks a sequence (a cluster, one
     kernel a layer) where that serves them, with chunks dealt by length and a combining kernel
     where not.  5 sequences have 8 chunks each, a cluster's size, so the near batch clusters too;
-    16 have 7, rounded to 4 in a cluster, which only a batch of equal lengths takes."""
+    16 have 7, rounded to 4 in a cluster, which only a batch of equal lengths takes; 80 sequences of
+    two KV heads would be more clusters of two than the SMs hold at once, so equal and near ones
+    run whole, a CTA a sequence and KV head."""
     from rustyllm_b200 import kernels
     d, cfg = model_dirs[name]
     V, layers, G = cfg["vocab_size"], cfg["num_hidden_layers"], cfg["num_key_value_heads"]
@@ -141,7 +143,7 @@ def test_batches_of_equal_near_and_far_lengths_take_their_own_decode_steps(model
         assert sorted(eng._graphs) == [(batch, False, 0), (batch, False, 1), (batch, False, 2)]
     if dtype == "bfloat16":
         cluster = {spread: kernels.decode_cluster_size(batch, G, False, spread) for spread in (0, 1, 2)}
-        assert cluster == ({0: 8, 1: 8, 2: 0} if batch == 5 else {0: 4, 1: 0, 2: 0})
+        assert cluster == {5: {0: 8, 1: 8, 2: 0}, 16: {0: 4, 1: 0, 2: 0}, 80: {0: 1, 1: 1, 2: 0}}[batch]
         dealt = launches[2]                         # a plan a step and a combining kernel a layer more than a cluster
         assert [launches[c] for c in (0, 1)] == [dealt - (layers + 1 if cluster[c] else 0) for c in (0, 1)]
 
