@@ -150,6 +150,28 @@ __global__ void attention_decode_plan_kernel(const int* __restrict__ seq_slots, 
   for (int x = base + lane; x < nchunk; x += 32) entries[x] = make_int4(-1, 0, 0, 0);
 }
 
+// A plan of whole sequences, the longest first (inside `window` if it is not 0; ties in the order of
+// the batch): entries[x] = {sequence, 0 | 1 << 16, length, cache slot}, seqs[b] = {place of sequence b, 1}.
+// Where a batch is more CTAs than the SMs hold at once, the CTAs that start last should be the
+// shortest.  One CTA, a thread a sequence (at most 1,024), every thread counting who goes before it.
+__global__ void __launch_bounds__(1024)
+attention_decode_order_kernel(const int* __restrict__ seq_slots, const int* __restrict__ kv_lens, int B, int window,
+                              int4* __restrict__ entries, int2* __restrict__ seqs) {
+  __shared__ int s_len[1024];
+  rl_pdl_wait();         // no early release of the kernels behind this one, as in the plan kernel
+  const int b = threadIdx.x;
+  int len = 0, inside = 0;
+  if (b < B) { len = kv_lens[b]; inside = (window > 0 && len > window) ? window : len; }
+  s_len[b] = inside;
+  __syncthreads();
+  if (b < B) {
+    int place = 0;
+    for (int j = 0; j < B; ++j) { const int other = s_len[j]; place += (other > inside || (other == inside && j < b)) ? 1 : 0; }
+    entries[place] = make_int4(b, 1 << 16, len, seq_slots[b]);
+    seqs[b] = make_int2(place, 1);
+  }
+}
+
 // shared memory of one CTA: the ring [warp][stage][keys | values][16 rows][HD] of bf16 (16-byte
 // pieces swizzled within their row), reused after the loop for the warps' (max, sum, output)
 template <int HD>
@@ -182,18 +204,22 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
   // Before waiting for the kernel in front (which writes this step's queries, keys and
   // values): the plan, the sequence's length and slot and its page numbers were complete
   // before that kernel began, so these dependent loads overlap with its tail.
-  const int gkv = blockIdx.y;
+  // Chunks along x and KV heads along y where the chunks of a sequence form a cluster (a cluster lies
+  // along x); else KV heads along x, the faster index: CTAs start in the order of the chunks, all KV
+  // heads of one before the next, which is what makes a plan's order (longest first) the order of work.
+  const bool clustered = dec_cluster_size() > 1;          // the chunks of a sequence are the CTAs of a cluster
+  const int gkv = clustered ? blockIdx.y : blockIdx.x;
+  const int chunk_id = clustered ? blockIdx.x : blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int m = H / G;                                   // query heads per KV head (<= 16)
   // which sequence, and which share of its keys
-  int b = blockIdx.x, split = 0, num_splits = 1, len, cache_slot;
-  const bool clustered = dec_cluster_size() > 1;          // the chunks of a sequence are the CTAs of a cluster
+  int b = chunk_id, split = 0, num_splits = 1, len, cache_slot;
   if (plan == nullptr) {                                 // no plan: every sequence in `even_splits` chunks
-    b = blockIdx.x / even_splits; split = blockIdx.x % even_splits; num_splits = even_splits;
+    b = chunk_id / even_splits; split = chunk_id % even_splits; num_splits = even_splits;
     len = kv_lens[b]; cache_slot = seq_slots[b];
   } else {
-    const int4 e = __ldg(&plan[blockIdx.x]);
+    const int4 e = __ldg(&plan[chunk_id]);
     if (e.x < 0) return;                                 // spare chunk
     b = e.x; split = e.y & 0xffff; num_splits = e.y >> 16; len = e.z; cache_slot = e.w;
   }
@@ -374,7 +400,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
       c_o[r * HD + d] = O;
       if (d == 0) { c_o[16 * HD + r] = M; c_o[16 * HD + 16 + r] = L; }
     } else {
-      const size_t p = (size_t)blockIdx.x * H + h;         // partial results lie in grid order
+      const size_t p = (size_t)chunk_id * H + h;           // partial results lie in the order of the chunks
       part_o[p * HD + d] = O;
       if (d == 0) { part_ml[2 * p] = M; part_ml[2 * p + 1] = L; }
     }
@@ -470,10 +496,10 @@ static int launch_decode(const void* q, int ldq, const void* k_pool, const void*
     configured = true;
   }
   const int nchunk = B * num_splits;
-  const int4* entries = (const int4*)plan;                                   // null with one split
+  const int4* entries = (const int4*)plan;                                   // null without a plan
   const int2* seqs = plan ? (const int2*)(plan + 4 * (size_t)nchunk) : nullptr;
-  dim3 grid(nchunk, G);
   if (num_splits > 1 && part_o == nullptr) {
+    dim3 grid(nchunk, G);
     // no scratch: the chunks of a sequence are the CTAs of a cluster and combine through shared memory
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -500,6 +526,7 @@ static int launch_decode(const void* q, int ldq, const void* k_pool, const void*
     RL_LAUNCH_CHECK("rl_attention_decode");
     return RL_OK;
   }
+  dim3 grid(G, nchunk);
   rl_launch_pdl(attention_decode_kernel<HD>, grid, dim3(DEC_WARPS * 32), (size_t)DecSmem<HD>::BYTES, stream,
       (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table, max_pages,
       seq_slots, kv_lens, entries, (__nv_bfloat16*)out, ldo, part_o, part_ml, H, G, scale * 1.4426950408889634f, window,
@@ -551,12 +578,31 @@ extern "C" int rl_attention_decode_plan(const int* seq_slots, const int* kv_lens
   return RL_OK;
 }
 
+// Ints of an order plan for num_seqs sequences.
+extern "C" long long rl_attention_decode_order_ints(int num_seqs) { return 6LL * num_seqs; }
+
+// The sequences whole, the longest first: a plan for rl_attention_decode with num_splits 1, for batches
+// that are more CTAs than the SMs hold at once (their last CTAs should be the shortest).  At most
+// 1,024 sequences.  plan: rl_attention_decode_order_ints(...) ints, 16-byte aligned; holds for every
+// rl_attention_decode call with the same seq_slots, kv_lens and window.
+extern "C" int rl_attention_decode_order(const int* seq_slots, const int* kv_lens, int num_seqs, int window, int* plan,
+                                         cudaStream_t stream) {
+  RL_REQUIRE(num_seqs >= 0 && num_seqs <= 1024 && window >= 0, "rl_attention_decode_order: takes 0 to 1024 sequences (got %d) "
+             "and a window that is not negative", num_seqs);
+  if (num_seqs == 0) return RL_OK;
+  RL_REQUIRE(plan != nullptr && ((uintptr_t)plan & 15) == 0, "rl_attention_decode_order: plan is null or not 16-byte aligned");
+  rl_launch_pdl(attention_decode_order_kernel, dim3(1), dim3((num_seqs + 31) / 32 * 32), 0, stream, seq_slots, kv_lens, num_seqs,
+                window, (int4*)plan, (int2*)(plan + 4 * (size_t)num_seqs));
+  RL_LAUNCH_CHECK("rl_attention_decode_order");
+  return RL_OK;
+}
+
 // q: [B, ldq] bf16, one token per sequence; seq_slots, kv_lens: [B] (kv_lens counts the
 // new token, whose key and value are already in the cache); out: [B, ldo] bf16.
 // scratch: rl_attention_decode_scratch_floats(...) floats (may be null with one split).
-// plan: what rl_attention_decode_plan made for these sequences, window and splits, or
-// null: then every sequence is cut into num_splits equal chunks whatever its length
-// (right for one sequence, or for sequences of like lengths).  Null scratch with 2, 4 or 8
+// plan: what rl_attention_decode_plan made for these sequences, window and splits (with one
+// split: what rl_attention_decode_order made), or null: then every sequence is cut into num_splits
+// equal chunks whatever its length (right for one sequence, or for sequences of like lengths).  Null scratch with 2, 4 or 8
 // splits and no plan: the chunks of a sequence run as a thread-block cluster and combine
 // through distributed shared memory (no scratch, no second kernel).
 extern "C" int rl_attention_decode(const void* q, int ldq, const void* k_pool, const void* v_pool,
@@ -568,7 +614,7 @@ extern "C" int rl_attention_decode(const void* q, int ldq, const void* k_pool, c
              "rl_attention_decode: unsupported shape (heads %d, KV heads %d, head_dim %d): needs head_dim 64 or 128 "
              "and at most 16 heads per KV head", num_heads, num_kv_heads, head_dim);
   RL_REQUIRE(num_seqs >= 0 && num_splits >= 1, "rl_attention_decode: bad sizes");
-  RL_REQUIRE(num_seqs <= 65535 && num_kv_heads <= 65535 && (long long)num_seqs * num_splits <= (num_splits > 1 ? 65535 : 0x7fffffffLL),
+  RL_REQUIRE(num_seqs <= 65535 && num_kv_heads <= 65535 && (long long)num_seqs * num_splits <= 65535,
              "rl_attention_decode: too many sequences, chunks (%d x %d splits) or KV heads for one grid", num_seqs, num_splits);
   RL_REQUIRE(ldq >= num_heads * head_dim && ldo >= num_heads * head_dim && ldq % 8 == 0,
              "rl_attention_decode: row strides too small or not a multiple of 8 elements");
@@ -582,7 +628,6 @@ extern "C" int rl_attention_decode(const void* q, int ldq, const void* k_pool, c
   const size_t parts = (size_t)num_seqs * num_heads * num_splits;
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + parts * head_dim : nullptr;
-  if (num_splits == 1) plan = nullptr;
   if (head_dim == 64)
     return launch_decode<64>(q, ldq, k_pool, v_pool, page_table, max_pages, seq_slots, kv_lens, out, ldo, part_o,
                              part_ml, plan, num_seqs, num_heads, num_kv_heads, scale, window, num_splits, stream);

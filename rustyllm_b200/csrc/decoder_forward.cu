@@ -37,6 +37,7 @@ int rl_attention_decode_supported(int num_heads, int num_kv_heads, int head_dim)
 long long rl_attention_decode_plan_ints(int num_seqs, int num_splits);
 long long rl_attention_decode_scratch_floats(int num_seqs, int num_heads, int head_dim, int num_splits);
 int rl_attention_decode_plan(const int* seq_slots, const int* kv_lens, int num_seqs, int window, int num_splits, int* plan, cudaStream_t stream);
+int rl_attention_decode_order(const int* seq_slots, const int* kv_lens, int num_seqs, int window, int* plan, cudaStream_t stream);
 int rl_attention_decode(const void* q, int ldq, const void* k_pool, const void* v_pool, const int* page_table, int max_pages,
                         const int* seq_slots, const int* kv_lens, void* out, int ldo, float* scratch, const int* plan, int num_seqs,
                         int num_heads, int num_kv_heads, int head_dim, float scale, int window, int num_splits, cudaStream_t stream);
@@ -103,22 +104,34 @@ int decode_splits(int num_seqs, int num_kv_heads) {
 }
 
 // How the decode attention cuts the sequences of a step: 8, 4 or 2 = so many equal chunks a sequence
-// as one cluster; 1 = every sequence whole in one CTA; 0 = chunks dealt to the sequences by their
-// lengths and combined by a second kernel.  Equal chunks cost a kernel less (about 2.5 us a layer)
-// and lose where sequences are unequal.  One sequence alone takes eight up to the long-context mark.
-// Several whose lengths are equal (spread 0) or within 768 tokens of their mean (spread 1): where two
-// chunks a sequence no longer fit two CTAs an SM (a second wave of clusters costs more than it
-// brings), every sequence whole; else the largest power of two within their splits - for spread 1
-// only if nothing is lost to the rounding.  (kernels.decode_cluster_size is the same rule;
-// measured on whole steps of 2 to 64 sequences.)
+// as one cluster; 1 = every sequence whole in one CTA a KV head; 0 = chunks dealt to the sequences by
+// their lengths and combined by a second kernel.  Equal chunks cost a kernel less (about 2.5 us a
+// layer) and lose where sequences are unequal.  length_spread: the longest sequence above the mean
+// of all, 0 within 16 tokens, 1 within 768, 2 within 4,096, 3 beyond.  One sequence alone takes
+// eight chunks up to the long-context mark.  A batch of more whole sequences than fit two CTAs an
+// SM runs them whole, the longest first (decode_order_wanted), unless one is far beyond the rest
+// (spread 3).  Smaller batches whose lengths are equal or near (spread 0, 1): where two chunks a
+// sequence no longer fit two CTAs an SM (a second wave of clusters costs more than it brings),
+// every sequence whole; else the largest power of two within their splits - for spread 1 only if
+// nothing is lost to the rounding.  (kernels.decode_cluster_size is the same rule; measured on
+// whole steps of 2 to 64 sequences.)
 int decode_cluster(int num_seqs, int num_kv_heads, int splits, int long_context, int length_spread) {
   if (num_seqs == 1) return (splits >= 8 && !long_context) ? 8 : 0;
-  if (splits < 2 || length_spread > 1) return 0;
-  const int slots = 2 * rl_num_sms();
-  if (num_seqs * num_kv_heads * 2 > slots) return 1;
+  if (splits < 2) return 0;
+  const int places = 2 * rl_num_sms();
+  if (num_seqs * num_kv_heads > places) return length_spread <= 2 ? 1 : 0;
+  if (length_spread > 1) return 0;
+  if (num_seqs * num_kv_heads * 2 > places) return 1;
   const int size = splits >= 8 ? 8 : splits >= 4 ? 4 : 2;
   if (length_spread == 1 && size != splits) return 0;
-  return num_seqs * num_kv_heads * size <= slots ? size : 0;
+  return num_seqs * num_kv_heads * size <= places ? size : 0;
+}
+
+// Whole sequences that are more CTAs than the SMs hold at once start in the order of their lengths,
+// the longest first (64 sequences of 128 to 2,047 tokens: 43 us, 6.45 TB/s, against 54 us in the
+// order of the batch); the order kernel takes up to 1,024 sequences.
+bool decode_order_wanted(int num_seqs, int num_kv_heads) {
+  return num_seqs * num_kv_heads > 2 * rl_num_sms() && num_seqs <= 1024;
 }
 
 bool can_fold(const RlLinear& l, int M) {
@@ -142,9 +155,20 @@ int attention(const RlLayerDesc& L, const RlRunDesc& R, const RlStepDesc& S, Ste
     const int splits = decode_splits(S.B, G);
     ++g_launches;
     const int cluster = decode_cluster(S.B, G, splits, S.long_context, S.length_spread);
-    if (cluster > 0)       // equal chunks a sequence as one cluster, combined through shared memory (or no chunks): one kernel, no plan
+    if (cluster > 0) {     // equal chunks a sequence as one cluster, combined through shared memory, or whole sequences: one kernel
+      const int* order = nullptr;
+      if (cluster == 1 && decode_order_wanted(S.B, G)) {
+        if (B.plan_window != L.window || B.plan_splits != 1) {        // once a step for all layers of one window
+          const int rc = rl_attention_decode_order(S.seq_slots, S.kv_lens, S.B, L.window, B.dec_plan, stream);
+          if (rc != RL_OK) return rc;
+          ++g_launches;
+          B.plan_window = L.window; B.plan_splits = 1;
+        }
+        order = B.dec_plan;
+      }
       return rl_attention_decode(B.qkv, ldq, R.k_pool, R.v_pool, R.page_table, R.max_pages, S.seq_slots, S.kv_lens, B.attn, H * hd,
-                                 nullptr, nullptr, S.B, H, G, hd, L.scale, L.window, cluster, stream);
+                                 nullptr, order, S.B, H, G, hd, L.scale, L.window, cluster, stream);
+    }
     const int* plan = nullptr;
     if (splits > 1 && S.B > 1) {
       if (B.plan_window != L.window || B.plan_splits != splits) {     // once a step for all layers of one window

@@ -46,8 +46,8 @@ class StepState:
     # launch shape by it: captured steps are kept per (number of sequences, this flag, the next).
     long_context: bool = False
     # how far the longest sequence lies above the mean of all (kernels.length_spread: 0 equal,
-    # 1 near, 2 far); 2 where nobody said: the choice that is right for any lengths
-    length_spread: int = 2
+    # 1 near, 2 far, 3 beyond); 3 where nobody said: the choice that is right for any lengths
+    length_spread: int = 3
 
 
 Want = Union[str, None, Sequence[Sequence[int]]]
@@ -58,7 +58,7 @@ class _DecodeGraph:
     the step's integers from ``static_in`` and leave logits in ``logits``; everything
     they read beyond that (page tables, cache pools, weights) keeps its address."""
 
-    def __init__(self, engine: "Engine", num_seqs: int, long_context: bool = False, length_spread: int = 2):
+    def __init__(self, engine: "Engine", num_seqs: int, long_context: bool = False, length_spread: int = 3):
         B = num_seqs
         self.num_seqs = B
         dev = engine.device
@@ -136,7 +136,7 @@ class Engine:
         if not self.use_graphs:
             return
         for B in sorted(set(int(b) for b in batch_sizes)):
-            classes = [(False, spread) for spread in ((0,) if B == 1 else (0, 1, 2))]
+            classes = [(False, spread) for spread in ((0,) if B == 1 else (0, 1, 2, 3))]
             if B <= 0 or all((B,) + c in self._graphs for c in classes):
                 continue
             slots: List[int] = []

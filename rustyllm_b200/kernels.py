@@ -52,6 +52,7 @@ _SIGNATURES = {
     "rl_attention_decode": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
                             _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p],
     "rl_attention_decode_plan": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "rl_attention_decode_order": [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
     "rl_attention_decode_supported": [_c_int, _c_int, _c_int],
     "rl_attention_prefill": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
                              _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p],
@@ -497,28 +498,32 @@ def decode_splits(num_seqs: int, num_kv_heads: int) -> int:
 # Several sequences: how far the longest lies above the mean of all decides whether equal chunks a
 # sequence (a cluster, one kernel) or chunks dealt by length (and a second kernel that combines
 # them) serve them better; a captured step keeps its launches, so the step carries the class
-# (``StepState.length_spread``): 0 = within EVEN_SPREAD tokens, 1 = within NEAR_SPREAD, 2 = beyond.
+# (``StepState.length_spread``): 0 = within EVEN_SPREAD tokens, 1 = within NEAR_SPREAD, 2 = within
+# FAR_SPREAD, 3 = beyond.
 EVEN_SPREAD = 16
 NEAR_SPREAD = 768
+FAR_SPREAD = 4096
 
 
 def length_spread(kv_lens: Sequence[int]) -> int:
     """The class of a batch's lengths (see above); one sequence is class 0."""
     n = len(kv_lens)
     over = max(kv_lens) * n - sum(kv_lens)        # (longest - mean) * n, in integers
-    return 0 if over <= EVEN_SPREAD * n else 1 if over <= NEAR_SPREAD * n else 2
+    return 0 if over <= EVEN_SPREAD * n else 1 if over <= NEAR_SPREAD * n else 2 if over <= FAR_SPREAD * n else 3
 
 
 def decode_cluster_size(num_seqs: int, num_kv_heads: int, long_context: bool, spread: int) -> int:
     """How the decode attention cuts the sequences of a step: 8, 4 or 2 = so many equal chunks a
-    sequence as one cluster; 1 = every sequence whole in one CTA; 0 = chunks dealt by length and
-    a combining kernel.  One sequence alone: eight chunks up to the long-context mark.  Several
-    whose lengths are equal (class 0) or near (class 1): where two chunks a sequence no longer fit
-    two CTAs an SM, every sequence whole; else the largest power of two within ``decode_splits``
-    - for class 1 only if nothing is lost to the rounding.  Whole decode steps of the 8B shape,
-    1,024 tokens a sequence, against dealt chunks: 2 sequences 2.91 / 2.95 ms, 6: 3.04 / 3.12,
-    8: 3.10 / 3.18, 16: 3.30 / 3.38, 20: 3.57 / 3.84, 32: 3.81 / 4.05, 64: 4.93 / 5.23; lengths
-    1,024 +- 30 %: 8: 3.13 / 3.19, 16: 3.36 / 3.42, 32: 3.84 / 4.06, 64: 5.05 / 5.20, but 4
+    sequence as one cluster; 1 = every sequence whole in one CTA a KV head; 0 = chunks dealt by
+    length and a combining kernel.  One sequence alone: eight chunks up to the long-context mark.
+    A batch of more whole sequences than fit two CTAs an SM: whole, the longest first
+    (``decode_order_wanted``), unless one lies far beyond the rest (class 3).  Smaller batches
+    whose lengths are equal (class 0) or near (class 1): where two chunks a sequence no longer
+    fit two CTAs an SM, every sequence whole; else the largest power of two within
+    ``decode_splits`` - for class 1 only if nothing is lost to the rounding.  Whole decode steps
+    of the 8B shape, 1,024 tokens a sequence, against dealt chunks: 2 sequences 2.91 / 2.95 ms,
+    6: 3.04 / 3.12, 8: 3.10 / 3.18, 16: 3.30 / 3.38, 20: 3.57 / 3.84, 32: 3.81 / 4.05, 64: 4.93 / 5.23;
+    lengths 1,024 +- 30 %: 8: 3.13 / 3.19, 16: 3.36 / 3.42, 32: 3.84 / 4.06, 64: 5.05 / 5.20, but 4
     sequences (7 splits rounded to 4): 3.07 / 3.04, so those stay dealt; with the longest 80 %
     above the mean the two are about even, and beyond, the longest sequence's few CTAs would
     finish last.  (A cluster of two at 20 sequences, 320 CTAs for 296 places: 17.7 us against
@@ -526,15 +531,39 @@ def decode_cluster_size(num_seqs: int, num_kv_heads: int, long_context: bool, sp
     splits = decode_splits(num_seqs, num_kv_heads)
     if num_seqs == 1:
         return 8 if splits >= 8 and not long_context else 0
-    if splits < 2 or spread > 1:
+    if splits < 2:
         return 0
     places = 2 * num_sms()
+    if num_seqs * num_kv_heads > places:
+        return 1 if spread <= 2 else 0
+    if spread > 1:
+        return 0
     if num_seqs * num_kv_heads * 2 > places:
         return 1
     size = 8 if splits >= 8 else 4 if splits >= 4 else 2
     if spread == 1 and size != splits:
         return 0
     return size if num_seqs * num_kv_heads * size <= places else 0
+
+
+def decode_order_wanted(num_seqs: int, num_kv_heads: int) -> bool:
+    """Whole sequences that are more CTAs than the SMs hold at once start in the order of their
+    lengths, the longest first (64 sequences of 128 to 2,047 tokens: 43 us, 6.45 TB/s, against
+    54 us in the order of the batch); the order kernel takes up to 1,024 sequences."""
+    return num_seqs * num_kv_heads > 2 * num_sms() and num_seqs <= 1024
+
+
+def decode_order(seq_slots: torch.Tensor, kv_lens: torch.Tensor, window: int) -> torch.Tensor:
+    """A plan of whole sequences, the longest first (inside ``window`` if it is not 0), made on the
+    device: for ``attention_decode`` with one split.  At most 1,024 sequences."""
+    _need(seq_slots, "seq_slots", torch.int32); _need(kv_lens, "kv_lens", torch.int32)
+    B = seq_slots.numel()
+    assert kv_lens.numel() == B
+    plan = torch.empty(6 * B, dtype=torch.int32, device=seq_slots.device)     # rl_attention_decode_order_ints
+    _check(library().rl_attention_decode_order(seq_slots.data_ptr(), kv_lens.data_ptr(), B, int(window), plan.data_ptr(), _stream()),
+           "rl_attention_decode_order")
+    _count(1)
+    return plan
 
 
 def decode_scratch_floats(num_seqs: int, num_heads: int, head_dim: int, num_splits: int) -> int:
@@ -567,7 +596,8 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     q: [B, >= H*hd] bf16 (a view into the qkv buffer is fine); out: [B, H*hd] bf16.
     ``num_splits``: chunks per sequence; with a ``plan`` (from ``decode_plan`` with the
     same sequences, window and splits) that many on average, dealt to the sequences by
-    length.  ``cluster`` (2, 4 or 8 splits, no plan): the chunks of a sequence run as a
+    length; with one split a ``plan`` from ``decode_order`` starts the longest sequences first.
+    ``cluster`` (2, 4 or 8 splits, no plan): the chunks of a sequence run as a
     thread-block cluster and combine through shared memory - no scratch, one kernel."""
     _need(q, "q", torch.bfloat16, contiguous=False); _need(k_pool, "k_pool", torch.bfloat16)
     _need(v_pool, "v_pool", torch.bfloat16); _need(out, "out", torch.bfloat16)
@@ -578,7 +608,7 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     if num_splits is None:
         num_splits = decode_splits(B, num_kv_heads)
     if cluster:
-        assert plan is None and scratch is None and num_splits in (1, 2, 4, 8)
+        assert plan is None and scratch is None and num_splits in (2, 4, 8)
     need = 0 if cluster else decode_scratch_floats(B, num_heads, head_dim, num_splits)
     if num_splits > 1 and scratch is None and not cluster:
         scratch = torch.empty(need, dtype=torch.float32, device=q.device)
@@ -587,7 +617,7 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
         assert scratch.numel() >= need
     if plan is not None:
         _need(plan, "plan", torch.int32)
-        assert num_splits > 1 and plan.numel() >= 4 * B * num_splits + 2 * B
+        assert plan.numel() >= 4 * B * num_splits + 2 * B
     ldq = q.stride(0) if B > 1 else max(q.stride(0), num_heads * head_dim)
     _check(library().rl_attention_decode(
         q.data_ptr(), ldq, k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr(), page_table.shape[1],
@@ -691,12 +721,19 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
     if step.is_decode and attention_decode_supported(q.dtype, num_heads, num_kv_heads, head_dim):
         splits = decode_splits(q.shape[0], num_kv_heads)
         cluster = decode_cluster_size(q.shape[0], num_kv_heads, getattr(step, "long_context", False),
-                                      getattr(step, "length_spread", 2))
+                                      getattr(step, "length_spread", 3))
         if cluster:
             # nothing to deal: equal chunks a sequence as one cluster, combined through shared memory,
             # or every sequence whole
+            order = None
+            derived = getattr(step, "derived", None)
+            if cluster == 1 and derived is not None and decode_order_wanted(q.shape[0], num_kv_heads):
+                order = derived.get(("decode_order", int(window)))
+                if order is None:
+                    order = derived[("decode_order", int(window))] = decode_order(step.seq_slots, step.kv_lens, window)
             attention_decode(q, k_pool, v_pool, page_table, step.seq_slots, step.kv_lens, out,
-                             num_heads, num_kv_heads, head_dim, scale, window, num_splits=cluster, cluster=cluster > 1)
+                             num_heads, num_kv_heads, head_dim, scale, window, num_splits=cluster, plan=order,
+                             cluster=cluster > 1)
             return
         plan = None
         derived = getattr(step, "derived", None)     # what layers of one step share

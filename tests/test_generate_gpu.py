@@ -160,7 +160,7 @@ def test_warm_up_captures_the_decode_steps_and_changes_no_token(model_dirs):
     want = [r.token_ids for r in cold.generate(prompts, opts)]
     warm, _ = Runner.from_path(d, dtype="bfloat16", max_cache_tokens=64 * 6, max_batch=3)
     warm.warm_up([1, 2, 3, 3])
-    assert sorted(warm.engine._graphs) == [(1, False, 0)] + [(n, False, spread) for n in (2, 3) for spread in (0, 1, 2)]
+    assert sorted(warm.engine._graphs) == [(1, False, 0)] + [(n, False, spread) for n in (2, 3) for spread in (0, 1, 2, 3)]
     warm.cache.check()
     assert warm.cache.free_pages == warm.cache.num_pages and warm.cache.slots.free_count == 3
     assert [r.token_ids for r in warm.generate(prompts, opts)] == want

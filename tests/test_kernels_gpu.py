@@ -612,6 +612,32 @@ def test_attention_decode_chunks_of_a_sequence_as_a_cluster(H, G, hd, splits):
         torch.testing.assert_close(out.double().cpu(), ref, **_tol(torch.bfloat16))
 
 
+@pytest.mark.parametrize("H,G,hd", [(32, 8, 128), (6, 2, 64)])
+def test_attention_decode_whole_sequences_longest_first(H, G, hd):
+    """Every sequence whole in one CTA a KV head, started in the order of their lengths (inside the
+    window): the order plan lists the sequences longest first, ties in the order of the batch, and
+    the answers are those of the batch's own order."""
+    k = K()
+    lens = [1 + (i * 131) % 700 for i in range(70)] + [1500, 64, 64, 1]
+    for window in (0, 90):
+        case = _attention_case(torch.bfloat16, H, G, hd, [1] * len(lens), lens, window=window, seed=hd + window)
+        q, kp, vp, pt, slots, kv_lens, ref = _decode_inputs(case)
+        order = k.decode_order(slots, kv_lens, window)
+        n = len(lens)
+        entries = order[:4 * n].view(n, 4).cpu().tolist()
+        inside = [min(v, window) if window else v for v in lens]
+        assert [e[0] for e in entries] == sorted(range(n), key=lambda b: (-inside[b], b))
+        assert all(e[1] == 1 << 16 and e[2] == lens[e[0]] and e[3] == int(slots[e[0]]) for e in entries)
+        out = torch.full((n, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        before = k.launch_count
+        k.attention_decode(q, kp, vp, pt, slots, kv_lens, out, H, G, hd, 1.0 / math.sqrt(hd), window, num_splits=1, plan=order)
+        assert k.launch_count - before == 1
+        torch.testing.assert_close(out.double().cpu(), ref, **_tol(torch.bfloat16))
+        plain = torch.empty_like(out)
+        k.attention_decode(q, kp, vp, pt, slots, kv_lens, plain, H, G, hd, 1.0 / math.sqrt(hd), window, num_splits=1)
+        assert torch.equal(out, plain)
+
+
 @pytest.mark.parametrize("splits,window", [(2, 0), (7, 0), (3, 100)])
 def test_attention_decode_deals_chunks_by_length(splits, window):
     """More sequences than a warp has lanes, one of them far longer than the rest: the

@@ -103,22 +103,28 @@ def test_one_sequence_decoding_across_the_long_context_mark(model_dirs, name, dt
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name,batch", [("F", 5), ("G", 16), ("F", 80)])
+@pytest.mark.parametrize("name,batch", [("F", 5), ("G", 16), ("F", 80), ("G", 150)])
 def test_batches_of_equal_near_and_far_lengths_take_their_own_decode_steps(model_dirs, name, batch, dtype):
-    """Batches whose lengths are equal, near one another (within 768 tokens of their mean) and far
-    apart decode through captured steps of their own: with equal chunks a sequence (a cluster, one
-    kernel a layer) where that serves them, with chunks dealt by length and a combining kernel
-    where not.  5 sequences have 8 chunks each, a cluster's size, so the near batch clusters too;
-    16 have 7, rounded to 4 in a cluster, which only a batch of equal lengths takes; 80 sequences of
-    two KV heads would be more clusters of two than the SMs hold at once, so equal and near ones
-    run whole, a CTA a sequence and KV head."""
+    """Batches whose lengths are equal, near one another (within 768 tokens of their mean), far
+    (within 4,096) and beyond decode through captured steps of their own: with equal chunks a
+    sequence (a cluster, one kernel a layer) or whole sequences where that serves them, with chunks
+    dealt by length and a combining kernel where not.  5 sequences have 8 chunks each, a cluster's
+    size, so the near batch clusters too; 16 have 7, rounded to 4 in a cluster, which only a batch of
+    equal lengths takes; 80 sequences of two KV heads would be more clusters of two than the SMs hold
+    at once, so equal and near ones run whole, a CTA a sequence and KV head; 150 are more whole
+    sequences than the SMs hold at once and run whole, the longest first (one more launch a step,
+    which orders them), unless one lies far beyond the rest."""
     from rustyllm_b200 import kernels
     d, cfg = model_dirs[name]
     V, layers, G = cfg["vocab_size"], cfg["num_hidden_layers"], cfg["num_key_value_heads"]
-    steps = 5
-    batches = {0: [300] * batch,
+    steps = 4
+    short = batch > 100                      # many sequences: short ones, and two of the classes
+    batches = {0: [70 if short else 300] * batch,
                1: [150 + (450 * i) // (batch - 1) for i in range(batch)],
-               2: [2400] + [40 + i for i in range(batch - 1)]}
+               2: [3 + (i * 37) % 60 for i in range(batch - 2)] + [1300, 700] if short else [2400] + [40 + i for i in range(batch - 1)],
+               3: [8000] + [40 + i for i in range(batch - 1)]}
+    if short:
+        del batches[1], batches[3]
     r = _runner(d, dtype, max(sum(-(-(n + steps) // 64) * 64 for n in lens) for lens in batches.values()), batch)
     eng = r.engine
     launches = {}
@@ -140,12 +146,17 @@ def test_batches_of_equal_near_and_far_lengths_take_their_own_decode_steps(model
     r.cache.check()
     kernels.check_device_errors()
     if eng.use_graphs:
-        assert sorted(eng._graphs) == [(batch, False, 0), (batch, False, 1), (batch, False, 2)]
+        assert sorted(eng._graphs) == sorted((batch, max(lens) > kernels.LONG_CONTEXT, spread) for spread, lens in batches.items())
     if dtype == "bfloat16":
-        cluster = {spread: kernels.decode_cluster_size(batch, G, False, spread) for spread in (0, 1, 2)}
-        assert cluster == {5: {0: 8, 1: 8, 2: 0}, 16: {0: 4, 1: 0, 2: 0}, 80: {0: 1, 1: 1, 2: 0}}[batch]
-        dealt = launches[2]                         # a plan a step and a combining kernel a layer more than a cluster
-        assert [launches[c] for c in (0, 1)] == [dealt - (layers + 1 if cluster[c] else 0) for c in (0, 1)]
+        cluster = {spread: kernels.decode_cluster_size(batch, G, False, spread) for spread in sorted(batches)}
+        assert cluster == {5: {0: 8, 1: 8, 2: 0, 3: 0}, 16: {0: 4, 1: 0, 2: 0, 3: 0}, 80: {0: 1, 1: 1, 2: 0, 3: 0},
+                           150: {0: 1, 2: 1}}[batch]
+        # dealt chunks: a plan a step and a combining kernel a layer more than a cluster or whole sequences,
+        # which are put in order by one launch a step where they are more than the SMs hold at once
+        ordered = 1 if kernels.decode_order_wanted(batch, G) else 0
+        assert ordered == (1 if batch == 150 else 0)
+        dealt = launches[3] if 3 in launches else launches[0] + layers + 1 - ordered
+        assert launches == {c: dealt - (layers + 1 - ordered if cluster[c] else 0) for c in launches}
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
