@@ -97,9 +97,11 @@ def attention_decode(a) -> None:
     out = torch.empty(a.batch, H * hd, device=DEV, dtype=BF)
     sp = a.splits or K.decode_splits(a.batch, G)
     plan = K.decode_plan(slots, kv, 0, sp) if a.batch > 1 and not a.cluster else None    # once a step, as the engine makes it
+    if a.ordered:                            # every sequence whole, the longest first
+        sp, plan = 1, K.decode_order(slots, kv, 0)
     us = _time(lambda i: K.attention_decode(q, pools[i % layers][0], pools[i % layers][1], pt, slots, kv, out, H, G, hd,
                                             1 / math.sqrt(hd), num_splits=sp, plan=plan, cluster=a.cluster), a.warmup, a.reps)
-    print(f"attention_decode B={a.batch} context={a.contexts or a.context_range or a.context} (mean {sum(lens) / len(lens):.0f}) H={H} G={G} hd={hd} splits={sp}: "
+    print(f"attention_decode B={a.batch} context={a.contexts or a.context_range or a.context} (mean {sum(lens) / len(lens):.0f}) H={H} G={G} hd={hd} splits={sp}{' in order' if a.ordered else ''}: "
           f"{us:.2f} us, {kv_bytes / us / 1e6:.2f} TB/s of cache")
 
 
@@ -181,6 +183,7 @@ def main(argv=None) -> int:
     p.add_argument("--top-k", type=int, default=0, help="sample: the top-k kernel with this k (and --top-p inside it)")
     p.add_argument("--top-p", type=float, default=1.0, help="sample: nucleus threshold; without --top-k the top-p kernel over the whole vocabulary")
     p.add_argument("--cluster", action="store_true", help="attention-decode: the chunks of a sequence as one thread-block cluster (--splits 2, 4 or 8)")
+    p.add_argument("--ordered", action="store_true", help="attention-decode: every sequence whole, the longest first (a plan made once)")
     p.add_argument("--mma", action="store_true", help="attention-prefill: the mma.sync kernel also where tcgen05 applies")
     p.add_argument("--warmup", type=int, default=3); p.add_argument("--reps", type=int, default=20)
     p.add_argument("--graph", action="store_true", help="capture the timed launches in one CUDA graph: kernels that take "

@@ -578,6 +578,30 @@ extern "C" int rl_attention_decode_plan(const int* seq_slots, const int* kv_lens
   return RL_OK;
 }
 
+// How many CTAs of the decode kernel the GPU holds at once at this head size (CTAs an SM by shared
+// memory and registers, times SMs), and how many bytes of keys and values one CTA keeps in flight:
+// what the choice between equal chunks, whole sequences and dealt chunks goes by.
+extern "C" int rl_attention_decode_places(int head_dim) {
+  static int places[2] = {0, 0};
+  RL_REQUIRE(head_dim == 64 || head_dim == 128, "rl_attention_decode_places: head_dim %d is not 64 or 128", head_dim);
+  int& p = places[head_dim == 128];
+  if (p == 0) {
+    int per_sm = 0;
+    cudaError_t e;
+    if (head_dim == 64) {
+      e = cudaFuncSetAttribute(attention_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecSmem<64>::BYTES);
+      if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<64>, DEC_WARPS * 32, DecSmem<64>::BYTES);
+    } else {
+      e = cudaFuncSetAttribute(attention_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecSmem<128>::BYTES);
+      if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<128>, DEC_WARPS * 32, DecSmem<128>::BYTES);
+    }
+    RL_REQUIRE(e == cudaSuccess && per_sm > 0, "rl_attention_decode_places: occupancy query failed: %s", cudaGetErrorString(e));
+    p = per_sm * rl_num_sms();
+  }
+  return p;
+}
+extern "C" int rl_attention_decode_ring_bytes(int head_dim) { return head_dim == 64 ? DecSmem<64>::RING_BYTES : DecSmem<128>::RING_BYTES; }
+
 // Ints of an order plan for num_seqs sequences.
 extern "C" long long rl_attention_decode_order_ints(int num_seqs) { return 6LL * num_seqs; }
 

@@ -37,6 +37,8 @@ int rl_attention_decode_supported(int num_heads, int num_kv_heads, int head_dim)
 long long rl_attention_decode_plan_ints(int num_seqs, int num_splits);
 long long rl_attention_decode_scratch_floats(int num_seqs, int num_heads, int head_dim, int num_splits);
 int rl_attention_decode_plan(const int* seq_slots, const int* kv_lens, int num_seqs, int window, int num_splits, int* plan, cudaStream_t stream);
+int rl_attention_decode_places(int head_dim);
+int rl_attention_decode_ring_bytes(int head_dim);
 int rl_attention_decode_order(const int* seq_slots, const int* kv_lens, int num_seqs, int window, int* plan, cudaStream_t stream);
 int rl_attention_decode(const void* q, int ldq, const void* k_pool, const void* v_pool, const int* page_table, int max_pages,
                         const int* seq_slots, const int* kv_lens, void* out, int ldo, float* scratch, const int* plan, int num_seqs,
@@ -103,35 +105,38 @@ int decode_splits(int num_seqs, int num_kv_heads) {
   return s;
 }
 
+// Whole sequences that are more CTAs than the GPU holds at once (and keep 30 MB in flight among
+// them) start in the order of their lengths, the longest first (64 sequences of 128 to 2,047 tokens
+// at head size 128: 43 us, 6.45 TB/s, against 54 us in the order of the batch); the order kernel
+// takes up to 1,024 sequences.
+bool decode_order_wanted(int num_seqs, int num_kv_heads, int head_dim) {
+  const long long ctas = (long long)num_seqs * num_kv_heads;
+  return ctas > rl_attention_decode_places(head_dim) && ctas * rl_attention_decode_ring_bytes(head_dim) >= 30000000LL && num_seqs <= 1024;
+}
+
 // How the decode attention cuts the sequences of a step: 8, 4 or 2 = so many equal chunks a sequence
 // as one cluster; 1 = every sequence whole in one CTA a KV head; 0 = chunks dealt to the sequences by
 // their lengths and combined by a second kernel.  Equal chunks cost a kernel less (about 2.5 us a
-// layer) and lose where sequences are unequal.  length_spread: the longest sequence above the mean
-// of all, 0 within 16 tokens, 1 within 768, 2 within 4,096, 3 beyond.  One sequence alone takes
-// eight chunks up to the long-context mark.  A batch of more whole sequences than fit two CTAs an
-// SM runs them whole, the longest first (decode_order_wanted), unless one is far beyond the rest
-// (spread 3).  Smaller batches whose lengths are equal or near (spread 0, 1): where two chunks a
-// sequence no longer fit two CTAs an SM (a second wave of clusters costs more than it brings),
-// every sequence whole; else the largest power of two within their splits - for spread 1 only if
-// nothing is lost to the rounding.  (kernels.decode_cluster_size is the same rule; measured on
-// whole steps of 2 to 64 sequences.)
-int decode_cluster(int num_seqs, int num_kv_heads, int splits, int long_context, int length_spread) {
+// layer) and lose where sequences are unequal.  length_spread: 0 the longest sequence within 16
+// tokens of the mean of all, 1 within 768, 2 within 4,096 and no more than a twentieth of all
+// tokens, 3 the rest.  One sequence alone takes eight chunks up to the long-context mark.  Whole
+// sequences in order (decode_order_wanted) serve every batch up to spread 2.  Else, lengths that
+// are equal or near (spread 0, 1): where two chunks a sequence no longer fit the GPU at once (a
+// second wave of clusters costs more than it brings), every sequence whole if that keeps 15 MB in
+// flight; else the largest power of two within their splits - for spread 1 only if nothing is
+// lost to the rounding.  (kernels.decode_cluster_size is the same rule; measured on whole steps of
+// 2 to 64 sequences at head size 128 and on the kernel alone at head size 64.)
+int decode_cluster(int num_seqs, int num_kv_heads, int head_dim, int splits, int long_context, int length_spread) {
   if (num_seqs == 1) return (splits >= 8 && !long_context) ? 8 : 0;
   if (splits < 2) return 0;
-  const int places = 2 * rl_num_sms();
-  if (num_seqs * num_kv_heads > places) return length_spread <= 2 ? 1 : 0;
+  if (decode_order_wanted(num_seqs, num_kv_heads, head_dim)) return length_spread <= 2 ? 1 : 0;
   if (length_spread > 1) return 0;
-  if (num_seqs * num_kv_heads * 2 > places) return 1;
+  const int places = rl_attention_decode_places(head_dim);
+  const long long ctas = (long long)num_seqs * num_kv_heads;
+  if (ctas * 2 > places) return ctas * rl_attention_decode_ring_bytes(head_dim) >= 15000000LL ? 1 : 0;
   const int size = splits >= 8 ? 8 : splits >= 4 ? 4 : 2;
   if (length_spread == 1 && size != splits) return 0;
-  return num_seqs * num_kv_heads * size <= places ? size : 0;
-}
-
-// Whole sequences that are more CTAs than the SMs hold at once start in the order of their lengths,
-// the longest first (64 sequences of 128 to 2,047 tokens: 43 us, 6.45 TB/s, against 54 us in the
-// order of the batch); the order kernel takes up to 1,024 sequences.
-bool decode_order_wanted(int num_seqs, int num_kv_heads) {
-  return num_seqs * num_kv_heads > 2 * rl_num_sms() && num_seqs <= 1024;
+  return ctas * size <= places ? size : 0;
 }
 
 bool can_fold(const RlLinear& l, int M) {
@@ -154,10 +159,10 @@ int attention(const RlLayerDesc& L, const RlRunDesc& R, const RlStepDesc& S, Ste
   if (same && S.is_decode && rl_attention_decode_supported(H, G, hd)) {
     const int splits = decode_splits(S.B, G);
     ++g_launches;
-    const int cluster = decode_cluster(S.B, G, splits, S.long_context, S.length_spread);
+    const int cluster = decode_cluster(S.B, G, hd, splits, S.long_context, S.length_spread);
     if (cluster > 0) {     // equal chunks a sequence as one cluster, combined through shared memory, or whole sequences: one kernel
       const int* order = nullptr;
-      if (cluster == 1 && decode_order_wanted(S.B, G)) {
+      if (cluster == 1 && decode_order_wanted(S.B, G, hd)) {
         if (B.plan_window != L.window || B.plan_splits != 1) {        // once a step for all layers of one window
           const int rc = rl_attention_decode_order(S.seq_slots, S.kv_lens, S.B, L.window, B.dec_plan, stream);
           if (rc != RL_OK) return rc;

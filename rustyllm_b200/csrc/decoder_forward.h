@@ -57,7 +57,7 @@ struct RlStepDesc {
   int tiles_tc, tiles_mma;      // query tiles of 128 and of 64 tokens over the step's sequences
   const int* tile_order;        // for the tcgen05 prefill attention (may be null)
   int long_context;             // the longest sequence holds more tokens than one cluster of chunks serves well
-  int length_spread;            // the longest sequence above the mean of all: 0 within 16 tokens, 1 within 768, 2 within 4096, 3 beyond
+  int length_spread;            // 0 the longest sequence within 16 tokens of the mean, 1 within 768, 2 within 4096 and at most a twentieth of all tokens, 3 the rest
 };
 
 #ifdef __cplusplus

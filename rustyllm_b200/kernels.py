@@ -53,6 +53,8 @@ _SIGNATURES = {
                             _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p],
     "rl_attention_decode_plan": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "rl_attention_decode_order": [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
+    "rl_attention_decode_places": [_c_int],
+    "rl_attention_decode_ring_bytes": [_c_int],
     "rl_attention_decode_supported": [_c_int, _c_int, _c_int],
     "rl_attention_prefill": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
                              _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p],
@@ -499,58 +501,75 @@ def decode_splits(num_seqs: int, num_kv_heads: int) -> int:
 # sequence (a cluster, one kernel) or chunks dealt by length (and a second kernel that combines
 # them) serve them better; a captured step keeps its launches, so the step carries the class
 # (``StepState.length_spread``): 0 = within EVEN_SPREAD tokens, 1 = within NEAR_SPREAD, 2 = within
-# FAR_SPREAD, 3 = beyond.
+# FAR_SPREAD and the longest no more than one in LONGEST_SHARE of all tokens (63 sequences of 100
+# tokens beside one of 4,000, whole: 50 us, dealt: 24 us), 3 = the rest.
 EVEN_SPREAD = 16
 NEAR_SPREAD = 768
 FAR_SPREAD = 4096
+LONGEST_SHARE = 20
 
 
 def length_spread(kv_lens: Sequence[int]) -> int:
     """The class of a batch's lengths (see above); one sequence is class 0."""
     n = len(kv_lens)
     over = max(kv_lens) * n - sum(kv_lens)        # (longest - mean) * n, in integers
-    return 0 if over <= EVEN_SPREAD * n else 1 if over <= NEAR_SPREAD * n else 2 if over <= FAR_SPREAD * n else 3
+    if over <= NEAR_SPREAD * n:
+        return 0 if over <= EVEN_SPREAD * n else 1
+    return 2 if over <= FAR_SPREAD * n and max(kv_lens) * LONGEST_SHARE <= sum(kv_lens) else 3
 
 
-def decode_cluster_size(num_seqs: int, num_kv_heads: int, long_context: bool, spread: int) -> int:
+def decode_places(head_dim: int) -> int:
+    """CTAs of the decode kernel the GPU holds at once at this head size (296 at 128, 444 at 64)."""
+    n = int(library().rl_attention_decode_places(int(head_dim)))
+    if n <= 0:
+        _check(n or -1, "rl_attention_decode_places")
+    return n
+
+
+def decode_order_wanted(num_seqs: int, num_kv_heads: int, head_dim: int) -> bool:
+    """Whole sequences that are more CTAs than the GPU holds at once (and keep 30 MB in flight
+    among them) start in the order of their lengths, the longest first.  Sequences of 128 to 2,047
+    tokens, in order against dealt chunks: head size 128, 40 sequences 36.4 / 38.6 us, 48: 39.1 /
+    43.2, 56: 40.7 / 48.8, 64: 43.0 / 54.3 (6.45 TB/s; 53 us sorted but KV head by KV head, 52.7
+    unsorted); head size 64, 96: 38.4 / 40.5, 128: 42.0 / 50.2, but 64 (24 MB in flight): 31.7 /
+    30.4.  The order kernel takes up to 1,024 sequences."""
+    ctas = num_seqs * num_kv_heads
+    ring = int(library().rl_attention_decode_ring_bytes(int(head_dim)))
+    return ctas > decode_places(head_dim) and ctas * ring >= 30_000_000 and num_seqs <= 1024
+
+
+def decode_cluster_size(num_seqs: int, num_kv_heads: int, head_dim: int, long_context: bool, spread: int) -> int:
     """How the decode attention cuts the sequences of a step: 8, 4 or 2 = so many equal chunks a
     sequence as one cluster; 1 = every sequence whole in one CTA a KV head; 0 = chunks dealt by
     length and a combining kernel.  One sequence alone: eight chunks up to the long-context mark.
-    A batch of more whole sequences than fit two CTAs an SM: whole, the longest first
-    (``decode_order_wanted``), unless one lies far beyond the rest (class 3).  Smaller batches
-    whose lengths are equal (class 0) or near (class 1): where two chunks a sequence no longer
-    fit two CTAs an SM, every sequence whole; else the largest power of two within
-    ``decode_splits`` - for class 1 only if nothing is lost to the rounding.  Whole decode steps
-    of the 8B shape, 1,024 tokens a sequence, against dealt chunks: 2 sequences 2.91 / 2.95 ms,
-    6: 3.04 / 3.12, 8: 3.10 / 3.18, 16: 3.30 / 3.38, 20: 3.57 / 3.84, 32: 3.81 / 4.05, 64: 4.93 / 5.23;
-    lengths 1,024 +- 30 %: 8: 3.13 / 3.19, 16: 3.36 / 3.42, 32: 3.84 / 4.06, 64: 5.05 / 5.20, but 4
-    sequences (7 splits rounded to 4): 3.07 / 3.04, so those stay dealt; with the longest 80 %
-    above the mean the two are about even, and beyond, the longest sequence's few CTAs would
-    finish last.  (A cluster of two at 20 sequences, 320 CTAs for 296 places: 17.7 us against
-    10.9 us whole at 512 tokens.)"""
+    Whole sequences in order (``decode_order_wanted``) serve every batch up to class 2.  Else,
+    lengths that are equal (class 0) or near (class 1): where two chunks a sequence no longer fit
+    the GPU at once, every sequence whole if that keeps 15 MB in flight (head size 64, 4,096
+    tokens a sequence, whole against dealt: 32 sequences 59 / 49 us, 40: 61 / 73); else the largest
+    power of two within ``decode_splits`` - for class 1 only if nothing is lost to the rounding.
+    Whole decode steps of the 8B shape, 1,024 tokens a sequence, against dealt chunks: 2 sequences
+    2.91 / 2.95 ms, 6: 3.04 / 3.12, 8: 3.10 / 3.18, 16: 3.30 / 3.38, 20: 3.57 / 3.84, 32: 3.81 / 4.05,
+    64: 4.93 / 5.23; lengths 1,024 +- 30 %: 8: 3.13 / 3.19, 16: 3.36 / 3.42, 32: 3.84 / 4.06, 64: 5.05 /
+    5.20, but 4 sequences (7 splits rounded to 4): 3.07 / 3.04, so those stay dealt; with the
+    longest 80 % above the mean the two are about even, and beyond, the longest sequence's few
+    CTAs would finish last.  (A cluster of two at 20 sequences, 320 CTAs for 296 places: 17.7 us
+    against 10.9 us whole at 512 tokens.)"""
     splits = decode_splits(num_seqs, num_kv_heads)
     if num_seqs == 1:
         return 8 if splits >= 8 and not long_context else 0
     if splits < 2:
         return 0
-    places = 2 * num_sms()
-    if num_seqs * num_kv_heads > places:
+    if decode_order_wanted(num_seqs, num_kv_heads, head_dim):
         return 1 if spread <= 2 else 0
     if spread > 1:
         return 0
-    if num_seqs * num_kv_heads * 2 > places:
-        return 1
+    places, ctas = decode_places(head_dim), num_seqs * num_kv_heads
+    if ctas * 2 > places:
+        return 1 if ctas * int(library().rl_attention_decode_ring_bytes(int(head_dim))) >= 15_000_000 else 0
     size = 8 if splits >= 8 else 4 if splits >= 4 else 2
     if spread == 1 and size != splits:
         return 0
-    return size if num_seqs * num_kv_heads * size <= places else 0
-
-
-def decode_order_wanted(num_seqs: int, num_kv_heads: int) -> bool:
-    """Whole sequences that are more CTAs than the SMs hold at once start in the order of their
-    lengths, the longest first (64 sequences of 128 to 2,047 tokens: 43 us, 6.45 TB/s, against
-    54 us in the order of the batch); the order kernel takes up to 1,024 sequences."""
-    return num_seqs * num_kv_heads > 2 * num_sms() and num_seqs <= 1024
+    return size if ctas * size <= places else 0
 
 
 def decode_order(seq_slots: torch.Tensor, kv_lens: torch.Tensor, window: int) -> torch.Tensor:
@@ -720,14 +739,14 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
         return
     if step.is_decode and attention_decode_supported(q.dtype, num_heads, num_kv_heads, head_dim):
         splits = decode_splits(q.shape[0], num_kv_heads)
-        cluster = decode_cluster_size(q.shape[0], num_kv_heads, getattr(step, "long_context", False),
+        cluster = decode_cluster_size(q.shape[0], num_kv_heads, head_dim, getattr(step, "long_context", False),
                                       getattr(step, "length_spread", 3))
         if cluster:
             # nothing to deal: equal chunks a sequence as one cluster, combined through shared memory,
             # or every sequence whole
             order = None
             derived = getattr(step, "derived", None)
-            if cluster == 1 and derived is not None and decode_order_wanted(q.shape[0], num_kv_heads):
+            if cluster == 1 and derived is not None and decode_order_wanted(q.shape[0], num_kv_heads, head_dim):
                 order = derived.get(("decode_order", int(window)))
                 if order is None:
                     order = derived[("decode_order", int(window))] = decode_order(step.seq_slots, step.kv_lens, window)

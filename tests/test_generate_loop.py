@@ -258,13 +258,15 @@ def test_rng_matches_the_reference_generator():
 
 
 def test_classes_of_a_batchs_lengths():
-    """Equal (the longest within 16 tokens of the mean), near (within 768), far (within 4,096) and
-    beyond; one sequence is always equal.  A step's launches may depend on the class, so captured steps are kept by it."""
+    """Equal (the longest within 16 tokens of the mean), near (within 768), far (within 4,096, and
+    the longest no more than a twentieth of all tokens) and the rest; one sequence is always equal.  A step's launches may depend on the class, so captured steps are kept by it."""
     from rustyllm_b200 import kernels as K
     assert K.length_spread([1]) == 0 and K.length_spread([100000]) == 0
     assert K.length_spread([500, 500, 500]) == 0
     assert K.length_spread([516, 500, 500, 500]) == 0          # 12 above the mean of 504
     assert K.length_spread([532, 500]) == 0 and K.length_spread([534, 500]) == 1
-    assert K.length_spread([2036, 500]) == 1 and K.length_spread([2038, 500]) == 2
-    assert K.length_spread([1] * 63 + [781]) == 1 and K.length_spread([1] * 63 + [782]) == 2
-    assert K.length_spread([8692, 500]) == 2 and K.length_spread([8694, 500]) == 3
+    assert K.length_spread([2036, 500]) == 1 and K.length_spread([2038, 500]) == 3
+    assert K.length_spread([1] * 63 + [781]) == 1 and K.length_spread([1] * 63 + [782]) == 3
+    assert K.length_spread([8692, 500]) == 3                      # near enough, but nearly all tokens are its own
+    assert K.length_spread([2000] + [1000] * 39) == 2 and K.length_spread([2000] + [900] * 39) == 3
+    assert K.length_spread([5000] + [4000] * 60) == 2 and K.length_spread([8200] + [4000] * 60) == 3

@@ -103,32 +103,35 @@ def test_one_sequence_decoding_across_the_long_context_mark(model_dirs, name, dt
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name,batch", [("F", 5), ("G", 16), ("F", 80), ("G", 150)])
+@pytest.mark.parametrize("name,batch", [("F", 5), ("G", 16), ("F", 80), ("F", 160)])
 def test_batches_of_equal_near_and_far_lengths_take_their_own_decode_steps(model_dirs, name, batch, dtype):
-    """Batches whose lengths are equal, near one another (within 768 tokens of their mean), far
-    (within 4,096) and beyond decode through captured steps of their own: with equal chunks a
-    sequence (a cluster, one kernel a layer) or whole sequences where that serves them, with chunks
-    dealt by length and a combining kernel where not.  5 sequences have 8 chunks each, a cluster's
-    size, so the near batch clusters too; 16 have 7, rounded to 4 in a cluster, which only a batch of
-    equal lengths takes; 80 sequences of two KV heads would be more clusters of two than the SMs hold
-    at once, so equal and near ones run whole, a CTA a sequence and KV head; 150 are more whole
-    sequences than the SMs hold at once and run whole, the longest first (one more launch a step,
-    which orders them), unless one lies far beyond the rest."""
+    """Batches by the class of their lengths - equal, near one another (the longest within 768 tokens
+    of the mean), far (within 4,096, and no sequence more than a twentieth of all tokens) and the
+    rest - decode through captured steps of their own: with equal chunks a sequence (a cluster, one
+    kernel a layer) or whole sequences where that serves them, with chunks dealt by length and a
+    combining kernel where not.  5 sequences have 8 chunks each, a cluster's size, so the near batch
+    clusters too; 16 have 7, rounded to 4 in a cluster, which only a batch of equal lengths takes; 80
+    sequences of two KV heads would be more clusters of two than the GPU holds at once, so equal and
+    near ones run whole, a CTA a sequence and KV head; 160 are more whole sequences than the GPU
+    holds at once and run whole, the longest first (one more launch a step, which orders them),
+    far ones too."""
     from rustyllm_b200 import kernels
     d, cfg = model_dirs[name]
-    V, layers, G = cfg["vocab_size"], cfg["num_hidden_layers"], cfg["num_key_value_heads"]
+    V, layers, G, hd = cfg["vocab_size"], cfg["num_hidden_layers"], cfg["num_key_value_heads"], cfg["head_dim"]
     steps = 4
-    short = batch > 100                      # many sequences: short ones, and two of the classes
-    batches = {0: [70 if short else 300] * batch,
+    batches = {0: [70 if batch > 100 else 300] * batch,
                1: [150 + (450 * i) // (batch - 1) for i in range(batch)],
-               2: [3 + (i * 37) % 60 for i in range(batch - 2)] + [1300, 700] if short else [2400] + [40 + i for i in range(batch - 1)],
-               3: [8000] + [40 + i for i in range(batch - 1)]}
-    if short:
-        del batches[1], batches[3]
+               3: [2400] + [40 + i % 50 for i in range(batch - 1)]}
+    if batch == 80:
+        batches[2] = [260] * 76 + [1100] * 4
+    if batch == 160:
+        del batches[1]
+        batches[2] = [150] * 77 + [1000] * 2 + [150] * 79 + [1000] * 2
     r = _runner(d, dtype, max(sum(-(-(n + steps) // 64) * 64 for n in lens) for lens in batches.values()), batch)
     eng = r.engine
     launches = {}
-    for spread, lens in batches.items():
+    for spread, lens in sorted(batches.items()):
+        assert len(lens) == batch
         assert kernels.length_spread([n + 1 for n in lens]) == spread == kernels.length_spread([n + steps for n in lens])
         seqs = [random_tokens(V, n + steps, 50 * spread + i) for i, n in enumerate(lens)]
         refs = [plain_logits(d, q) for q in seqs]
@@ -148,15 +151,13 @@ def test_batches_of_equal_near_and_far_lengths_take_their_own_decode_steps(model
     if eng.use_graphs:
         assert sorted(eng._graphs) == sorted((batch, max(lens) > kernels.LONG_CONTEXT, spread) for spread, lens in batches.items())
     if dtype == "bfloat16":
-        cluster = {spread: kernels.decode_cluster_size(batch, G, False, spread) for spread in sorted(batches)}
-        assert cluster == {5: {0: 8, 1: 8, 2: 0, 3: 0}, 16: {0: 4, 1: 0, 2: 0, 3: 0}, 80: {0: 1, 1: 1, 2: 0, 3: 0},
-                           150: {0: 1, 2: 1}}[batch]
+        cluster = {spread: kernels.decode_cluster_size(batch, G, hd, False, spread) for spread in sorted(batches)}
+        assert cluster == {5: {0: 8, 1: 8, 3: 0}, 16: {0: 4, 1: 0, 3: 0}, 80: {0: 1, 1: 1, 2: 0, 3: 0}, 160: {0: 1, 2: 1, 3: 0}}[batch]
         # dealt chunks: a plan a step and a combining kernel a layer more than a cluster or whole sequences,
-        # which are put in order by one launch a step where they are more than the SMs hold at once
-        ordered = 1 if kernels.decode_order_wanted(batch, G) else 0
-        assert ordered == (1 if batch == 150 else 0)
-        dealt = launches[3] if 3 in launches else launches[0] + layers + 1 - ordered
-        assert launches == {c: dealt - (layers + 1 - ordered if cluster[c] else 0) for c in launches}
+        # which are put in order by one launch a step where they are more than the GPU holds at once
+        ordered = 1 if kernels.decode_order_wanted(batch, G, hd) else 0
+        assert ordered == (1 if batch == 160 else 0)
+        assert launches == {c: launches[3] - (layers + 1 - ordered if cluster[c] else 0) for c in launches}
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
